@@ -1,0 +1,218 @@
+/*
+ * tidal_b200 — C ABI of the B200 (sm_100a) decode-attention path of TidalDecode.
+ *
+ * Conventions
+ *   - every pointer named d_* or documented "device" is a CUDA device pointer on
+ *     the current device; `stream` is a cudaStream_t passed as void*;
+ *   - no entry point allocates, frees or synchronises, except tidal_ws_init
+ *     (one memset on the stream) and tidal_ws_status (one blocking 4-byte read);
+ *   - return value: 0 = launched; negative = argument rejected on the host
+ *     (message via tidal_last_error()); device-side faults (a bounded wait that
+ *     ran out, an out-of-range index that was skipped) are recorded in the
+ *     workspace and read back with tidal_ws_status();
+ *   - KV pool layout ("NHD", one pool per layer) is the reference's
+ *     [pages][2][page_size][Hkv][D] with K at plane 0 and V at plane 1
+ *     (kernels/include/decode/decode_page.cuh:191-200,223-234;
+ *     tidal/utils/kv_cache.py:21-25).
+ *
+ * Each entry point names the reference interface it stands in for
+ * (paths relative to the TidalDecode repository).
+ */
+#ifndef TIDAL_B200_H_
+#define TIDAL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TIDAL_DTYPE_F16 0
+#define TIDAL_DTYPE_BF16 1
+#define TIDAL_DTYPE_F32 2
+
+#define TIDAL_OK 0
+#define TIDAL_ERR_ARG (-1)      /* bad shape / null pointer / unsupported combination */
+#define TIDAL_ERR_WORKSPACE (-2) /* workspace too small or misaligned */
+#define TIDAL_ERR_CUDA (-3)      /* a CUDA runtime call failed (launch error) */
+
+/* device-side status bits, tidal_ws_status() */
+#define TIDAL_DEV_WAIT_TIMEOUT 1u /* an mbarrier wait hit its iteration limit */
+#define TIDAL_DEV_BAD_INDEX 2u    /* a token/page index was out of range and skipped */
+#define TIDAL_DEV_TOPK_OVERFLOW 4u /* internal top-k buffer overflow (result invalid) */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int tidal_version(void);
+
+/* Message of the last negative return on this host thread. */
+const char* tidal_last_error(void);
+
+/* Kernels this library has launched since it was loaded (all threads). */
+uint64_t tidal_launch_count(void);
+
+/* ---------------------------------------------------------------- workspace
+ * Stands in for BatchDecodeHandler::BeginForward's per-call cudaMallocAsync of
+ * the split-KV scratch (kernels/include/decode/decode_handler.cuh:73-136) and
+ * for the top-k `buf` (tidal/utils/controller.py:164-168): the caller allocates
+ * one buffer once, sized by tidal_ws_bytes, and passes it to every call.
+ *   max_rows   = rows the top-k may see at once (B for head-summed scores,
+ *                B*Hq for per-head scores);
+ *   max_n      = longest score row;
+ * The buffer must be 256-byte aligned.  tidal_ws_init (same geometry as given to
+ * tidal_ws_bytes) must run once, and again after any non-zero tidal_ws_status,
+ * before the first use: it records the geometry on the host under the buffer's
+ * address and zeroes the counters, which kernels leave zero at rest.
+ * Calls that share one workspace must not overlap on the GPU. */
+size_t tidal_ws_bytes(int max_batch, int num_qo_heads, int head_dim, int max_rows, int64_t max_n);
+int tidal_ws_init(void* d_ws, size_t ws_bytes, int max_batch, int num_qo_heads, int head_dim, int max_rows,
+                  int64_t max_n, void* stream);
+/* Forget a workspace (host bookkeeping only; the memory stays the caller's). */
+int tidal_ws_release(void* d_ws);
+/* Blocking: returns the OR of TIDAL_DEV_* bits seen since the last init (>= 0),
+ * or a negative TIDAL_ERR_*. */
+int tidal_ws_status(void* d_ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------- decode attention
+ * One decode step of attention for `batch` sequences, one new query each.
+ * Stands in for BatchDecodeWithPagedKVCachePyTorchWrapper::Forward
+ * (tidal/ops/csrc/approx_attn.cu:68-151 → BatchDecodeWithPagedKVCacheKernel,
+ * kernels/include/decode/decode_attn.cuh:446-658, plus VariableLengthMergeStates
+ * :1012-1020), for all three layer kinds:
+ *   full layer       sel_idx = NULL, scores_out = NULL
+ *   selection layer  sel_idx = NULL, scores_out != NULL  (attends to ALL tokens and
+ *                    writes the pre-softmax logits q·k/sqrt(D) in fp32 —
+ *                    src/tidal_build/modify_llama.py:105-120)
+ *   sparse layer     sel_idx != NULL (attends only to the listed tokens — :121-133)
+ */
+typedef struct tidal_attn_args {
+    /* tensors */
+    const void* d_q;            /* [batch][Hq][D], dtype */
+    void* d_o;                  /* [batch][Hq][D], dtype; may be NULL if d_part_* given */
+    const void* d_kv;           /* pool of this layer */
+    const int32_t* d_page_table;/* [batch][page_table_stride] page ids; NULL: page j of
+                                   sequence b is page b*page_table_stride + j */
+    int64_t page_table_stride;
+    const int32_t* d_seq_lens;  /* [batch] tokens per sequence, or NULL → all = seq_len */
+    int32_t seq_len;            /* host-side upper bound of (and default for) the lengths */
+    /* selection list (sparse layer) */
+    const int32_t* d_sel_idx;   /* [batch][sel_rows][sel_stride] token positions, or NULL */
+    int32_t sel_rows;           /* 1 = one shared list per sequence, Hq = one per q head */
+    int32_t sel_count;          /* entries per list */
+    int64_t sel_stride;         /* elements between lists */
+    int32_t sel_physical;       /* 1: entries are pool page ids, page_size must be 1
+                                   (tidal/utils/controller.py:20,122-137) */
+    const int32_t* d_sel_counts;/* NULL, or [batch][sel_rows] valid entries per list (<= sel_count):
+                                   lists that tidal_topk filtered to one shard's positions */
+    int32_t extra_page;         /* >= 0: also attend this pool page — the newest token, as
+                                   the reference appends it (decode_attn.cuh:726-730); -1 none */
+    /* logits out (selection layer) */
+    float* d_scores;            /* NULL, or [batch][score_rows][score_stride] fp32 */
+    int32_t score_rows;         /* 1 = summed over all Hq heads, Hq = per q head */
+    int64_t score_stride;
+    uint32_t* d_hist;           /* NULL, or [batch*score_rows][TIDAL_TOPK_BINS] zeroed counters
+                                   that receive the first radix digit of every logit, so that
+                                   tidal_topk can skip its own histogram pass (see there) */
+    int32_t force_last;         /* histogram counts the newest token as +inf (kernel-path rule) */
+    /* un-normalised partials out (sequence-sharded KV); all three or none */
+    float* d_part_m;            /* [batch][Hq]   running max, log2 domain */
+    float* d_part_l;            /* [batch][Hq]   sum of exp2(s - m) */
+    float* d_part_o;            /* [batch][Hq][D] sum of exp2(s - m) * v */
+    /* geometry */
+    int32_t batch, num_qo_heads, num_kv_heads, head_dim, page_size, dtype;
+    int64_t num_pages;          /* pages in the pool, for the bounds check */
+    float sm_scale;             /* <= 0 → 1/sqrt(D) */
+    int32_t num_chunks;         /* 0 = planner's choice; else force the KV split */
+    int32_t heads_per_cta;      /* 0 = planner's choice; else KV heads one CTA covers */
+} tidal_attn_args;
+
+int tidal_decode_attention(const tidal_attn_args* args, void* d_ws, size_t ws_bytes, void* stream);
+
+/* The planner's choice of CTAs along the KV split for `tokens` tokens per list and
+ * batch*head_slices lists; what PartitionPagedKVCacheBinarySearchMinNumPagePerBatch
+ * computes in the reference (decode_attn.cuh:763-791). Pure host arithmetic. */
+int tidal_plan_chunks(int batch, int head_slices, int tokens, int min_tokens_per_chunk, int sm_count);
+
+/* ------------------------------------------------------------------ top-k
+ * Row-wise top-k of fp32 scores → unsorted-set semantics, emitted in ascending
+ * index order when k <= 4096.  Stands in for topk_filtering
+ * (tidal/ops/csrc/topk.cu:7-44 → decode_select_k, RAFT radix select) and for
+ * torch.topk at src/tidal_build/modify_llama.py:118.  k >= n selects everything
+ * (:112-113).  Exact ties are broken towards the lower index, so equal inputs
+ * give equal sets on every rank.
+ *   d_scores  [rows][row_stride] fp32
+ *   d_in_idx  NULL, or [rows][row_stride] int32: emit d_in_idx[j] instead of j
+ *             (the reference's `estimated_indices`, topk.cu:9)
+ *   d_out_idx [rows][out_stride] int32, first min(k,n) entries written
+ *   d_out_val NULL or [rows][out_stride] fp32, scores of the emitted entries
+ *   d_hist    NULL, or the histogram tidal_decode_attention filled for exactly
+ *             these rows (then pass the same force_last)
+ *   idx_offset added to emitted positions (global position of a shard's first token)
+ *   own_lo/own_hi  when own_hi > own_lo, only emitted values v with own_lo <= v < own_hi
+ *             are written, as v - own_lo, and d_out_count[row] receives how many
+ *             (the rank-local part of a global selection); otherwise d_out_count,
+ *             if given, receives min(k, n)
+ */
+#define TIDAL_TOPK_BINS 4096
+typedef struct tidal_topk_args {
+    const float* d_scores;
+    const int32_t* d_in_idx;
+    int32_t rows;
+    int64_t n, row_stride;
+    int32_t k;
+    int32_t* d_out_idx;
+    float* d_out_val;
+    int64_t out_stride;
+    int32_t idx_offset, force_last;
+    int32_t own_lo, own_hi;
+    int32_t* d_out_count;
+    uint32_t* d_hist;
+} tidal_topk_args;
+int tidal_topk(const tidal_topk_args* args, void* d_ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------ RoPE + KV append
+ * Rotates q (in place) and the new k, then writes k,v into their pool slots.
+ * Stands in for apply_rope_in_place + append_kv_cache_decode / _prefill
+ * (tidal/ops/csrc/page.cu:212-253, 6-99, 101-210 → QKApplyRotaryInPlaceKernel
+ * decode_page.cuh:639-687, AppendPagedKVCache{Decode,Prefill}Kernel :393-557).
+ * Token i (of n_tokens = batch*tokens_per_seq) belongs to sequence
+ * b = i / tokens_per_seq at position pos0[b] + i % tokens_per_seq.
+ *   d_q  [n_tokens][Hq][D] or NULL;  d_k, d_v [n_tokens][Hkv][D] (d_v NULL: no append)
+ *   d_pos0     [batch] int32 device, or NULL → every sequence starts at `pos0`
+ *   d_inv_freq [D/2] fp32 device or NULL → theta^(-2i/D) computed in the kernel
+ *   rope_mode  0 none; 1 reference-model rounding (cos, sin and both products rounded
+ *              to dtype: src/models/llama_tidaldecoding.py:200-220,255-279);
+ *              2 fp32 rotation rounded once (decode_page.cuh:650-669)
+ *   k is rotated in place as well when rotate_k_in_place != 0 (the reference op does).
+ */
+typedef struct tidal_rope_append_args {
+    void* d_q;
+    void* d_k;
+    const void* d_v;
+    void* d_kv;                  /* pool of this layer, or NULL: rotate only */
+    const int32_t* d_page_table; /* as in tidal_attn_args */
+    int64_t page_table_stride;
+    const int32_t* d_pos0;
+    int32_t pos0;
+    const float* d_inv_freq;
+    float rope_theta, rope_scale;
+    int32_t rope_mode, rotate_k_in_place;
+    int32_t batch, tokens_per_seq, num_qo_heads, num_kv_heads, head_dim, page_size, dtype;
+    int64_t num_pages;
+    uint32_t* d_status;          /* NULL or a device word that receives TIDAL_DEV_* bits */
+} tidal_rope_append_args;
+
+int tidal_rope_append(const tidal_rope_append_args* args, void* stream);
+
+/* -------------------------------------------- cross-shard merge of partials
+ * o[b][h][:] = sum_r 2^(m_r-M) o_r / sum_r 2^(m_r-M) l_r over `shards` sets of
+ * partials laid out [shards][batch*Hq(*D)] — what every rank runs after the
+ * all-gather when the KV cache is sharded by sequence.  Same arithmetic as the
+ * reference's merge across KV chunks (decode_attn.cuh:213-232, state_t::merge). */
+int tidal_merge_partials(const float* d_m, const float* d_l, const float* d_o, int shards, int batch,
+                         int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TIDAL_B200_H_ */

@@ -1,0 +1,392 @@
+"""GPU parity: the sm_100a kernels, called through the C ABI, against the CPU
+oracle and against the fixtures the reference produced (tests/golden)."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import tidal_oracle as O
+from tests.golden.cases import ATTN_CASES, input_digest, make_case
+from tests.helpers import assert_close, build_pool, from_np, load_golden, make_qkv
+
+pytestmark = pytest.mark.gpu
+
+DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+
+@pytest.fixture(scope="module")
+def T():
+    import tidaldecode_b200.ops as ops
+    return ops
+
+
+def _ws(T, B, Hq, D, rows, n):
+    return T.Workspace(B, Hq, D, rows, n)
+
+
+def _run_full(T, q, K, V, page_size, shuffle, **kw):
+    B, Hq, _, D = q.shape
+    N = K.shape[2]
+    pool, table, ppb = build_pool(K, V, page_size, shuffle_seed=7 if shuffle else None)
+    ws = _ws(T, B, Hq, D, B * Hq, N)
+    o = T.decode_attention(q[:, :, 0].contiguous().cuda(), pool.cuda(), N, ws,
+                           page_table=None if table is None else table.cuda(), pages_per_seq=ppb, **kw)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    return o, ws
+
+
+FULL_CASES = [
+    # dtype, B, Hq, Hkv, D, N, page_size, shuffle, chunks
+    ("f16", 1, 32, 32, 128, 4099, 1, False, 0),
+    ("f16", 1, 32, 32, 128, 63, 1, True, 0),
+    ("f16", 1, 32, 32, 128, 1, 1, False, 0),
+    ("f16", 1, 8, 8, 128, 2000, 16, True, 0),
+    ("f16", 2, 8, 8, 64, 1110, 7, True, 3),
+    ("bf16", 4, 32, 8, 128, 1500, 1, False, 0),
+    ("bf16", 2, 16, 2, 128, 777, 3, True, 5),
+    ("bf16", 1, 64, 8, 128, 3000, 1, False, 0),
+    ("f16", 1, 16, 8, 128, 513, 1, False, 2),
+    ("f32", 1, 4, 4, 64, 2055, 1, False, 0),
+    ("f32", 2, 4, 4, 128, 300, 1, True, 0),
+    ("f16", 1, 64, 64, 128, 600, 1, False, 0),
+    ("f16", 1, 4, 1, 128, 127, 1, False, 0),
+]
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,N,page,shuffle,chunks", FULL_CASES)
+def test_full_attention(T, dt, B, Hq, Hkv, D, N, page, shuffle, chunks):
+    dtype = DT[dt]
+    q, K, V = make_qkv(100 + N, B, Hq, Hkv, D, N, dtype)
+    o, _ = _run_full(T, q, K, V, page, shuffle, num_chunks=chunks)
+    want = O.gathered_attention(q, K, V, torch.arange(N, dtype=torch.int32)[None].expand(B, N))
+    assert_close(o, want[:, :, 0], dtype, "full attention")
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,N,page", [
+    ("f16", 1, 32, 32, 128, 4099, 1), ("bf16", 2, 32, 8, 128, 1029, 1), ("f32", 1, 4, 4, 64, 700, 1),
+    ("f16", 2, 8, 8, 64, 333, 4), ("bf16", 1, 64, 8, 128, 2048, 1),
+])
+@pytest.mark.parametrize("reduce", ["sum", "none"])
+def test_selection_scores(T, dt, B, Hq, Hkv, D, N, page, reduce):
+    """Logits written by the selection layer equal q.k/sqrt(D) of the stored inputs."""
+    dtype = DT[dt]
+    q, K, V = make_qkv(200 + N, B, Hq, Hkv, D, N, dtype, planted=8)
+    shape = (B, N) if reduce == "sum" else (B, Hq, N)
+    scores = torch.full(shape, float("nan"), dtype=torch.float32, device="cuda")
+    o, _ = _run_full(T, q, K, V, page, True, scores=scores)
+    want = O.scores_fp32(q, K, reduce)
+    tol = 2e-4 * (Hq if reduce == "sum" else 1)
+    assert torch.allclose(scores.cpu(), want, rtol=1e-4, atol=tol), (scores.cpu() - want).abs().max()
+    full = O.gathered_attention(q, K, V, torch.arange(N, dtype=torch.int32)[None].expand(B, N))
+    assert_close(o, full[:, :, 0], dtype, "selection layer output")
+
+
+TOPK_CASES = [
+    # rows, n, k
+    (1, 32768, 256), (32, 4099, 256), (4, 131072, 128), (2, 1000, 1), (3, 1000, 999), (3, 1000, 1000),
+    (3, 1000, 5000), (1, 63, 16), (8, 50000, 1024), (2, 17, 16), (1, 300000, 4096), (1, 20000, 8192),
+]
+
+
+@pytest.mark.parametrize("rows,n,k", TOPK_CASES)
+def test_topk_random(T, rows, n, k):
+    g = torch.Generator().manual_seed(n + k)
+    s = torch.randn(rows, n, generator=g)
+    ws = _ws(T, 1, 1, 64, rows, n)
+    idx = T.topk(s.cuda(), k, ws)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    ok, why = O.topk_sets_match(s, idx.cpu(), k, tie_band=0.0)
+    assert ok, why
+    if min(k, n) <= 4096:
+        assert bool((idx[:, 1:] > idx[:, :-1]).all()), "indices must ascend"
+    # the counters are zero at rest: a second call on the same workspace agrees
+    idx2 = T.topk(s.cuda(), k, ws)
+    assert torch.equal(torch.sort(idx, -1).values, torch.sort(idx2, -1).values)
+
+
+def test_topk_ties_and_values(T):
+    """All-equal rows and heavy ties resolve towards the lower index; values are returned."""
+    n, k = 5000, 100
+    ws = _ws(T, 1, 1, 64, 4, n)
+    s = torch.zeros(4, n)
+    s[1] = torch.randint(0, 3, (n,)).float()           # three distinct values
+    s[2, 1234] = 5.0
+    s[3] = -torch.arange(n).float()
+    val = torch.empty(4, k, device="cuda")
+    idx = T.topk(s.cuda(), k, ws, out_val=val).cpu()
+    assert ws.status() == 0
+    assert torch.equal(idx[0], torch.arange(k, dtype=torch.int32))
+    twos = torch.nonzero(s[1] == 2).flatten()[:k].to(torch.int32)
+    assert torch.equal(idx[1], twos)
+    assert 1234 in idx[2].tolist() and set(idx[2].tolist()) == set(range(k - 1)) | {1234}
+    assert torch.equal(idx[3], torch.arange(k, dtype=torch.int32))
+    assert torch.equal(val.cpu(), torch.gather(s, 1, idx.long()))
+
+
+def test_topk_special_values(T):
+    n, k = 3000, 10
+    ws = _ws(T, 1, 1, 64, 1, n)
+    s = torch.randn(1, n)
+    s[0, 5] = float("inf")
+    s[0, 6] = -float("inf")
+    s[0, 7] = -0.0
+    s[0, 8] = 1e-42          # denormal
+    idx = T.topk(s.cuda(), k, ws).cpu()
+    assert ws.status() == 0
+    ok, why = O.topk_sets_match(s, idx, k, tie_band=0.0)
+    assert ok, why
+    assert 5 in idx[0].tolist() and 6 not in idx[0].tolist()
+
+
+def test_topk_force_last_offset_in_idx_own(T):
+    n, k = 2000, 64
+    g = torch.Generator().manual_seed(5)
+    s = torch.randn(2, n, generator=g)
+    ws = _ws(T, 1, 1, 64, 2, n)
+    idx = T.topk(s.cuda(), k, ws, force_last=True).cpu()
+    ok, why = O.topk_sets_match(s, idx, k, tie_band=0.0, force_last=True)
+    assert ok, why
+    base = torch.sort(T.topk(s.cuda(), k, ws).cpu(), -1).values
+    off = torch.sort(T.topk(s.cuda(), k, ws, idx_offset=1000).cpu(), -1).values
+    assert torch.equal(off, base + 1000)
+    remap = torch.randperm(n, generator=g).to(torch.int32)[None].expand(2, n).contiguous()
+    got = T.topk(s.cuda(), k, ws, in_idx=remap.cuda()).cpu()
+    assert torch.equal(torch.sort(got, -1).values, torch.sort(torch.gather(remap, 1, base.long()), -1).values)
+    cnt = torch.zeros(2, dtype=torch.int32, device="cuda")
+    own = T.topk(s.cuda(), k, ws, own_range=(500, 1500), out_count=cnt).cpu()
+    for r in range(2):
+        want = base[r][(base[r] >= 500) & (base[r] < 1500)] - 500
+        assert int(cnt[r]) == want.numel()
+        assert torch.equal(own[r, : want.numel()], want)
+    assert ws.status() == 0
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,N,k,page", [
+    ("f16", 1, 32, 32, 128, 4099, 256, 1), ("bf16", 2, 32, 8, 128, 3000, 128, 1), ("f32", 1, 4, 4, 64, 2055, 128, 1),
+    ("f16", 1, 8, 8, 128, 500, 16, 16), ("bf16", 1, 64, 8, 128, 5000, 1024, 1), ("f16", 2, 8, 2, 64, 900, 33, 5),
+])
+@pytest.mark.parametrize("reduce", ["sum", "none"])
+def test_select_then_sparse(T, dt, B, Hq, Hkv, D, N, k, page, reduce):
+    """Selection layer (+ fused first-digit histogram) -> top-k -> sparse layer."""
+    dtype = DT[dt]
+    q, K, V = make_qkv(300 + N, B, Hq, Hkv, D, N, dtype, planted=min(64, k // 2))
+    pool, table, ppb = build_pool(K, V, page, shuffle_seed=3)
+    rows = B if reduce == "sum" else B * Hq
+    ws = _ws(T, B, Hq, D, rows, N)
+    shape = (B, N) if reduce == "sum" else (B, Hq, N)
+    scores = torch.empty(shape, dtype=torch.float32, device="cuda")
+    qd, pd, td = q[:, :, 0].contiguous().cuda(), pool.cuda(), table.cuda()
+    T.decode_attention(qd, pd, N, ws, page_table=td, scores=scores, hist=ws.hist)
+    idx = T.topk(scores, k, ws, hist=ws.hist)
+    assert int(ws.hist.abs().sum()) == 0, "histogram must be left zeroed"
+    want_scores = O.scores_fp32(q, K, reduce)
+    ok, why = O.topk_sets_match(want_scores.reshape(rows, N), idx.reshape(rows, -1).cpu(), k, tie_band=1e-4)
+    assert ok, why
+    # without the fused histogram the same set comes out
+    idx_b = T.topk(scores, k, ws)
+    assert torch.equal(idx, idx_b)
+    o = T.decode_attention(qd, pd, N, ws, page_table=td, sel_idx=idx)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    want = O.gathered_attention(q, K, V, idx.cpu())
+    assert_close(o, want[:, :, 0], dtype, "sparse layer")
+    # and equals the reference's dense-masked formulation within tolerance
+    mask = torch.zeros(B, rows // B, 1, N).scatter_(-1, idx.cpu().long().view(B, rows // B, 1, -1), 1.0)
+    dense = O.sparse_layer(q, K, V, mask)
+    assert_close(o, dense[:, :, 0], dtype, "sparse layer vs masked dense")
+
+
+@pytest.mark.parametrize("case", ATTN_CASES, ids=[c[0] for c in ATTN_CASES])
+def test_golden_reference_outputs(T, case):
+    """Outputs of the reference's llama_tidal_attention_forward (fixtures) vs the kernels
+    in reference-parity mode: per-q-head sets, newest token not forced."""
+    name, seed, B, Hq, Hkv, D, N, k, dtype, planted = case
+    z = load_golden(f"attn_{name}.npz")
+    q, K, V = make_case(seed, B, Hq, Hkv, D, N, k, dtype, planted)
+    assert input_digest(q, K, V) == str(z["input_sha256"]), "seeded inputs differ from the ones the fixture was made from"
+    pool, table, ppb = build_pool(K, V, 1)
+    ws = _ws(T, B, Hq, D, B * Hq, N)
+    scores = torch.empty(B, Hq, N, dtype=torch.float32, device="cuda")
+    qd, pd = q[:, :, 0].contiguous().cuda(), pool.cuda()
+    o_sel = T.decode_attention(qd, pd, N, ws, pages_per_seq=ppb, scores=scores, hist=ws.hist)
+    idx = T.topk(scores, k, ws, hist=ws.hist)
+    assert_close(o_sel, from_np(z["o_select"], dtype)[:, :, 0], dtype, "selection layer vs reference")
+    ref_sets = torch.from_numpy(z["sel_idx"])
+    kk = min(N, k)
+    if dtype == torch.float32:
+        assert torch.equal(torch.sort(idx.cpu(), -1).values, torch.sort(ref_sets, -1).values)
+    else:
+        # the reference ranks logits rounded to 16 bits; compare through the tie rule on fp32 logits,
+        # with a band of one 16-bit ulp at the k-th logit
+        s32 = O.scores_fp32(q, K, "none").reshape(B * Hq, N)
+        ok, why = O.topk_sets_match(s32, idx.reshape(B * Hq, kk).cpu(), k, tie_band=1e-4)
+        assert ok, why
+        kth = torch.topk(s32, kk).values[:, -1].abs().max().item()
+        band = kth * (2 ** -7 if dtype == torch.bfloat16 else 2 ** -10) * 2 + 1e-4
+        ok, why = O.topk_sets_match(s32, ref_sets.reshape(B * Hq, kk), k, tie_band=band)
+        assert ok, "fixture itself outside the rounding band: " + why
+    # sparse layer on the REFERENCE's sets must reproduce the reference's output
+    o_sp = T.decode_attention(qd, pd, N, ws, pages_per_seq=ppb, sel_idx=ref_sets.cuda())
+    assert_close(o_sp, from_np(z["o_sparse"], dtype)[:, :, 0], dtype, "sparse layer vs reference")
+    assert ws.status() == 0
+
+
+def test_physical_lists_and_extra_page(T):
+    """Reference-shaped call: per-head lists of pool pages plus the newest token's page
+    (tidal/utils/__init__.py:275-286, decode_attn.cuh:726-730)."""
+    B, H, D, N, k = 1, 32, 128, 900, 64
+    q, K, V = make_qkv(9, B, H, H, D, N, torch.float16)
+    pool, table, _ = build_pool(K, V, 1, shuffle_seed=11)
+    g = torch.Generator().manual_seed(1)
+    logical = torch.stack([torch.randperm(N - 1, generator=g)[: k - 1] for _ in range(H)])[None]   # history only
+    phys = table[0][logical.long()].to(torch.int32)
+    ws = _ws(T, B, H, D, H, N)
+    o = T.decode_attention(q[:, :, 0].contiguous().cuda(), pool.cuda(), N, ws, sel_idx=phys.cuda(), sel_physical=True,
+                           extra_page=int(table[0, N - 1]))
+    full = torch.cat((logical, torch.full((1, H, 1), N - 1)), dim=-1).to(torch.int32)
+    want = O.gathered_attention(q, K, V, full)
+    assert_close(o, want[:, :, 0], torch.float16, "physical lists + newest token")
+    assert ws.status() == 0
+
+
+def test_variable_lengths_and_counts(T):
+    B, Hq, Hkv, D, N = 3, 8, 2, 128, 640
+    q, K, V = make_qkv(17, B, Hq, Hkv, D, N, torch.bfloat16)
+    pool, table, ppb = build_pool(K, V, 1)
+    lens = torch.tensor([640, 1, 333], dtype=torch.int32)
+    ws = _ws(T, B, Hq, D, B, N)
+    qd, pd = q[:, :, 0].contiguous().cuda(), pool.cuda()
+    o = T.decode_attention(qd, pd, N, ws, pages_per_seq=ppb, seq_lens=lens.cuda())
+    for b in range(B):
+        n = int(lens[b])
+        want = O.gathered_attention(q[b:b + 1], K[b:b + 1, :, :n], V[b:b + 1, :, :n], torch.arange(n, dtype=torch.int32)[None])
+        assert_close(o[b], want[0, :, 0], torch.bfloat16, f"sequence {b}")
+    # shared lists with per-sequence valid counts (an empty list gives zeros)
+    sel = torch.stack([torch.randperm(300)[:40] for _ in range(B)]).to(torch.int32)
+    cnt = torch.tensor([40, 0, 7], dtype=torch.int32)
+    o = T.decode_attention(qd, pd, N, ws, pages_per_seq=ppb, sel_idx=sel.cuda(), sel_counts=cnt.cuda())
+    for b in range(B):
+        c = int(cnt[b])
+        if c == 0:
+            assert float(o[b].float().abs().max()) == 0.0
+            continue
+        want = O.gathered_attention(q[b:b + 1], K[b:b + 1], V[b:b + 1], sel[b:b + 1, :c])
+        assert_close(o[b], want[0, :, 0], torch.bfloat16, f"list {b}")
+    assert ws.status() == 0
+
+
+def test_bad_index_is_flagged_not_followed(T):
+    B, H, D, N = 1, 8, 128, 100
+    q, K, V = make_qkv(1, B, H, H, D, N, torch.float16)
+    pool, _, ppb = build_pool(K, V, 1)
+    ws = _ws(T, B, H, D, B, N)
+    sel = torch.tensor([[3, 5, 100000, -4]], dtype=torch.int32)
+    T.decode_attention(q[:, :, 0].contiguous().cuda(), pool.cuda(), N, ws, pages_per_seq=ppb, sel_idx=sel.cuda())
+    torch.cuda.synchronize()
+    assert ws.status() & 2
+    ws.reset()
+    assert ws.status() == 0
+
+
+def test_sharded_partials_merge(T):
+    """Sequence-sharded KV emulated on one GPU: per-shard partials + candidates, merged."""
+    B, Hq, Hkv, D, N, k, g = 2, 32, 8, 128, 4000, 128, 4
+    dtype = torch.bfloat16
+    q, K, V = make_qkv(23, B, Hq, Hkv, D, N, dtype, planted=32)
+    bounds = [0, 1000, 1001, 2500, N]       # uneven shards, one of a single token
+    qd = q[:, :, 0].contiguous().cuda()
+    ws = _ws(T, B, Hq, D, B, N)
+    m = torch.empty(g, B, Hq, device="cuda")
+    l = torch.empty(g, B, Hq, device="cuda")
+    o = torch.empty(g, B, Hq, D, device="cuda")
+    cs = torch.full((B, g, k), -float("inf"), device="cuda")
+    ci = torch.zeros((B, g, k), dtype=torch.int32, device="cuda")
+    pools = []
+    for r in range(g):
+        lo, hi = bounds[r], bounds[r + 1]
+        pool, _, ppb = build_pool(K[:, :, lo:hi].contiguous(), V[:, :, lo:hi].contiguous(), 1)
+        pools.append((pool.cuda(), ppb))
+        sc = torch.empty(B, hi - lo, device="cuda")
+        T.decode_attention(qd, pools[r][0], hi - lo, ws, pages_per_seq=ppb, scores=sc, hist=ws.hist,
+                           partials=(m[r], l[r], o[r]), want_out=False)
+        kk = min(k, hi - lo)
+        idx = torch.zeros(B, k, dtype=torch.int32, device="cuda")
+        val = torch.full((B, k), -float("inf"), device="cuda")
+        T.topk(sc, k, ws, out_idx=idx, out_val=val, idx_offset=lo, hist=ws.hist)
+        cs[:, r], ci[:, r] = val, idx
+        if kk < k:
+            cs[:, r, kk:] = -float("inf")
+    out = T.merge_partials(m, l, o, dtype)
+    want = O.gathered_attention(q, K, V, torch.arange(N, dtype=torch.int32)[None].expand(B, N))
+    assert_close(out, want[:, :, 0], dtype, "merged shards")
+    gidx = T.topk(cs.view(B, g * k), k, ws, in_idx=ci.view(B, g * k))
+    ok, why = O.topk_sets_match(O.scores_fp32(q, K, "sum"), gidx.cpu(), k, tie_band=1e-4)
+    assert ok, why
+    # sparse layer: every shard attends to the selected tokens it owns
+    for r in range(g):
+        lo, hi = bounds[r], bounds[r + 1]
+        cnt = torch.zeros(B, dtype=torch.int32, device="cuda")
+        loc = torch.zeros(B, k, dtype=torch.int32, device="cuda")
+        T.topk(cs.view(B, g * k), k, ws, in_idx=ci.view(B, g * k), out_idx=loc, own_range=(lo, hi), out_count=cnt)
+        T.decode_attention(qd, pools[r][0], hi - lo, ws, pages_per_seq=pools[r][1], sel_idx=loc, sel_counts=cnt,
+                           partials=(m[r], l[r], o[r]), want_out=False)
+    out = T.merge_partials(m, l, o, dtype)
+    want = O.gathered_attention(q, K, V, gidx.cpu())
+    assert_close(out, want[:, :, 0], dtype, "sharded sparse layer")
+    assert ws.status() == 0
+
+
+@pytest.mark.parametrize("name,dtype,D", [("f32_d64", torch.float32, 64), ("f16_d128", torch.float16, 128),
+                                          ("bf16_d128", torch.bfloat16, 128)])
+def test_rope_golden(T, name, dtype, D):
+    """apply_rotary_pos_emb of the reference model (fixture) vs the fused kernel, per position."""
+    z = load_golden("rope.npz")
+    q, k = from_np(z[f"{name}_q"], dtype), from_np(z[f"{name}_k"], dtype)        # [1,H,n,D]
+    qe, ke = from_np(z[f"{name}_qe"], dtype), from_np(z[f"{name}_ke"], dtype)
+    theta = float(z[f"{name}_theta"])
+    inv = O.rope_inv_freq(D, theta).cuda()
+    for j, pos in enumerate(z[f"{name}_pos"][0].tolist()):
+        qd, kd = q[0, :, j][None].contiguous().cuda(), k[0, :, j][None].contiguous().cuda()
+        T.rope_append(qd, kd, None, None, pos0=pos, rope_theta=theta, rope_mode=1, inv_freq=inv)
+        tol = dict(rtol=0, atol=2e-6) if dtype == torch.float32 else dict(rtol=0, atol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -9)
+        # large angles lose fp32 precision in the sincos argument itself; one storage ulp of slack
+        assert torch.allclose(qd.cpu().float()[0], qe[0, :, j].float(), **tol), (name, pos)
+        assert torch.allclose(kd.cpu().float()[0], ke[0, :, j].float(), **tol), (name, pos)
+        exact = (qd.cpu()[0] == qe[0, :, j]).float().mean().item()
+        assert exact > 0.97, f"{name} pos {pos}: only {exact:.3f} of elements bit-equal"
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,page,tps", [("f16", 1, 32, 32, 128, 1, 1), ("bf16", 4, 32, 8, 128, 1, 1),
+                                                     ("f32", 1, 4, 4, 64, 1, 1), ("f16", 2, 8, 8, 128, 16, 37),
+                                                     ("bf16", 1, 64, 8, 128, 3, 5)])
+def test_rope_append(T, dt, B, Hq, Hkv, D, page, tps):
+    """q/k rotated, k/v land in the right pool slots (cpu_reference.h:294-327), nothing else is touched."""
+    dtype = DT[dt]
+    g = torch.Generator().manual_seed(77)
+    n = B * tps
+    q = torch.randn(n, Hq, D, generator=g).to(dtype)
+    k = torch.randn(n, Hkv, D, generator=g).to(dtype)
+    v = torch.randn(n, Hkv, D, generator=g).to(dtype)
+    past = torch.tensor([5, 1000, 31, 64][:B], dtype=torch.int32)
+    ppb = (int(past.max()) + tps + page - 1) // page + 1
+    total = B * ppb + 2
+    table = torch.randperm(total, generator=g)[: B * ppb].view(B, ppb).to(torch.int32)
+    pool0 = torch.randn(total, 2, page, Hkv, D, generator=g).to(dtype)
+    pool = pool0.clone().cuda()
+    qd, kd = q.clone().cuda(), k.clone().cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    T.rope_append(qd, kd, v.cuda(), pool, batch=B, pos0_dev=past.cuda(), page_table=table.cuda(), rope_theta=1e4,
+                  rope_mode=2, status=status)
+    pos = (past[:, None] + torch.arange(tps)[None]).reshape(-1)
+    q_want, k_want = O.apply_rope_fp32(q, pos, 1e4), O.apply_rope_fp32(k, pos, 1e4)
+    tol = dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=0, atol=2 ** -6 if dtype == torch.bfloat16 else 2 ** -8)
+    assert torch.allclose(qd.cpu().float(), q_want.float(), **tol)
+    assert torch.allclose(kd.cpu().float(), k_want.float(), **tol)
+    want_pool = pool0.clone()
+    for b in range(B):
+        seq_len = int(past[b]) + tps
+        O.append_paged_kv(want_pool, table[b].tolist(), seq_len, kd.cpu()[b * tps:(b + 1) * tps], v[b * tps:(b + 1) * tps])
+    assert torch.equal(pool.cpu(), want_pool), "pool contents differ from the CPU append"
+    assert int(status) == 0

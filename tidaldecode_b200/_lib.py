@@ -1,0 +1,108 @@
+"""ctypes binding of libtidal_b200.so (the C ABI declared in include/tidal_b200.h).
+
+There is no fallback: if the library is missing or a symbol cannot be resolved,
+importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libtidal_b200.so")
+
+DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
+ERR_ARG, ERR_WORKSPACE, ERR_CUDA = -1, -2, -3
+DEV_WAIT_TIMEOUT, DEV_BAD_INDEX, DEV_TOPK_OVERFLOW = 1, 2, 4
+TOPK_BINS = 4096
+
+EXPORTS = (
+    "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_rope_append", "tidal_merge_partials",
+)
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [
+        ("d_q", C.c_void_p), ("d_o", C.c_void_p), ("d_kv", C.c_void_p),
+        ("d_page_table", C.c_void_p), ("page_table_stride", C.c_int64),
+        ("d_seq_lens", C.c_void_p), ("seq_len", C.c_int32),
+        ("d_sel_idx", C.c_void_p), ("sel_rows", C.c_int32), ("sel_count", C.c_int32), ("sel_stride", C.c_int64),
+        ("sel_physical", C.c_int32), ("d_sel_counts", C.c_void_p), ("extra_page", C.c_int32),
+        ("d_scores", C.c_void_p), ("score_rows", C.c_int32), ("score_stride", C.c_int64),
+        ("d_hist", C.c_void_p), ("force_last", C.c_int32),
+        ("d_part_m", C.c_void_p), ("d_part_l", C.c_void_p), ("d_part_o", C.c_void_p),
+        ("batch", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("page_size", C.c_int32), ("dtype", C.c_int32),
+        ("num_pages", C.c_int64), ("sm_scale", C.c_float), ("num_chunks", C.c_int32), ("heads_per_cta", C.c_int32),
+    ]
+
+
+class TopkArgs(C.Structure):
+    _fields_ = [
+        ("d_scores", C.c_void_p), ("d_in_idx", C.c_void_p), ("rows", C.c_int32),
+        ("n", C.c_int64), ("row_stride", C.c_int64), ("k", C.c_int32),
+        ("d_out_idx", C.c_void_p), ("d_out_val", C.c_void_p), ("out_stride", C.c_int64),
+        ("idx_offset", C.c_int32), ("force_last", C.c_int32), ("own_lo", C.c_int32), ("own_hi", C.c_int32),
+        ("d_out_count", C.c_void_p), ("d_hist", C.c_void_p),
+    ]
+
+
+class RopeAppendArgs(C.Structure):
+    _fields_ = [
+        ("d_q", C.c_void_p), ("d_k", C.c_void_p), ("d_v", C.c_void_p), ("d_kv", C.c_void_p),
+        ("d_page_table", C.c_void_p), ("page_table_stride", C.c_int64),
+        ("d_pos0", C.c_void_p), ("pos0", C.c_int32), ("d_inv_freq", C.c_void_p),
+        ("rope_theta", C.c_float), ("rope_scale", C.c_float), ("rope_mode", C.c_int32), ("rotate_k_in_place", C.c_int32),
+        ("batch", C.c_int32), ("tokens_per_seq", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32), ("page_size", C.c_int32), ("dtype", C.c_int32),
+        ("num_pages", C.c_int64), ("d_status", C.c_void_p),
+    ]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python -m tidaldecode_b200.build` "
+            "(tidaldecode_b200 has no CPU or PyTorch fallback)")
+    lib = C.CDLL(LIB_PATH)
+    for name in EXPORTS:
+        if not hasattr(lib, name):
+            raise ImportError(f"{LIB_PATH} does not export {name}")
+    lib.tidal_version.restype = C.c_int
+    lib.tidal_last_error.restype = C.c_char_p
+    lib.tidal_launch_count.restype = C.c_uint64
+    lib.tidal_ws_bytes.restype = C.c_size_t
+    lib.tidal_ws_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64]
+    lib.tidal_ws_init.restype = C.c_int
+    lib.tidal_ws_init.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p]
+    lib.tidal_ws_release.restype = C.c_int
+    lib.tidal_ws_release.argtypes = [C.c_void_p]
+    lib.tidal_ws_status.restype = C.c_int
+    lib.tidal_ws_status.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.tidal_decode_attention.restype = C.c_int
+    lib.tidal_decode_attention.argtypes = [C.POINTER(AttnArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.tidal_plan_chunks.restype = C.c_int
+    lib.tidal_plan_chunks.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+    lib.tidal_topk.restype = C.c_int
+    lib.tidal_topk.argtypes = [C.POINTER(TopkArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.tidal_rope_append.restype = C.c_int
+    lib.tidal_rope_append.argtypes = [C.POINTER(RopeAppendArgs), C.c_void_p]
+    lib.tidal_merge_partials.restype = C.c_int
+    lib.tidal_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         C.c_void_p, C.c_int, C.c_void_p]
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return lib.tidal_last_error().decode()
+
+
+def check(rc: int, what: str) -> None:
+    """Negative return codes become RuntimeError, as TORCH_CHECK failures do in
+    the reference's extension (tidal/ops/csrc/page.cu:20-41)."""
+    if rc < 0:
+        raise RuntimeError(f"{what} failed ({rc}): {last_error()}")

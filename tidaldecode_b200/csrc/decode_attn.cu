@@ -1,0 +1,655 @@
+// Decode attention over a paged KV pool for sm_100a: one kernel serves full,
+// token-selection and sparse layers (tidal_decode_attention), one kernel merges
+// the split-KV partials.
+//
+// Data movement: a producer warp walks the CTA's token list and, per token,
+// issues two one-dimensional TMA bulk copies (cp.async.bulk) — the K row and the
+// V row of the CTA's KV heads, HC*D*sizeof(T) bytes each, contiguous in the
+// [pages][2][page_size][Hkv][D] pool — into a ring of shared-memory stages
+// tracked by full/empty mbarriers.  Consumer warps read the rows back with
+// 128-bit shared loads, LPR = D*sizeof(T)/16 lanes per row ("slot"), reduce the
+// dot product with warp shuffles and keep an online softmax per (slot, q head)
+// in the log2 domain.  Every wait is bounded.
+//
+// Work split: grid = (chunks of the token list, head slices, sequences).  A CTA
+// covers HC KV heads (all of them when logits are summed over heads, so the sum
+// is formed in shared memory in a fixed order); its slots either own HPS heads
+// each (HC = slots*HPS) or share a head among TG token groups (slots = HC*TG).
+#include "common.cuh"
+
+namespace tidal {
+
+struct AttnParams {
+    const void* q;
+    void* o;
+    const char* kv;
+    const int32_t* page_table;
+    int64_t pt_stride;
+    const int32_t* seq_lens;
+    int32_t seq_len;
+    const int32_t* sel_idx;
+    const int32_t* sel_counts;
+    int32_t sel_rows, sel_count, sel_physical, extra_page;
+    int64_t sel_stride;
+    float* scores;
+    int32_t score_rows;
+    int64_t score_stride;
+    uint32_t* hist;
+    int32_t force_last;
+    float* part_o;   // [B][Hq][nchunks][D]
+    float* part_ml;  // [B][Hq][nchunks][2]
+    float* shard_m;  // optional [B][Hq]
+    float* shard_l;
+    float* shard_o;  // optional [B][Hq][D]
+    uint32_t* status;
+    int32_t B, Hq, Hkv, page_size;
+    int64_t num_pages;
+    float sm_scale;
+    int32_t nchunks;
+    int32_t HC;       // KV heads per CTA
+    int32_t greal;    // Hq / Hkv (the kernel's G is 1 in per-q-head list mode)
+    int32_t per_head; // 1: head slice index is a q head, HC == 1
+    int32_t T, S, TG; // tokens per stage, stages, token groups
+    int32_t CW;       // consumer warps
+};
+
+__host__ __device__ inline size_t round16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+__host__ __device__ inline size_t attn_smem_bytes(int S, int T, int row_bytes, int HC, int CW, int slots, int hps,
+                                                  int G, int D, bool want_scores) {
+    size_t stage = (size_t)S * 2 * T * row_bytes;
+    size_t ep = (size_t)slots * hps * G * (D + 2) * sizeof(float);
+    size_t main_bytes = round16(stage > ep ? stage : ep);
+    size_t sc = want_scores ? round16((size_t)S * T * HC * sizeof(float)) : 0;
+    return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
+}
+
+// T: storage type; D: head dim; G: q heads per KV head handled by one slot;
+// HPS: KV heads per slot.
+template <typename T, int D, int G, int HPS>
+__global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const AttnParams p) {
+    using V = Vec16<T>;
+    constexpr int VEC = V::N;
+    constexpr int LPR = D / VEC;          // lanes per row
+    constexpr int SPW = 32 / LPR;         // slots per warp
+    static_assert(LPR <= 32 && (32 % LPR) == 0, "row must fit a warp");
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int row_bytes = p.HC * D * (int)sizeof(T);
+    const int S = p.S, TT = p.T, TG = p.TG, HC = p.HC;
+    const int slots = p.CW * SPW;
+    const size_t stage_bytes = (size_t)S * 2 * TT * row_bytes;
+    const size_t ep_bytes = (size_t)slots * HPS * G * (D + 2) * sizeof(float);
+    const size_t main_bytes = round16(stage_bytes > ep_bytes ? stage_bytes : ep_bytes);
+    const bool want_scores = p.scores != nullptr;
+    const bool sum_heads = want_scores && p.score_rows == 1;
+    unsigned char* stage_base = smem;
+    float* sc_smem = reinterpret_cast<float*>(smem + main_bytes);                  // [S][T][HC]
+    const size_t sc_bytes = sum_heads ? round16((size_t)S * TT * HC * sizeof(float)) : 0;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + main_bytes + sc_bytes);
+    uint64_t* empty_bar = full_bar + S;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
+
+    const int chunk = blockIdx.x, slice = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // ---- token list of this CTA
+    const int sel_row = p.sel_idx ? (p.sel_rows == 1 ? 0 : slice) : 0;
+    int list_len;
+    if (p.sel_idx) {
+        list_len = p.sel_counts ? p.sel_counts[(size_t)b * p.sel_rows + sel_row] : p.sel_count;
+        if (list_len > p.sel_count) list_len = p.sel_count;
+        if (list_len < 0) list_len = 0;
+    } else {
+        list_len = p.seq_lens ? p.seq_lens[b] : p.seq_len;
+        if (list_len > p.seq_len) list_len = p.seq_len;
+        if (list_len < 0) list_len = 0;
+    }
+    const int seq_len_b = p.seq_lens ? min(p.seq_lens[b], p.seq_len) : p.seq_len;
+    const int ntok_all = list_len + (p.extra_page >= 0 ? 1 : 0);
+    const int ctok = (ntok_all + p.nchunks - 1) / p.nchunks;
+    const int tok0 = chunk * ctok;
+    const int ntok = max(0, min(ntok_all, tok0 + ctok) - tok0);
+    const int n_iters = (ntok + TT - 1) / TT;
+
+    const int kvh0 = p.per_head ? slice / p.greal : slice * HC;   // first KV head of the CTA
+    const int qh0 = p.per_head ? slice : kvh0 * G;                // first q head of the CTA
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], p.CW);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        // =============================================================== producer
+        const size_t plane = (size_t)p.page_size * p.Hkv * D * sizeof(T);   // bytes of one K (or V) plane of a page
+        const size_t tok_bytes = (size_t)p.Hkv * D * sizeof(T);
+        for (int it = 0; it < n_iters; ++it) {
+            const int s = it % S;
+            if (it >= S) mbar_wait_bounded(&empty_bar[s], ((it / S) - 1) & 1, abort_flag, p.status);
+            const int valid = min(TT, ntok - it * TT);
+            if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(valid * 2 * row_bytes));
+            __syncwarp();
+            unsigned char* kdst = stage_base + (size_t)s * 2 * TT * row_bytes;
+            unsigned char* vdst = kdst + (size_t)TT * row_bytes;
+            for (int t = lane; t < valid; t += 32) {
+                const int li = tok0 + it * TT + t;   // index into the CTA's sequence-wide list
+                int64_t page;
+                int entry = 0;
+                bool ok = true;
+                if (p.sel_idx) {
+                    if (li >= list_len) {
+                        page = p.extra_page;           // the appended newest token
+                    } else {
+                        const int e = p.sel_idx[((size_t)b * p.sel_rows + sel_row) * p.sel_stride + li];
+                        if (p.sel_physical) {
+                            page = e;
+                        } else {
+                            ok = (e >= 0 && e < seq_len_b);
+                            const int pos = ok ? e : 0;
+                            const int pg = pos / p.page_size;
+                            entry = pos - pg * p.page_size;
+                            page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
+                        }
+                    }
+                } else {
+                    const int pg = li / p.page_size;
+                    entry = li - pg * p.page_size;
+                    page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
+                }
+                if (!ok || page < 0 || page >= p.num_pages) {
+                    atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
+                    page = 0;
+                    entry = 0;
+                }
+                const char* ksrc = p.kv + (size_t)page * 2 * plane + (size_t)entry * tok_bytes + (size_t)kvh0 * D * sizeof(T);
+                bulk_g2s(kdst + (size_t)t * row_bytes, ksrc, (uint32_t)row_bytes, &full_bar[s]);
+                bulk_g2s(vdst + (size_t)t * row_bytes, ksrc + plane, (uint32_t)row_bytes, &full_bar[s]);
+            }
+        }
+        // Nothing of this CTA may still be in flight when it retires: the consumers
+        // waited on every full barrier unless a wait ran out; cover that case here.
+        if (*abort_flag && lane == 0) {
+            for (int it = max(0, n_iters - S); it < n_iters; ++it) {
+                const int s = it % S;
+                for (uint32_t i = 0; i < kWaitSpinLimit; ++i)
+                    if (mbar_try_wait(&full_bar[s], (it / S) & 1)) break;
+            }
+        }
+        return;
+    }
+
+    // ================================================================= consumers
+    const int cw = warp - 1;
+    const int slot = cw * SPW + lane / LPR;
+    const int sl = lane % LPR;                    // lane within the slot
+    const unsigned slot_mask = (LPR == 32) ? 0xffffffffu : (((1u << LPR) - 1u) << ((lane / LPR) * LPR));
+    int head_local, tg;                           // first KV head (within the CTA) and token group of this slot
+    if (TG == 1) {
+        head_local = slot * HPS;
+        tg = 0;
+    } else {
+        head_local = slot % HC;
+        tg = slot / HC;
+    }
+    const bool slot_active = head_local < HC;
+    const int consumer_threads = p.CW * 32;
+    const int ctid = threadIdx.x - 32;
+
+    float qf[HPS][G][VEC], of[HPS][G][VEC], mrun[HPS][G], lrun[HPS][G];
+#pragma unroll
+    for (int hh = 0; hh < HPS; ++hh)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            mrun[hh][g] = -INFINITY;
+            lrun[hh][g] = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) of[hh][g][i] = 0.f;
+            if (slot_active) {
+                const int hq = qh0 + (head_local + hh) * G + g;
+                const uint4 v = *reinterpret_cast<const uint4*>(
+                    reinterpret_cast<const T*>(p.q) + ((size_t)b * p.Hq + hq) * D + sl * VEC);
+                V::to_float(v, qf[hh][g]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) qf[hh][g][i] = 0.f;
+            }
+        }
+    const float scale_log2 = p.sm_scale * kLog2e;
+
+    for (int it = 0; it < n_iters; ++it) {
+        const int s = it % S;
+        mbar_wait_bounded(&full_bar[s], (it / S) & 1, abort_flag, p.status);
+        const int valid = min(TT, ntok - it * TT);
+        const unsigned char* kst = stage_base + (size_t)s * 2 * TT * row_bytes;
+        const unsigned char* vst = kst + (size_t)TT * row_bytes;
+        float* sc = sc_smem + (size_t)s * TT * HC;
+        if (slot_active) {
+            for (int t = tg; t < valid; t += TG) {
+                const int pos = tok0 + it * TT + t;       // position (full / selection layers)
+#pragma unroll
+                for (int hh = 0; hh < HPS; ++hh) {
+                    const size_t off = (size_t)t * row_bytes + (size_t)(head_local + hh) * D * sizeof(T) + sl * 16;
+                    float kf[VEC], vf[VEC];
+                    V::to_float(*reinterpret_cast<const uint4*>(kst + off), kf);
+                    V::to_float(*reinterpret_cast<const uint4*>(vst + off), vf);
+                    float ssum = 0.f;
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        float d = 0.f;
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) d = fmaf(qf[hh][g][i], kf[i], d);
+#pragma unroll
+                        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(slot_mask, d, o);
+                        const float sraw = d * p.sm_scale;
+                        if (want_scores) {
+                            if (sum_heads) {
+                                ssum += sraw;
+                            } else if (sl == 0) {
+                                const int hq = qh0 + (head_local + hh) * G + g;
+                                const size_t row = (size_t)b * p.score_rows + hq;
+                                p.scores[row * p.score_stride + pos] = sraw;
+                                if (p.hist) {
+                                    uint32_t bin = ordered_key(sraw) >> kDigit0Shift;
+                                    if (p.force_last && pos == seq_len_b - 1) bin = TIDAL_TOPK_BINS - 1;
+                                    atomicAdd(&p.hist[row * TIDAL_TOPK_BINS + bin], 1u);
+                                }
+                            }
+                        }
+                        const float s2 = d * scale_log2;
+                        const float mnew = fmaxf(mrun[hh][g], s2);
+                        const float alpha = fast_exp2(mrun[hh][g] - mnew);
+                        const float pexp = fast_exp2(s2 - mnew);
+                        mrun[hh][g] = mnew;
+                        lrun[hh][g] = fmaf(lrun[hh][g], alpha, pexp);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) of[hh][g][i] = fmaf(of[hh][g][i], alpha, pexp * vf[i]);
+                    }
+                    if (sum_heads && sl == 0) sc[t * HC + head_local + hh] = ssum;
+                }
+            }
+        }
+        if (sum_heads) {
+            // head sum in a fixed order, one thread per token of the stage
+            named_bar_sync(1, consumer_threads);
+            for (int t = ctid; t < valid; t += consumer_threads) {
+                float a = 0.f;
+                for (int h = 0; h < HC; ++h) a += sc[t * HC + h];
+                const int pos = tok0 + it * TT + t;
+                p.scores[(size_t)b * p.score_stride + pos] = a;
+                if (p.hist) {
+                    uint32_t bin = ordered_key(a) >> kDigit0Shift;
+                    if (p.force_last && pos == seq_len_b - 1) bin = TIDAL_TOPK_BINS - 1;
+                    atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + bin], 1u);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+
+    // ---------------------------------------------------------------- epilogue
+    // All stages are drained (every consumer waited on every full barrier), so the
+    // stage ring is reused to combine the token groups of each head.
+    named_bar_sync(2, consumer_threads);
+    float* ep_o = reinterpret_cast<float*>(stage_base);                    // [slots][HPS*G][D]
+    float* ep_ml = ep_o + (size_t)slots * HPS * G * D;                     // [slots][HPS*G][2]
+#pragma unroll
+    for (int hh = 0; hh < HPS; ++hh)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const int e = (slot * HPS + hh) * G + g;
+            float4* dst = reinterpret_cast<float4*>(ep_o + (size_t)e * D + sl * VEC);
+#pragma unroll
+            for (int i = 0; i < VEC / 4; ++i)
+                dst[i] = make_float4(of[hh][g][4 * i], of[hh][g][4 * i + 1], of[hh][g][4 * i + 2], of[hh][g][4 * i + 3]);
+            if (sl == 0) {
+                ep_ml[2 * e] = mrun[hh][g];
+                ep_ml[2 * e + 1] = lrun[hh][g];
+            }
+        }
+    named_bar_sync(2, consumer_threads);
+    // outputs of the CTA: HC*G q heads x D
+    const int nout = HC * G * D;
+    for (int idx = ctid; idx < nout; idx += consumer_threads) {
+        const int d = idx % D;
+        const int hg = idx / D;             // local (kv head, g)
+        const int hl = hg / G, g = hg % G;
+        // the slots that hold head hl: TG == 1 → slot hl/HPS, sub-head hl%HPS; else slots hl + j*HC
+        float M = -INFINITY;
+        for (int j = 0; j < TG; ++j) {
+            const int e = (TG == 1) ? ((hl / HPS) * HPS + hl % HPS) * G + g : ((hl + j * HC) * HPS) * G + g;
+            M = fmaxf(M, ep_ml[2 * e]);
+        }
+        float acc = 0.f, L = 0.f;
+        for (int j = 0; j < TG; ++j) {
+            const int e = (TG == 1) ? ((hl / HPS) * HPS + hl % HPS) * G + g : ((hl + j * HC) * HPS) * G + g;
+            const float m = ep_ml[2 * e];
+            const float w = (m == -INFINITY) ? 0.f : fast_exp2(m - M);
+            acc = fmaf(w, ep_o[(size_t)e * D + d], acc);
+            L = fmaf(w, ep_ml[2 * e + 1], L);
+        }
+        const int hq = qh0 + hl * G + g;
+        const size_t ph = (size_t)b * p.Hq + hq;
+        if (p.nchunks == 1) {
+            if (p.o) reinterpret_cast<T*>(p.o)[ph * D + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
+            if (p.shard_o) {
+                p.shard_o[ph * D + d] = acc;
+                if (d == 0) {
+                    p.shard_m[ph] = M;
+                    p.shard_l[ph] = L;
+                }
+            }
+        } else {
+            p.part_o[(ph * p.nchunks + chunk) * D + d] = acc;
+            if (d == 0) {
+                p.part_ml[(ph * p.nchunks + chunk) * 2] = M;
+                p.part_ml[(ph * p.nchunks + chunk) * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// Merge the split-KV partials of one (sequence, q head): grid (Hq, B), D threads.
+template <typename T>
+__global__ void merge_chunks_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nchunks,
+                                    int Hq, int D, T* __restrict__ o, float* __restrict__ shard_m,
+                                    float* __restrict__ shard_l, float* __restrict__ shard_o) {
+    const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const size_t ph = (size_t)b * Hq + hq;
+    const float* ml = part_ml + ph * nchunks * 2;
+    float M = -INFINITY;
+    for (int c = 0; c < nchunks; ++c) M = fmaxf(M, ml[2 * c]);
+    float acc = 0.f, L = 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+        const float m = ml[2 * c];
+        const float w = (m == -INFINITY) ? 0.f : fast_exp2(m - M);
+        acc = fmaf(w, part_o[(ph * nchunks + c) * D + d], acc);
+        L = fmaf(w, ml[2 * c + 1], L);
+    }
+    if (o) o[ph * D + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
+    if (shard_o) {
+        shard_o[ph * D + d] = acc;
+        if (d == 0) {
+            shard_m[ph] = M;
+            shard_l[ph] = L;
+        }
+    }
+}
+
+// Merge `shards` sets of un-normalised partials laid out [shards][B*Hq(*D)].
+template <typename T>
+__global__ void merge_shards_kernel(const float* __restrict__ m, const float* __restrict__ l,
+                                    const float* __restrict__ o, int shards, int rows, int D, T* __restrict__ out) {
+    const int r = blockIdx.x, d = threadIdx.x;
+    float M = -INFINITY;
+    for (int s = 0; s < shards; ++s) M = fmaxf(M, m[(size_t)s * rows + r]);
+    float acc = 0.f, L = 0.f;
+    for (int s = 0; s < shards; ++s) {
+        const float ms = m[(size_t)s * rows + r];
+        const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+        acc = fmaf(w, o[((size_t)s * rows + r) * D + d], acc);
+        L = fmaf(w, l[(size_t)s * rows + r], L);
+    }
+    out[(size_t)r * D + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
+}
+
+// ------------------------------------------------------------------ planning
+struct AttnPlan {
+    int HC, HPS, TG, CW, T, S, nchunks, nslices;
+    size_t smem;
+};
+
+static int sm_count_cached() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+constexpr size_t kSmemBudget = 200 * 1024;   // per CTA, leaves room for a second small CTA's static use
+
+// Pick the slot geometry for HC heads per CTA; false if HC cannot be mapped.
+static bool plan_slots(int HC, int lpr, bool allow_hps2, int max_cw, int* CW, int* HPS, int* TG) {
+    const int spw = 32 / lpr;
+    for (int cw : {8, 16, 4}) {
+        if (cw > max_cw) continue;
+        const int slots = cw * spw;
+        if (slots % HC == 0) {
+            *CW = cw; *HPS = 1; *TG = slots / HC;
+            return true;
+        }
+        if (allow_hps2 && HC == slots * 2) {
+            *CW = cw; *HPS = 2; *TG = 1;
+            return true;
+        }
+    }
+    return false;
+}
+
+}  // namespace tidal
+
+using namespace tidal;
+
+extern "C" int tidal_plan_chunks(int batch, int head_slices, int tokens, int min_tokens_per_chunk, int sm_count) {
+    if (batch <= 0 || head_slices <= 0 || tokens < 0) return TIDAL_ERR_ARG;
+    if (sm_count <= 0) sm_count = 148;
+    if (min_tokens_per_chunk < 1) min_tokens_per_chunk = 1;
+    const int rows = batch * head_slices;
+    // one wave of CTAs over the SMs: the shared-memory ring allows one CTA per SM
+    int n = sm_count / rows;
+    if (n < 1) n = 1;
+    const int by_work = (tokens + min_tokens_per_chunk - 1) / min_tokens_per_chunk;
+    if (n > by_work) n = by_work < 1 ? 1 : by_work;
+    if (n > kMaxChunks) n = kMaxChunks;
+    return n;
+}
+
+namespace tidal {
+
+template <typename T, int D, int G, int HPS>
+static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t st) {
+    auto kern = decode_attn_kernel<T, D, G, HPS>;
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
+    dim3 grid(plan.nchunks, plan.nslices, p.B);
+    dim3 block((plan.CW + 1) * 32);
+    kern<<<grid, block, plan.smem, st>>>(p);
+    TIDAL_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return TIDAL_OK;
+}
+
+template <typename T, int D>
+static int dispatch_g(const AttnParams& p, const AttnPlan& plan, int G, cudaStream_t st) {
+    if (plan.HPS == 2) {
+        if (G == 1) return launch_attn<T, D, 1, 2>(p, plan, st);
+        set_error("two KV heads per slot is only built for MHA (group size 1), got %d", G);
+        return TIDAL_ERR_ARG;
+    }
+    switch (G) {
+        case 1: return launch_attn<T, D, 1, 1>(p, plan, st);
+        case 2: return launch_attn<T, D, 2, 1>(p, plan, st);
+        case 4: return launch_attn<T, D, 4, 1>(p, plan, st);
+        case 8: return launch_attn<T, D, 8, 1>(p, plan, st);
+        default:
+            set_error("unsupported GQA group size %d (built: 1, 2, 4, 8)", G);
+            return TIDAL_ERR_ARG;
+    }
+}
+
+template <typename T>
+static int dispatch_d(const AttnParams& p, const AttnPlan& plan, int D, int G, cudaStream_t st) {
+    switch (D) {
+        case 64: return dispatch_g<T, 64>(p, plan, G, st);
+        case 128: return dispatch_g<T, 128>(p, plan, G, st);
+        default:
+            set_error("unsupported head_dim %d (built: 64, 128)", D);
+            return TIDAL_ERR_ARG;
+    }
+}
+
+template <typename T>
+static int launch_merge(const AttnParams& p, int D, cudaStream_t st) {
+    merge_chunks_kernel<T><<<dim3(p.Hq, p.B), D, 0, st>>>(p.part_o, p.part_ml, p.nchunks, p.Hq, D, (T*)p.o, p.shard_m,
+                                                          p.shard_l, p.shard_o);
+    TIDAL_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return TIDAL_OK;
+}
+
+}  // namespace tidal
+
+extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size_t ws_bytes, void* stream) {
+    TIDAL_REQUIRE(a != nullptr, TIDAL_ERR_ARG, "args is NULL");
+    TIDAL_REQUIRE(a->d_q && a->d_kv, TIDAL_ERR_ARG, "q and kv must be given");
+    TIDAL_REQUIRE(((uintptr_t)a->d_q & 15) == 0 && ((uintptr_t)a->d_kv & 15) == 0 && ((uintptr_t)a->d_o & 15) == 0,
+                  TIDAL_ERR_ARG, "q, o and kv must be 16-byte aligned");
+    TIDAL_REQUIRE(a->d_o || a->d_part_o, TIDAL_ERR_ARG, "neither o nor partial outputs given");
+    TIDAL_REQUIRE((a->d_part_o != nullptr) == (a->d_part_m != nullptr) && (a->d_part_o != nullptr) == (a->d_part_l != nullptr),
+                  TIDAL_ERR_ARG, "part_m, part_l, part_o must be given together");
+    TIDAL_REQUIRE(a->batch > 0 && a->num_qo_heads > 0 && a->num_kv_heads > 0, TIDAL_ERR_ARG, "bad batch/heads");
+    TIDAL_REQUIRE(a->num_qo_heads % a->num_kv_heads == 0, TIDAL_ERR_ARG,
+                  "num_qo_heads %d is not a multiple of num_kv_heads %d", a->num_qo_heads, a->num_kv_heads);
+    TIDAL_REQUIRE(a->page_size >= 1 && a->num_pages >= 1, TIDAL_ERR_ARG, "bad page_size/num_pages");
+    TIDAL_REQUIRE(a->seq_len >= 0, TIDAL_ERR_ARG, "negative seq_len");
+    TIDAL_REQUIRE(a->dtype >= 0 && a->dtype <= 2, TIDAL_ERR_ARG, "unknown dtype %d", a->dtype);
+    const int G = a->num_qo_heads / a->num_kv_heads;
+    const int D = a->head_dim;
+    const int es = a->dtype == TIDAL_DTYPE_F32 ? 4 : 2;
+    TIDAL_REQUIRE(D == 64 || D == 128, TIDAL_ERR_ARG, "unsupported head_dim %d (built: 64, 128)", D);
+    const int lpr = D * es / 16;
+    const bool sel = a->d_sel_idx != nullptr;
+    if (sel) {
+        TIDAL_REQUIRE(a->sel_rows == 1 || a->sel_rows == a->num_qo_heads, TIDAL_ERR_ARG,
+                      "sel_rows must be 1 or num_qo_heads, got %d", a->sel_rows);
+        TIDAL_REQUIRE(a->sel_count >= 0 && a->sel_stride >= a->sel_count, TIDAL_ERR_ARG, "bad sel_count/sel_stride");
+        TIDAL_REQUIRE(!a->sel_physical || a->page_size == 1, TIDAL_ERR_ARG, "physical page lists need page_size 1");
+        TIDAL_REQUIRE(a->d_scores == nullptr, TIDAL_ERR_ARG, "logits are only written by layers that attend to all tokens");
+    } else {
+        TIDAL_REQUIRE(a->extra_page < 0, TIDAL_ERR_ARG, "extra_page needs a selection list");
+    }
+    if (a->d_scores) {
+        TIDAL_REQUIRE(a->score_rows == 1 || a->score_rows == a->num_qo_heads, TIDAL_ERR_ARG,
+                      "score_rows must be 1 or num_qo_heads, got %d", a->score_rows);
+        TIDAL_REQUIRE(a->score_stride >= a->seq_len, TIDAL_ERR_ARG, "score_stride shorter than seq_len");
+    } else {
+        TIDAL_REQUIRE(a->d_hist == nullptr, TIDAL_ERR_ARG, "a histogram needs d_scores");
+    }
+    const WsLayout* L = find_ws(d_ws);
+    TIDAL_REQUIRE(L != nullptr, TIDAL_ERR_WORKSPACE, "workspace %p was not initialised with tidal_ws_init", d_ws);
+    TIDAL_REQUIRE(ws_bytes >= L->total, TIDAL_ERR_WORKSPACE, "workspace is %zu bytes, layout needs %zu", ws_bytes, L->total);
+
+    AttnPlan plan;
+    const bool per_head = sel && a->sel_rows != 1 && a->num_qo_heads > 1;
+    const bool sum_heads = a->d_scores && a->score_rows == 1;
+    int kernel_G = G;
+    if (per_head) {
+        plan.HC = 1;
+        plan.nslices = a->num_qo_heads;
+        kernel_G = 1;
+    } else {
+        plan.HC = a->heads_per_cta > 0 ? a->heads_per_cta : a->num_kv_heads;
+        if (sum_heads) plan.HC = a->num_kv_heads;
+        TIDAL_REQUIRE(a->num_kv_heads % plan.HC == 0, TIDAL_ERR_ARG, "heads_per_cta %d does not divide num_kv_heads %d",
+                      plan.HC, a->num_kv_heads);
+        plan.nslices = a->num_kv_heads / plan.HC;
+    }
+    const int max_cw = kernel_G >= 4 ? 8 : 16;   // the kernel's launch bound
+    if (!plan_slots(plan.HC, lpr, kernel_G == 1, max_cw, &plan.CW, &plan.HPS, &plan.TG)) {
+        // fall back to one KV head per CTA unless the head sum must stay in one CTA
+        TIDAL_REQUIRE(!sum_heads, TIDAL_ERR_ARG, "head-summed logits need num_kv_heads in {1,2,4,...,%d} for this head_dim/dtype, got %d",
+                      16 * (32 / lpr) * (kernel_G == 1 ? 2 : 1), a->num_kv_heads);
+        plan.HC = 1;
+        plan.nslices = a->num_kv_heads;
+        plan_slots(1, lpr, false, max_cw, &plan.CW, &plan.HPS, &plan.TG);
+    }
+    const int ntok = sel ? a->sel_count + (a->extra_page >= 0 ? 1 : 0) : a->seq_len;
+    const int row_bytes = plan.HC * D * es;
+    // a chunk should move at least ~64 KB so that its pipeline fills
+    int min_tok = (64 * 1024) / (2 * row_bytes);
+    if (min_tok < 1) min_tok = 1;
+    plan.nchunks = a->num_chunks > 0 ? a->num_chunks
+                                     : tidal_plan_chunks(a->batch, plan.nslices, ntok, min_tok, sm_count_cached());
+    TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
+                  plan.nchunks, kMaxChunks);
+    const int ctok = (ntok + plan.nchunks - 1) / plan.nchunks;
+    // tokens per stage: about 64 KB per stage, a multiple of TG, no more than the chunk needs
+    int T = (64 * 1024) / (2 * row_bytes);
+    if (T < 1) T = 1;
+    if (T > 64) T = 64;
+    T = (T + plan.TG - 1) / plan.TG * plan.TG;
+    const int need = (ctok + plan.TG - 1) / plan.TG * plan.TG;
+    if (T > need && need > 0) T = need;
+    plan.T = T;
+    const int slots = plan.CW * (32 / lpr);
+    int S = 4;
+    while (S > 1 && attn_smem_bytes(S, T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads) > kSmemBudget) --S;
+    plan.S = S;
+    plan.smem = attn_smem_bytes(S, T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads);
+    TIDAL_REQUIRE(plan.smem <= 227 * 1024, TIDAL_ERR_ARG, "shared memory %zu exceeds 227 KB (row %d bytes)", plan.smem, row_bytes);
+
+    AttnParams p;
+    p.q = a->d_q; p.o = a->d_o; p.kv = (const char*)a->d_kv;
+    p.page_table = a->d_page_table; p.pt_stride = a->page_table_stride;
+    p.seq_lens = a->d_seq_lens; p.seq_len = a->seq_len;
+    p.sel_idx = a->d_sel_idx; p.sel_counts = a->d_sel_counts;
+    p.sel_rows = sel ? a->sel_rows : 1; p.sel_count = a->sel_count; p.sel_physical = a->sel_physical;
+    p.extra_page = sel ? a->extra_page : -1; p.sel_stride = a->sel_stride;
+    p.scores = a->d_scores; p.score_rows = a->score_rows; p.score_stride = a->score_stride;
+    p.hist = a->d_hist; p.force_last = a->force_last;
+    p.part_o = (float*)((char*)d_ws + L->part_o_off);
+    p.part_ml = (float*)((char*)d_ws + L->part_ml_off);
+    p.shard_m = a->d_part_m; p.shard_l = a->d_part_l; p.shard_o = a->d_part_o;
+    p.status = (uint32_t*)((char*)d_ws + L->status_off);
+    p.B = a->batch; p.Hq = a->num_qo_heads; p.Hkv = a->num_kv_heads; p.page_size = a->page_size;
+    p.num_pages = a->num_pages;
+    p.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)D);
+    p.nchunks = plan.nchunks; p.HC = plan.HC; p.greal = G; p.per_head = per_head ? 1 : 0;
+    p.T = plan.T; p.S = plan.S; p.TG = plan.TG; p.CW = plan.CW;
+    const size_t part_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * D;
+    TIDAL_REQUIRE(plan.nchunks == 1 || L->part_o_off + part_need <= L->part_ml_off, TIDAL_ERR_WORKSPACE,
+                  "workspace was sized for a smaller batch/heads/head_dim than this call");
+
+    cudaStream_t st = (cudaStream_t)stream;
+    int rc;
+    switch (a->dtype) {
+        case TIDAL_DTYPE_F16: rc = dispatch_d<__half>(p, plan, D, kernel_G, st); break;
+        case TIDAL_DTYPE_BF16: rc = dispatch_d<__nv_bfloat16>(p, plan, D, kernel_G, st); break;
+        default: rc = dispatch_d<float>(p, plan, D, kernel_G, st); break;
+    }
+    if (rc != TIDAL_OK) return rc;
+    if (plan.nchunks > 1) {
+        switch (a->dtype) {
+            case TIDAL_DTYPE_F16: rc = launch_merge<__half>(p, D, st); break;
+            case TIDAL_DTYPE_BF16: rc = launch_merge<__nv_bfloat16>(p, D, st); break;
+            default: rc = launch_merge<float>(p, D, st); break;
+        }
+    }
+    return rc;
+}
+
+extern "C" int tidal_merge_partials(const float* d_m, const float* d_l, const float* d_o, int shards, int batch,
+                                    int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream) {
+    TIDAL_REQUIRE(d_m && d_l && d_o && d_out, TIDAL_ERR_ARG, "null pointer");
+    TIDAL_REQUIRE(shards >= 1 && batch >= 1 && num_qo_heads >= 1, TIDAL_ERR_ARG, "bad shards/batch/heads");
+    TIDAL_REQUIRE(head_dim >= 1 && head_dim <= 1024, TIDAL_ERR_ARG, "bad head_dim %d", head_dim);
+    const int rows = batch * num_qo_heads;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (dtype) {
+        case TIDAL_DTYPE_F16: merge_shards_kernel<__half><<<rows, head_dim, 0, st>>>(d_m, d_l, d_o, shards, rows, head_dim, (__half*)d_out); break;
+        case TIDAL_DTYPE_BF16: merge_shards_kernel<__nv_bfloat16><<<rows, head_dim, 0, st>>>(d_m, d_l, d_o, shards, rows, head_dim, (__nv_bfloat16*)d_out); break;
+        case TIDAL_DTYPE_F32: merge_shards_kernel<float><<<rows, head_dim, 0, st>>>(d_m, d_l, d_o, shards, rows, head_dim, (float*)d_out); break;
+        default: set_error("unknown dtype %d", dtype); return TIDAL_ERR_ARG;
+    }
+    TIDAL_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return TIDAL_OK;
+}

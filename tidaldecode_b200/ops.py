@@ -1,0 +1,254 @@
+"""Tensor-level wrappers of the C ABI: torch supplies device memory and the
+current stream, every computation happens in libtidal_b200.so.
+
+These are the calls the reference-shaped layers (`tidaldecode_b200.utils`,
+`tidaldecode_b200.models`) are written on; they add batch > 1, GQA, bf16/fp32,
+head-summed selection scores and sequence-sharded KV to what the reference's
+operators offer (tidal/utils/__init__.py:26-287).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import AttnArgs, RopeAppendArgs, TopkArgs, check, lib
+
+_DTYPES = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"unsupported dtype {t.dtype} (float16, bfloat16, float32)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("tidaldecode_b200 runs on CUDA tensors only (there is no CPU path)")
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError("tensors must be contiguous")
+
+
+class Workspace:
+    """Caller-owned scratch for the split-KV partials and the top-k, allocated once
+    (the reference allocates per call: decode_handler.cuh:104-117, controller.py:149-168)."""
+
+    def __init__(self, max_batch: int, num_qo_heads: int, head_dim: int, max_rows: int, max_n: int, device="cuda"):
+        self.geometry = (int(max_batch), int(num_qo_heads), int(head_dim), int(max_rows), int(max_n))
+        self.nbytes = lib.tidal_ws_bytes(*self.geometry)
+        if self.nbytes == 0:
+            raise RuntimeError(f"bad workspace geometry {self.geometry}: {_lib.last_error()}")
+        self.buf = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+        if self.buf.data_ptr() % 256:
+            raise RuntimeError("allocator returned a buffer that is not 256-byte aligned")
+        self.max_rows = int(max_rows)
+        # per-row first-digit histograms the attention kernel may fill for the top-k
+        self.hist = torch.zeros((max_rows, _lib.TOPK_BINS), dtype=torch.int32, device=device)
+        self.reset()
+
+    def reset(self) -> None:
+        with torch.cuda.device(self.buf.device):
+            check(lib.tidal_ws_init(self.buf.data_ptr(), self.nbytes, *self.geometry, _stream()), "tidal_ws_init")
+        self.hist.zero_()
+
+    def status(self) -> int:
+        """Blocking read of the device-side fault bits (0 = clean)."""
+        with torch.cuda.device(self.buf.device):
+            rc = lib.tidal_ws_status(self.buf.data_ptr(), self.nbytes, _stream())
+        check(rc, "tidal_ws_status")
+        return rc
+
+    def __del__(self):
+        try:
+            lib.tidal_ws_release(self.buf.data_ptr())
+        except Exception:
+            pass
+
+
+def decode_attention(
+    q: torch.Tensor,                 # [B, Hq, D]
+    kv: torch.Tensor,                # [pages, 2, page_size, Hkv, D]
+    seq_len: int,
+    ws: Workspace,
+    *,
+    out: Optional[torch.Tensor] = None,
+    page_table: Optional[torch.Tensor] = None,   # int32 [B, max_pages]
+    pages_per_seq: Optional[int] = None,          # identity mapping: sequence b starts at page b*pages_per_seq
+    seq_lens: Optional[torch.Tensor] = None,      # int32 [B]
+    sel_idx: Optional[torch.Tensor] = None,       # int32 [B, k] or [B, Hq, k]
+    sel_counts: Optional[torch.Tensor] = None,    # int32 [B] or [B, Hq]
+    sel_physical: bool = False,
+    extra_page: int = -1,
+    scores: Optional[torch.Tensor] = None,        # fp32 [B, N] (head-summed) or [B, Hq, N]
+    hist: Optional[torch.Tensor] = None,          # int32 [rows, 4096] zeroed, rows = B or B*Hq
+    force_last: bool = False,
+    partials: Optional[tuple] = None,             # (m [B,Hq], l [B,Hq], o [B,Hq,D]) fp32 outputs
+    sm_scale: float = 0.0,
+    num_chunks: int = 0,
+    heads_per_cta: int = 0,
+    want_out: bool = True,
+) -> Optional[torch.Tensor]:
+    """One decode step of attention; see tidal_decode_attention in include/tidal_b200.h."""
+    _need_cuda(q, kv, out, page_table, seq_lens, sel_idx, sel_counts, scores, hist)
+    if q.dim() != 3 or kv.dim() != 5 or kv.shape[1] != 2:
+        raise RuntimeError("q must be [B,Hq,D] and kv [pages,2,page_size,Hkv,D]")
+    if kv.dtype != q.dtype:
+        raise RuntimeError("q and kv must share a dtype")
+    B, Hq, D = q.shape
+    pages, _, page_size, Hkv, Dk = kv.shape
+    if Dk != D:
+        raise RuntimeError("head_dim of q and kv differ")
+    if out is None and want_out:
+        out = torch.empty_like(q)
+    a = AttnArgs()
+    a.d_q, a.d_o, a.d_kv = q.data_ptr(), _ptr(out), kv.data_ptr()
+    if page_table is not None:
+        if page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.shape[0] != B:
+            raise RuntimeError("page_table must be int32 [B, max_pages]")
+        a.d_page_table, a.page_table_stride = page_table.data_ptr(), page_table.shape[1]
+    else:
+        a.d_page_table = None
+        a.page_table_stride = pages_per_seq if pages_per_seq is not None else (pages // B)
+    a.d_seq_lens, a.seq_len = _ptr(seq_lens), int(seq_len)
+    if sel_idx is not None:
+        if sel_idx.dtype != torch.int32:
+            raise RuntimeError("sel_idx must be int32")
+        if sel_idx.dim() == 2:
+            a.sel_rows = 1
+        elif sel_idx.dim() == 3 and sel_idx.shape[1] == Hq:
+            a.sel_rows = Hq
+        else:
+            raise RuntimeError("sel_idx must be [B,k] or [B,Hq,k]")
+        a.d_sel_idx, a.sel_count, a.sel_stride = sel_idx.data_ptr(), sel_idx.shape[-1], sel_idx.shape[-1]
+        a.sel_physical = 1 if sel_physical else 0
+        a.d_sel_counts = _ptr(sel_counts)
+    a.extra_page = int(extra_page)
+    if scores is not None:
+        if scores.dtype != torch.float32:
+            raise RuntimeError("scores must be float32")
+        a.d_scores = scores.data_ptr()
+        a.score_rows = 1 if scores.dim() == 2 else Hq
+        a.score_stride = scores.shape[-1]
+        if hist is not None:
+            a.d_hist = hist.data_ptr()
+        a.force_last = 1 if force_last else 0
+    if partials is not None:
+        m, l, o = partials
+        _need_cuda(m, l, o)
+        a.d_part_m, a.d_part_l, a.d_part_o = m.data_ptr(), l.data_ptr(), o.data_ptr()
+    a.batch, a.num_qo_heads, a.num_kv_heads, a.head_dim = B, Hq, Hkv, D
+    a.page_size, a.dtype, a.num_pages = page_size, _dtype_code(q), pages
+    a.sm_scale, a.num_chunks, a.heads_per_cta = float(sm_scale), int(num_chunks), int(heads_per_cta)
+    with torch.cuda.device(q.device):
+        check(lib.tidal_decode_attention(C.byref(a), ws.buf.data_ptr(), ws.nbytes, _stream()), "tidal_decode_attention")
+    return out
+
+
+def topk(
+    scores: torch.Tensor,            # fp32 [rows, n] (any leading dims are flattened)
+    k: int,
+    ws: Workspace,
+    *,
+    n: Optional[int] = None,
+    in_idx: Optional[torch.Tensor] = None,
+    out_idx: Optional[torch.Tensor] = None,
+    out_val: Optional[torch.Tensor] = None,
+    idx_offset: int = 0,
+    force_last: bool = False,
+    own_range: Optional[tuple] = None,
+    out_count: Optional[torch.Tensor] = None,
+    hist: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Row-wise top-k index sets; see tidal_topk in include/tidal_b200.h."""
+    _need_cuda(scores, in_idx, out_idx, out_val, out_count, hist)
+    if scores.dtype != torch.float32:
+        raise RuntimeError("scores must be float32")
+    stride = scores.shape[-1]
+    rows = scores.numel() // stride
+    n = stride if n is None else int(n)
+    kk = min(int(k), n)
+    if out_idx is None:
+        out_idx = torch.empty(scores.shape[:-1] + (kk,), dtype=torch.int32, device=scores.device)
+    if out_idx.dtype != torch.int32:
+        raise RuntimeError("out_idx must be int32")
+    a = TopkArgs()
+    a.d_scores, a.d_in_idx, a.rows, a.n, a.row_stride, a.k = scores.data_ptr(), _ptr(in_idx), rows, n, stride, int(k)
+    a.d_out_idx, a.d_out_val, a.out_stride = out_idx.data_ptr(), _ptr(out_val), out_idx.shape[-1]
+    a.idx_offset, a.force_last = int(idx_offset), 1 if force_last else 0
+    if own_range is not None:
+        a.own_lo, a.own_hi = int(own_range[0]), int(own_range[1])
+    a.d_out_count, a.d_hist = _ptr(out_count), _ptr(hist)
+    with torch.cuda.device(scores.device):
+        check(lib.tidal_topk(C.byref(a), ws.buf.data_ptr(), ws.nbytes, _stream()), "tidal_topk")
+    return out_idx
+
+
+def rope_append(
+    q: Optional[torch.Tensor],       # [n_tokens, Hq, D], rotated in place
+    k: torch.Tensor,                 # [n_tokens, Hkv, D]
+    v: Optional[torch.Tensor],       # [n_tokens, Hkv, D]
+    kv: Optional[torch.Tensor],      # pool [pages, 2, page_size, Hkv, D] or None (rotate only)
+    *,
+    batch: int = 1,
+    pos0: int = 0,
+    pos0_dev: Optional[torch.Tensor] = None,
+    page_table: Optional[torch.Tensor] = None,
+    pages_per_seq: Optional[int] = None,
+    rope_theta: float = 1e4,
+    rope_scale: float = 1.0,
+    rope_mode: int = 1,
+    inv_freq: Optional[torch.Tensor] = None,
+    rotate_k_in_place: bool = True,
+    status: Optional[torch.Tensor] = None,
+) -> None:
+    """RoPE on q and k fused with the KV append; see tidal_rope_append in include/tidal_b200.h."""
+    _need_cuda(q, k, v, kv, pos0_dev, page_table, inv_freq, status)
+    if k.dim() != 3:
+        raise RuntimeError("k must be [n_tokens, Hkv, D]")
+    n_tokens, Hkv, D = k.shape
+    if n_tokens % batch:
+        raise RuntimeError("n_tokens must be a multiple of batch")
+    a = RopeAppendArgs()
+    a.d_q, a.d_k, a.d_v, a.d_kv = _ptr(q), k.data_ptr(), _ptr(v), _ptr(kv)
+    if page_table is not None:
+        a.d_page_table, a.page_table_stride = page_table.data_ptr(), page_table.shape[1]
+    elif kv is not None:
+        a.page_table_stride = pages_per_seq if pages_per_seq is not None else kv.shape[0] // batch
+    a.d_pos0, a.pos0, a.d_inv_freq = _ptr(pos0_dev), int(pos0), _ptr(inv_freq)
+    a.rope_theta, a.rope_scale, a.rope_mode = float(rope_theta), float(rope_scale), int(rope_mode)
+    a.rotate_k_in_place = 1 if rotate_k_in_place else 0
+    a.batch, a.tokens_per_seq = int(batch), n_tokens // batch
+    a.num_qo_heads = q.shape[1] if q is not None else 0
+    a.num_kv_heads, a.head_dim = Hkv, D
+    a.page_size = kv.shape[2] if kv is not None else 1
+    a.num_pages = kv.shape[0] if kv is not None else 1
+    a.dtype = _dtype_code(k)
+    a.d_status = _ptr(status)
+    with torch.cuda.device(k.device):
+        check(lib.tidal_rope_append(C.byref(a), _stream()), "tidal_rope_append")
+
+
+def merge_partials(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, dtype: torch.dtype,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LSE-merge of [shards, B, Hq(, D)] partials; see tidal_merge_partials."""
+    _need_cuda(m, l, o, out)
+    shards, B, Hq, D = o.shape
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=dtype, device=o.device)
+    with torch.cuda.device(o.device):
+        check(lib.tidal_merge_partials(m.data_ptr(), l.data_ptr(), o.data_ptr(), shards, B, Hq, D, out.data_ptr(),
+                                       _DTYPES[dtype], _stream()), "tidal_merge_partials")
+    return out
