@@ -145,7 +145,7 @@ def run_ours(args, rank, world, device):
     plan = ShardPlan.contiguous(N, world)
     lo, hi = plan.range_of(rank)
     n_loc = hi - lo
-    pairs = w["layer_pairs"]
+    pairs = args.layer_pairs if args.layer_pairs > 0 else w["layer_pairs"]
     gq = torch.Generator().manual_seed(1)
     q_host = torch.randn(pairs * 2, B, Hq, D, generator=gq).to(dtype).pin_memory()
     q_dev = q_host.to(device)
@@ -310,6 +310,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layer-pairs", type=int, default=0, help="distinct (selection, sparse) KV pool pairs to rotate over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))

@@ -107,7 +107,8 @@ typedef struct tidal_attn_args {
     int32_t extra_page;         /* >= 0: also attend this pool page — the newest token, as
                                    the reference appends it (decode_attn.cuh:726-730); -1 none */
     /* logits out (selection layer) */
-    float* d_scores;            /* NULL, or [batch][score_rows][score_stride] fp32 */
+    float* d_scores;            /* NULL, or [batch][score_rows][score_stride] fp32; column = token position,
+                                   or, with a selection list, the entry's place in the list (newest token last) */
     int32_t score_rows;         /* 1 = summed over all Hq heads, Hq = per q head */
     int64_t score_stride;
     uint32_t* d_hist;           /* NULL, or [batch*score_rows][TIDAL_TOPK_BINS] zeroed counters
@@ -157,6 +158,7 @@ int tidal_plan_chunks(int batch, int head_slices, int tokens, int min_tokens_per
 typedef struct tidal_topk_args {
     const float* d_scores;
     const int32_t* d_in_idx;
+    int64_t in_idx_stride;      /* elements between rows of d_in_idx; 0 = one row shared by all */
     int32_t rows;
     int64_t n, row_stride;
     int32_t k;

@@ -354,8 +354,10 @@ def test_rope_golden(T, name, dtype, D):
         # large angles lose fp32 precision in the sincos argument itself; one storage ulp of slack
         assert torch.allclose(qd.cpu().float()[0], qe[0, :, j].float(), **tol), (name, pos)
         assert torch.allclose(kd.cpu().float()[0], ke[0, :, j].float(), **tol), (name, pos)
-        exact = (qd.cpu()[0] == qe[0, :, j]).float().mean().item()
-        assert exact > 0.97, f"{name} pos {pos}: only {exact:.3f} of elements bit-equal"
+        if dtype != torch.float32:
+            # after rounding to 16 bits the last-ulp differences of cosf/sinf between host and device vanish
+            exact = (qd.cpu()[0] == qe[0, :, j]).float().mean().item()
+            assert exact > 0.97, f"{name} pos {pos}: only {exact:.3f} of elements bit-equal"
 
 
 @pytest.mark.parametrize("dt,B,Hq,Hkv,D,page,tps", [("f16", 1, 32, 32, 128, 1, 1), ("bf16", 4, 32, 8, 128, 1, 1),

@@ -40,7 +40,7 @@ class AttnArgs(C.Structure):
 
 class TopkArgs(C.Structure):
     _fields_ = [
-        ("d_scores", C.c_void_p), ("d_in_idx", C.c_void_p), ("rows", C.c_int32),
+        ("d_scores", C.c_void_p), ("d_in_idx", C.c_void_p), ("in_idx_stride", C.c_int64), ("rows", C.c_int32),
         ("n", C.c_int64), ("row_stride", C.c_int64), ("k", C.c_int32),
         ("d_out_idx", C.c_void_p), ("d_out_val", C.c_void_p), ("out_stride", C.c_int64),
         ("idx_offset", C.c_int32), ("force_last", C.c_int32), ("own_lo", C.c_int32), ("own_hi", C.c_int32),

@@ -15,6 +15,8 @@
 // covers HC KV heads (all of them when logits are summed over heads, so the sum
 // is formed in shared memory in a fixed order); its slots either own HPS heads
 // each (HC = slots*HPS) or share a head among TG token groups (slots = HC*TG).
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace tidal {
@@ -64,6 +66,10 @@ __host__ __device__ inline size_t attn_smem_bytes(int S, int T, int row_bytes, i
     return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
 }
 
+// Tokens one slot processes per stage (unrolled): fewer under wide GQA groups,
+// whose q and accumulator registers leave less room.
+__host__ __device__ constexpr int attn_tps(int G) { return G >= 4 ? 2 : 4; }
+
 // T: storage type; D: head dim; G: q heads per KV head handled by one slot;
 // HPS: KV heads per slot.
 template <typename T, int D, int G, int HPS>
@@ -72,6 +78,7 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     constexpr int VEC = V::N;
     constexpr int LPR = D / VEC;          // lanes per row
     constexpr int SPW = 32 / LPR;         // slots per warp
+    constexpr int TPS = attn_tps(G);      // tokens a slot takes from one stage
     static_assert(LPR <= 32 && (32 % LPR) == 0, "row must fit a warp");
 
     extern __shared__ __align__(128) unsigned char smem[];
@@ -107,6 +114,8 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     }
     const int seq_len_b = p.seq_lens ? min(p.seq_lens[b], p.seq_len) : p.seq_len;
     const int ntok_all = list_len + (p.extra_page >= 0 ? 1 : 0);
+    // index of the newest token in the score row: its position, or its place in the list
+    const int last_index = (p.sel_idx ? ntok_all : seq_len_b) - 1;
     const int ctok = (ntok_all + p.nchunks - 1) / p.nchunks;
     const int tok0 = chunk * ctok;
     const int ntok = max(0, min(ntok_all, tok0 + ctok) - tok0);
@@ -230,62 +239,113 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
         const unsigned char* vst = kst + (size_t)TT * row_bytes;
         float* sc = sc_smem + (size_t)s * TT * HC;
         if (slot_active) {
-            for (int t = tg; t < valid; t += TG) {
-                const int pos = tok0 + it * TT + t;       // position (full / selection layers)
+            // The slot's TPS tokens of this stage are processed together: independent dot
+            // products and shuffles overlap, and the running softmax is rescaled once.
 #pragma unroll
-                for (int hh = 0; hh < HPS; ++hh) {
-                    const size_t off = (size_t)t * row_bytes + (size_t)(head_local + hh) * D * sizeof(T) + sl * 16;
-                    float kf[VEC], vf[VEC];
-                    V::to_float(*reinterpret_cast<const uint4*>(kst + off), kf);
-                    V::to_float(*reinterpret_cast<const uint4*>(vst + off), vf);
-                    float ssum = 0.f;
+            for (int hh = 0; hh < HPS; ++hh) {
+                const size_t hoff = (size_t)(head_local + hh) * D * sizeof(T) + sl * 16;
+                float d[TPS][G];
+                {
+                    float kf[TPS][VEC];
 #pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        float d = 0.f;
+                    for (int j = 0; j < TPS; ++j)
+                        V::to_float(*reinterpret_cast<const uint4*>(kst + (size_t)(tg + j * TG) * row_bytes + hoff), kf[j]);
 #pragma unroll
-                        for (int i = 0; i < VEC; ++i) d = fmaf(qf[hh][g][i], kf[i], d);
+                    for (int j = 0; j < TPS; ++j)
 #pragma unroll
-                        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(slot_mask, d, o);
-                        const float sraw = d * p.sm_scale;
-                        if (want_scores) {
-                            if (sum_heads) {
-                                ssum += sraw;
-                            } else if (sl == 0) {
+                        for (int g = 0; g < G; ++g) {
+                            float acc = 0.f;
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) acc = fmaf(qf[hh][g][i], kf[j][i], acc);
+                            d[j][g] = acc;
+                        }
+                }
+#pragma unroll
+                for (int o = LPR / 2; o > 0; o >>= 1)
+#pragma unroll
+                    for (int j = 0; j < TPS; ++j)
+#pragma unroll
+                        for (int g = 0; g < G; ++g) d[j][g] += __shfl_xor_sync(slot_mask, d[j][g], o);
+                float vf[TPS][VEC];
+#pragma unroll
+                for (int j = 0; j < TPS; ++j)
+                    V::to_float(*reinterpret_cast<const uint4*>(vst + (size_t)(tg + j * TG) * row_bytes + hoff), vf[j]);
+                if (want_scores) {
+#pragma unroll
+                    for (int j = 0; j < TPS; ++j) {
+                        const int t = tg + j * TG;
+                        if (t >= valid) continue;
+                        const int pos = tok0 + it * TT + t;   // position, or index into the list (score column)
+                        if (sum_heads) {
+                            float ssum = 0.f;
+#pragma unroll
+                            for (int g = 0; g < G; ++g) ssum += d[j][g] * p.sm_scale;
+                            if (sl == 0) sc[t * HC + head_local + hh] = ssum;
+                        } else if (sl == 0) {
+#pragma unroll
+                            for (int g = 0; g < G; ++g) {
+                                const float sraw = d[j][g] * p.sm_scale;
                                 const int hq = qh0 + (head_local + hh) * G + g;
                                 const size_t row = (size_t)b * p.score_rows + hq;
                                 p.scores[row * p.score_stride + pos] = sraw;
                                 if (p.hist) {
                                     uint32_t bin = ordered_key(sraw) >> kDigit0Shift;
-                                    if (p.force_last && pos == seq_len_b - 1) bin = TIDAL_TOPK_BINS - 1;
+                                    if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
                                     atomicAdd(&p.hist[row * TIDAL_TOPK_BINS + bin], 1u);
                                 }
                             }
                         }
-                        const float s2 = d * scale_log2;
-                        const float mnew = fmaxf(mrun[hh][g], s2);
-                        const float alpha = fast_exp2(mrun[hh][g] - mnew);
-                        const float pexp = fast_exp2(s2 - mnew);
-                        mrun[hh][g] = mnew;
-                        lrun[hh][g] = fmaf(lrun[hh][g], alpha, pexp);
-#pragma unroll
-                        for (int i = 0; i < VEC; ++i) of[hh][g][i] = fmaf(of[hh][g][i], alpha, pexp * vf[i]);
                     }
-                    if (sum_heads && sl == 0) sc[t * HC + head_local + hh] = ssum;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float s2[TPS];
+                    float mnew = mrun[hh][g];
+#pragma unroll
+                    for (int j = 0; j < TPS; ++j) {
+                        s2[j] = (tg + j * TG < valid) ? d[j][g] * scale_log2 : -INFINITY;
+                        mnew = fmaxf(mnew, s2[j]);
+                    }
+                    const float msafe = (mnew == -INFINITY) ? 0.f : mnew;   // nothing seen yet: keep zeros, no NaN
+                    const float alpha = fast_exp2(mrun[hh][g] - msafe);
+                    float pe[TPS], psum = 0.f;
+#pragma unroll
+                    for (int j = 0; j < TPS; ++j) {
+                        pe[j] = fast_exp2(s2[j] - msafe);
+                        psum += pe[j];
+                    }
+                    mrun[hh][g] = mnew;
+                    lrun[hh][g] = fmaf(lrun[hh][g], alpha, psum);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) {
+                        float acc = of[hh][g][i] * alpha;
+#pragma unroll
+                        for (int j = 0; j < TPS; ++j) acc = fmaf(pe[j], vf[j][i], acc);
+                        of[hh][g][i] = acc;
+                    }
                 }
             }
         }
         if (sum_heads) {
-            // head sum in a fixed order, one thread per token of the stage
+            // head sum in a fixed order: 8 lanes per token, each adds every 8th head, then a butterfly
             named_bar_sync(1, consumer_threads);
-            for (int t = ctid; t < valid; t += consumer_threads) {
+            for (int base = 0; base < TT; base += consumer_threads / 8) {   // uniform per warp
+                const int t = base + (ctid >> 3), j = ctid & 7;
+                const bool in = t < TT;
                 float a = 0.f;
-                for (int h = 0; h < HC; ++h) a += sc[t * HC + h];
-                const int pos = tok0 + it * TT + t;
-                p.scores[(size_t)b * p.score_stride + pos] = a;
-                if (p.hist) {
-                    uint32_t bin = ordered_key(a) >> kDigit0Shift;
-                    if (p.force_last && pos == seq_len_b - 1) bin = TIDAL_TOPK_BINS - 1;
-                    atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + bin], 1u);
+                if (in)
+                    for (int h = j; h < HC; h += 8) a += sc[t * HC + h];
+                a += __shfl_xor_sync(0xffffffffu, a, 4);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                if (j == 0 && in && t < valid) {
+                    const int pos = tok0 + it * TT + t;
+                    p.scores[(size_t)b * p.score_stride + pos] = a;
+                    if (p.hist) {
+                        uint32_t bin = ordered_key(a) >> kDigit0Shift;
+                        if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
+                        atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + bin], 1u);
+                    }
                 }
             }
         }
@@ -355,29 +415,60 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     }
 }
 
-// Merge the split-KV partials of one (sequence, q head): grid (Hq, B), D threads.
+// Merge the split-KV partials of one (sequence, q head): grid (Hq, B), block
+// (D, kMergeGroups).  The chunk weights are formed once in shared memory; the
+// groups then stride over the chunks so that many loads are in flight, and their
+// sums are combined in a fixed order.
+constexpr int kMergeGroups = 8;
 template <typename T>
 __global__ void merge_chunks_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nchunks,
                                     int Hq, int D, T* __restrict__ o, float* __restrict__ shard_m,
                                     float* __restrict__ shard_l, float* __restrict__ shard_o) {
-    const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    extern __shared__ float msm[];           // [nchunks] weights, then [kMergeGroups][D] partial sums
+    float* wgt = msm;
+    float* red = msm + nchunks;
+    __shared__ float s_M, s_L;
+    const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x, grp = threadIdx.y;
+    const int tid = grp * D + d, nthreads = D * kMergeGroups;
     const size_t ph = (size_t)b * Hq + hq;
     const float* ml = part_ml + ph * nchunks * 2;
-    float M = -INFINITY;
-    for (int c = 0; c < nchunks; ++c) M = fmaxf(M, ml[2 * c]);
-    float acc = 0.f, L = 0.f;
-    for (int c = 0; c < nchunks; ++c) {
-        const float m = ml[2 * c];
-        const float w = (m == -INFINITY) ? 0.f : fast_exp2(m - M);
-        acc = fmaf(w, part_o[(ph * nchunks + c) * D + d], acc);
-        L = fmaf(w, ml[2 * c + 1], L);
+    if (tid < 32) {
+        float M = -INFINITY;
+        for (int c = tid; c < nchunks; c += 32) M = fmaxf(M, ml[2 * c]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+        if (tid == 0) s_M = M;
     }
-    if (o) o[ph * D + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
-    if (shard_o) {
-        shard_o[ph * D + d] = acc;
-        if (d == 0) {
-            shard_m[ph] = M;
-            shard_l[ph] = L;
+    __syncthreads();
+    const float M = s_M;
+    for (int c = tid; c < nchunks; c += nthreads) {
+        const float m = ml[2 * c];
+        wgt[c] = (m == -INFINITY) ? 0.f : fast_exp2(m - M);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float L = 0.f;
+        for (int c = 0; c < nchunks; ++c) L = fmaf(wgt[c], ml[2 * c + 1], L);
+        s_L = L;
+    }
+    float acc = 0.f;
+    const float* po = part_o + ph * nchunks * D + d;
+#pragma unroll 4
+    for (int c = grp; c < nchunks; c += kMergeGroups) acc = fmaf(wgt[c], po[(size_t)c * D], acc);
+    red[grp * D + d] = acc;
+    __syncthreads();
+    if (grp == 0) {
+        float tot = 0.f;
+#pragma unroll
+        for (int g2 = 0; g2 < kMergeGroups; ++g2) tot += red[g2 * D + d];
+        const float L = s_L;
+        if (o) o[ph * D + d] = from_f32<T>(L > 0.f ? tot / L : 0.f);
+        if (shard_o) {
+            shard_o[ph * D + d] = tot;
+            if (d == 0) {
+                shard_m[ph] = M;
+                shard_l[ph] = L;
+            }
         }
     }
 }
@@ -420,7 +511,9 @@ constexpr size_t kSmemBudget = 200 * 1024;   // per CTA, leaves room for a secon
 // Pick the slot geometry for HC heads per CTA; false if HC cannot be mapped.
 static bool plan_slots(int HC, int lpr, bool allow_hps2, int max_cw, int* CW, int* HPS, int* TG) {
     const int spw = 32 / lpr;
-    for (int cw : {8, 16, 4}) {
+    static const int prefer16 = getenv("TIDAL_PLAN_CW16") ? atoi(getenv("TIDAL_PLAN_CW16")) : 0;
+    const int order_a[3] = {8, 16, 4}, order_b[3] = {16, 8, 4};
+    for (int cw : (prefer16 ? order_b : order_a)) {
         if (cw > max_cw) continue;
         const int slots = cw * spw;
         if (slots % HC == 0) {
@@ -498,8 +591,9 @@ static int dispatch_d(const AttnParams& p, const AttnPlan& plan, int D, int G, c
 
 template <typename T>
 static int launch_merge(const AttnParams& p, int D, cudaStream_t st) {
-    merge_chunks_kernel<T><<<dim3(p.Hq, p.B), D, 0, st>>>(p.part_o, p.part_ml, p.nchunks, p.Hq, D, (T*)p.o, p.shard_m,
-                                                          p.shard_l, p.shard_o);
+    const size_t smem = sizeof(float) * ((size_t)p.nchunks + (size_t)kMergeGroups * D);
+    merge_chunks_kernel<T><<<dim3(p.Hq, p.B), dim3(D, kMergeGroups), smem, st>>>(p.part_o, p.part_ml, p.nchunks, p.Hq, D,
+                                                                                  (T*)p.o, p.shard_m, p.shard_l, p.shard_o);
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();
     return TIDAL_OK;
@@ -532,14 +626,16 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
                       "sel_rows must be 1 or num_qo_heads, got %d", a->sel_rows);
         TIDAL_REQUIRE(a->sel_count >= 0 && a->sel_stride >= a->sel_count, TIDAL_ERR_ARG, "bad sel_count/sel_stride");
         TIDAL_REQUIRE(!a->sel_physical || a->page_size == 1, TIDAL_ERR_ARG, "physical page lists need page_size 1");
-        TIDAL_REQUIRE(a->d_scores == nullptr, TIDAL_ERR_ARG, "logits are only written by layers that attend to all tokens");
+        TIDAL_REQUIRE(a->d_scores == nullptr || a->score_rows == a->sel_rows || a->sel_rows == 1, TIDAL_ERR_ARG,
+                      "head-summed logits over per-head lists are undefined");
     } else {
         TIDAL_REQUIRE(a->extra_page < 0, TIDAL_ERR_ARG, "extra_page needs a selection list");
     }
     if (a->d_scores) {
         TIDAL_REQUIRE(a->score_rows == 1 || a->score_rows == a->num_qo_heads, TIDAL_ERR_ARG,
                       "score_rows must be 1 or num_qo_heads, got %d", a->score_rows);
-        TIDAL_REQUIRE(a->score_stride >= a->seq_len, TIDAL_ERR_ARG, "score_stride shorter than seq_len");
+        TIDAL_REQUIRE(a->score_stride >= (sel ? a->sel_count + (a->extra_page >= 0 ? 1 : 0) : a->seq_len), TIDAL_ERR_ARG,
+                      "score_stride shorter than the token list");
     } else {
         TIDAL_REQUIRE(a->d_hist == nullptr, TIDAL_ERR_ARG, "a histogram needs d_scores");
     }
@@ -581,16 +677,11 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
                   plan.nchunks, kMaxChunks);
     const int ctok = (ntok + plan.nchunks - 1) / plan.nchunks;
-    // tokens per stage: about 64 KB per stage, a multiple of TG, no more than the chunk needs
-    int T = (64 * 1024) / (2 * row_bytes);
-    if (T < 1) T = 1;
-    if (T > 64) T = 64;
-    T = (T + plan.TG - 1) / plan.TG * plan.TG;
-    const int need = (ctok + plan.TG - 1) / plan.TG * plan.TG;
-    if (T > need && need > 0) T = need;
+    // tokens per stage: every slot takes attn_tps(G) tokens from a stage
+    const int T = plan.TG * attn_tps(kernel_G);
     plan.T = T;
     const int slots = plan.CW * (32 / lpr);
-    int S = 4;
+    int S = 8;
     while (S > 1 && attn_smem_bytes(S, T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads) > kSmemBudget) --S;
     plan.S = S;
     plan.smem = attn_smem_bytes(S, T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads);

@@ -25,6 +25,7 @@ constexpr int kSortMax = 4096;   // winners are position-sorted up to this k
 struct TopkParams {
     const float* scores;
     const int32_t* in_idx;
+    int64_t in_idx_stride;
     int32_t rows;
     int64_t n, row_stride;
     int32_t k;            // already min(k, n)
@@ -167,7 +168,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
     const bool own = p.own_hi > p.own_lo;
 
     auto emit_value = [&](uint32_t pos) -> int32_t {
-        return p.in_idx ? p.in_idx[(size_t)row * p.row_stride + pos] : (int32_t)pos + p.idx_offset;
+        return p.in_idx ? p.in_idx[(size_t)row * p.in_idx_stride + pos] : (int32_t)pos + p.idx_offset;
     };
 
     if (select_all) {
@@ -361,6 +362,8 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
                   a->rows, (long long)a->n, a->k);
     TIDAL_REQUIRE(a->n <= 0x7FFFFFFFll, TIDAL_ERR_ARG, "row length %lld does not fit int32 positions", (long long)a->n);
     TIDAL_REQUIRE(a->row_stride >= a->n, TIDAL_ERR_ARG, "row_stride shorter than n");
+    TIDAL_REQUIRE(a->d_in_idx == nullptr || a->in_idx_stride == 0 || a->in_idx_stride >= a->n, TIDAL_ERR_ARG,
+                  "in_idx_stride must be 0 (shared row) or at least n");
     const int k = (int64_t)a->k < a->n ? a->k : (int)a->n;
     TIDAL_REQUIRE(k <= kMaxK || (int64_t)a->k >= a->n, TIDAL_ERR_ARG, "k %d exceeds the built maximum %d", k, kMaxK);
     TIDAL_REQUIRE(a->out_stride >= k, TIDAL_ERR_ARG, "out_stride %lld shorter than min(k, n) = %d", (long long)a->out_stride, k);
@@ -371,7 +374,7 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     TIDAL_REQUIRE((size_t)a->rows <= rows_cap, TIDAL_ERR_WORKSPACE, "workspace was sized for %zu rows, call has %d", rows_cap, a->rows);
 
     TopkParams p;
-    p.scores = a->d_scores; p.in_idx = a->d_in_idx; p.rows = a->rows; p.n = a->n; p.row_stride = a->row_stride;
+    p.scores = a->d_scores; p.in_idx = a->d_in_idx; p.in_idx_stride = a->in_idx_stride; p.rows = a->rows; p.n = a->n; p.row_stride = a->row_stride;
     p.k = k; p.out_idx = a->d_out_idx; p.out_val = a->d_out_val; p.out_stride = a->out_stride;
     p.idx_offset = a->idx_offset; p.force_last = a->force_last; p.own_lo = a->own_lo; p.own_hi = a->own_hi;
     p.out_count = a->d_out_count;

@@ -186,6 +186,10 @@ def topk(
         raise RuntimeError("out_idx must be int32")
     a = TopkArgs()
     a.d_scores, a.d_in_idx, a.rows, a.n, a.row_stride, a.k = scores.data_ptr(), _ptr(in_idx), rows, n, stride, int(k)
+    if in_idx is not None:
+        if in_idx.dtype != torch.int32:
+            raise RuntimeError("in_idx must be int32")
+        a.in_idx_stride = 0 if in_idx.dim() == 1 else in_idx.shape[-1]
     a.d_out_idx, a.d_out_val, a.out_stride = out_idx.data_ptr(), _ptr(out_val), out_idx.shape[-1]
     a.idx_offset, a.force_last = int(idx_offset), 1 if force_last else 0
     if own_range is not None:
