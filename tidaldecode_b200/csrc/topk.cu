@@ -1,26 +1,32 @@
-// Row-wise top-k of fp32 scores by radix selection, block-then-global.
+// Row-wise top-k of fp32 scores by radix selection.
 //
 // Keys are 64-bit and distinct: (order-preserving image of the score) << 32 |
 // (0xFFFFFFFF - position), so the result is one well-defined set — equal scores
 // resolve towards the lower position — and every rank that sees the same scores
 // selects the same tokens.
 //
-//   pass 0  histogram of the top 12 key bits over the whole row, many CTAs per
-//           row (skipped when the attention kernel already counted the logits
-//           while it wrote them);
-//   pass 1  every CTA finds the threshold bin from the histogram and scans its
-//           slice: keys in higher bins are certainly selected (appended to
-//           `sel`), keys in the threshold bin become candidates (`cand`);
-//   pass 2  one CTA per row resolves the candidates with 8-bit radix passes over
-//           the remaining 52 bits, orders the k winners by position, applies the
-//           ownership filter, writes the outputs and re-zeroes the counters.
+//   digit 0   histogram of the top 12 key bits of the row.  The attention kernel
+//             can count the logits while it writes them; otherwise it is built here.
+//   split     the threshold bin b* is read off the histogram; keys in higher bins
+//             are certainly selected (`sel`), keys in b* are candidates (`cand`).
+//   resolve   8-bit radix passes over the remaining 52 bits of the candidates,
+//             stopping as soon as a digit's population equals what is still needed.
+//   emit      winners ordered by position, ownership filter, outputs, counters
+//             back to zero.
+//
+// Rows up to kFusedMaxN run all four steps in ONE launch, one CTA per row (the
+// score row is a few hundred KB that sits in L2 behind the attention kernel).
+// Longer rows split the histogram and the scan over many CTAs per row
+// (block-then-global) and finish with one CTA per row.
 #include "common.cuh"
 
 namespace tidal {
 
 constexpr int kBins = TIDAL_TOPK_BINS;
 constexpr int kTopkThreads = 1024;
-constexpr int kSortMax = 4096;   // winners are position-sorted up to this k
+constexpr int kSortMax = 4096;        // winners are position-sorted up to this k
+constexpr int kRankSortMax = 1024;    // ... by counting up to this k, by a bitonic network above
+constexpr int64_t kFusedMaxN = 1 << 18;
 
 struct TopkParams {
     const float* scores;
@@ -34,7 +40,7 @@ struct TopkParams {
     int64_t out_stride;
     int32_t idx_offset, force_last, own_lo, own_hi;
     int32_t* out_count;
-    uint32_t* hist;       // [rows][kBins]
+    uint32_t* hist;       // [rows][kBins] in global memory, or nullptr (fused kernel builds its own)
     uint32_t* row_state;  // [rows][8]: 0 sel count, 1 cand count
     uint64_t* cand;       // [rows][cand_cap]
     uint64_t* sel;        // [rows][kMaxK]
@@ -48,49 +54,48 @@ __device__ __forceinline__ uint64_t make_key(float s, uint32_t pos, int64_t n, i
     return ((uint64_t)k32 << 32) | (uint64_t)(0xFFFFFFFFu - pos);
 }
 __device__ __forceinline__ uint32_t key_pos(uint64_t key) { return 0xFFFFFFFFu - (uint32_t)(key & 0xFFFFFFFFull); }
+__device__ __forceinline__ int key_bin(uint64_t key) { return (int)((uint32_t)(key >> 32) >> kDigit0Shift); }
 
-__global__ void __launch_bounds__(kTopkThreads) topk_hist_kernel(const TopkParams p) {
-    __shared__ uint32_t h[kBins];
-    const int row = blockIdx.y;
-    for (int i = threadIdx.x; i < kBins; i += blockDim.x) h[i] = 0;
+// Inclusive scan over the kTopkThreads threads of the block; `ws` has 32 words.
+// Ends with a barrier, so `ws` may be reused at once.
+__device__ __forceinline__ uint32_t block_scan_incl(uint32_t v, uint32_t* ws) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xffffffffu, v, off);
+        if (lane >= off) v += n;
+    }
+    if (lane == 31) ws[warp] = v;
     __syncthreads();
-    const float* s = p.scores + (size_t)row * p.row_stride;
-    const int64_t per = (p.n + gridDim.x - 1) / gridDim.x;
-    const int64_t lo = (int64_t)blockIdx.x * per, hi = min(p.n, lo + per);
-    for (int64_t j = lo + threadIdx.x; j < hi; j += blockDim.x) {
-        const uint64_t key = make_key(s[j], (uint32_t)j, p.n, p.force_last);
-        atomicAdd(&h[(uint32_t)(key >> 32) >> kDigit0Shift], 1u);
+    if (warp == 0) {
+        uint32_t w = ws[lane];
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t n = __shfl_up_sync(0xffffffffu, w, off);
+            if (lane >= off) w += n;
+        }
+        ws[lane] = w;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < kBins; i += blockDim.x)
-        if (h[i]) atomicAdd(&p.hist[(size_t)row * kBins + i], h[i]);
+    if (warp > 0) v += ws[warp - 1];
+    __syncthreads();
+    return v;
 }
 
-// Threshold bin b*: count(bins > b*) < k <= count(bins >= b*).  Every thread of
-// the block returns the same (bin, above).  `h` is a shared copy of the row's
-// histogram, `scratch` has blockDim.x words.
-__device__ void find_threshold_bin(const uint32_t* h, uint32_t* scratch, uint32_t k, int* bin_out, uint32_t* above_out) {
-    // each thread owns kBins/blockDim.x consecutive bins, highest bins first
-    const int per = kBins / kTopkThreads;     // 4
+// Threshold bin b*: count(bins > b*) < k <= count(bins >= b*).  `h` is a shared
+// copy of the row's histogram; every thread returns the same (bin, above).
+__device__ void find_threshold_bin(const uint32_t* h, uint32_t* ws, uint32_t k, int* bin_out, uint32_t* above_out) {
+    constexpr int per = kBins / kTopkThreads;     // 4 bins per thread, thread 0 owns the top ones
     const int t = threadIdx.x;
+    const int base = kBins - (t + 1) * per;
     uint32_t mine = 0;
-    const int base = kBins - (t + 1) * per;    // thread 0 owns the top bins
 #pragma unroll
     for (int i = 0; i < per; ++i) mine += h[base + i];
-    scratch[t] = mine;
-    __syncthreads();
-    // inclusive scan over threads (Hillis-Steele)
-    for (int off = 1; off < kTopkThreads; off <<= 1) {
-        uint32_t v = (t >= off) ? scratch[t - off] : 0;
-        __syncthreads();
-        scratch[t] += v;
-        __syncthreads();
-    }
+    const uint32_t incl = block_scan_incl(mine, ws), excl = incl - mine;
     __shared__ int s_bin;
     __shared__ uint32_t s_above;
     if (t == 0) { s_bin = 0; s_above = 0; }
     __syncthreads();
-    const uint32_t incl = scratch[t], excl = incl - mine;
     if (excl < k && k <= incl) {
         uint32_t above = excl;
         for (int i = per - 1; i >= 0; --i) {
@@ -105,32 +110,89 @@ __device__ void find_threshold_bin(const uint32_t* h, uint32_t* scratch, uint32_
     __syncthreads();
 }
 
+// One warp finds, in a 256-bin digit histogram, the digit d with
+// count(digits > d) < need <= count(digits >= d).  Results through shared words.
+__device__ __forceinline__ void warp_find_digit(const uint32_t* h, int nbins, uint32_t need, uint32_t* s_digit,
+                                                uint32_t* s_need, uint32_t* s_done) {
+    const int lane = threadIdx.x & 31;
+    const int per = nbins / 32 > 0 ? nbins / 32 : 1;      // 8 bins per lane (256), or 1 with 16 active lanes (16)
+    const bool active = lane * per < nbins;
+    const int base = nbins - (lane + 1) * per;            // lane 0 owns the top bins
+    uint32_t mine = 0;
+    if (active)
+        for (int i = 0; i < per; ++i) mine += h[base + i];
+    uint32_t incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += n;
+    }
+    const uint32_t excl = incl - mine;
+    if (active && excl < need && need <= incl) {
+        uint32_t above = excl;
+        for (int i = per - 1; i >= 0; --i) {
+            const uint32_t c = h[base + i];
+            if (above + c >= need) {
+                *s_digit = (uint32_t)(base + i);
+                *s_need = need - above;
+                *s_done = (c == need - above) ? 1u : 0u;
+                break;
+            }
+            above += c;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kTopkThreads) topk_hist_kernel(const TopkParams p) {
+    __shared__ uint32_t h[kBins];
+    const int row = blockIdx.y;
+    for (int i = threadIdx.x; i < kBins; i += blockDim.x) h[i] = 0;
+    __syncthreads();
+    const float* s = p.scores + (size_t)row * p.row_stride;
+    const int64_t per = (p.n + gridDim.x - 1) / gridDim.x;
+    const int64_t lo = (int64_t)blockIdx.x * per, hi = min(p.n, lo + per);
+#pragma unroll 4
+    for (int64_t j = lo + threadIdx.x; j < hi; j += blockDim.x)
+        atomicAdd(&h[key_bin(make_key(s[j], (uint32_t)j, p.n, p.force_last))], 1u);
+    __syncthreads();
+    for (int i = threadIdx.x; i < kBins; i += blockDim.x)
+        if (h[i]) atomicAdd(&p.hist[(size_t)row * kBins + i], h[i]);
+}
+
+// Scan positions [lo, hi) of a row and append to `sel` / `cand`; counters may
+// live in shared or global memory.
+__device__ __forceinline__ void split_range(const TopkParams& p, int row, int64_t lo, int64_t hi, int bstar,
+                                            uint32_t* sel_cnt, uint32_t* cand_cnt) {
+    const float* s = p.scores + (size_t)row * p.row_stride;
+    uint64_t* sel = p.sel + (size_t)row * kMaxK;
+    uint64_t* cand = p.cand + (size_t)row * p.cand_cap;
+#pragma unroll 4
+    for (int64_t j = lo + threadIdx.x; j < hi; j += blockDim.x) {
+        const uint64_t key = make_key(s[j], (uint32_t)j, p.n, p.force_last);
+        const int bin = key_bin(key);
+        if (bin > bstar) {
+            const uint32_t at = atomicAdd(sel_cnt, 1u);
+            if (at < (uint32_t)kMaxK) sel[at] = key;
+        } else if (bin == bstar) {
+            const uint32_t at = atomicAdd(cand_cnt, 1u);
+            if ((int64_t)at < p.cand_cap) cand[at] = key;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kTopkThreads) topk_partition_kernel(const TopkParams p) {
     __shared__ uint32_t h[kBins];
-    __shared__ uint32_t scratch[kTopkThreads];
+    __shared__ uint32_t ws[32];
     const int row = blockIdx.y;
     for (int i = threadIdx.x; i < kBins; i += blockDim.x) h[i] = p.hist[(size_t)row * kBins + i];
     __syncthreads();
     int bstar;
     uint32_t above;
-    find_threshold_bin(h, scratch, (uint32_t)p.k, &bstar, &above);
-    const float* s = p.scores + (size_t)row * p.row_stride;
+    find_threshold_bin(h, ws, (uint32_t)p.k, &bstar, &above);
     uint32_t* st = p.row_state + (size_t)row * 8;
-    uint64_t* sel = p.sel + (size_t)row * kMaxK;
-    uint64_t* cand = p.cand + (size_t)row * p.cand_cap;
     const int64_t per = (p.n + gridDim.x - 1) / gridDim.x;
-    const int64_t lo = (int64_t)blockIdx.x * per, hi = min(p.n, lo + per);
-    for (int64_t j = lo + threadIdx.x; j < hi; j += blockDim.x) {
-        const uint64_t key = make_key(s[j], (uint32_t)j, p.n, p.force_last);
-        const int bin = (int)((uint32_t)(key >> 32) >> kDigit0Shift);
-        if (bin > bstar) {
-            const uint32_t at = atomicAdd(&st[0], 1u);
-            if (at < (uint32_t)kMaxK) sel[at] = key;
-        } else if (bin == bstar) {
-            const uint32_t at = atomicAdd(&st[1], 1u);
-            if ((int64_t)at < p.cand_cap) cand[at] = key;
-        }
-    }
+    const int64_t lo = (int64_t)blockIdx.x * per;
+    split_range(p, row, lo, min(p.n, lo + per), bstar, &st[0], &st[1]);
 }
 
 // Iterate the candidates of a row: the compacted list, or — if it overflowed —
@@ -144,25 +206,27 @@ __device__ __forceinline__ void for_each_candidate(const TopkParams& p, int row,
         const float* s = p.scores + (size_t)row * p.row_stride;
         for (int64_t j = threadIdx.x; j < p.n; j += blockDim.x) {
             const uint64_t key = make_key(s[j], (uint32_t)j, p.n, p.force_last);
-            if ((int)((uint32_t)(key >> 32) >> kDigit0Shift) == bstar) f(key);
+            if (key_bin(key) == bstar) f(key);
         }
     }
 }
 
+// FUSED: the CTA also builds the histogram (unless one is supplied) and splits the row.
+// select_all: k >= n, every position is emitted in order.
+template <bool FUSED>
 __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkParams p, int select_all) {
-    // `h` (threshold search, then the 256-bin pass histograms) is dead before the
+    // `h` (threshold search, then the per-pass digit histograms) is dead before the
     // winners are collected, so both live in one 32 KB array.
     __shared__ uint64_t winners[kSortMax];
     uint32_t* h = reinterpret_cast<uint32_t*>(winners);
     static_assert(sizeof(uint64_t) * kSortMax >= sizeof(uint32_t) * kBins, "winners must cover the histogram");
-    __shared__ uint32_t scratch[kTopkThreads];
-    __shared__ uint32_t s_cnt, s_digit, s_need, s_done;
+    __shared__ uint32_t ws[32];
+    __shared__ uint32_t s_cnt, s_digit, s_need, s_done, s_nsel, s_ncand;
     const int row = blockIdx.x;
     const int t = threadIdx.x;
     uint32_t* st = p.row_state + (size_t)row * 8;
     const float* srow = p.scores + (size_t)row * p.row_stride;
     const uint32_t k = (uint32_t)p.k;
-    const bool sorted = k <= (uint32_t)kSortMax;
     int32_t* out_idx = p.out_idx + (size_t)row * p.out_stride;
     float* out_val = p.out_val ? p.out_val + (size_t)row * p.out_stride : nullptr;
     const bool own = p.own_hi > p.own_lo;
@@ -170,54 +234,72 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
     auto emit_value = [&](uint32_t pos) -> int32_t {
         return p.in_idx ? p.in_idx[(size_t)row * p.in_idx_stride + pos] : (int32_t)pos + p.idx_offset;
     };
-
-    if (select_all) {
-        // k >= n: every position is selected, already in ascending order
-        if (t == 0) s_cnt = 0;
-        __syncthreads();
-        for (uint32_t base = 0; base < k; base += blockDim.x) {
+    // Order-preserving emission of `count` items; item j is described by get(j, &pos, &score)
+    // returning false for padding.
+    auto emit_ordered = [&](uint32_t count, auto get) {
+        uint32_t before = 0;
+        for (uint32_t base = 0; base < count; base += kTopkThreads) {
             const uint32_t j = base + t;
             int32_t v = 0;
+            float sc = 0.f;
             bool keep = false;
-            if (j < k) {
-                v = emit_value(j);
+            uint32_t pos = 0;
+            if (j < count && get(j, &pos, &sc)) {
+                v = emit_value(pos);
                 keep = !own || (v >= p.own_lo && v < p.own_hi);
             }
-            // order-preserving compaction, one tile of blockDim.x at a time
-            scratch[t] = keep ? 1u : 0u;
-            __syncthreads();
-            for (int off = 1; off < kTopkThreads; off <<= 1) {
-                uint32_t x = (t >= off) ? scratch[t - off] : 0;
-                __syncthreads();
-                scratch[t] += x;
-                __syncthreads();
-            }
-            const uint32_t before = s_cnt;
+            const uint32_t incl = block_scan_incl(keep ? 1u : 0u, ws);
             if (keep) {
-                const uint32_t at = before + scratch[t] - 1;
+                const uint32_t at = before + incl - 1;
                 out_idx[at] = own ? v - p.own_lo : v;
-                if (out_val) out_val[at] = srow[j];
+                if (out_val) out_val[at] = sc;
             }
+            if (t == kTopkThreads - 1) s_cnt = before + incl;
             __syncthreads();
-            if (t == kTopkThreads - 1) s_cnt = before + scratch[t];
+            before = s_cnt;
             __syncthreads();
         }
-        if (t == 0 && p.out_count) p.out_count[row] = (int32_t)s_cnt;
+        if (t == 0 && p.out_count) p.out_count[row] = (int32_t)before;
+    };
+
+    if (select_all) {
+        emit_ordered(k, [&](uint32_t j, uint32_t* pos, float* sc) { *pos = j; *sc = srow[j]; return true; });
         // a histogram the attention kernel filled for this row is not needed: clear it
-        for (int i = t; i < kBins; i += blockDim.x) p.hist[(size_t)row * kBins + i] = 0;
+        if (p.hist)
+            for (int i = t; i < kBins; i += kTopkThreads) p.hist[(size_t)row * kBins + i] = 0;
         return;
     }
 
-    for (int i = t; i < kBins; i += blockDim.x) h[i] = p.hist[(size_t)row * kBins + i];
+    // ---- digit-0 histogram into shared memory
+    if (p.hist) {
+        for (int i = t; i < kBins; i += kTopkThreads) h[i] = p.hist[(size_t)row * kBins + i];
+    } else {
+        for (int i = t; i < kBins; i += kTopkThreads) h[i] = 0;
+        __syncthreads();
+#pragma unroll 4
+        for (int64_t j = t; j < p.n; j += kTopkThreads)
+            atomicAdd(&h[key_bin(make_key(srow[j], (uint32_t)j, p.n, p.force_last))], 1u);
+    }
     __syncthreads();
     int bstar;
     uint32_t above;
-    find_threshold_bin(h, scratch, k, &bstar, &above);
-    const uint32_t nsel = min(st[0], (uint32_t)kMaxK);
-    const uint32_t ncand_total = st[1];
+    find_threshold_bin(h, ws, k, &bstar, &above);
+
+    // ---- split (fused) or pick up the counts the partition kernel left
+    if (FUSED) {
+        if (t == 0) { s_nsel = 0; s_ncand = 0; }
+        __syncthreads();
+        split_range(p, row, 0, p.n, bstar, &s_nsel, &s_ncand);
+        __syncthreads();
+    } else {
+        if (t == 0) { s_nsel = st[0]; s_ncand = st[1]; }
+        __syncthreads();
+    }
+    const uint32_t nsel = min(s_nsel, (uint32_t)kMaxK);
+    const uint32_t ncand_total = s_ncand;
     const bool overflow = (int64_t)ncand_total > p.cand_cap;
     uint32_t need = k - above;                 // how many candidates win (>= 1)
-    if (nsel != above && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
+    if (s_nsel != above && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
 
     // ---- radix passes over key bits 51..0 among the candidates
     uint64_t prefix = (uint64_t)bstar << 52;   // known high bits
@@ -225,25 +307,15 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
     bool done = (need == ncand_total);         // all candidates win
     for (int shift = 44; !done && shift >= -4; shift -= 8) {
         const int sh = shift < 0 ? 0 : shift;
-        const int bits = shift < 0 ? 4 : 8;
-        const uint32_t dmask = (1u << bits) - 1u;
-        for (int i = t; i < 256; i += blockDim.x) h[i] = 0;
+        const int nb = shift < 0 ? 16 : 256;
+        const uint32_t dmask = (uint32_t)nb - 1u;
+        if (t < 256) h[t] = 0;
         __syncthreads();
         for_each_candidate(p, row, bstar, ncand_total, overflow, [&](uint64_t key) {
             if ((key & known_mask) == prefix) atomicAdd(&h[(uint32_t)(key >> sh) & dmask], 1u);
         });
         __syncthreads();
-        if (t == 0) {
-            uint32_t acc = 0;
-            int d = (int)dmask;
-            for (; d > 0; --d) {
-                if (acc + h[d] >= need) break;
-                acc += h[d];
-            }
-            s_digit = (uint32_t)d;
-            s_need = need - acc;
-            s_done = (h[d] == need - acc) ? 1u : 0u;
-        }
+        if (t < 32) warp_find_digit(h, nb, need, &s_digit, &s_need, &s_done);
         __syncthreads();
         prefix |= (uint64_t)s_digit << sh;
         known_mask |= (uint64_t)dmask << sh;
@@ -251,80 +323,60 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
         done = s_done != 0;
         __syncthreads();
     }
-    // winners among candidates: keys >= prefix (unknown low bits zero)
-    const uint64_t thr = prefix;
+    const uint64_t thr = prefix;               // winners among candidates: key >= thr
 
     // ---- collect the k winners
     if (t == 0) s_cnt = 0;
     __syncthreads();
     const uint64_t* sel = p.sel + (size_t)row * kMaxK;
-    if (sorted) {
-        for (uint32_t j = t; j < nsel; j += blockDim.x) winners[atomicAdd(&s_cnt, 1u) % kSortMax] = sel[j];
+    if (k <= (uint32_t)kSortMax) {
+        // as (position << 32 | score bits), so that an ascending order is the position order
+        auto push = [&](uint64_t key) {
+            const uint32_t pos = key_pos(key);
+            winners[atomicAdd(&s_cnt, 1u) % kSortMax] = ((uint64_t)pos << 32) | (uint64_t)__float_as_uint(srow[pos]);
+        };
+        for (uint32_t j = t; j < nsel; j += kTopkThreads) push(sel[j]);
         for_each_candidate(p, row, bstar, ncand_total, overflow, [&](uint64_t key) {
-            if (key >= thr) winners[atomicAdd(&s_cnt, 1u) % kSortMax] = key;
+            if (key >= thr) push(key);
         });
         __syncthreads();
-        const uint32_t got = s_cnt;
-        if (got != k && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
-        // re-key by position ascending: (pos << 32) | score bits ; pad with ~0
-        uint32_t np2 = 1;
-        while (np2 < k) np2 <<= 1;
-        __syncthreads();
-        for (uint32_t j = t; j < np2; j += blockDim.x) {
-            if (j < min(got, k)) {
-                const uint32_t pos = key_pos(winners[j]);
-                winners[j] = ((uint64_t)pos << 32) | (uint64_t)__float_as_uint(srow[pos]);
-            } else {
-                winners[j] = ~0ull;
+        const uint32_t got = min(s_cnt, k);
+        if (s_cnt != k && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
+        if (k <= (uint32_t)kRankSortMax) {
+            // rank by counting: thread j finds how many winners precede its own
+            uint64_t mine = ~0ull;
+            uint32_t rank = 0;
+            if ((uint32_t)t < got) {
+                mine = winners[t];
+                for (uint32_t i = 0; i < got; ++i) rank += (winners[i] < mine) ? 1u : 0u;
             }
-        }
-        __syncthreads();
-        for (uint32_t size = 2; size <= np2; size <<= 1) {
-            for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-                for (uint32_t j = t; j < np2 / 2; j += blockDim.x) {
-                    const uint32_t lo = 2 * j - (j & (stride - 1));
-                    const uint32_t hi = lo + stride;
-                    const bool asc = ((lo & size) == 0);
-                    const uint64_t a = winners[lo], b = winners[hi];
-                    if ((a > b) == asc) { winners[lo] = b; winners[hi] = a; }
-                }
-                __syncthreads();
-            }
-        }
-        // emit with the ownership filter, order preserved
-        if (t == 0) s_cnt = 0;
-        __syncthreads();
-        for (uint32_t base = 0; base < k; base += blockDim.x) {
-            const uint32_t j = base + t;
-            int32_t v = 0;
-            bool keep = false;
-            uint64_t w = 0;
-            if (j < k) {
-                w = winners[j];
-                if (w != ~0ull) {
-                    v = emit_value((uint32_t)(w >> 32));
-                    keep = !own || (v >= p.own_lo && v < p.own_hi);
+            __syncthreads();
+            if ((uint32_t)t < got) winners[rank] = mine;
+            __syncthreads();
+        } else {
+            uint32_t np2 = 1;
+            while (np2 < k) np2 <<= 1;
+            for (uint32_t j = got + t; j < np2; j += kTopkThreads) winners[j] = ~0ull;
+            __syncthreads();
+            for (uint32_t size = 2; size <= np2; size <<= 1) {
+                for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+                    for (uint32_t j = t; j < np2 / 2; j += kTopkThreads) {
+                        const uint32_t lo = 2 * j - (j & (stride - 1));
+                        const uint32_t hi = lo + stride;
+                        const bool asc = ((lo & size) == 0);
+                        const uint64_t a = winners[lo], b = winners[hi];
+                        if ((a > b) == asc) { winners[lo] = b; winners[hi] = a; }
+                    }
+                    __syncthreads();
                 }
             }
-            scratch[t] = keep ? 1u : 0u;
-            __syncthreads();
-            for (int off = 1; off < kTopkThreads; off <<= 1) {
-                uint32_t x = (t >= off) ? scratch[t - off] : 0;
-                __syncthreads();
-                scratch[t] += x;
-                __syncthreads();
-            }
-            const uint32_t before = s_cnt;
-            if (keep) {
-                const uint32_t at = before + scratch[t] - 1;
-                out_idx[at] = own ? v - p.own_lo : v;
-                if (out_val) out_val[at] = __uint_as_float((uint32_t)(w & 0xFFFFFFFFull));
-            }
-            __syncthreads();
-            if (t == kTopkThreads - 1) s_cnt = before + scratch[t];
-            __syncthreads();
         }
-        if (t == 0 && p.out_count) p.out_count[row] = (int32_t)s_cnt;
+        emit_ordered(got, [&](uint32_t j, uint32_t* pos, float* sc) {
+            const uint64_t w = winners[j];
+            *pos = (uint32_t)(w >> 32);
+            *sc = __uint_as_float((uint32_t)(w & 0xFFFFFFFFull));
+            return true;
+        });
     } else {
         // large k: unordered emission straight to the output
         auto put = [&](uint64_t key) {
@@ -337,7 +389,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
                 if (out_val) out_val[at] = srow[pos];
             }
         };
-        for (uint32_t j = t; j < nsel; j += blockDim.x) put(sel[j]);
+        for (uint32_t j = t; j < nsel; j += kTopkThreads) put(sel[j]);
         for_each_candidate(p, row, bstar, ncand_total, overflow, [&](uint64_t key) {
             if (key >= thr) put(key);
         });
@@ -345,10 +397,10 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
         if (t == 0 && p.out_count) p.out_count[row] = (int32_t)min(s_cnt, k);
     }
 
-    // ---- leave the counters zero at rest
-    __syncthreads();
-    for (int i = t; i < kBins; i += blockDim.x) p.hist[(size_t)row * kBins + i] = 0;
-    if (t < 8) st[t] = 0;
+    // ---- leave the global counters zero at rest
+    if (p.hist)
+        for (int i = t; i < kBins; i += kTopkThreads) p.hist[(size_t)row * kBins + i] = 0;
+    if (!FUSED && t < 8) st[t] = 0;
 }
 
 }  // namespace tidal
@@ -378,7 +430,7 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     p.k = k; p.out_idx = a->d_out_idx; p.out_val = a->d_out_val; p.out_stride = a->out_stride;
     p.idx_offset = a->idx_offset; p.force_last = a->force_last; p.own_lo = a->own_lo; p.own_hi = a->own_hi;
     p.out_count = a->d_out_count;
-    p.hist = a->d_hist ? a->d_hist : (uint32_t*)((char*)d_ws + L->hist_off);
+    p.hist = a->d_hist;
     p.row_state = (uint32_t*)((char*)d_ws + L->row_state_off);
     p.cand = (uint64_t*)((char*)d_ws + L->cand_off);
     p.sel = (uint64_t*)((char*)d_ws + L->sel_off);
@@ -387,11 +439,19 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     cudaStream_t st = (cudaStream_t)stream;
 
     if ((int64_t)a->k >= a->n) {
-        topk_finish_kernel<<<a->rows, kTopkThreads, 0, st>>>(p, 1);
+        topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, st>>>(p, 1);
         TIDAL_CUDA_OK(cudaGetLastError());
-    count_launch();
+        count_launch();
         return TIDAL_OK;
     }
+    if (a->n <= kFusedMaxN) {
+        topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, st>>>(p, 0);
+        TIDAL_CUDA_OK(cudaGetLastError());
+        count_launch();
+        return TIDAL_OK;
+    }
+    // long rows: many CTAs per row for the histogram and the split
+    if (!p.hist) p.hist = (uint32_t*)((char*)d_ws + L->hist_off);
     int nblk = (int)((a->n + 16383) / 16384);
     const int max_blk = (2 * 148 + a->rows - 1) / a->rows;
     if (nblk > max_blk) nblk = max_blk;
@@ -399,12 +459,12 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     if (!a->d_hist) {
         topk_hist_kernel<<<dim3(nblk, a->rows), kTopkThreads, 0, st>>>(p);
         TIDAL_CUDA_OK(cudaGetLastError());
-    count_launch();
+        count_launch();
     }
     topk_partition_kernel<<<dim3(nblk, a->rows), kTopkThreads, 0, st>>>(p);
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();
-    topk_finish_kernel<<<a->rows, kTopkThreads, 0, st>>>(p, 0);
+    topk_finish_kernel<false><<<a->rows, kTopkThreads, 0, st>>>(p, 0);
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();
     return TIDAL_OK;
