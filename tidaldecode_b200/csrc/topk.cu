@@ -14,11 +14,18 @@
 //   emit      winners ordered by position, ownership filter, outputs, counters
 //             back to zero.
 //
-// Rows up to kFusedMaxN run all four steps in ONE launch, one CTA per row (the
-// score row is a few hundred KB that sits in L2 behind the attention kernel).
-// Longer rows split the histogram and the scan over many CTAs per row
-// (block-then-global) and finish with one CTA per row.
+// Usual case (k <= kClusterMaxK, rows up to kClusterMaxN): ONE launch, one
+// thread-block cluster of up to 8 CTAs per row.  Every CTA scans a slice of the
+// row and pushes what it finds into the shared memory of the cluster's first CTA
+// through distributed shared memory; after one cluster barrier that CTA resolves,
+// orders and emits without touching global memory again.  Larger problems split
+// the histogram and the scan over many independent CTAs per row with lists in
+// global memory (block-then-global) and finish with one CTA per row.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace tidal {
 
@@ -403,6 +410,202 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
     if (!FUSED && t < 8) st[t] = 0;
 }
 
+
+// ------------------------------------------------------------------ cluster path
+constexpr int kClusterMaxK = 2048;            // winners kept in shared memory
+constexpr int kClusterCand = 4096;            // candidates kept in shared memory
+constexpr int64_t kClusterMaxN = 1 << 21;
+constexpr size_t kClusterSmem = sizeof(uint32_t) * kBins                       // h
+                                + sizeof(uint64_t) * (kClusterMaxK + kClusterCand);  // lists (first CTA) / local histogram
+
+struct ClusterShared {
+    uint32_t nsel, ncand, cnt, digit, need, done;
+};
+
+template <typename F>
+__device__ __forceinline__ void for_each_cluster_candidate(const TopkParams& p, int row, int bstar, const uint64_t* cand,
+                                                           uint32_t ncand, bool overflow, F f) {
+    if (!overflow) {
+        for (uint32_t j = threadIdx.x; j < ncand; j += kTopkThreads) f(cand[j]);
+    } else {
+        const float* s = p.scores + (size_t)row * p.row_stride;
+        for (int64_t j = threadIdx.x; j < p.n; j += kTopkThreads) {
+            const uint64_t key = make_key(s[j], (uint32_t)j, p.n, p.force_last);
+            if (key_bin(key) == bstar) f(key);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkParams p) {
+    extern __shared__ __align__(16) unsigned char csm[];
+    uint32_t* h = reinterpret_cast<uint32_t*>(csm);                                   // [kBins]
+    uint64_t* sel = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);      // [kClusterMaxK]
+    uint64_t* cand = sel + kClusterMaxK;                                              // [kClusterCand]
+    uint32_t* h_local = reinterpret_cast<uint32_t*>(sel);                             // own-slice histogram (no-hist path)
+    __shared__ uint32_t ws[32];
+    __shared__ ClusterShared sh;
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned CS = cluster.num_blocks();
+    const unsigned rank = cluster.block_rank();
+    const int row = blockIdx.x / CS;
+    const int t = threadIdx.x;
+    const float* srow = p.scores + (size_t)row * p.row_stride;
+    const uint32_t k = (uint32_t)p.k;
+    const int64_t per = ((p.n + CS - 1) / CS + 3) & ~(int64_t)3;      // slice length, a multiple of 4
+    const int64_t lo = (int64_t)rank * per, hi = min(p.n, lo + per);
+
+    if (t == 0) { sh.nsel = 0; sh.ncand = 0; sh.cnt = 0; }
+
+    // ---- digit-0 histogram of the whole row into h
+    if (p.hist) {
+        for (int i = t; i < kBins; i += kTopkThreads) h[i] = p.hist[(size_t)row * kBins + i];
+        cluster.sync();            // the first CTA's counters are initialised before anyone pushes to them
+    } else {
+        for (int i = t; i < kBins; i += kTopkThreads) h_local[i] = 0;
+        __syncthreads();
+#pragma unroll 4
+        for (int64_t j = lo + t; j < hi; j += kTopkThreads)
+            atomicAdd(&h_local[key_bin(make_key(srow[j], (uint32_t)j, p.n, p.force_last))], 1u);
+        cluster.sync();
+        for (int i = t; i < kBins; i += kTopkThreads) {
+            uint32_t a = 0;
+            for (unsigned r = 0; r < CS; ++r) a += cluster.map_shared_rank(h_local, r)[i];
+            h[i] = a;
+        }
+        cluster.sync();            // every CTA has read every local histogram: the list area may be written now
+    }
+    int bstar;
+    uint32_t above;
+    find_threshold_bin(h, ws, k, &bstar, &above);
+
+    // ---- scan the slice, push into the first CTA's lists
+    {
+        uint64_t* sel0 = cluster.map_shared_rank(sel, 0);
+        uint64_t* cand0 = cluster.map_shared_rank(cand, 0);
+        ClusterShared* sh0 = cluster.map_shared_rank(&sh, 0);
+        auto push = [&](float v, int64_t j) {
+            const uint64_t key = make_key(v, (uint32_t)j, p.n, p.force_last);
+            const int bin = key_bin(key);
+            if (bin > bstar) {
+                const uint32_t at = atomicAdd(&sh0->nsel, 1u);
+                if (at < (uint32_t)kClusterMaxK) sel0[at] = key;
+            } else if (bin == bstar) {
+                const uint32_t at = atomicAdd(&sh0->ncand, 1u);
+                if (at < (uint32_t)kClusterCand) cand0[at] = key;
+            }
+        };
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(srow) & 15) == 0);
+        if (vec_ok) {
+            const int64_t hi4 = lo + ((hi - lo) & ~(int64_t)3);
+#pragma unroll 2
+            for (int64_t j = lo + 4 * (int64_t)t; j < hi4; j += 4 * kTopkThreads) {
+                const float4 v = *reinterpret_cast<const float4*>(srow + j);
+                push(v.x, j); push(v.y, j + 1); push(v.z, j + 2); push(v.w, j + 3);
+            }
+            for (int64_t j = hi4 + t; j < hi; j += kTopkThreads) push(srow[j], j);
+        } else {
+#pragma unroll 4
+            for (int64_t j = lo + t; j < hi; j += kTopkThreads) push(srow[j], j);
+        }
+    }
+    cluster.sync();
+    if (rank != 0) return;
+
+    // ---- first CTA: resolve, order, emit — all in shared memory
+    int32_t* out_idx = p.out_idx + (size_t)row * p.out_stride;
+    float* out_val = p.out_val ? p.out_val + (size_t)row * p.out_stride : nullptr;
+    const bool own = p.own_hi > p.own_lo;
+    const uint32_t nsel = min(sh.nsel, (uint32_t)kClusterMaxK);
+    const uint32_t ncand_total = sh.ncand;
+    const bool overflow = ncand_total > (uint32_t)kClusterCand;
+    uint32_t need = k - above;
+    if (sh.nsel != above && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
+
+    uint64_t prefix = (uint64_t)bstar << 52;
+    uint64_t known_mask = 0xFFFull << 52;
+    bool done = (need == ncand_total);
+    for (int shift = 44; !done && shift >= -4; shift -= 8) {
+        const int sft = shift < 0 ? 0 : shift;
+        const int nb = shift < 0 ? 16 : 256;
+        const uint32_t dmask = (uint32_t)nb - 1u;
+        if (t < 256) h[t] = 0;
+        __syncthreads();
+        for_each_cluster_candidate(p, row, bstar, cand, ncand_total, overflow, [&](uint64_t key) {
+            if ((key & known_mask) == prefix) atomicAdd(&h[(uint32_t)(key >> sft) & dmask], 1u);
+        });
+        __syncthreads();
+        if (t < 32) warp_find_digit(h, nb, need, &sh.digit, &sh.need, &sh.done);
+        __syncthreads();
+        prefix |= (uint64_t)sh.digit << sft;
+        known_mask |= (uint64_t)dmask << sft;
+        need = sh.need;
+        done = sh.done != 0;
+        __syncthreads();
+    }
+    const uint64_t thr = prefix;
+
+    // winners: sel[0, nsel) plus the candidates at or above the threshold, appended behind them
+    for_each_cluster_candidate(p, row, bstar, cand, ncand_total, overflow, [&](uint64_t key) {
+        if (key >= thr) {
+            const uint32_t at = nsel + atomicAdd(&sh.cnt, 1u);
+            if (at < (uint32_t)kClusterMaxK) sel[at] = key;
+        }
+    });
+    __syncthreads();
+    const uint32_t got = min(nsel + sh.cnt, k);
+    if (nsel + sh.cnt != k && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
+    // order by position: a key's low word is 0xFFFFFFFF - position, so rank by descending low word
+    uint64_t mine[kClusterMaxK / kTopkThreads];
+    uint32_t rank_of[kClusterMaxK / kTopkThreads];
+#pragma unroll
+    for (int u = 0; u < kClusterMaxK / kTopkThreads; ++u) {
+        const uint32_t j = t + u * kTopkThreads;
+        rank_of[u] = 0;
+        mine[u] = 0;
+        if (j < got) {
+            mine[u] = sel[j];
+            const uint32_t lowm = (uint32_t)mine[u];
+            uint32_t r = 0;
+            for (uint32_t i = 0; i < got; ++i) r += ((uint32_t)sel[i] > lowm) ? 1u : 0u;
+            rank_of[u] = r;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < kClusterMaxK / kTopkThreads; ++u)
+        if (t + u * kTopkThreads < got) sel[rank_of[u]] = mine[u];
+    __syncthreads();
+    // emit in order with the ownership filter
+    uint32_t before = 0;
+    for (uint32_t base = 0; base < got; base += kTopkThreads) {
+        const uint32_t j = base + t;
+        int32_t v = 0;
+        float sc = 0.f;
+        bool keep = false;
+        if (j < got) {
+            const uint64_t key = sel[j];
+            const uint32_t pos = key_pos(key);
+            v = p.in_idx ? p.in_idx[(size_t)row * p.in_idx_stride + pos] : (int32_t)pos + p.idx_offset;
+            keep = !own || (v >= p.own_lo && v < p.own_hi);
+            if (out_val) sc = (p.force_last && (int64_t)pos == p.n - 1) ? srow[pos] : key_to_float((uint32_t)(key >> 32));
+        }
+        const uint32_t incl = block_scan_incl(keep ? 1u : 0u, ws);
+        if (keep) {
+            const uint32_t at = before + incl - 1;
+            out_idx[at] = own ? v - p.own_lo : v;
+            if (out_val) out_val[at] = sc;
+        }
+        if (t == kTopkThreads - 1) sh.cnt = before + incl;
+        __syncthreads();
+        before = sh.cnt;
+        __syncthreads();
+    }
+    if (t == 0 && p.out_count) p.out_count[row] = (int32_t)before;
+    if (p.hist)
+        for (int i = t; i < kBins; i += kTopkThreads) p.hist[(size_t)row * kBins + i] = 0;
+}
+
 }  // namespace tidal
 
 using namespace tidal;
@@ -441,6 +644,31 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     if ((int64_t)a->k >= a->n) {
         topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, st>>>(p, 1);
         TIDAL_CUDA_OK(cudaGetLastError());
+        count_launch();
+        return TIDAL_OK;
+    }
+    if (k <= kClusterMaxK && a->n <= kClusterMaxN) {
+        // one cluster per row; 8 CTAs unless the row is short
+        int cs = 8;
+        while (cs > 1 && a->n < (int64_t)cs * 2048) cs >>= 1;
+        static bool attr_set = false;
+        if (!attr_set) {
+            TIDAL_CUDA_OK(cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kClusterSmem));
+            attr_set = true;
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(a->rows * cs));
+        cfg.blockDim = dim3(kTopkThreads);
+        cfg.dynamicSmemBytes = kClusterSmem;
+        cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = (unsigned)cs;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        TIDAL_CUDA_OK(cudaLaunchKernelEx(&cfg, topk_cluster_kernel, p));
         count_launch();
         return TIDAL_OK;
     }
