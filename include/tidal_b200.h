@@ -125,6 +125,8 @@ typedef struct tidal_attn_args {
     float sm_scale;             /* <= 0 → 1/sqrt(D) */
     int32_t num_chunks;         /* 0 = planner's choice; else force the KV split */
     int32_t heads_per_cta;      /* 0 = planner's choice; else KV heads one CTA covers */
+    int32_t use_tensor_cores;   /* 0 = when 2..16 query heads share a KV head (f16/bf16); 1 = whenever
+                                   possible; -1 = never (CUDA-core kernel) */
 } tidal_attn_args;
 
 int tidal_decode_attention(const tidal_attn_args* args, void* d_ws, size_t ws_bytes, void* stream);

@@ -82,6 +82,57 @@ def test_selection_scores(T, dt, B, Hq, Hkv, D, N, page, reduce):
     assert_close(o, full[:, :, 0], dtype, "selection layer output")
 
 
+PATH_CASES = [
+    # dtype, B, Hq, Hkv, D, N, page
+    ("f16", 1, 32, 32, 128, 1500, 1),     # MHA forced onto tensor cores (4 head slices)
+    ("bf16", 2, 32, 8, 128, 2049, 1),
+    ("f16", 1, 64, 8, 128, 1000, 1),
+    ("bf16", 1, 16, 2, 64, 777, 3),
+    ("f16", 2, 16, 1, 128, 300, 1),       # MQA, 16 query heads on one KV head
+    ("bf16", 1, 8, 4, 128, 17, 1),
+    ("f16", 1, 24, 12, 64, 500, 2),       # 12 KV heads: slices of 4
+]
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,N,page", PATH_CASES)
+@pytest.mark.parametrize("tc", [1, -1])
+def test_tensor_core_and_cuda_core_paths(T, dt, B, Hq, Hkv, D, N, page, tc):
+    """Both kernels, forced, on full / selection (per-head logits) / sparse layers."""
+    dtype = DT[dt]
+    q, K, V = make_qkv(400 + N, B, Hq, Hkv, D, N, dtype, planted=4)
+    pool, table, ppb = build_pool(K, V, page, shuffle_seed=5)
+    ws = _ws(T, B, Hq, D, B * Hq, N)
+    qd, pd, td = q[:, :, 0].contiguous().cuda(), pool.cuda(), table.cuda()
+    scores = torch.full((B, Hq, N), float("nan"), dtype=torch.float32, device="cuda")
+    o = T.decode_attention(qd, pd, N, ws, page_table=td, scores=scores, use_tensor_cores=tc)
+    allidx = torch.arange(N, dtype=torch.int32)[None].expand(B, N)
+    assert_close(o, O.gathered_attention(q, K, V, allidx)[:, :, 0], dtype, "full")
+    want = O.scores_fp32(q, K, "none")
+    assert torch.allclose(scores.cpu(), want, rtol=1e-4, atol=2e-4), (scores.cpu() - want).abs().max()
+    if Hkv in (1, 2, 4, 8, 16, 32):
+        ssum = torch.full((B, N), float("nan"), dtype=torch.float32, device="cuda")
+        T.decode_attention(qd, pd, N, ws, page_table=td, scores=ssum, use_tensor_cores=tc if Hkv <= 8 else -1)
+        assert torch.allclose(ssum.cpu(), want.sum(1), rtol=1e-4, atol=2e-4 * Hq)
+    g = torch.Generator().manual_seed(N)
+    k = min(48, N)
+    shared = torch.stack([torch.randperm(N, generator=g)[:k] for _ in range(B)]).to(torch.int32)
+    o = T.decode_attention(qd, pd, N, ws, page_table=td, sel_idx=shared.cuda(), use_tensor_cores=tc)
+    assert_close(o, O.gathered_attention(q, K, V, shared)[:, :, 0], dtype, "shared list")
+    per_head = torch.stack([torch.stack([torch.randperm(N, generator=g)[:k] for _ in range(Hq)]) for _ in range(B)]).to(torch.int32)
+    o = T.decode_attention(qd, pd, N, ws, page_table=td, sel_idx=per_head.cuda(), use_tensor_cores=tc)
+    assert_close(o, O.gathered_attention(q, K, V, per_head)[:, :, 0], dtype, "per-head lists")
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+
+
+def test_tensor_core_request_is_refused_where_it_cannot_run(T):
+    q, K, V = make_qkv(1, 1, 4, 4, 64, 50, torch.float32)
+    pool, _, ppb = build_pool(K, V, 1)
+    ws = _ws(T, 1, 4, 64, 4, 50)
+    with pytest.raises(RuntimeError):
+        T.decode_attention(q[:, :, 0].contiguous().cuda(), pool.cuda(), 50, ws, pages_per_seq=ppb, use_tensor_cores=1)
+
+
 TOPK_CASES = [
     # rows, n, k
     (1, 32768, 256), (32, 4099, 256), (4, 131072, 128), (2, 1000, 1), (3, 1000, 999), (3, 1000, 1000),

@@ -35,6 +35,7 @@ class AttnArgs(C.Structure):
         ("batch", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
         ("page_size", C.c_int32), ("dtype", C.c_int32),
         ("num_pages", C.c_int64), ("sm_scale", C.c_float), ("num_chunks", C.c_int32), ("heads_per_cta", C.c_int32),
+        ("use_tensor_cores", C.c_int32),
     ]
 
 

@@ -15,45 +15,9 @@
 // covers HC KV heads (all of them when logits are summed over heads, so the sum
 // is formed in shared memory in a fixed order); its slots either own HPS heads
 // each (HC = slots*HPS) or share a head among TG token groups (slots = HC*TG).
-#include "common.cuh"
+#include "attn_params.cuh"
 
 namespace tidal {
-
-struct AttnParams {
-    const void* q;
-    void* o;
-    const char* kv;
-    const int32_t* page_table;
-    int64_t pt_stride;
-    const int32_t* seq_lens;
-    int32_t seq_len;
-    const int32_t* sel_idx;
-    const int32_t* sel_counts;
-    int32_t sel_rows, sel_count, sel_physical, extra_page;
-    int64_t sel_stride;
-    float* scores;
-    int32_t score_rows;
-    int64_t score_stride;
-    uint32_t* hist;
-    int32_t force_last;
-    float* part_o;   // [B][Hq][nchunks][D]
-    float* part_ml;  // [B][Hq][nchunks][2]
-    float* shard_m;  // optional [B][Hq]
-    float* shard_l;
-    float* shard_o;  // optional [B][Hq][D]
-    uint32_t* status;
-    int32_t B, Hq, Hkv, page_size;
-    int64_t num_pages;
-    float sm_scale;
-    int32_t nchunks;
-    int32_t HC;       // KV heads per CTA
-    int32_t greal;    // Hq / Hkv (the kernel's G is 1 in per-q-head list mode)
-    int32_t per_head; // 1: head slice index is a q head, HC == 1
-    int32_t T, S, TG; // tokens per stage, stages, token groups
-    int32_t CW;       // consumer warps
-};
-
-__host__ __device__ inline size_t round16(size_t x) { return (x + 15) & ~(size_t)15; }
 
 __host__ __device__ inline size_t attn_smem_bytes(int S, int T, int row_bytes, int HC, int CW, int slots, int hps,
                                                   int G, int D, bool want_scores) {
@@ -652,28 +616,57 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     AttnPlan plan;
     const bool per_head = sel && a->sel_rows != 1 && a->num_qo_heads > 1;
     const bool sum_heads = a->d_scores && a->score_rows == 1;
-    int kernel_G = G;
-    if (per_head) {
-        plan.HC = 1;
-        plan.nslices = a->num_qo_heads;
-        kernel_G = 1;
-    } else {
-        plan.HC = a->heads_per_cta > 0 ? a->heads_per_cta : a->num_kv_heads;
-        if (sum_heads) plan.HC = a->num_kv_heads;
-        TIDAL_REQUIRE(a->num_kv_heads % plan.HC == 0, TIDAL_ERR_ARG, "heads_per_cta %d does not divide num_kv_heads %d",
-                      plan.HC, a->num_kv_heads);
-        plan.nslices = a->num_kv_heads / plan.HC;
-    }
-    const int max_cw = kernel_G >= 4 ? 8 : 16;   // the kernel's launch bound
-    if (!plan_slots(plan.HC, lpr, kernel_G == 1, max_cw, &plan.CW, &plan.HPS, &plan.TG)) {
-        // fall back to one KV head per CTA unless the head sum must stay in one CTA
-        TIDAL_REQUIRE(!sum_heads, TIDAL_ERR_ARG, "head-summed logits need num_kv_heads in {1,2,4,...,%d} for this head_dim/dtype, got %d",
-                      16 * (32 / lpr) * (kernel_G == 1 ? 2 : 1), a->num_kv_heads);
-        plan.HC = 1;
-        plan.nslices = a->num_kv_heads;
-        plan_slots(1, lpr, false, max_cw, &plan.CW, &plan.HPS, &plan.TG);
-    }
+    int kernel_G = per_head ? 1 : G;
     const int ntok = sel ? a->sel_count + (a->extra_page >= 0 ? 1 : 0) : a->seq_len;
+
+    // Tensor cores where the query group makes q.K^T a tile contraction: 16-bit storage and
+    // 2..16 query heads per KV head.  use_tensor_cores: 0 = this rule, 1 = whenever the
+    // kernel can run (G = 1 included), -1 = never.
+    bool use_mma = false;
+    if (es == 2 && kernel_G <= 16 && a->use_tensor_cores >= 0 && (kernel_G >= 2 || a->use_tensor_cores > 0)) {
+        int hc = per_head ? 1 : 0;
+        if (!hc) {
+            if (sum_heads) {
+                hc = a->num_kv_heads;
+            } else if (a->heads_per_cta > 0) {
+                hc = a->heads_per_cta;
+            } else {
+                for (int c : {8, 4, 2, 1})
+                    if (a->num_kv_heads % c == 0) { hc = c; break; }
+            }
+        }
+        if ((hc == 1 || hc == 2 || hc == 4 || hc == 8) && (per_head || a->num_kv_heads % hc == 0)) {
+            use_mma = true;
+            plan.HC = hc;
+            plan.nslices = per_head ? a->num_qo_heads : a->num_kv_heads / hc;
+            plan.CW = kMmaWarps; plan.HPS = 1; plan.TG = kMmaWarps / hc;
+            plan.T = kMmaTile * plan.TG;
+        }
+    }
+    TIDAL_REQUIRE(use_mma || a->use_tensor_cores <= 0, TIDAL_ERR_ARG,
+                  "tensor-core attention needs f16/bf16, at most 16 query heads per KV head and 1, 2, 4 or 8 KV heads per CTA");
+    if (!use_mma) {
+        if (per_head) {
+            plan.HC = 1;
+            plan.nslices = a->num_qo_heads;
+        } else {
+            plan.HC = a->heads_per_cta > 0 ? a->heads_per_cta : a->num_kv_heads;
+            if (sum_heads) plan.HC = a->num_kv_heads;
+            TIDAL_REQUIRE(a->num_kv_heads % plan.HC == 0, TIDAL_ERR_ARG, "heads_per_cta %d does not divide num_kv_heads %d",
+                          plan.HC, a->num_kv_heads);
+            plan.nslices = a->num_kv_heads / plan.HC;
+        }
+        const int max_cw = kernel_G >= 4 ? 8 : 16;   // the kernel's launch bound
+        if (!plan_slots(plan.HC, lpr, kernel_G == 1, max_cw, &plan.CW, &plan.HPS, &plan.TG)) {
+            // fall back to one KV head per CTA unless the head sum must stay in one CTA
+            TIDAL_REQUIRE(!sum_heads, TIDAL_ERR_ARG, "head-summed logits need num_kv_heads in {1,2,4,...,%d} for this head_dim/dtype, got %d",
+                          16 * (32 / lpr) * (kernel_G == 1 ? 2 : 1), a->num_kv_heads);
+            plan.HC = 1;
+            plan.nslices = a->num_kv_heads;
+            plan_slots(1, lpr, false, max_cw, &plan.CW, &plan.HPS, &plan.TG);
+        }
+        plan.T = plan.TG * attn_tps(kernel_G);
+    }
     const int row_bytes = plan.HC * D * es;
     // a chunk should move at least ~64 KB so that its pipeline fills
     int min_tok = (64 * 1024) / (2 * row_bytes);
@@ -682,15 +675,15 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
                                      : tidal_plan_chunks(a->batch, plan.nslices, ntok, min_tok, sm_count_cached());
     TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
                   plan.nchunks, kMaxChunks);
-    const int ctok = (ntok + plan.nchunks - 1) / plan.nchunks;
-    // tokens per stage: every slot takes attn_tps(G) tokens from a stage
-    const int T = plan.TG * attn_tps(kernel_G);
-    plan.T = T;
     const int slots = plan.CW * (32 / lpr);
+    auto smem_of = [&](int S) {
+        return use_mma ? attn_mma_smem_bytes(S, plan.HC, D, sum_heads)
+                       : attn_smem_bytes(S, plan.T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads);
+    };
     int S = 8;
-    while (S > 1 && attn_smem_bytes(S, T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads) > kSmemBudget) --S;
+    while (S > 1 && smem_of(S) > kSmemBudget) --S;
     plan.S = S;
-    plan.smem = attn_smem_bytes(S, T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads);
+    plan.smem = smem_of(S);
     TIDAL_REQUIRE(plan.smem <= 227 * 1024, TIDAL_ERR_ARG, "shared memory %zu exceeds 227 KB (row %d bytes)", plan.smem, row_bytes);
 
     AttnParams p;
@@ -717,10 +710,14 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
 
     cudaStream_t st = (cudaStream_t)stream;
     int rc;
-    switch (a->dtype) {
-        case TIDAL_DTYPE_F16: rc = dispatch_d<__half>(p, plan, D, kernel_G, st); break;
-        case TIDAL_DTYPE_BF16: rc = dispatch_d<__nv_bfloat16>(p, plan, D, kernel_G, st); break;
-        default: rc = dispatch_d<float>(p, plan, D, kernel_G, st); break;
+    if (use_mma) {
+        rc = launch_attn_mma(p, D, a->dtype, dim3(plan.nchunks, plan.nslices, p.B), plan.smem, st);
+    } else {
+        switch (a->dtype) {
+            case TIDAL_DTYPE_F16: rc = dispatch_d<__half>(p, plan, D, kernel_G, st); break;
+            case TIDAL_DTYPE_BF16: rc = dispatch_d<__nv_bfloat16>(p, plan, D, kernel_G, st); break;
+            default: rc = dispatch_d<float>(p, plan, D, kernel_G, st); break;
+        }
     }
     if (rc != TIDAL_OK) return rc;
     if (plan.nchunks > 1) {

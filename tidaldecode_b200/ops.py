@@ -99,6 +99,7 @@ def decode_attention(
     sm_scale: float = 0.0,
     num_chunks: int = 0,
     heads_per_cta: int = 0,
+    use_tensor_cores: int = 0,
     want_out: bool = True,
 ) -> Optional[torch.Tensor]:
     """One decode step of attention; see tidal_decode_attention in include/tidal_b200.h."""
@@ -152,6 +153,7 @@ def decode_attention(
     a.batch, a.num_qo_heads, a.num_kv_heads, a.head_dim = B, Hq, Hkv, D
     a.page_size, a.dtype, a.num_pages = page_size, _dtype_code(q), pages
     a.sm_scale, a.num_chunks, a.heads_per_cta = float(sm_scale), int(num_chunks), int(heads_per_cta)
+    a.use_tensor_cores = int(use_tensor_cores)
     with torch.cuda.device(q.device):
         check(lib.tidal_decode_attention(C.byref(a), ws.buf.data_ptr(), ws.nbytes, _stream()), "tidal_decode_attention")
     return out
