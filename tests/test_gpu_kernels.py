@@ -98,6 +98,8 @@ PATH_CASES = [
 @pytest.mark.parametrize("tc", [1, -1])
 def test_tensor_core_and_cuda_core_paths(T, dt, B, Hq, Hkv, D, N, page, tc):
     """Both kernels, forced, on full / selection (per-head logits) / sparse layers."""
+    if tc < 0 and Hq // Hkv > 8:
+        pytest.skip("the CUDA-core kernel is built for up to 8 query heads per KV head")
     dtype = DT[dt]
     q, K, V = make_qkv(400 + N, B, Hq, Hkv, D, N, dtype, planted=4)
     pool, table, ppb = build_pool(K, V, page, shuffle_seed=5)
