@@ -174,6 +174,29 @@ typedef struct tidal_topk_args {
 } tidal_topk_args;
 int tidal_topk(const tidal_topk_args* args, void* d_ws, size_t ws_bytes, void* stream);
 
+/* ------------------------------------------------ top-k without a workspace
+ * Has no counterpart in the reference.  Same selection as tidal_topk, for callers
+ * that are not in a position to hand over (or allocate) a workspace: a plugin that
+ * was given only its input and output buffers by a host runtime which owns all device
+ * memory, or a decode loop that runs under a "no allocator calls after warm-up" rule
+ * because cudaMalloc/cudaFree may synchronise the device and stall every stream.
+ * The scratch the kernel needs (the lists of certain and candidate keys and the fault
+ * word) lives in a fixed ~2 MB array inside the library image instead; each GPU that
+ * loads the library keeps that array until the process exits.
+ *
+ * Limits (anything beyond is refused with TIDAL_ERR_ARG and a message): at most 8 rows
+ * per call, rows of at most 262144 scores, k at most 16384; d_hist must be NULL.
+ * The call itself allocates nothing and frees nothing.  Its first use on a device
+ * looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current) and caches it, so make that first call outside any stream capture.
+ * All calls on one device share the array, which still holds what the previous call
+ * left there: nothing in it needs to start at zero except the fault word, which is
+ * sticky by design; two calls whose kernels can overlap on the GPU (different streams,
+ * no dependency) would overwrite each other's lists — order them.
+ * d_status: NULL, or a device word of the caller's that receives TIDAL_DEV_* bits
+ * instead of the internal fault word. */
+int tidal_topk_static(const tidal_topk_args* args, uint32_t* d_status, void* stream);
+
 /* ------------------------------------------------------ RoPE + KV append
  * Rotates q (in place) and the new k, then writes k,v into their pool slots.
  * Stands in for apply_rope_in_place + append_kv_cache_decode / _prefill

@@ -18,7 +18,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_rope_append", "tidal_merge_partials",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials",
 )
 
 
@@ -87,6 +87,8 @@ def _load() -> C.CDLL:
     lib.tidal_plan_chunks.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
     lib.tidal_topk.restype = C.c_int
     lib.tidal_topk.argtypes = [C.POINTER(TopkArgs), C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.tidal_topk_static.restype = C.c_int
+    lib.tidal_topk_static.argtypes = [C.POINTER(TopkArgs), C.c_void_p, C.c_void_p]
     lib.tidal_rope_append.restype = C.c_int
     lib.tidal_rope_append.argtypes = [C.POINTER(RopeAppendArgs), C.c_void_p]
     lib.tidal_merge_partials.restype = C.c_int

@@ -23,6 +23,8 @@
 // global memory (block-then-global) and finish with one CTA per row.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cg = cooperative_groups;
@@ -693,6 +695,87 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();
     topk_finish_kernel<false><<<a->rows, kTopkThreads, 0, st>>>(p, 0);
+    TIDAL_CUDA_OK(cudaGetLastError());
+    count_launch();
+    return TIDAL_OK;
+}
+
+// ------------------------------------------------- allocation-free entry point
+// tidal_topk_static: the one-CTA-per-row kernel above (topk_finish_kernel<true>) with
+// its `sel` / `cand` lists and fault word in a fixed array that is part of the loaded
+// library image instead of a caller-supplied workspace.  Every call on a device shares
+// the array.
+namespace tidal {
+
+constexpr int kStaticRows = 8;                 // rows per call
+constexpr int64_t kStaticCand = 16384;         // candidate slots per row (more candidates: the kernel rescans the row)
+constexpr int64_t kStaticMaxN = kFusedMaxN;    // longest row
+constexpr int kStaticMaxK = kMaxK;
+
+struct StaticTopkScratch {
+    uint32_t status[64];                       // [0]: TIDAL_DEV_* bits, sticky
+    uint64_t sel[kStaticRows][kMaxK];
+    uint64_t cand[kStaticRows][kStaticCand];
+};
+
+// ~2 MB per GPU that loads the library, held until the process exits.
+static __device__ __align__(256) unsigned char g_static_topk_scratch[sizeof(StaticTopkScratch)];
+
+// In host code the name above is only a handle for the runtime, never a device address:
+// the address is looked up once per device and cached here.
+static std::mutex g_static_mu;
+static StaticTopkScratch* g_static_ptr[64] = {};
+
+static int static_scratch_for_current_device(StaticTopkScratch** out) {
+    int dev = -1;
+    TIDAL_CUDA_OK(cudaGetDevice(&dev));
+    TIDAL_REQUIRE(dev >= 0 && dev < 64, TIDAL_ERR_ARG, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+        void* ptr = nullptr;
+        TIDAL_CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_topk_scratch));
+        TIDAL_REQUIRE(ptr != nullptr, TIDAL_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        g_static_ptr[dev] = static_cast<StaticTopkScratch*>(ptr);
+    }
+    *out = g_static_ptr[dev];
+    return TIDAL_OK;
+}
+
+}  // namespace tidal
+
+extern "C" int tidal_topk_static(const tidal_topk_args* a, uint32_t* d_status, void* stream) {
+    TIDAL_REQUIRE(a != nullptr, TIDAL_ERR_ARG, "args is NULL");
+    TIDAL_REQUIRE(a->d_scores && a->d_out_idx, TIDAL_ERR_ARG, "scores and out_idx must be given");
+    TIDAL_REQUIRE(a->rows >= 1 && a->n >= 1 && a->k >= 1, TIDAL_ERR_ARG, "rows, n and k must be positive (rows %d n %lld k %d)",
+                  a->rows, (long long)a->n, a->k);
+    TIDAL_REQUIRE(a->rows <= kStaticRows, TIDAL_ERR_ARG, "tidal_topk_static takes at most %d rows per call, got %d", kStaticRows,
+                  a->rows);
+    TIDAL_REQUIRE(a->n <= kStaticMaxN, TIDAL_ERR_ARG, "tidal_topk_static takes rows of at most %lld scores, got %lld",
+                  (long long)kStaticMaxN, (long long)a->n);
+    TIDAL_REQUIRE(a->row_stride >= a->n, TIDAL_ERR_ARG, "row_stride shorter than n");
+    TIDAL_REQUIRE(a->d_in_idx == nullptr || a->in_idx_stride == 0 || a->in_idx_stride >= a->n, TIDAL_ERR_ARG,
+                  "in_idx_stride must be 0 (shared row) or at least n");
+    TIDAL_REQUIRE(a->d_hist == nullptr, TIDAL_ERR_ARG, "tidal_topk_static builds its own histogram: d_hist must be NULL");
+    const int k = (int64_t)a->k < a->n ? a->k : (int)a->n;
+    TIDAL_REQUIRE(k <= kStaticMaxK || (int64_t)a->k >= a->n, TIDAL_ERR_ARG, "tidal_topk_static takes k of at most %d, got %d",
+                  kStaticMaxK, k);
+    TIDAL_REQUIRE(a->out_stride >= k, TIDAL_ERR_ARG, "out_stride %lld shorter than min(k, n) = %d", (long long)a->out_stride, k);
+    StaticTopkScratch* sc = nullptr;
+    const int rc = static_scratch_for_current_device(&sc);
+    if (rc != TIDAL_OK) return rc;
+
+    TopkParams p;
+    p.scores = a->d_scores; p.in_idx = a->d_in_idx; p.in_idx_stride = a->in_idx_stride; p.rows = a->rows; p.n = a->n;
+    p.row_stride = a->row_stride; p.k = k; p.out_idx = a->d_out_idx; p.out_val = a->d_out_val; p.out_stride = a->out_stride;
+    p.idx_offset = a->idx_offset; p.force_last = a->force_last; p.own_lo = a->own_lo; p.own_hi = a->own_hi;
+    p.out_count = a->d_out_count;
+    p.hist = nullptr;                       // the kernel counts the first digit in shared memory
+    p.row_state = nullptr;                  // its list counters live in shared memory too: nothing to clear between calls
+    p.cand = &sc->cand[0][0];
+    p.sel = &sc->sel[0][0];
+    p.cand_cap = kStaticCand;
+    p.status = d_status ? d_status : &sc->status[0];
+    topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, (cudaStream_t)stream>>>(p, (int64_t)a->k >= a->n ? 1 : 0);
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();
     return TIDAL_OK;
