@@ -69,8 +69,10 @@ class ShardedDecodeAttention:
     """Per-rank driver of the kernels for one (batch, heads, context) geometry."""
 
     def __init__(self, batch: int, hq: int, hkv: int, d: int, dtype: torch.dtype, plan: ShardPlan, rank: int,
-                 top_k: int, head_reduce: str = "sum", group: Optional[dist.ProcessGroup] = None, device="cuda"):
-        from . import ops  # CUDA only: raises if the library is missing
+                 top_k: int, head_reduce: str = "sum", group: Optional[dist.ProcessGroup] = None, device="cuda",
+                 ops=None):
+        if ops is None:
+            from . import ops  # the CUDA library; raises if it is missing (tests of the exchange logic inject a stand-in)
 
         self.ops = ops
         self.B, self.Hq, self.Hkv, self.D, self.dtype = batch, hq, hkv, d, dtype
