@@ -171,7 +171,7 @@ def run_ours(args, rank, world, device):
     q_step = torch.empty(2, B, Hq, D, dtype=dtype, device=device)
     ev_sel = []
 
-    def step(i, timed_kernel=False, e2e=False):
+    def step(i, timed_kernel=False, e2e=False, sync=True):
         ls, lp = (2 * i) % (2 * pairs), (2 * i + 1) % (2 * pairs)
         if e2e:
             q_step.copy_(q_host[ls:ls + 2], non_blocking=True)    # ls is even and lp == ls + 1
@@ -190,7 +190,7 @@ def run_ours(args, rank, world, device):
             T.decode_attention(qp, pools[lp], n_loc, ws, pages_per_seq=n_loc, sel_idx=idx, out=o_sp)
             outs = (o_sel, o_sp)
         else:
-            a1 = sh.selection_layer(qs, pools[ls], pages_per_seq=max(n_loc, 1))
+            a1 = sh.selection_layer(qs, pools[ls], pages_per_seq=max(n_loc, 1), timing=ev_sel if timed_kernel else None)
             if e2e:
                 out_host[0].copy_(a1, non_blocking=True)
             a2 = sh.sparse_layer(qp, pools[lp], pages_per_seq=max(n_loc, 1))
@@ -199,19 +199,43 @@ def run_ours(args, rank, world, device):
             if outs[0] is not None:
                 out_host[0].copy_(outs[0], non_blocking=True)
             out_host[1].copy_(outs[1], non_blocking=True)
-            torch.cuda.current_stream().synchronize()     # the caller reads the step's result
+            if sync:
+                torch.cuda.current_stream().synchronize()     # the caller reads the step's result
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    use_graph = args.graph == 1 or (args.graph < 0 and world > 1)
+    graphs = {}
+
+    def step_graph(i, e2e):
+        """One CUDA graph per (layer pair, variant): the sharded step is a dozen small launches and two
+        collectives, which the host cannot issue as fast as the GPUs retire them."""
+        key = (i % pairs, e2e)
+        g = graphs.get(key)
+        if g is None:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step(i % pairs, e2e=e2e, sync=False)
+            graphs[key] = g
+        return g
+
+    def run_step(i, timed_kernel=False, e2e=False):
+        if use_graph and not timed_kernel:
+            step_graph(i, e2e).replay()
+            if e2e:
+                torch.cuda.current_stream().synchronize()
+        else:
+            step(i, timed_kernel=timed_kernel, e2e=e2e)
+
     def timed(n_steps, **kw):
         barrier()
         a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for i in range(n_steps):
-            step(i, **kw)
+            run_step(i, **kw)
         b_.record()
         barrier()
         ms = a.elapsed_time(b_)
@@ -226,11 +250,32 @@ def run_ours(args, rank, world, device):
         step(i, e2e=True)
     torch.cuda.synchronize()
     assert ws.status() == 0 and (sh is None or sh.ws.status() == 0), "device-side fault bits set during warm-up"
+    if use_graph:
+        for i in range(pairs):
+            step_graph(i, False)
+            step_graph(i, True)
+        for i in range(args.warmup):
+            run_step(i)
+            run_step(i, e2e=True)
+        torch.cuda.synchronize()
 
     launches0 = T.lib.tidal_launch_count()
+    launches_eager = None
     with ClockSampler(torch.cuda.current_device()) as cs:
-        ms = timed(args.steps, timed_kernel=True)
+        if use_graph:
+            # kernel-level events cannot be recorded inside a graph: time the dominant kernel in an eager pass
+            # over the same steps first, then the graph-replayed region
+            for i in range(min(args.steps, 4 * pairs)):
+                step(i, timed_kernel=True)
+            launches_eager = T.lib.tidal_launch_count() - launches0
+            ms = timed(args.steps)
+        else:
+            ms = timed(args.steps, timed_kernel=True)
     launches = T.lib.tidal_launch_count() - launches0
+    if use_graph:
+        # graph replays do not pass through the library's host entry points: count what one captured step
+        # launches (measured in the eager pass) times the steps
+        launches = int(round(launches_eager / min(args.steps, 4 * pairs) * args.steps))
     ms_e2e = timed(args.steps, e2e=True)
     assert ws.status() == 0 and (sh is None or sh.ws.status() == 0), "device-side fault bits set"
 
@@ -257,6 +302,9 @@ def run_ours(args, rank, world, device):
         "gpu_launches": int(launches),
         "clocks": cs.summary(),
     }
+    if use_graph:
+        line["config"]["launch"] = "each step replayed as one CUDA graph (kernels + NCCL all-gathers); roofline kernel timed in an eager pass"
+
     if roof:
         line["roofline"] = roof
     return line
@@ -310,6 +358,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", type=int, default=-1, help="1: replay each step as a CUDA graph; 0: never; default: when N > 1")
     ap.add_argument("--layer-pairs", type=int, default=0, help="distinct (selection, sparse) KV pool pairs to rotate over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -171,6 +171,11 @@ typedef struct tidal_topk_args {
     int32_t own_lo, own_hi;
     int32_t* d_out_count;
     uint32_t* d_hist;
+    int32_t seg_len;            /* 0, or: a row is made of segments of seg_len elements that lie seg_stride */
+    int64_t seg_stride;         /*    elements apart (element j of row r is at (j/seg_len)*seg_stride +
+                                      r*row_stride + j%seg_len); d_in_idx is addressed the same way.  This is how the
+                                      per-rank candidate blocks of an all-gathered buffer are ranked in place.
+                                      Needs k <= 2048 and n <= 2097152. */
 } tidal_topk_args;
 int tidal_topk(const tidal_topk_args* args, void* d_ws, size_t ws_bytes, void* stream);
 
@@ -238,6 +243,10 @@ int tidal_rope_append(const tidal_rope_append_args* args, void* stream);
  * reference's merge across KV chunks (decode_attn.cuh:213-232, state_t::merge). */
 int tidal_merge_partials(const float* d_m, const float* d_l, const float* d_o, int shards, int batch,
                          int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream);
+/* Same, with the shards' blocks shard_stride elements apart in each of d_m, d_l, d_o (the
+ * packed receive buffer of an all-gather is merged in place). */
+int tidal_merge_partials_strided(const float* d_m, const float* d_l, const float* d_o, int64_t shard_stride, int shards,
+                                 int batch, int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -70,7 +70,15 @@ class _OracleOps:
 
     @staticmethod
     def topk(scores, k, ws, *, n=None, in_idx=None, out_idx=None, out_val=None, idx_offset=0, own_range=None,
-             out_count=None, hist=None, **kw):
+             out_count=None, hist=None, segments=None, **kw):
+        if segments is not None:
+            # element j of row r lives at (j // seg_len) * seg_stride + r * row_stride + j % seg_len
+            nrows, seg_len, seg_stride, row_stride = segments
+            j = torch.arange(n)
+            off = (j // seg_len) * seg_stride + (j % seg_len)
+            at = off[None, :] + torch.arange(nrows)[:, None] * row_stride
+            scores = scores.reshape(-1)[at]
+            in_idx = in_idx.reshape(-1)[at]
         rows = scores.reshape(-1, scores.shape[-1])
         n = rows.shape[1] if n is None else n
         kk = min(k, n)
@@ -93,7 +101,12 @@ class _OracleOps:
         return out_idx
 
     @staticmethod
-    def merge_partials(m, l, o, dtype, out=None):
+    def merge_partials(m, l, o, dtype, out=None, geometry=None):
+        if geometry is not None:
+            shards, B, Hq, D, stride = geometry
+            pick = lambda t, cnt, shape: torch.stack([t.reshape(-1)[s * stride: s * stride + cnt].view(shape)
+                                                      for s in range(shards)])
+            m, l, o = pick(m, B * Hq, (B, Hq)), pick(l, B * Hq, (B, Hq)), pick(o, B * Hq * D, (B, Hq, D))
         M = m.max(dim=0).values
         w = torch.where(torch.isfinite(m), torch.exp2(m - M), torch.zeros_like(m))
         num = (w[..., None] * o).sum(0)

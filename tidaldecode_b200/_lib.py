@@ -18,7 +18,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided",
 )
 
 
@@ -46,6 +46,7 @@ class TopkArgs(C.Structure):
         ("d_out_idx", C.c_void_p), ("d_out_val", C.c_void_p), ("out_stride", C.c_int64),
         ("idx_offset", C.c_int32), ("force_last", C.c_int32), ("own_lo", C.c_int32), ("own_hi", C.c_int32),
         ("d_out_count", C.c_void_p), ("d_hist", C.c_void_p),
+        ("seg_len", C.c_int32), ("seg_stride", C.c_int64),
     ]
 
 
@@ -94,6 +95,9 @@ def _load() -> C.CDLL:
     lib.tidal_merge_partials.restype = C.c_int
     lib.tidal_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                          C.c_void_p, C.c_int, C.c_void_p]
+    lib.tidal_merge_partials_strided.restype = C.c_int
+    lib.tidal_merge_partials_strided.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
+                                                 C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     return lib
 
 

@@ -44,6 +44,8 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     static_assert(LPR <= 32 && (32 % LPR) == 0, "row must fit a warp");
 
     extern __shared__ __align__(128) unsigned char smem[];
+    pdl_wait();                 // ordered after the earlier kernels of the stream (see common.cuh)
+    pdl_launch_dependents();
     const int row_bytes = p.HC * D * (int)sizeof(T);
     const int S = p.S, TT = p.T, TG = p.TG, HC = p.HC;
     const int slots = p.CW * SPW;
@@ -394,6 +396,8 @@ __global__ void merge_chunks_kernel(const float* __restrict__ part_o, const floa
                                     int Hq, int D, T* __restrict__ o, float* __restrict__ shard_m,
                                     float* __restrict__ shard_l, float* __restrict__ shard_o) {
     extern __shared__ float msm[];           // [nchunks] weights, then [kMergeGroups][D] partial sums
+    pdl_wait();
+    pdl_launch_dependents();
     float* wgt = msm;
     float* red = msm + nchunks;
     __shared__ float s_M, s_L;
@@ -445,16 +449,19 @@ __global__ void merge_chunks_kernel(const float* __restrict__ part_o, const floa
 // Merge `shards` sets of un-normalised partials laid out [shards][B*Hq(*D)].
 template <typename T>
 __global__ void merge_shards_kernel(const float* __restrict__ m, const float* __restrict__ l,
-                                    const float* __restrict__ o, int shards, int rows, int D, T* __restrict__ out) {
+                                    const float* __restrict__ o, int shards, int rows, int D, T* __restrict__ out,
+                                    int64_t stride_ml, int64_t stride_o) {
     const int r = blockIdx.x, d = threadIdx.x;
+    pdl_wait();
+    pdl_launch_dependents();
     float M = -INFINITY;
-    for (int s = 0; s < shards; ++s) M = fmaxf(M, m[(size_t)s * rows + r]);
+    for (int s = 0; s < shards; ++s) M = fmaxf(M, m[(size_t)s * stride_ml + r]);
     float acc = 0.f, L = 0.f;
     for (int s = 0; s < shards; ++s) {
-        const float ms = m[(size_t)s * rows + r];
+        const float ms = m[(size_t)s * stride_ml + r];
         const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
-        acc = fmaf(w, o[((size_t)s * rows + r) * D + d], acc);
-        L = fmaf(w, l[(size_t)s * rows + r], L);
+        acc = fmaf(w, o[(size_t)s * stride_o + (size_t)r * D + d], acc);
+        L = fmaf(w, l[(size_t)s * stride_ml + r], L);
     }
     out[(size_t)r * D + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
 }
@@ -524,8 +531,7 @@ static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t s
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
     dim3 grid(plan.nchunks, plan.nslices, p.B);
     dim3 block((plan.CW + 1) * 32);
-    kern<<<grid, block, plan.smem, st>>>(p);
-    TIDAL_CUDA_OK(cudaGetLastError());
+    TIDAL_CUDA_OK(launch_pdl(kern, grid, block, plan.smem, st, 1, p));
     count_launch();
     return TIDAL_OK;
 }
@@ -562,9 +568,9 @@ static int dispatch_d(const AttnParams& p, const AttnPlan& plan, int D, int G, c
 template <typename T>
 static int launch_merge(const AttnParams& p, int D, cudaStream_t st) {
     const size_t smem = sizeof(float) * ((size_t)p.nchunks + (size_t)kMergeGroups * D);
-    merge_chunks_kernel<T><<<dim3(p.Hq, p.B), dim3(D, kMergeGroups), smem, st>>>(p.part_o, p.part_ml, p.nchunks, p.Hq, D,
-                                                                                  (T*)p.o, p.shard_m, p.shard_l, p.shard_o);
-    TIDAL_CUDA_OK(cudaGetLastError());
+    TIDAL_CUDA_OK(launch_pdl(merge_chunks_kernel<T>, dim3(p.Hq, p.B), dim3(D, kMergeGroups), smem, st, 1,
+                             (const float*)p.part_o, (const float*)p.part_ml, (int)p.nchunks, (int)p.Hq, D, (T*)p.o, p.shard_m,
+                             p.shard_l, p.shard_o));
     count_launch();
     return TIDAL_OK;
 }
@@ -730,20 +736,29 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     return rc;
 }
 
-extern "C" int tidal_merge_partials(const float* d_m, const float* d_l, const float* d_o, int shards, int batch,
-                                    int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream) {
+extern "C" int tidal_merge_partials_strided(const float* d_m, const float* d_l, const float* d_o, int64_t shard_stride,
+                                            int shards, int batch, int num_qo_heads, int head_dim, void* d_out, int dtype,
+                                            void* stream) {
     TIDAL_REQUIRE(d_m && d_l && d_o && d_out, TIDAL_ERR_ARG, "null pointer");
     TIDAL_REQUIRE(shards >= 1 && batch >= 1 && num_qo_heads >= 1, TIDAL_ERR_ARG, "bad shards/batch/heads");
     TIDAL_REQUIRE(head_dim >= 1 && head_dim <= 1024, TIDAL_ERR_ARG, "bad head_dim %d", head_dim);
     const int rows = batch * num_qo_heads;
+    const int64_t sml = shard_stride > 0 ? shard_stride : rows;
+    const int64_t so = shard_stride > 0 ? shard_stride : (int64_t)rows * head_dim;
     cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
     switch (dtype) {
-        case TIDAL_DTYPE_F16: merge_shards_kernel<__half><<<rows, head_dim, 0, st>>>(d_m, d_l, d_o, shards, rows, head_dim, (__half*)d_out); break;
-        case TIDAL_DTYPE_BF16: merge_shards_kernel<__nv_bfloat16><<<rows, head_dim, 0, st>>>(d_m, d_l, d_o, shards, rows, head_dim, (__nv_bfloat16*)d_out); break;
-        case TIDAL_DTYPE_F32: merge_shards_kernel<float><<<rows, head_dim, 0, st>>>(d_m, d_l, d_o, shards, rows, head_dim, (float*)d_out); break;
+        case TIDAL_DTYPE_F16: e = launch_pdl(merge_shards_kernel<__half>, dim3(rows), dim3(head_dim), 0, st, 1, d_m, d_l, d_o, shards, rows, head_dim, (__half*)d_out, sml, so); break;
+        case TIDAL_DTYPE_BF16: e = launch_pdl(merge_shards_kernel<__nv_bfloat16>, dim3(rows), dim3(head_dim), 0, st, 1, d_m, d_l, d_o, shards, rows, head_dim, (__nv_bfloat16*)d_out, sml, so); break;
+        case TIDAL_DTYPE_F32: e = launch_pdl(merge_shards_kernel<float>, dim3(rows), dim3(head_dim), 0, st, 1, d_m, d_l, d_o, shards, rows, head_dim, (float*)d_out, sml, so); break;
         default: set_error("unknown dtype %d", dtype); return TIDAL_ERR_ARG;
     }
-    TIDAL_CUDA_OK(cudaGetLastError());
+    TIDAL_CUDA_OK(e);
     count_launch();
     return TIDAL_OK;
+}
+
+extern "C" int tidal_merge_partials(const float* d_m, const float* d_l, const float* d_o, int shards, int batch,
+                                    int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream) {
+    return tidal_merge_partials_strided(d_m, d_l, d_o, 0, shards, batch, num_qo_heads, head_dim, d_out, dtype, stream);
 }

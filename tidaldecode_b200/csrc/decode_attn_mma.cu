@@ -97,6 +97,24 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = p.per_head ? 1 : p.greal;
 
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kMmaWarps);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Rows of a stage that no copy fills (a short last stage) still enter the P V product
+    // with weight zero; zero * stale NaN would poison the accumulator, so the ring starts
+    // out as zeros (later contents are real K/V rows, finite whenever the cache is).
+    for (size_t i = (size_t)threadIdx.x * 16; i < stage_bytes; i += (size_t)blockDim.x * 16)
+        *reinterpret_cast<uint4*>(stage_base + i) = make_uint4(0, 0, 0, 0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // the prologue above touched no global memory; from here on this kernel is ordered
+    // after the earlier kernels of the stream (see common.cuh)
+    pdl_wait();
+    pdl_launch_dependents();
     // ---- token list of this CTA (same rules as the CUDA-core kernel)
     const int sel_row = p.sel_idx ? (p.sel_rows == 1 ? 0 : slice) : 0;
     int list_len;
@@ -117,20 +135,6 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     const int kvh0 = p.per_head ? slice / p.greal : slice * HC;
     const int qh0 = p.per_head ? slice : kvh0 * G;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], kMmaWarps);
-        }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    // Rows of a stage that no copy fills (a short last stage) still enter the P V product
-    // with weight zero; zero * stale NaN would poison the accumulator, so the ring starts
-    // out as zeros (later contents are real K/V rows, finite whenever the cache is).
-    for (size_t i = (size_t)threadIdx.x * 16; i < stage_bytes; i += (size_t)blockDim.x * 16)
-        *reinterpret_cast<uint4*>(stage_base + i) = make_uint4(0, 0, 0, 0);
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
     if (warp == 0) {
@@ -433,8 +437,7 @@ template <typename T, int D>
 static int launch_one(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     auto kern = decode_attn_mma_kernel<T, D>;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, (kMmaWarps + 1) * 32, smem, st>>>(p);
-    TIDAL_CUDA_OK(cudaGetLastError());
+    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 1) * 32), smem, st, 1, p));
     count_launch();
     return TIDAL_OK;
 }

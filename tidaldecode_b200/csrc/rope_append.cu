@@ -55,6 +55,8 @@ __global__ void rope_append_kernel(const RopeParams p) {
     using V = Vec16<T>;
     constexpr int VEC = V::N;
     constexpr int VPR = D / VEC;  // vectors per row
+    pdl_wait();
+    pdl_launch_dependents();
     const int tok = blockIdx.x;
     const int b = tok / p.tokens_per_seq;
     const int tpos = (p.pos0_dev ? p.pos0_dev[b] : p.pos0) + tok % p.tokens_per_seq;
@@ -122,13 +124,14 @@ __global__ void rope_append_kernel(const RopeParams p) {
 
 template <typename T>
 static int launch_rope(const RopeParams& p, int D, int n_tokens, int threads, cudaStream_t st) {
-    if (D == 64) rope_append_kernel<T, 64><<<n_tokens, threads, 0, st>>>(p);
-    else if (D == 128) rope_append_kernel<T, 128><<<n_tokens, threads, 0, st>>>(p);
+    cudaError_t e;
+    if (D == 64) e = launch_pdl(rope_append_kernel<T, 64>, dim3(n_tokens), dim3(threads), 0, st, 1, p);
+    else if (D == 128) e = launch_pdl(rope_append_kernel<T, 128>, dim3(n_tokens), dim3(threads), 0, st, 1, p);
     else {
         set_error("unsupported head_dim %d (built: 64, 128)", D);
         return TIDAL_ERR_ARG;
     }
-    TIDAL_CUDA_OK(cudaGetLastError());
+    TIDAL_CUDA_OK(e);
     count_launch();
     return TIDAL_OK;
 }

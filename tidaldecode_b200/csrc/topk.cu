@@ -55,7 +55,16 @@ struct TopkParams {
     uint64_t* sel;        // [rows][kMaxK]
     int64_t cand_cap;
     uint32_t* status;
+    int32_t seg_len;      // 0, or rows are made of segments seg_stride elements apart (cluster kernel only)
+    int64_t seg_stride;
 };
+
+// Offset of element j of a row whose contiguous layout would start at row*stride.
+__device__ __forceinline__ size_t elem_off(const TopkParams& p, int64_t stride, int row, int64_t j) {
+    if (p.seg_len == 0) return (size_t)row * stride + (size_t)j;
+    const int64_t sg = j / p.seg_len;
+    return (size_t)sg * p.seg_stride + (size_t)row * stride + (size_t)(j - sg * p.seg_len);
+}
 
 __device__ __forceinline__ uint64_t make_key(float s, uint32_t pos, int64_t n, int force_last) {
     uint32_t k32 = ordered_key(s);
@@ -154,6 +163,8 @@ __device__ __forceinline__ void warp_find_digit(const uint32_t* h, int nbins, ui
 
 __global__ void __launch_bounds__(kTopkThreads) topk_hist_kernel(const TopkParams p) {
     __shared__ uint32_t h[kBins];
+    pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.y;
     for (int i = threadIdx.x; i < kBins; i += blockDim.x) h[i] = 0;
     __syncthreads();
@@ -192,6 +203,8 @@ __device__ __forceinline__ void split_range(const TopkParams& p, int row, int64_
 __global__ void __launch_bounds__(kTopkThreads) topk_partition_kernel(const TopkParams p) {
     __shared__ uint32_t h[kBins];
     __shared__ uint32_t ws[32];
+    pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.y;
     for (int i = threadIdx.x; i < kBins; i += blockDim.x) h[i] = p.hist[(size_t)row * kBins + i];
     __syncthreads();
@@ -231,6 +244,8 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
     static_assert(sizeof(uint64_t) * kSortMax >= sizeof(uint32_t) * kBins, "winners must cover the histogram");
     __shared__ uint32_t ws[32];
     __shared__ uint32_t s_cnt, s_digit, s_need, s_done, s_nsel, s_ncand;
+    pdl_wait();
+    pdl_launch_dependents();
     const int row = blockIdx.x;
     const int t = threadIdx.x;
     uint32_t* st = p.row_state + (size_t)row * 8;
@@ -430,9 +445,8 @@ __device__ __forceinline__ void for_each_cluster_candidate(const TopkParams& p, 
     if (!overflow) {
         for (uint32_t j = threadIdx.x; j < ncand; j += kTopkThreads) f(cand[j]);
     } else {
-        const float* s = p.scores + (size_t)row * p.row_stride;
         for (int64_t j = threadIdx.x; j < p.n; j += kTopkThreads) {
-            const uint64_t key = make_key(s[j], (uint32_t)j, p.n, p.force_last);
+            const uint64_t key = make_key(p.scores[elem_off(p, p.row_stride, row, j)], (uint32_t)j, p.n, p.force_last);
             if (key_bin(key) == bstar) f(key);
         }
     }
@@ -446,13 +460,16 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     uint32_t* h_local = reinterpret_cast<uint32_t*>(sel);                             // own-slice histogram (no-hist path)
     __shared__ uint32_t ws[32];
     __shared__ ClusterShared sh;
+    pdl_wait();
+    pdl_launch_dependents();
 
     cg::cluster_group cluster = cg::this_cluster();
     const unsigned CS = cluster.num_blocks();
     const unsigned rank = cluster.block_rank();
     const int row = blockIdx.x / CS;
     const int t = threadIdx.x;
-    const float* srow = p.scores + (size_t)row * p.row_stride;
+    const float* srow = p.seg_len ? nullptr : p.scores + (size_t)row * p.row_stride;   // contiguous rows only
+    auto score_at = [&](int64_t j) -> float { return p.scores[elem_off(p, p.row_stride, row, j)]; };
     const uint32_t k = (uint32_t)p.k;
     const int64_t per = ((p.n + CS - 1) / CS + 3) & ~(int64_t)3;      // slice length, a multiple of 4
     const int64_t lo = (int64_t)rank * per, hi = min(p.n, lo + per);
@@ -468,7 +485,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
         __syncthreads();
 #pragma unroll 4
         for (int64_t j = lo + t; j < hi; j += kTopkThreads)
-            atomicAdd(&h_local[key_bin(make_key(srow[j], (uint32_t)j, p.n, p.force_last))], 1u);
+            atomicAdd(&h_local[key_bin(make_key(score_at(j), (uint32_t)j, p.n, p.force_last))], 1u);
         cluster.sync();
         for (int i = t; i < kBins; i += kTopkThreads) {
             uint32_t a = 0;
@@ -497,7 +514,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
                 if (at < (uint32_t)kClusterCand) cand0[at] = key;
             }
         };
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(srow) & 15) == 0);
+        const bool vec_ok = p.seg_len == 0 && ((reinterpret_cast<uintptr_t>(srow) & 15) == 0);
         if (vec_ok) {
             const int64_t hi4 = lo + ((hi - lo) & ~(int64_t)3);
 #pragma unroll 2
@@ -508,7 +525,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
             for (int64_t j = hi4 + t; j < hi; j += kTopkThreads) push(srow[j], j);
         } else {
 #pragma unroll 4
-            for (int64_t j = lo + t; j < hi; j += kTopkThreads) push(srow[j], j);
+            for (int64_t j = lo + t; j < hi; j += kTopkThreads) push(score_at(j), j);
         }
     }
     cluster.sync();
@@ -588,9 +605,9 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
         if (j < got) {
             const uint64_t key = sel[j];
             const uint32_t pos = key_pos(key);
-            v = p.in_idx ? p.in_idx[(size_t)row * p.in_idx_stride + pos] : (int32_t)pos + p.idx_offset;
+            v = p.in_idx ? p.in_idx[elem_off(p, p.in_idx_stride, row, pos)] : (int32_t)pos + p.idx_offset;
             keep = !own || (v >= p.own_lo && v < p.own_hi);
-            if (out_val) sc = (p.force_last && (int64_t)pos == p.n - 1) ? srow[pos] : key_to_float((uint32_t)(key >> 32));
+            if (out_val) sc = (p.force_last && (int64_t)pos == p.n - 1) ? score_at(pos) : key_to_float((uint32_t)(key >> 32));
         }
         const uint32_t incl = block_scan_incl(keep ? 1u : 0u, ws);
         if (keep) {
@@ -618,8 +635,8 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     TIDAL_REQUIRE(a->rows >= 1 && a->n >= 1 && a->k >= 1, TIDAL_ERR_ARG, "rows, n and k must be positive (rows %d n %lld k %d)",
                   a->rows, (long long)a->n, a->k);
     TIDAL_REQUIRE(a->n <= 0x7FFFFFFFll, TIDAL_ERR_ARG, "row length %lld does not fit int32 positions", (long long)a->n);
-    TIDAL_REQUIRE(a->row_stride >= a->n, TIDAL_ERR_ARG, "row_stride shorter than n");
-    TIDAL_REQUIRE(a->d_in_idx == nullptr || a->in_idx_stride == 0 || a->in_idx_stride >= a->n, TIDAL_ERR_ARG,
+    TIDAL_REQUIRE(a->seg_len > 0 || a->row_stride >= a->n, TIDAL_ERR_ARG, "row_stride shorter than n");
+    TIDAL_REQUIRE(a->seg_len > 0 || a->d_in_idx == nullptr || a->in_idx_stride == 0 || a->in_idx_stride >= a->n, TIDAL_ERR_ARG,
                   "in_idx_stride must be 0 (shared row) or at least n");
     const int k = (int64_t)a->k < a->n ? a->k : (int)a->n;
     TIDAL_REQUIRE(k <= kMaxK || (int64_t)a->k >= a->n, TIDAL_ERR_ARG, "k %d exceeds the built maximum %d", k, kMaxK);
@@ -641,11 +658,14 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     p.sel = (uint64_t*)((char*)d_ws + L->sel_off);
     p.cand_cap = L->cand_cap;
     p.status = (uint32_t*)((char*)d_ws + L->status_off);
+    p.seg_len = a->seg_len; p.seg_stride = a->seg_stride;
+    TIDAL_REQUIRE(a->seg_len >= 0, TIDAL_ERR_ARG, "negative seg_len");
+    TIDAL_REQUIRE(a->seg_len == 0 || ((int64_t)a->k < a->n && k <= kClusterMaxK && a->n <= kClusterMaxN), TIDAL_ERR_ARG,
+                  "segmented rows need k < n, k <= %d and n <= %lld", kClusterMaxK, (long long)kClusterMaxN);
     cudaStream_t st = (cudaStream_t)stream;
 
     if ((int64_t)a->k >= a->n) {
-        topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, st>>>(p, 1);
-        TIDAL_CUDA_OK(cudaGetLastError());
+        TIDAL_CUDA_OK(launch_pdl(topk_finish_kernel<true>, dim3(a->rows), dim3(kTopkThreads), 0, st, 1, p, 1));
         count_launch();
         return TIDAL_OK;
     }
@@ -658,25 +678,13 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
             TIDAL_CUDA_OK(cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kClusterSmem));
             attr_set = true;
         }
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(a->rows * cs));
-        cfg.blockDim = dim3(kTopkThreads);
-        cfg.dynamicSmemBytes = kClusterSmem;
-        cfg.stream = st;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = (unsigned)cs;
-        at[0].val.clusterDim.y = 1;
-        at[0].val.clusterDim.z = 1;
-        cfg.attrs = at;
-        cfg.numAttrs = 1;
-        TIDAL_CUDA_OK(cudaLaunchKernelEx(&cfg, topk_cluster_kernel, p));
+        TIDAL_CUDA_OK(launch_pdl(topk_cluster_kernel, dim3((unsigned)(a->rows * cs)), dim3(kTopkThreads), kClusterSmem, st,
+                                 (unsigned)cs, p));
         count_launch();
         return TIDAL_OK;
     }
     if (a->n <= kFusedMaxN) {
-        topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, st>>>(p, 0);
-        TIDAL_CUDA_OK(cudaGetLastError());
+        TIDAL_CUDA_OK(launch_pdl(topk_finish_kernel<true>, dim3(a->rows), dim3(kTopkThreads), 0, st, 1, p, 0));
         count_launch();
         return TIDAL_OK;
     }
@@ -687,15 +695,12 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     if (nblk > max_blk) nblk = max_blk;
     if (nblk < 1) nblk = 1;
     if (!a->d_hist) {
-        topk_hist_kernel<<<dim3(nblk, a->rows), kTopkThreads, 0, st>>>(p);
-        TIDAL_CUDA_OK(cudaGetLastError());
+        TIDAL_CUDA_OK(launch_pdl(topk_hist_kernel, dim3(nblk, a->rows), dim3(kTopkThreads), 0, st, 1, p));
         count_launch();
     }
-    topk_partition_kernel<<<dim3(nblk, a->rows), kTopkThreads, 0, st>>>(p);
-    TIDAL_CUDA_OK(cudaGetLastError());
+    TIDAL_CUDA_OK(launch_pdl(topk_partition_kernel, dim3(nblk, a->rows), dim3(kTopkThreads), 0, st, 1, p));
     count_launch();
-    topk_finish_kernel<false><<<a->rows, kTopkThreads, 0, st>>>(p, 0);
-    TIDAL_CUDA_OK(cudaGetLastError());
+    TIDAL_CUDA_OK(launch_pdl(topk_finish_kernel<false>, dim3(a->rows), dim3(kTopkThreads), 0, st, 1, p, 0));
     count_launch();
     return TIDAL_OK;
 }
@@ -775,6 +780,7 @@ extern "C" int tidal_topk_static(const tidal_topk_args* a, uint32_t* d_status, v
     p.sel = &sc->sel[0][0];
     p.cand_cap = kStaticCand;
     p.status = d_status ? d_status : &sc->status[0];
+    p.seg_len = 0; p.seg_stride = 0;
     topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, (cudaStream_t)stream>>>(p, (int64_t)a->k >= a->n ? 1 : 0);
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();

@@ -173,17 +173,25 @@ def topk(
     own_range: Optional[tuple] = None,
     out_count: Optional[torch.Tensor] = None,
     hist: Optional[torch.Tensor] = None,
+    segments: Optional[tuple] = None,     # (rows, seg_len, seg_stride, row_stride): rows scattered over equal blocks
 ) -> torch.Tensor:
     """Row-wise top-k index sets; see tidal_topk in include/tidal_b200.h."""
-    _need_cuda(scores, in_idx, out_idx, out_val, out_count, hist)
+    _need_cuda(out_idx, out_val, out_count, hist)
     if scores.dtype != torch.float32:
         raise RuntimeError("scores must be float32")
-    stride = scores.shape[-1]
-    rows = scores.numel() // stride
+    if segments is not None:
+        rows, seg_len, seg_stride, stride = (int(x) for x in segments)
+        if n is None:
+            raise RuntimeError("segmented rows need n")
+    else:
+        _need_cuda(scores, in_idx)
+        stride = scores.shape[-1]
+        rows = scores.numel() // stride
     n = stride if n is None else int(n)
     kk = min(int(k), n)
     if out_idx is None:
-        out_idx = torch.empty(scores.shape[:-1] + (kk,), dtype=torch.int32, device=scores.device)
+        out_idx = torch.empty((rows, kk) if segments is not None else scores.shape[:-1] + (kk,), dtype=torch.int32,
+                              device=scores.device)
     if out_idx.dtype != torch.int32:
         raise RuntimeError("out_idx must be int32")
     a = TopkArgs()
@@ -191,7 +199,9 @@ def topk(
     if in_idx is not None:
         if in_idx.dtype != torch.int32:
             raise RuntimeError("in_idx must be int32")
-        a.in_idx_stride = 0 if in_idx.dim() == 1 else in_idx.shape[-1]
+        a.in_idx_stride = stride if segments is not None else (0 if in_idx.dim() == 1 else in_idx.shape[-1])
+    if segments is not None:
+        a.seg_len, a.seg_stride = seg_len, seg_stride
     a.d_out_idx, a.d_out_val, a.out_stride = out_idx.data_ptr(), _ptr(out_val), out_idx.shape[-1]
     a.idx_offset, a.force_last = int(idx_offset), 1 if force_last else 0
     if own_range is not None:
@@ -248,13 +258,19 @@ def rope_append(
 
 
 def merge_partials(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, dtype: torch.dtype,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """LSE-merge of [shards, B, Hq(, D)] partials; see tidal_merge_partials."""
-    _need_cuda(m, l, o, out)
-    shards, B, Hq, D = o.shape
+                   out: Optional[torch.Tensor] = None, geometry: Optional[tuple] = None) -> torch.Tensor:
+    """LSE-merge of [shards, B, Hq(, D)] partials; see tidal_merge_partials.  With
+    geometry = (shards, B, Hq, D, shard_stride) the three tensors are views whose first element is
+    shard 0's block and whose shards lie shard_stride elements apart (a packed receive buffer)."""
+    if geometry is None:
+        _need_cuda(m, l, o, out)
+        shards, B, Hq, D = o.shape
+        stride = 0
+    else:
+        shards, B, Hq, D, stride = (int(x) for x in geometry)
     if out is None:
         out = torch.empty((B, Hq, D), dtype=dtype, device=o.device)
     with torch.cuda.device(o.device):
-        check(lib.tidal_merge_partials(m.data_ptr(), l.data_ptr(), o.data_ptr(), shards, B, Hq, D, out.data_ptr(),
-                                       _DTYPES[dtype], _stream()), "tidal_merge_partials")
+        check(lib.tidal_merge_partials_strided(m.data_ptr(), l.data_ptr(), o.data_ptr(), stride, shards, B, Hq, D,
+                                               out.data_ptr(), _DTYPES[dtype], _stream()), "tidal_merge_partials")
     return out

@@ -94,15 +94,26 @@ class ShardedDecodeAttention:
         self.recv = torch.zeros(self.world, L["total"], **f32)
         self.scores = torch.empty((batch, max(self.local_len, 1)) if head_reduce == "sum"
                                   else (batch, hq, max(self.local_len, 1)), **f32)
-        self.gm = torch.empty(self.world, batch, hq, **f32)
-        self.gl = torch.empty(self.world, batch, hq, **f32)
-        self.go = torch.empty(self.world, batch, hq, d, **f32)
-        self.cand_s = torch.empty(self.rows, self.world * top_k, **f32)
-        self.cand_i = torch.empty(self.rows, self.world * top_k, dtype=torch.int32, device=device)
         self.sel_local = torch.zeros(self.rows, top_k, dtype=torch.int32, device=device)
         self.sel_count = torch.zeros(self.rows, dtype=torch.int32, device=device)
         self.sel_global = torch.zeros(self.rows, top_k, dtype=torch.int32, device=device)
         self.out = torch.empty(batch, hq, d, dtype=dtype, device=device)
+        # views of rank 0's block inside the receive buffer: the merge and the candidate top-k read
+        # all ranks' blocks in place, L["total"] words apart
+        flat = self.recv.view(-1)
+        self._rm, self._rl, self._ro = flat[L["m"]:], flat[L["l"]:], flat[L["o"]:]
+        self._rcs, self._rci = flat[L["cs"]:], flat.view(torch.int32)[L["ci"]:]
+        self._partial_geom = (self.world, batch, hq, d, L["total"])
+        # one rank: its block is the whole row, plain addressing (and k == n selects everything)
+        self._cand_segments = (self.rows, top_k, L["total"], top_k) if self.world > 1 else None
+        if self.world == 1:
+            self._rcs = self._rcs[: self.rows * top_k].view(self.rows, top_k)
+            self._rci = self._rci[: self.rows * top_k].view(self.rows, top_k)
+        if self.local_len < top_k:
+            # fewer local tokens than candidates: the unused slots stay at -inf / 0 for good
+            _, _, _, cs, ci = self._send_views()
+            cs.fill_(-float("inf"))
+            ci.zero_()
 
     # views into the send buffer
     def _send_views(self):
@@ -117,23 +128,22 @@ class ShardedDecodeAttention:
         else:
             dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
 
-    def _unpack_partials(self):
-        L, B, Hq, D = self.layout, self.B, self.Hq, self.D
-        r = self.recv
-        self.gm.copy_(r[:, L["m"]:L["l"]].reshape(self.world, B, Hq))
-        self.gl.copy_(r[:, L["l"]:L["o"]].reshape(self.world, B, Hq))
-        self.go.copy_(r[:, L["o"]:L["cs"]].reshape(self.world, B, Hq, D))
-
     def selection_layer(self, q: torch.Tensor, kv_local: torch.Tensor, pages_per_seq: Optional[int] = None,
-                        page_table: Optional[torch.Tensor] = None, want_global: bool = False) -> torch.Tensor:
-        """q [B,Hq,D]; kv_local: this rank's pool holding positions [lo, hi) of every sequence."""
+                        page_table: Optional[torch.Tensor] = None, want_global: bool = False,
+                        timing: Optional[list] = None) -> torch.Tensor:
+        """q [B,Hq,D]; kv_local: this rank's pool holding positions [lo, hi) of every sequence.
+        timing: a list that receives a (start, end) CUDA-event pair around the local attention."""
         ops, k = self.ops, self.k
         m, l, o, cs, ci = self._send_views()
-        cs.fill_(-float("inf"))
-        ci.zero_()
         if self.local_len > 0:
+            if timing is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
             ops.decode_attention(q, kv_local, self.local_len, self.ws, page_table=page_table, pages_per_seq=pages_per_seq,
                                  scores=self.scores, hist=self.ws.hist[: self.rows], partials=(m, l, o), want_out=False)
+            if timing is not None:
+                e1.record()
+                timing.append((e0, e1))
             ops.topk(self.scores, k, self.ws, n=self.local_len, out_idx=ci, out_val=cs, idx_offset=self.lo,
                      hist=self.ws.hist[: self.rows])
         else:
@@ -141,19 +151,14 @@ class ShardedDecodeAttention:
             l.zero_()
             o.zero_()
         self._all_gather()
-        self._unpack_partials()
-        ops.merge_partials(self.gm, self.gl, self.go, self.dtype, out=self.out)
-        L, R = self.layout, self.rows
-        # [world][rows][k] -> [rows][world*k]
-        self.cand_s.view(R, self.world, k).copy_(self.recv[:, L["cs"]:L["ci"]].reshape(self.world, R, k).permute(1, 0, 2))
-        self.cand_i.view(R, self.world, k).copy_(
-            self.recv[:, L["ci"]:L["total"]].view(torch.int32).reshape(self.world, R, k).permute(1, 0, 2))
-        # global set (for callers that want it) and the part of it this rank owns
+        ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
+        # global top-k of the world*k candidates, read in place; keep the positions this rank owns
+        n_cand = self.world * k
         if want_global:
-            ops.topk(self.cand_s, self.k_global, self.ws, in_idx=self.cand_i, out_idx=self.sel_global)
-        ops.topk(self.cand_s, self.k_global, self.ws, in_idx=self.cand_i, out_idx=self.sel_local,
-                 own_range=(self.lo, max(self.hi, self.lo + 1)) if self.local_len > 0 else (self.lo, self.lo + 1),
-                 out_count=self.sel_count)
+            ops.topk(self._rcs, self.k_global, self.ws, n=n_cand, in_idx=self._rci, out_idx=self.sel_global,
+                     segments=self._cand_segments)
+        ops.topk(self._rcs, self.k_global, self.ws, n=n_cand, in_idx=self._rci, out_idx=self.sel_local,
+                 own_range=(self.lo, max(self.hi, self.lo + 1)), out_count=self.sel_count, segments=self._cand_segments)
         if self.local_len == 0:
             self.sel_count.zero_()
         return self.out
@@ -167,8 +172,7 @@ class ShardedDecodeAttention:
         ops.decode_attention(q, kv_local, max(self.local_len, 1), self.ws, page_table=page_table, pages_per_seq=pages_per_seq,
                              sel_idx=sel, sel_counts=cnt, partials=(m, l, o), want_out=False)
         self._all_gather()
-        self._unpack_partials()
-        return ops.merge_partials(self.gm, self.gl, self.go, self.dtype, out=self.out)
+        return ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
 
     def selected_global(self) -> torch.Tensor:
         """[B, k] or [B, Hq, k] global positions chosen by the last selection layer."""
