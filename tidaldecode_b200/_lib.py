@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtidal_b200.so")
+# TIDAL_B200_LIB names another build of the same library (e.g. one compiled with extra -D flags)
+LIB_PATH = os.environ.get("TIDAL_B200_LIB") or os.path.join(_HERE, "libtidal_b200.so")
 
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 ERR_ARG, ERR_WORKSPACE, ERR_CUDA = -1, -2, -3

@@ -41,6 +41,17 @@ struct AttnParams {
 
 __host__ __device__ inline size_t round16(size_t x) { return (x + 15) & ~(size_t)15; }
 
+// Head-summed logits are reduced across the CTA's heads once per "super-block" of R stages, not
+// per stage: slots park their per-head logits in shared memory [2][R*T][HC] (double-buffered, so one
+// named barrier per super-block is enough) and all consumer threads then sum, store and count them.
+__host__ __device__ inline int score_block_stages(int T, int HC) {
+    int r = 2048 / (T * HC);          // 8 KB per buffer
+    return r < 1 ? 1 : (r > 16 ? 16 : r);
+}
+__host__ __device__ inline size_t score_smem_bytes(int T, int HC) {
+    return round16((size_t)2 * score_block_stages(T, HC) * T * HC * sizeof(float));
+}
+
 // Tensor-core kernel (decode_attn_mma.cu): 16-bit storage, up to 16 query heads per
 // KV head, HC in {1,2,4,8} KV heads per CTA, 8 consumer warps.
 constexpr int kMmaWarps = 8;

@@ -67,7 +67,7 @@ size_t attn_mma_smem_bytes(int S, int HC, int D, bool sum_heads) {
     const size_t stage = (size_t)S * 2 * T * mma_pitch(HC, D);
     const size_t ep = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float);
     const size_t main_bytes = round16(stage > ep ? stage : ep);
-    const size_t sc = sum_heads ? round16((size_t)S * T * HC * sizeof(float)) : 0;
+    const size_t sc = sum_heads ? score_smem_bytes(T, HC) : 0;
     return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
 }
 
@@ -87,8 +87,9 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     const bool want_scores = p.scores != nullptr;
     const bool sum_heads = want_scores && p.score_rows == 1;
     unsigned char* stage_base = smem;
-    float* sc_smem = reinterpret_cast<float*>(smem + main_bytes);                      // [S][TT][HC]
-    const size_t sc_bytes = sum_heads ? round16((size_t)S * TT * HC * sizeof(float)) : 0;
+    float* sc_smem = reinterpret_cast<float*>(smem + main_bytes);                      // [2][R*TT][HC]
+    const size_t sc_bytes = sum_heads ? score_smem_bytes(TT, HC) : 0;
+    const int R = score_block_stages(TT, HC);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + main_bytes + sc_bytes);
     uint64_t* empty_bar = full_bar + S;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
@@ -233,7 +234,7 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
         const int mine = min(kMmaTile, valid - tbase);          // valid tokens of this warp's tile (may be <= 0)
         const uint32_t kst = smem_u32(stage_base + (size_t)s * 2 * TT * pitch);
         const uint32_t vst = kst + (uint32_t)(TT * pitch);
-        float* sc = sc_smem + (size_t)s * TT * HC;
+        float* sc = sc_smem + ((size_t)((it / R) & 1) * R + (it % R)) * TT * HC;   // this stage's rows of the super-block
         if (mine > 0) {
             // ---- S = Q K^T for 16 tokens: two n-tiles of 8
             float sf[2][4];
@@ -350,19 +351,27 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
                 M::mma(o[2 * np + 1], pa, bv[2], bv[3]);
             }
         }
-        if (sum_heads) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[s]);          // the stage is free: the logits wait in their own buffer
+        if (sum_heads && ((it % R) == R - 1 || it == n_iters - 1)) {
+            // head sum in a fixed order for the whole super-block: 8 lanes per token, each adds every 8th
+            // head, then a butterfly; one thread per token stores the logit and counts its first radix digit
             named_bar_sync(1, consumer_threads);
-            for (int base = 0; base < TT; base += consumer_threads / 8) {
-                const int t = base + (ctid >> 3), j = ctid & 7;
-                const bool in = t < TT;
+            const int sb = it / R;
+            const float* blk = sc_smem + (size_t)(sb & 1) * R * TT * HC;
+            const int rows = ((it % R) + 1) * TT;
+            const int first = sb * R * TT;                  // token index (within the chunk) of row 0
+            for (int base = 0; base < rows; base += consumer_threads / 8) {   // uniform per warp
+                const int r = base + (ctid >> 3), j = ctid & 7;
+                const bool in = r < rows && first + r < ntok;
                 float a = 0.f;
-                if (in && t < valid)
-                    for (int h = j; h < HC; h += 8) a += sc[t * HC + h];
+                if (in)
+                    for (int h = j; h < HC; h += 8) a += blk[r * HC + h];
                 a += __shfl_xor_sync(0xffffffffu, a, 4);
                 a += __shfl_xor_sync(0xffffffffu, a, 2);
                 a += __shfl_xor_sync(0xffffffffu, a, 1);
-                if (j == 0 && in && t < valid) {
-                    const int pos = tok0 + it * TT + t;
+                if (j == 0 && in) {
+                    const int pos = tok0 + first + r;
                     p.scores[(size_t)b * p.score_stride + pos] = a;
                     if (p.hist) {
                         uint32_t bin = ordered_key(a) >> kDigit0Shift;
@@ -372,8 +381,6 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty_bar[s]);
     }
 
     // ---------------------------------------------------------------- epilogue
