@@ -22,7 +22,7 @@ namespace tidal {
 __host__ __device__ inline size_t attn_smem_bytes(int S, int T, int row_bytes, int HC, int CW, int slots, int hps,
                                                   int G, int D, bool want_scores) {
     size_t stage = (size_t)S * 2 * T * row_bytes;
-    size_t ep = (size_t)slots * hps * G * (D + 2) * sizeof(float);
+    size_t ep = (size_t)slots * hps * G * (D + 2) * sizeof(float) + cta_result_bytes(HC, G, D);
     size_t main_bytes = round16(stage > ep ? stage : ep);
     size_t sc = want_scores ? score_smem_bytes(T, HC) : 0;
     return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
@@ -51,7 +51,10 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     const int slots = p.CW * SPW;
     const size_t stage_bytes = (size_t)S * 2 * TT * row_bytes;
     const size_t ep_bytes = (size_t)slots * HPS * G * (D + 2) * sizeof(float);
-    const size_t main_bytes = round16(stage_bytes > ep_bytes ? stage_bytes : ep_bytes);
+    const size_t main_bytes = round16(stage_bytes > ep_bytes + cta_result_bytes(p.HC, G, D) ? stage_bytes
+                                                                                             : ep_bytes + cta_result_bytes(p.HC, G, D));
+    float* cta_o = reinterpret_cast<float*>(smem + ep_bytes);                      // [HC*G][D], then [HC*G][2]
+    float* cta_ml = cta_o + (size_t)p.HC * G * D;
     const bool want_scores = p.scores != nullptr;
     const bool sum_heads = want_scores && p.score_rows == 1;
     unsigned char* stage_base = smem;
@@ -155,9 +158,7 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
                     if (mbar_try_wait(&full_bar[s], (it / S) & 1)) break;
             }
         }
-        return;
-    }
-
+    } else {
     // ================================================================= consumers
     const int cw = warp - 1;
     const int slot = cw * SPW + lane / LPR;
@@ -371,25 +372,14 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
             acc = fmaf(w, ep_o[(size_t)e * D + d], acc);
             L = fmaf(w, ep_ml[2 * e + 1], L);
         }
-        const int hq = qh0 + hl * G + g;
-        const size_t ph = (size_t)b * p.Hq + hq;
-        if (p.nchunks == 1) {
-            if (p.o) reinterpret_cast<T*>(p.o)[ph * D + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
-            if (p.shard_o) {
-                p.shard_o[ph * D + d] = acc;
-                if (d == 0) {
-                    p.shard_m[ph] = M;
-                    p.shard_l[ph] = L;
-                }
-            }
-        } else {
-            p.part_o[(ph * p.nchunks + chunk) * D + d] = acc;
-            if (d == 0) {
-                p.part_ml[(ph * p.nchunks + chunk) * 2] = M;
-                p.part_ml[(ph * p.nchunks + chunk) * 2 + 1] = L;
-            }
+        cta_o[idx] = acc;
+        if (d == 0) {
+            cta_ml[2 * hg] = M;
+            cta_ml[2 * hg + 1] = L;
         }
     }
+    }   // consumers
+    store_attention_result<T>(p, cta_o, cta_ml, HC, G, D, qh0, b, chunk);
 }
 
 // Merge the split-KV partials of one (sequence, q head): grid (Hq, B), block
@@ -537,7 +527,7 @@ static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t s
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
     dim3 grid(plan.nchunks, plan.nslices, p.B);
     dim3 block((plan.CW + 1) * 32);
-    TIDAL_CUDA_OK(launch_pdl(kern, grid, block, plan.smem, st, 1, p));
+    TIDAL_CUDA_OK(launch_pdl(kern, grid, block, plan.smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
 }
@@ -634,69 +624,84 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     // Tensor cores where the query group makes q.K^T a tile contraction: 16-bit storage and
     // 2..16 query heads per KV head.  use_tensor_cores: 0 = this rule, 1 = whenever the
     // kernel can run (G = 1 included), -1 = never.
+    const bool want_mma = es == 2 && kernel_G <= 16 && a->use_tensor_cores >= 0 && (kernel_G >= 2 || a->use_tensor_cores > 0);
+    const int max_cw = kernel_G >= 4 ? 8 : 16;   // the CUDA-core kernel's launch bound
     bool use_mma = false;
-    if (es == 2 && kernel_G <= 16 && a->use_tensor_cores >= 0 && (kernel_G >= 2 || a->use_tensor_cores > 0)) {
-        int hc = per_head ? 1 : 0;
-        if (!hc) {
-            if (sum_heads) {
-                hc = a->num_kv_heads;
-            } else if (a->heads_per_cta > 0) {
-                hc = a->heads_per_cta;
-            } else {
-                for (int c : {8, 4, 2, 1})
-                    if (a->num_kv_heads % c == 0) { hc = c; break; }
-            }
-        }
-        if ((hc == 1 || hc == 2 || hc == 4 || hc == 8) && (per_head || a->num_kv_heads % hc == 0)) {
-            use_mma = true;
-            plan.HC = hc;
-            plan.nslices = per_head ? a->num_qo_heads : a->num_kv_heads / hc;
+    // Geometry for `hc` KV heads per CTA on the chosen kernel; false if that kernel cannot take it.
+    auto set_heads = [&](int hc, bool mma) -> bool {
+        if (hc < 1 || (!per_head && a->num_kv_heads % hc != 0)) return false;
+        if (mma) {
+            if (!(hc == 1 || hc == 2 || hc == 4 || hc == 8)) return false;
             plan.CW = kMmaWarps; plan.HPS = 1; plan.TG = kMmaWarps / hc;
             plan.T = kMmaTile * plan.TG;
+        } else {
+            if (!plan_slots(hc, lpr, kernel_G == 1, max_cw, &plan.CW, &plan.HPS, &plan.TG)) return false;
+            plan.T = plan.TG * attn_tps(kernel_G);
         }
+        plan.HC = hc;
+        plan.nslices = per_head ? a->num_qo_heads : a->num_kv_heads / hc;
+        return true;
+    };
+    int hc0;                                        // preferred KV heads per CTA
+    if (per_head) hc0 = 1;
+    else if (sum_heads) hc0 = a->num_kv_heads;      // the head sum of the logits is formed inside one CTA
+    else if (a->heads_per_cta > 0) hc0 = a->heads_per_cta;
+    else hc0 = 0;
+    if (want_mma) {
+        if (hc0) use_mma = set_heads(hc0, true);
+        else
+            for (int c : {8, 4, 2, 1})
+                if ((use_mma = set_heads(c, true))) break;
     }
     TIDAL_REQUIRE(use_mma || a->use_tensor_cores <= 0, TIDAL_ERR_ARG,
                   "tensor-core attention needs f16/bf16, at most 16 query heads per KV head and 1, 2, 4 or 8 KV heads per CTA");
     if (!use_mma) {
-        if (per_head) {
-            plan.HC = 1;
-            plan.nslices = a->num_qo_heads;
-        } else {
-            plan.HC = a->heads_per_cta > 0 ? a->heads_per_cta : a->num_kv_heads;
-            // rows of 4 KB stream a little faster than rows of 8 KB (measured 88.7 vs 92.8 us at 32 x 128 fp16);
-            // the head sum of the logits needs all heads in one CTA
-            if (a->heads_per_cta <= 0 && a->num_kv_heads % 2 == 0 && a->num_kv_heads * D * es >= 8192) plan.HC = a->num_kv_heads / 2;
-            if (sum_heads) plan.HC = a->num_kv_heads;
-            TIDAL_REQUIRE(a->num_kv_heads % plan.HC == 0, TIDAL_ERR_ARG, "heads_per_cta %d does not divide num_kv_heads %d",
-                          plan.HC, a->num_kv_heads);
-            plan.nslices = a->num_kv_heads / plan.HC;
-        }
-        const int max_cw = kernel_G >= 4 ? 8 : 16;   // the kernel's launch bound
-        if (!plan_slots(plan.HC, lpr, kernel_G == 1, max_cw, &plan.CW, &plan.HPS, &plan.TG)) {
+        int hc = hc0 ? hc0 : a->num_kv_heads;
+        // rows of 4 KB stream a little faster than rows of 8 KB (measured 88.7 vs 92.8 us at 32 x 128 fp16)
+        if (!hc0 && a->num_kv_heads % 2 == 0 && a->num_kv_heads * D * es >= 8192) hc = a->num_kv_heads / 2;
+        TIDAL_REQUIRE(per_head || a->num_kv_heads % hc == 0, TIDAL_ERR_ARG, "heads_per_cta %d does not divide num_kv_heads %d", hc,
+                      a->num_kv_heads);
+        if (!set_heads(hc, false)) {
             // fall back to one KV head per CTA unless the head sum must stay in one CTA
             TIDAL_REQUIRE(!sum_heads, TIDAL_ERR_ARG, "head-summed logits need num_kv_heads in {1,2,4,...,%d} for this head_dim/dtype, got %d",
                           16 * (32 / lpr) * (kernel_G == 1 ? 2 : 1), a->num_kv_heads);
-            plan.HC = 1;
-            plan.nslices = a->num_kv_heads;
-            plan_slots(1, lpr, false, max_cw, &plan.CW, &plan.HPS, &plan.TG);
+            set_heads(1, false);
         }
-        plan.T = plan.TG * attn_tps(kernel_G);
+    }
+    // Short token lists (sparse layers): the whole list is covered by ONE cluster of up to 8 CTAs per
+    // (sequence, head slice), which merges through distributed shared memory and writes the result
+    // itself — no partials in global memory, no merge launch.  Heads are split over more CTAs until
+    // about half the SMs are busy.
+    int cluster = 1;
+    const size_t list_bytes = (size_t)ntok * 2 * a->num_kv_heads * D * es;
+    if (sel && a->num_chunks == 0 && ntok >= 1 && list_bytes <= ((size_t)8 << 20)) {
+        if (!hc0) {
+            int hc = plan.HC;
+            while (hc > 1 && a->batch * plan.nslices * 8 < 64 && set_heads(hc / 2, use_mma)) hc = plan.HC;
+        }
+        const int per_cta = (int)((64 * 1024) / (2 * (size_t)plan.HC * D * es)) > 0 ? (int)((64 * 1024) / (2 * (size_t)plan.HC * D * es)) : 1;
+        cluster = 8;
+        while (cluster > 1 && ntok < cluster * per_cta / 2) cluster >>= 1;     // at least half a stage-load per CTA
     }
     const int row_bytes = plan.HC * D * es;
     // a chunk should move at least ~64 KB so that its pipeline fills
     int min_tok = (64 * 1024) / (2 * row_bytes);
     if (min_tok < 1) min_tok = 1;
-    plan.nchunks = a->num_chunks > 0 ? a->num_chunks
-                                     : tidal_plan_chunks(a->batch, plan.nslices, ntok, min_tok, sm_count_cached());
+    if (cluster > 1) plan.nchunks = cluster;
+    else plan.nchunks = a->num_chunks > 0 ? a->num_chunks
+                                          : tidal_plan_chunks(a->batch, plan.nslices, ntok, min_tok, sm_count_cached());
     TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
                   plan.nchunks, kMaxChunks);
     const int slots = plan.CW * (32 / lpr);
     auto smem_of = [&](int S) {
-        return use_mma ? attn_mma_smem_bytes(S, plan.HC, D, sum_heads)
+        return use_mma ? attn_mma_smem_bytes(S, plan.HC, kernel_G, D, sum_heads)
                        : attn_smem_bytes(S, plan.T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads);
     };
     int S = 8;
     while (S > 1 && smem_of(S) > kSmemBudget) --S;
+    // no more stages than the longest chunk can use (short lists: less shared memory to set up)
+    const int iters = ((ntok + plan.nchunks - 1) / plan.nchunks + plan.T - 1) / plan.T;
+    if (S > iters) S = iters < 1 ? 1 : iters;
     plan.S = S;
     plan.smem = smem_of(S);
     TIDAL_REQUIRE(plan.smem <= 227 * 1024, TIDAL_ERR_ARG, "shared memory %zu exceeds 227 KB (row %d bytes)", plan.smem, row_bytes);
@@ -718,9 +723,9 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     p.num_pages = a->num_pages;
     p.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)D);
     p.nchunks = plan.nchunks; p.HC = plan.HC; p.greal = G; p.per_head = per_head ? 1 : 0;
-    p.T = plan.T; p.S = plan.S; p.TG = plan.TG; p.CW = plan.CW;
+    p.T = plan.T; p.S = plan.S; p.TG = plan.TG; p.CW = plan.CW; p.cluster = cluster;
     const size_t part_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * D;
-    TIDAL_REQUIRE(plan.nchunks == 1 || L->part_o_off + part_need <= L->part_ml_off, TIDAL_ERR_WORKSPACE,
+    TIDAL_REQUIRE(plan.nchunks == 1 || cluster > 1 || L->part_o_off + part_need <= L->part_ml_off, TIDAL_ERR_WORKSPACE,
                   "workspace was sized for a smaller batch/heads/head_dim than this call");
 
     cudaStream_t st = (cudaStream_t)stream;
@@ -735,7 +740,7 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
         }
     }
     if (rc != TIDAL_OK) return rc;
-    if (plan.nchunks > 1) {
+    if (plan.nchunks > 1 && cluster == 1) {
         switch (a->dtype) {
             case TIDAL_DTYPE_F16: rc = launch_merge<__half>(p, D, st); break;
             case TIDAL_DTYPE_BF16: rc = launch_merge<__nv_bfloat16>(p, D, st); break;

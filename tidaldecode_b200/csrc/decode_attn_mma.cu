@@ -62,10 +62,10 @@ struct Mma16<__nv_bfloat16> {
 
 __host__ __device__ inline int mma_pitch(int HC, int D) { return HC * D * 2 + 16; }
 
-size_t attn_mma_smem_bytes(int S, int HC, int D, bool sum_heads) {
+size_t attn_mma_smem_bytes(int S, int HC, int G, int D, bool sum_heads) {
     const int T = kMmaTile * (kMmaWarps / HC);
     const size_t stage = (size_t)S * 2 * T * mma_pitch(HC, D);
-    const size_t ep = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float);
+    const size_t ep = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float) + cta_result_bytes(HC, G, D);
     const size_t main_bytes = round16(stage > ep ? stage : ep);
     const size_t sc = sum_heads ? score_smem_bytes(T, HC) : 0;
     return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
@@ -82,8 +82,12 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     const int pitch = mma_pitch(HC, D);
     const int row_bytes = HC * D * 2;
     const size_t stage_bytes = (size_t)S * 2 * TT * pitch;
+    const int G = p.per_head ? 1 : p.greal;
     const size_t ep_bytes = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float);
-    const size_t main_bytes = round16(stage_bytes > ep_bytes ? stage_bytes : ep_bytes);
+    const size_t main_bytes = round16(stage_bytes > ep_bytes + cta_result_bytes(HC, G, D) ? stage_bytes
+                                                                                           : ep_bytes + cta_result_bytes(HC, G, D));
+    float* cta_o = reinterpret_cast<float*>(smem + ep_bytes);                          // [HC*G][D], then [HC*G][2]
+    float* cta_ml = cta_o + (size_t)HC * G * D;
     const bool want_scores = p.scores != nullptr;
     const bool sum_heads = want_scores && p.score_rows == 1;
     unsigned char* stage_base = smem;
@@ -96,7 +100,6 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
 
     const int chunk = blockIdx.x, slice = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = p.per_head ? 1 : p.greal;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -192,9 +195,7 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
                     if (mbar_try_wait(&full_bar[s], (it / S) & 1)) break;
             }
         }
-        return;
-    }
-
+    } else {
     // ================================================================= consumers
     const int cw = warp - 1;
     const int head_local = cw % HC, tg = cw / HC;
@@ -419,32 +420,21 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
             acc = fmaf(w, ep_o[e * D + d], acc);
             L = fmaf(w, ep_ml[e * 2 + 1], L);
         }
-        const int hq = qh0 + hl * G + g;
-        const size_t ph = (size_t)b * p.Hq + hq;
-        if (p.nchunks == 1) {
-            if (p.o) reinterpret_cast<T*>(p.o)[ph * D + d] = from_f32<T>(L > 0.f ? acc / L : 0.f);
-            if (p.shard_o) {
-                p.shard_o[ph * D + d] = acc;
-                if (d == 0) {
-                    p.shard_m[ph] = Mx;
-                    p.shard_l[ph] = L;
-                }
-            }
-        } else {
-            p.part_o[(ph * p.nchunks + chunk) * D + d] = acc;
-            if (d == 0) {
-                p.part_ml[(ph * p.nchunks + chunk) * 2] = Mx;
-                p.part_ml[(ph * p.nchunks + chunk) * 2 + 1] = L;
-            }
+        cta_o[idx] = acc;
+        if (d == 0) {
+            cta_ml[2 * hg] = Mx;
+            cta_ml[2 * hg + 1] = L;
         }
     }
+    }   // consumers
+    store_attention_result<T>(p, cta_o, cta_ml, HC, G, D, qh0, b, chunk);
 }
 
 template <typename T, int D>
 static int launch_one(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     auto kern = decode_attn_mma_kernel<T, D>;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 1) * 32), smem, st, 1, p));
+    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 1) * 32), smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
 }
