@@ -207,7 +207,7 @@ def run_ours(args, rank, world, device):
             dist.barrier()
         torch.cuda.synchronize()
 
-    use_graph = args.graph == 1 or (args.graph < 0 and world > 1)
+    use_graph = args.graph != 0
     graphs = {}
 
     def step_graph(i, e2e):
@@ -290,6 +290,47 @@ def run_ours(args, rank, world, device):
         roof = {"bound": "hbm", "kernel": "decode_attn_kernel (selection layer: K,V streamed once, fp32 logits written)",
                 "achieved": round(ach, 1), "peak": hbm, "peak_source": which, "unit": "GB/s", "frac": round(ach / hbm, 4),
                 "algorithmic_bytes": alg, "us_per_launch": round(sel_ms * 1e3, 2), "traffic": None}
+    per_layer = None
+    if sh is None:
+        # steady-state device time of each layer type: 2*pairs back-to-back launches (distinct pools) replayed as a graph
+        def op_us(fn, reps=2 * pairs, iters=10):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for i in range(reps):
+                    fn(i % (2 * pairs))
+            g.replay()
+            torch.cuda.synchronize()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                g.replay()
+            b_.record()
+            torch.cuda.synchronize()
+            return round(a.elapsed_time(b_) * 1e3 / (reps * iters), 2)
+
+        kn = torch.randn(B, Hkv, D, device=device).to(dtype)
+        vn = torch.randn(B, Hkv, D, device=device).to(dtype)
+        qr = q_dev[0].clone()
+
+        def sel_layer(i):
+            T.decode_attention(q_dev[i], pools[i], n_loc, ws, pages_per_seq=n_loc, scores=scores, hist=ws.hist, out=o_sel)
+            T.topk(scores, k, ws, out_idx=idx, hist=ws.hist)
+
+        per_layer = {
+            "full_attention": op_us(lambda i: T.decode_attention(q_dev[i], pools[i], n_loc, ws, pages_per_seq=n_loc, out=o_sel)),
+            "selection_attention_plus_topk": op_us(sel_layer),
+            "sparse_attention": op_us(lambda i: T.decode_attention(q_dev[i], pools[i], n_loc, ws, pages_per_seq=n_loc,
+                                                                    sel_idx=idx, out=o_sp), reps=8 * pairs),
+            "rope_append": op_us(lambda i: T.rope_append(qr, kn, vn, pools[i], batch=B, pos0=n_loc - 1, rope_mode=2,
+                                                         rope_theta=1e4), reps=8 * pairs),
+            "note": "steady-state device time per launch group, back-to-back launches on distinct layer pools replayed as a CUDA graph",
+        }
+        full_bytes = bytes_kv_layer
+        per_layer["full_attention_frac_of_hbm_peak"] = round(full_bytes / (per_layer["full_attention"] * 1e-6) / 1e9 / peaks()[0], 4)
+        per_layer["selection_frac_of_hbm_peak"] = round((bytes_kv_layer + 4 * B * n_loc) / (per_layer["selection_attention_plus_topk"] * 1e-6) / 1e9 / peaks()[0], 4)
+        sparse_bytes = 2 * B * k * Hkv * D * es + 4 * B * k
+        per_layer["sparse_frac_of_hbm_peak"] = round(sparse_bytes / (per_layer["sparse_attention"] * 1e-6) / 1e9 / peaks()[0], 4)
+        assert ws.status() == 0
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -303,10 +344,13 @@ def run_ours(args, rank, world, device):
         "clocks": cs.summary(),
     }
     if use_graph:
-        line["config"]["launch"] = "each step replayed as one CUDA graph (kernels + NCCL all-gathers); roofline kernel timed in an eager pass"
+        line["config"]["launch"] = ("each step is the public operator calls captured once into a CUDA graph and replayed "
+                                    "(kernels, copies, NCCL all-gathers); the roofline kernel is timed with CUDA events in an eager pass over the same steps")
 
     if roof:
         line["roofline"] = roof
+    if per_layer:
+        line["us_per_layer"] = per_layer
     return line
 
 
@@ -358,7 +402,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--graph", type=int, default=-1, help="1: replay each step as a CUDA graph; 0: never; default: when N > 1")
+    ap.add_argument("--graph", type=int, default=-1, help="replay each step as one CUDA graph (default); 0: issue every launch from the host")
     ap.add_argument("--layer-pairs", type=int, default=0, help="distinct (selection, sparse) KV pool pairs to rotate over")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

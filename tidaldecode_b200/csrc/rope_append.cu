@@ -23,8 +23,9 @@ struct RopeParams {
     uint32_t* status;
 };
 
+// cs[i] = (cos, sin) of the token's angle for frequency index i < D/2, already rounded to T in mode 1.
 template <typename T, int D>
-__device__ __forceinline__ void rotate_vec(const T* row, int d0, float pos, const RopeParams& p, float* out) {
+__device__ __forceinline__ void rotate_vec(const T* row, int d0, const float2* cs, int rope_mode, float* out) {
     using V = Vec16<T>;
     constexpr int VEC = V::N;
     constexpr int HALF = D / 2;
@@ -33,16 +34,12 @@ __device__ __forceinline__ void rotate_vec(const T* row, int d0, float pos, cons
     const int d1 = d0 < HALF ? d0 + HALF : d0 - HALF;
     V::to_float(*reinterpret_cast<const uint4*>(row + d1), y);
     const float sign = d0 < HALF ? -1.f : 1.f;
+    const int f0 = d0 % HALF;                    // a 16-byte vector never straddles the two halves
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
-        const int fi = (d0 + i) % HALF;
-        const float inv = p.inv_freq ? p.inv_freq[fi] : 1.0f / powf(p.theta, (float)(2 * fi) / (float)D);
-        const float ang = (pos / p.scale) * inv;
-        float c = cosf(ang), s = sinf(ang);
-        if (p.rope_mode == 1) {
-            // reference-model order: cos/sin rounded to T, each product rounded, then the sum
-            c = V::round(c);
-            s = V::round(s);
+        const float c = cs[f0 + i].x, s = cs[f0 + i].y;
+        if (rope_mode == 1) {
+            // reference-model order: each product rounded to T, then the sum
             out[i] = V::round(__fadd_rn(V::round(__fmul_rn(x[i], c)), V::round(__fmul_rn(sign * y[i], s))));
         } else {
             out[i] = x[i] * c + sign * y[i] * s;
@@ -55,12 +52,26 @@ __global__ void rope_append_kernel(const RopeParams p) {
     using V = Vec16<T>;
     constexpr int VEC = V::N;
     constexpr int VPR = D / VEC;  // vectors per row
+    __shared__ float2 cs[D / 2];
     pdl_wait();
     pdl_launch_dependents();
     const int tok = blockIdx.x;
     const int b = tok / p.tokens_per_seq;
     const int tpos = (p.pos0_dev ? p.pos0_dev[b] : p.pos0) + tok % p.tokens_per_seq;
-    const float posf = (float)tpos;
+    // The angle depends on the position and the frequency index only: D/2 threads evaluate the
+    // transcendental functions once, all heads then rotate from the table.
+    if (p.rope_mode != 0 && threadIdx.x < D / 2) {
+        const int fi = threadIdx.x;
+        const float inv = p.inv_freq ? p.inv_freq[fi] : 1.0f / powf(p.theta, (float)(2 * fi) / (float)D);
+        const float ang = ((float)tpos / p.scale) * inv;
+        float c = cosf(ang), s = sinf(ang);
+        if (p.rope_mode == 1) {       // the reference model rounds cos and sin to the storage type first
+            c = V::round(c);
+            s = V::round(s);
+        }
+        cs[fi] = make_float2(c, s);
+    }
+    __syncthreads();
 
     char* kdst = nullptr;
     size_t plane = 0;
@@ -92,7 +103,7 @@ __global__ void rope_append_kernel(const RopeParams p) {
         const T* row = is_q ? reinterpret_cast<const T*>(p.q) + ((size_t)tok * p.Hq + h) * D
                             : reinterpret_cast<const T*>(p.k) + ((size_t)tok * p.Hkv + h) * D;
         if (p.rope_mode != 0) {
-            rotate_vec<T, D>(row, d0, posf, p, res[cnt]);
+            rotate_vec<T, D>(row, d0, cs, p.rope_mode, res[cnt]);
         } else {
             V::to_float(*reinterpret_cast<const uint4*>(row + d0), res[cnt]);
         }
