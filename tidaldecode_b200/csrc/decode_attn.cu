@@ -24,7 +24,7 @@ __host__ __device__ inline size_t attn_smem_bytes(int S, int T, int row_bytes, i
     size_t stage = (size_t)S * 2 * T * row_bytes;
     size_t ep = (size_t)slots * hps * G * (D + 2) * sizeof(float) + cta_result_bytes(HC, G, D);
     size_t main_bytes = round16(stage > ep ? stage : ep);
-    size_t sc = want_scores ? score_smem_bytes(T, HC) : 0;
+    size_t sc = want_scores ? score_smem_bytes(T, HC) + sizeof(uint32_t) * TIDAL_TOPK_BINS : 0;
     return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
 }
 
@@ -59,7 +59,8 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     const bool sum_heads = want_scores && p.score_rows == 1;
     unsigned char* stage_base = smem;
     float* sc_smem = reinterpret_cast<float*>(smem + main_bytes);                  // [2][R*T][HC]
-    const size_t sc_bytes = sum_heads ? score_smem_bytes(TT, HC) : 0;
+    const size_t sc_bytes = sum_heads ? score_smem_bytes(TT, HC) + sizeof(uint32_t) * TIDAL_TOPK_BINS : 0;
+    uint32_t* sh_hist = reinterpret_cast<uint32_t*>(smem + main_bytes + score_smem_bytes(TT, HC));   // CTA-local digit counts
     const int R = score_block_stages(TT, HC);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + main_bytes + sc_bytes);
     uint64_t* empty_bar = full_bar + S;
@@ -100,6 +101,8 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (sum_heads && p.hist)
+        for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x) sh_hist[i] = 0;
     __syncthreads();
 
     if (warp == 0) {
@@ -324,11 +327,16 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
                     if (p.hist) {
                         uint32_t bin = ordered_key(a) >> kDigit0Shift;
                         if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
-                        atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + bin], 1u);
+                        atomicAdd(&sh_hist[bin], 1u);       // flushed to the row's global histogram once, below
                     }
                 }
             }
         }
+    }
+    if (sum_heads && p.hist) {
+        named_bar_sync(1, consumer_threads);
+        for (int i = ctid; i < TIDAL_TOPK_BINS; i += consumer_threads)
+            if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
     }
 
     // ---------------------------------------------------------------- epilogue
@@ -382,59 +390,90 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     store_attention_result<T>(p, cta_o, cta_ml, HC, G, D, qh0, b, chunk);
 }
 
-// Merge the split-KV partials of one (sequence, q head): grid (Hq, B), block
-// (D, kMergeGroups).  The chunk weights are formed once in shared memory; the
-// groups then stride over the chunks so that many loads are in flight, and their
-// sums are combined in a fixed order.
-constexpr int kMergeGroups = 8;
+// Merge the split-KV partials of one (sequence, q head): grid (Hq, B), 1024 threads as
+// kMergeGroups groups of D/4 lanes.  A lane owns four consecutive output elements (float4 loads);
+// the groups stride over the chunks, so with up to a few hundred chunks every load of the kernel
+// is in flight at once.  Weights, denominator and the cross-group sum use fixed orders.
+constexpr int kMergeThreads = 1024;
 template <typename T>
-__global__ void merge_chunks_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int nchunks,
-                                    int Hq, int D, T* __restrict__ o, float* __restrict__ shard_m,
-                                    float* __restrict__ shard_l, float* __restrict__ shard_o) {
-    extern __shared__ float msm[];           // [nchunks] weights, then [kMergeGroups][D] partial sums
+__global__ void __launch_bounds__(kMergeThreads) merge_chunks_kernel(const float* __restrict__ part_o,
+                                                                     const float* __restrict__ part_ml, int nchunks, int Hq,
+                                                                     int D, T* __restrict__ o, float* __restrict__ shard_m,
+                                                                     float* __restrict__ shard_l, float* __restrict__ shard_o) {
+    extern __shared__ __align__(16) float msm[];     // [nchunks] weights, then [groups][D] partial sums
+    __shared__ float s_red[32];
+    __shared__ float s_M, s_L;
     pdl_wait();
     pdl_launch_dependents();
+    const int hq = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+    const int lanes = D / 4, groups = kMergeThreads / lanes;
+    const int lane4 = tid % lanes, grp = tid / lanes;
+    const int wlane = tid & 31, warp = tid >> 5;
     float* wgt = msm;
-    float* red = msm + nchunks;
-    __shared__ float s_M, s_L;
-    const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x, grp = threadIdx.y;
-    const int tid = grp * D + d, nthreads = D * kMergeGroups;
+    float* red = msm + ((nchunks + 3) & ~3);
     const size_t ph = (size_t)b * Hq + hq;
     const float* ml = part_ml + ph * nchunks * 2;
-    if (tid < 32) {
-        float M = -INFINITY;
-        for (int c = tid; c < nchunks; c += 32) M = fmaxf(M, ml[2 * c]);
+    // running maximum over the chunks
+    float m_mine = -INFINITY, l_mine = 0.f;
+    float2 mlv = make_float2(-INFINITY, 0.f);
+    if (tid < nchunks) mlv = *reinterpret_cast<const float2*>(ml + 2 * tid);
+    m_mine = mlv.x;
+    for (int c = tid + kMergeThreads; c < nchunks; c += kMergeThreads) m_mine = fmaxf(m_mine, ml[2 * c]);
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
-        if (tid == 0) s_M = M;
+    for (int off = 16; off > 0; off >>= 1) m_mine = fmaxf(m_mine, __shfl_xor_sync(0xffffffffu, m_mine, off));
+    if (wlane == 0) s_red[warp] = m_mine;
+    __syncthreads();
+    if (warp == 0) {
+        float v = s_red[wlane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+        if (wlane == 0) s_M = v;
     }
     __syncthreads();
     const float M = s_M;
-    for (int c = tid; c < nchunks; c += nthreads) {
-        const float m = ml[2 * c];
-        wgt[c] = (m == -INFINITY) ? 0.f : fast_exp2(m - M);
+    // weights and denominator
+    for (int c = tid; c < nchunks; c += kMergeThreads) {
+        const float m = (c == tid) ? mlv.x : ml[2 * c];
+        const float l = (c == tid) ? mlv.y : ml[2 * c + 1];
+        const float w = (m == -INFINITY) ? 0.f : fast_exp2(m - M);
+        wgt[c] = w;
+        l_mine = fmaf(w, l, l_mine);
     }
-    __syncthreads();
-    if (tid == 0) {
-        float L = 0.f;
-        for (int c = 0; c < nchunks; ++c) L = fmaf(wgt[c], ml[2 * c + 1], L);
-        s_L = L;
-    }
-    float acc = 0.f;
-    const float* po = part_o + ph * nchunks * D + d;
-#pragma unroll 4
-    for (int c = grp; c < nchunks; c += kMergeGroups) acc = fmaf(wgt[c], po[(size_t)c * D], acc);
-    red[grp * D + d] = acc;
-    __syncthreads();
-    if (grp == 0) {
-        float tot = 0.f;
 #pragma unroll
-        for (int g2 = 0; g2 < kMergeGroups; ++g2) tot += red[g2 * D + d];
+    for (int off = 16; off > 0; off >>= 1) l_mine += __shfl_xor_sync(0xffffffffu, l_mine, off);
+    __syncthreads();                 // s_red reuse
+    if (wlane == 0) s_red[warp] = l_mine;
+    __syncthreads();
+    if (warp == 0) {
+        float v = s_red[wlane];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        if (wlane == 0) s_L = v;
+    }
+    // weighted sum of the partial outputs
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* po = part_o + ph * nchunks * D + 4 * lane4;
+    if (grp < groups) {
+#pragma unroll 8
+        for (int c = grp; c < nchunks; c += groups) {
+            const float4 v = *reinterpret_cast<const float4*>(po + (size_t)c * D);
+            const float w = wgt[c];
+            acc.x = fmaf(w, v.x, acc.x);
+            acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z);
+            acc.w = fmaf(w, v.w, acc.w);
+        }
+        *reinterpret_cast<float4*>(red + (size_t)grp * D + 4 * lane4) = acc;
+    }
+    __syncthreads();
+    if (tid < D) {
+        float tot = 0.f;
+        for (int g2 = 0; g2 < groups; ++g2) tot += red[g2 * D + tid];
         const float L = s_L;
-        if (o) o[ph * D + d] = from_f32<T>(L > 0.f ? tot / L : 0.f);
+        if (o) o[ph * D + tid] = from_f32<T>(L > 0.f ? tot / L : 0.f);
         if (shard_o) {
-            shard_o[ph * D + d] = tot;
-            if (d == 0) {
+            shard_o[ph * D + tid] = tot;
+            if (tid == 0) {
                 shard_m[ph] = M;
                 shard_l[ph] = L;
             }
@@ -478,7 +517,7 @@ static int sm_count_cached() {
     return n;
 }
 
-constexpr size_t kSmemBudget = 220 * 1024;   // per CTA (227 KB is the hardware limit)
+constexpr size_t kSmemBudget = 227 * 1024 - 512;   // per CTA (227 KB is the hardware limit)
 
 // Pick the slot geometry for HC heads per CTA; false if HC cannot be mapped.
 static bool plan_slots(int HC, int lpr, bool allow_hps2, int max_cw, int* CW, int* HPS, int* TG) {
@@ -563,8 +602,9 @@ static int dispatch_d(const AttnParams& p, const AttnPlan& plan, int D, int G, c
 
 template <typename T>
 static int launch_merge(const AttnParams& p, int D, cudaStream_t st) {
-    const size_t smem = sizeof(float) * ((size_t)p.nchunks + (size_t)kMergeGroups * D);
-    TIDAL_CUDA_OK(launch_pdl(merge_chunks_kernel<T>, dim3(p.Hq, p.B), dim3(D, kMergeGroups), smem, st, 1,
+    const int groups = kMergeThreads / (D / 4);
+    const size_t smem = sizeof(float) * ((size_t)((p.nchunks + 3) & ~3) + (size_t)groups * D);
+    TIDAL_CUDA_OK(launch_pdl(merge_chunks_kernel<T>, dim3(p.Hq, p.B), dim3(kMergeThreads), smem, st, 1,
                              (const float*)p.part_o, (const float*)p.part_ml, (int)p.nchunks, (int)p.Hq, D, (T*)p.o, p.shard_m,
                              p.shard_l, p.shard_o));
     count_launch();

@@ -67,7 +67,7 @@ size_t attn_mma_smem_bytes(int S, int HC, int G, int D, bool sum_heads) {
     const size_t stage = (size_t)S * 2 * T * mma_pitch(HC, D);
     const size_t ep = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float) + cta_result_bytes(HC, G, D);
     const size_t main_bytes = round16(stage > ep ? stage : ep);
-    const size_t sc = sum_heads ? score_smem_bytes(T, HC) : 0;
+    const size_t sc = sum_heads ? score_smem_bytes(T, HC) + sizeof(uint32_t) * TIDAL_TOPK_BINS : 0;
     return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
 }
 
@@ -92,7 +92,8 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     const bool sum_heads = want_scores && p.score_rows == 1;
     unsigned char* stage_base = smem;
     float* sc_smem = reinterpret_cast<float*>(smem + main_bytes);                      // [2][R*TT][HC]
-    const size_t sc_bytes = sum_heads ? score_smem_bytes(TT, HC) : 0;
+    const size_t sc_bytes = sum_heads ? score_smem_bytes(TT, HC) + sizeof(uint32_t) * TIDAL_TOPK_BINS : 0;
+    uint32_t* sh_hist = reinterpret_cast<uint32_t*>(smem + main_bytes + score_smem_bytes(TT, HC));   // CTA-local digit counts
     const int R = score_block_stages(TT, HC);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + main_bytes + sc_bytes);
     uint64_t* empty_bar = full_bar + S;
@@ -114,6 +115,8 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     // out as zeros (later contents are real K/V rows, finite whenever the cache is).
     for (size_t i = (size_t)threadIdx.x * 16; i < stage_bytes; i += (size_t)blockDim.x * 16)
         *reinterpret_cast<uint4*>(stage_base + i) = make_uint4(0, 0, 0, 0);
+    if (sum_heads && p.hist)
+        for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x) sh_hist[i] = 0;
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // the prologue above touched no global memory; from here on this kernel is ordered
     // after the earlier kernels of the stream (see common.cuh)
@@ -377,11 +380,16 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
                     if (p.hist) {
                         uint32_t bin = ordered_key(a) >> kDigit0Shift;
                         if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
-                        atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + bin], 1u);
+                        atomicAdd(&sh_hist[bin], 1u);       // flushed to the row's global histogram once, below
                     }
                 }
             }
         }
+    }
+    if (sum_heads && p.hist) {
+        named_bar_sync(1, consumer_threads);
+        for (int i = ctid; i < TIDAL_TOPK_BINS; i += consumer_threads)
+            if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
     }
 
     // ---------------------------------------------------------------- epilogue
