@@ -159,6 +159,26 @@ def test_topk_random(T, rows, n, k):
     assert torch.equal(torch.sort(idx, -1).values, torch.sort(idx2, -1).values)
 
 
+@pytest.mark.parametrize("rows,n,k", [(2, 200000, 1000), (1, 1 << 20, 1024), (3, 70000, 2048)])
+def test_topk_crowded_threshold_bin(T, rows, n, k):
+    """Thousands of keys share the threshold bin (quantised scores, and a planted 1 % of
+    near-equal high scores as in the long-context configuration): more candidates than fit
+    in shared memory."""
+    g = torch.Generator().manual_seed(n)
+    s = torch.round(torch.randn(rows, n, generator=g) * 2) / 2
+    hot = torch.randperm(n, generator=g)[: n // 100]
+    s[:, hot] = 40.0 + 0.001 * torch.randn(rows, hot.numel(), generator=g)
+    ws = _ws(T, 1, 1, 64, rows, n)
+    idx = T.topk(s.cuda(), k, ws)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    ok, why = O.topk_sets_match(s, idx.cpu(), k, tie_band=0.0)
+    assert ok, why
+    # ties resolve towards the lower position: the result is exactly torch's stable descending sort prefix
+    order = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :k]
+    assert torch.equal(torch.sort(idx.cpu().long(), -1).values, torch.sort(order, -1).values)
+
+
 def test_topk_ties_and_values(T):
     """All-equal rows and heavy ties resolve towards the lower index; values are returned."""
     n, k = 5000, 100

@@ -432,6 +432,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
 constexpr int kClusterMaxK = 2048;            // winners kept in shared memory
 constexpr int kClusterCand = 4096;            // candidates kept in shared memory
 constexpr int64_t kClusterMaxN = 1 << 21;
+constexpr int64_t kClusterSmemCandMaxN = 1 << 16;   // longer rows keep their candidates in the workspace
 constexpr size_t kClusterSmem = sizeof(uint32_t) * kBins                       // h
                                 + sizeof(uint64_t) * (kClusterMaxK + kClusterCand);  // lists (first CTA) / local histogram
 
@@ -456,7 +457,12 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     extern __shared__ __align__(16) unsigned char csm[];
     uint32_t* h = reinterpret_cast<uint32_t*>(csm);                                   // [kBins]
     uint64_t* sel = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);      // [kClusterMaxK]
-    uint64_t* cand = sel + kClusterMaxK;                                              // [kClusterCand]
+    // Candidates of the threshold bin: in shared memory for short rows; long rows can put thousands of
+    // keys into one bin (e.g. 1 % of 1 M tokens with high affinity), so theirs go to the workspace.
+    const bool cand_global = p.n > kClusterSmemCandMaxN && p.cand != nullptr;
+    uint64_t* cand = cand_global ? p.cand + (size_t)blockIdx.x / cg::this_cluster().num_blocks() * p.cand_cap
+                                 : sel + kClusterMaxK;                                // [kClusterCand] in shared memory
+    const uint32_t cand_capacity = cand_global ? (uint32_t)min(p.cand_cap, (int64_t)0x7fffffff) : (uint32_t)kClusterCand;
     uint32_t* h_local = reinterpret_cast<uint32_t*>(sel);                             // own-slice histogram (no-hist path)
     __shared__ uint32_t ws[32];
     __shared__ ClusterShared sh;
@@ -501,7 +507,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     // ---- scan the slice, push into the first CTA's lists
     {
         uint64_t* sel0 = cluster.map_shared_rank(sel, 0);
-        uint64_t* cand0 = cluster.map_shared_rank(cand, 0);
+        uint64_t* cand0 = cand_global ? cand : cluster.map_shared_rank(cand, 0);
         ClusterShared* sh0 = cluster.map_shared_rank(&sh, 0);
         auto push = [&](float v, int64_t j) {
             const uint64_t key = make_key(v, (uint32_t)j, p.n, p.force_last);
@@ -511,7 +517,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
                 if (at < (uint32_t)kClusterMaxK) sel0[at] = key;
             } else if (bin == bstar) {
                 const uint32_t at = atomicAdd(&sh0->ncand, 1u);
-                if (at < (uint32_t)kClusterCand) cand0[at] = key;
+                if (at < cand_capacity) cand0[at] = key;
             }
         };
         const bool vec_ok = p.seg_len == 0 && ((reinterpret_cast<uintptr_t>(srow) & 15) == 0);
@@ -537,7 +543,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     const bool own = p.own_hi > p.own_lo;
     const uint32_t nsel = min(sh.nsel, (uint32_t)kClusterMaxK);
     const uint32_t ncand_total = sh.ncand;
-    const bool overflow = ncand_total > (uint32_t)kClusterCand;
+    const bool overflow = ncand_total > cand_capacity;
     uint32_t need = k - above;
     if (sh.nsel != above && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
 
