@@ -1,0 +1,84 @@
+"""enable_tidal on a Hugging Face Llama (the installed transformers): same call as the
+reference's src/enable_tidal.py, same greedy tokens as the reference model produced
+(fixture), attention by the sm_100a kernels during decode."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import tidal_oracle as O
+from tests.helpers import load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+def _hf_model(W, dtype):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    cfg = LlamaConfig(vocab_size=W.vocab, hidden_size=W.hidden, intermediate_size=W.ffn, num_hidden_layers=W.layers,
+                      num_attention_heads=W.heads, num_key_value_heads=W.kv_heads, rms_norm_eps=W.eps,
+                      max_position_embeddings=4096, hidden_act="silu", tie_word_embeddings=False, rope_theta=W.theta)
+    cfg._attn_implementation = "sdpa"
+    m = LlamaForCausalLM(cfg).eval()
+    missing = m.load_state_dict(W.hf_state_dict(), strict=False)
+    assert not [k for k in missing.missing_keys if "inv_freq" not in k], missing
+    return m.to(dtype).cuda()
+
+
+def _greedy(model, prompt, steps):
+    from transformers.cache_utils import DynamicCache
+
+    toks = []
+    with torch.inference_mode():
+        cache = DynamicCache()
+        out = model(prompt, past_key_values=cache, use_cache=True)
+        tok = out.logits[:, -1:].argmax(-1)
+        toks.append(int(tok))
+        for _ in range(steps - 1):
+            out = model(tok.view(1, 1), past_key_values=cache, use_cache=True)
+            tok = out.logits[:, -1:].argmax(-1)
+            toks.append(int(tok))
+    return toks
+
+
+def test_enable_tidal_on_hf_llama_matches_reference_tokens():
+    from tidaldecode_b200.enable_tidal import enable_tidal
+
+    z = load_golden("tiny_llama_cfg1.npz")
+    W = O.TinyLlamaWeights()
+    g = torch.Generator().manual_seed(int(z["prompt_seed"]))
+    prompt = torch.randint(0, W.vocab, (1, 2048), generator=g).cuda()
+    model = _hf_model(W, torch.float32)
+    enable_tidal(model, attn_type="tidal", top_k=128, sparse_layer_start=2, correction_layer=3, max_seq_len=2048 + 64)
+    attn = model.model.layers[0].self_attn
+    assert hasattr(attn, "flash_forward")                       # the original forward is kept (modify_llama.py:366)
+    toks = _greedy(model, prompt, 32)
+    assert toks == z["tokens"].tolist()
+    c = model._tidal_state.controller
+    assert c.workspace.status() == 0
+    sets = torch.sort(c.topk_dindices_buffer[0].cpu(), dim=-1).values
+    want = torch.from_numpy(z["layer3_sets"][-1])
+    diff = sum(len(set(sets[h].tolist()) ^ set(want[h].tolist())) for h in range(W.heads))
+    assert diff <= 4, diff
+    # a second sequence through the same model: state is reset when the cache is empty again
+    assert _greedy(model, prompt, 4) == z["tokens"][:4].tolist()
+    # attn_type other than "tidal" leaves the original forward in place
+    enable_tidal(model, attn_type="full", top_k=128)
+    assert model.model.layers[0].self_attn.forward == model.model.layers[0].self_attn.flash_forward
+
+
+def test_enable_tidal_gqa_bf16_head_sum():
+    """Shared-set mode on a GQA bf16 model: decode logits stay close to the dense model's
+    when the budget covers the context (nothing is dropped)."""
+    from tidaldecode_b200.enable_tidal import enable_tidal
+
+    W = O.TinyLlamaWeights(vocab=256, hidden=512, layers=4, heads=8, kv_heads=2, ffn=256, seed=5, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, W.vocab, (1, 200), generator=g).cuda()
+    dense = _hf_model(W, torch.bfloat16)
+    want = _greedy(dense, prompt, 6)
+    model = _hf_model(W, torch.bfloat16)
+    enable_tidal(model, top_k=1024, sparse_layer_start=1, correction_layer=2, head_reduce="sum", max_seq_len=512)
+    got = _greedy(model, prompt, 6)
+    assert sum(a == b for a, b in zip(got, want)) >= 5, (got, want)
+    assert model._tidal_state.controller.workspace.status() == 0

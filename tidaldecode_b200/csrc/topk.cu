@@ -504,20 +504,23 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     uint32_t above;
     find_threshold_bin(h, ws, k, &bstar, &above);
 
-    // ---- scan the slice, push into the first CTA's lists
+    // ---- scan the slice into this CTA's own lists (local shared-memory atomics), then hand them
+    //      over to the first CTA in two bulk copies: one remote atomic per CTA instead of one per key
+    __shared__ uint32_t my_nsel, my_ncand, base_sel, base_cand;
+    uint64_t* my_sel = sel;                      // [kClusterMaxK]   (every CTA has the same layout)
+    uint64_t* my_cand = sel + kClusterMaxK;      // [kClusterCand]
+    if (t == 0) { my_nsel = 0; my_ncand = 0; }
+    __syncthreads();
     {
-        uint64_t* sel0 = cluster.map_shared_rank(sel, 0);
-        uint64_t* cand0 = cand_global ? cand : cluster.map_shared_rank(cand, 0);
-        ClusterShared* sh0 = cluster.map_shared_rank(&sh, 0);
         auto push = [&](float v, int64_t j) {
             const uint64_t key = make_key(v, (uint32_t)j, p.n, p.force_last);
             const int bin = key_bin(key);
             if (bin > bstar) {
-                const uint32_t at = atomicAdd(&sh0->nsel, 1u);
-                if (at < (uint32_t)kClusterMaxK) sel0[at] = key;
+                const uint32_t at = atomicAdd(&my_nsel, 1u);
+                if (at < (uint32_t)kClusterMaxK) my_sel[at] = key;
             } else if (bin == bstar) {
-                const uint32_t at = atomicAdd(&sh0->ncand, 1u);
-                if (at < cand_capacity) cand0[at] = key;
+                const uint32_t at = atomicAdd(&my_ncand, 1u);
+                if (at < (uint32_t)kClusterCand) my_cand[at] = key;
             }
         };
         const bool vec_ok = p.seg_len == 0 && ((reinterpret_cast<uintptr_t>(srow) & 15) == 0);
@@ -533,6 +536,44 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
 #pragma unroll 4
             for (int64_t j = lo + t; j < hi; j += kTopkThreads) push(score_at(j), j);
         }
+    }
+    __syncthreads();
+    if (CS > 1 || cand_global) {
+        ClusterShared* sh0 = cluster.map_shared_rank(&sh, 0);
+        // a CTA whose own candidate list overflowed reports a count beyond any capacity: the resolver
+        // then rescans the row instead of trusting the lists
+        const uint32_t nc = my_ncand > (uint32_t)kClusterCand ? 0x40000000u : my_ncand;
+        if (t == 0) {
+            base_sel = atomicAdd(&sh0->nsel, my_nsel);
+            base_cand = atomicAdd(&sh0->ncand, nc);
+        }
+        __syncthreads();
+        uint64_t* sel0 = cluster.map_shared_rank(sel, 0);
+        uint64_t* cand0 = cand_global ? cand : cluster.map_shared_rank(sel + kClusterMaxK, 0);
+        // read everything this thread will move before anyone writes (rank 0's source is its destination array)
+        constexpr int kSelPer = kClusterMaxK / kTopkThreads, kCandPer = kClusterCand / kTopkThreads;
+        uint64_t vs[kSelPer], vc[kCandPer];
+        const uint32_t ns = min(my_nsel, (uint32_t)kClusterMaxK), ncl = min(my_ncand, (uint32_t)kClusterCand);
+#pragma unroll
+        for (int u = 0; u < kSelPer; ++u) vs[u] = (t + u * kTopkThreads < ns) ? my_sel[t + u * kTopkThreads] : 0;
+#pragma unroll
+        for (int u = 0; u < kCandPer; ++u) vc[u] = (t + u * kTopkThreads < ncl) ? my_cand[t + u * kTopkThreads] : 0;
+        cluster.sync();               // all CTAs hold their keys in registers and know their offsets
+#pragma unroll
+        for (int u = 0; u < kSelPer; ++u) {
+            const uint32_t i = t + u * kTopkThreads;
+            if (i < ns && base_sel + i < (uint32_t)kClusterMaxK) sel0[base_sel + i] = vs[u];
+        }
+        if (nc < 0x40000000u) {
+#pragma unroll
+            for (int u = 0; u < kCandPer; ++u) {
+                const uint32_t i = t + u * kTopkThreads;
+                if (i < ncl && base_cand + i < cand_capacity) cand0[base_cand + i] = vc[u];
+            }
+        }
+    } else if (t == 0) {
+        sh.nsel = my_nsel;            // single CTA, lists already in place
+        sh.ncand = my_ncand;
     }
     cluster.sync();
     if (rank != 0) return;
