@@ -68,11 +68,11 @@ size_t attn_mma_smem_bytes(int S, int HC, int G, int D, bool sum_heads) {
     const size_t ep = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float) + cta_result_bytes(HC, G, D);
     const size_t main_bytes = round16(stage > ep ? stage : ep);
     const size_t sc = sum_heads ? score_smem_bytes(T, HC) + sizeof(uint32_t) * TIDAL_TOPK_BINS : 0;
-    return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
+    return main_bytes + sc + (2 * S + 4) * sizeof(uint64_t) + 64;
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(const AttnParams p) {
     constexpr int KS = D / 16;    // k-steps of Q K^T
     constexpr int NT = D / 8;     // n-tiles of P V
     using M = Mma16<T>;
@@ -97,7 +97,9 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     const int R = score_block_stages(TT, HC);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + main_bytes + sc_bytes);
     uint64_t* empty_bar = full_bar + S;
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
+    uint64_t* sc_full = empty_bar + S;        // [2] consumers -> reducer: a super-block of logits is parked
+    uint64_t* sc_empty = sc_full + 2;         // [2] reducer -> consumers: the buffer may be overwritten
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(sc_empty + 2);
 
     const int chunk = blockIdx.x, slice = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,6 +108,10 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
         for (int s = 0; s < S; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kMmaWarps);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sc_full[i], kMmaWarps);
+            mbar_init(&sc_empty[i], 1);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -198,12 +204,44 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
                     if (mbar_try_wait(&full_bar[s], (it / S) & 1)) break;
             }
         }
+    } else if (warp == 1) {
+        // ================================================================== reducer
+        // Sums the logits of each token over the CTA's heads (fixed order), stores them, counts their
+        // first radix digit — one super-block of R stages at a time, while the consumers stream on.
+        if (sum_heads) {
+            const int n_sb = (n_iters + R - 1) / R;
+            for (int sb = 0; sb < n_sb; ++sb) {
+                const int buf = sb & 1;
+                mbar_wait_bounded(&sc_full[buf], (sb >> 1) & 1, abort_flag, p.status);
+                const float* blk = sc_smem + (size_t)buf * R * TT * HC;
+                const int first = sb * R * TT;                       // token index (within the chunk) of row 0
+                const int rows = min(R * TT, ntok - first);
+                for (int r = lane; r < rows; r += 32) {
+                    float a = 0.f;
+                    for (int h = 0; h < HC; ++h) a += blk[r * HC + h];
+                    const int pos = tok0 + first + r;
+                    p.scores[(size_t)b * p.score_stride + pos] = a;
+                    if (p.hist) {
+                        uint32_t bin = ordered_key(a) >> kDigit0Shift;
+                        if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
+                        atomicAdd(&sh_hist[bin], 1u);               // flushed to the row's global histogram once, below
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sc_empty[buf]);
+            }
+            if (p.hist) {
+                __syncwarp();
+                for (int i = lane; i < TIDAL_TOPK_BINS; i += 32)
+                    if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
+            }
+        }
     } else {
     // ================================================================= consumers
-    const int cw = warp - 1;
+    const int cw = warp - 2;
     const int head_local = cw % HC, tg = cw / HC;
     const int consumer_threads = kMmaWarps * 32;
-    const int ctid = threadIdx.x - 32;
+    const int ctid = threadIdx.x - 64;
     const int r0 = lane >> 2;            // fragment row (query head within the group); the second row is r0 + 8
     const int cq = (lane & 3) * 2;       // fragment column pair
 
@@ -233,6 +271,8 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
     for (int it = 0; it < n_iters; ++it) {
         const int s = it % S;
         mbar_wait_bounded(&full_bar[s], (it / S) & 1, abort_flag, p.status);
+        if (sum_heads && (it % R) == 0 && it >= 2 * R)               // the reducer is done with this buffer's previous use
+            mbar_wait_bounded(&sc_empty[(it / R) & 1], ((it / R) / 2 - 1) & 1, abort_flag, p.status);
         const int valid = min(TT, ntok - it * TT);
         const int tbase = tg * kMmaTile;
         const int mine = min(kMmaTile, valid - tbase);          // valid tokens of this warp's tile (may be <= 0)
@@ -358,38 +398,9 @@ __global__ void __launch_bounds__((kMmaWarps + 1) * 32) decode_attn_mma_kernel(c
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);          // the stage is free: the logits wait in their own buffer
         if (sum_heads && ((it % R) == R - 1 || it == n_iters - 1)) {
-            // head sum in a fixed order for the whole super-block: 8 lanes per token, each adds every 8th
-            // head, then a butterfly; one thread per token stores the logit and counts its first radix digit
-            named_bar_sync(1, consumer_threads);
-            const int sb = it / R;
-            const float* blk = sc_smem + (size_t)(sb & 1) * R * TT * HC;
-            const int rows = ((it % R) + 1) * TT;
-            const int first = sb * R * TT;                  // token index (within the chunk) of row 0
-            for (int base = 0; base < rows; base += consumer_threads / 8) {   // uniform per warp
-                const int r = base + (ctid >> 3), j = ctid & 7;
-                const bool in = r < rows && first + r < ntok;
-                float a = 0.f;
-                if (in)
-                    for (int h = j; h < HC; h += 8) a += blk[r * HC + h];
-                a += __shfl_xor_sync(0xffffffffu, a, 4);
-                a += __shfl_xor_sync(0xffffffffu, a, 2);
-                a += __shfl_xor_sync(0xffffffffu, a, 1);
-                if (j == 0 && in) {
-                    const int pos = tok0 + first + r;
-                    p.scores[(size_t)b * p.score_stride + pos] = a;
-                    if (p.hist) {
-                        uint32_t bin = ordered_key(a) >> kDigit0Shift;
-                        if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
-                        atomicAdd(&sh_hist[bin], 1u);       // flushed to the row's global histogram once, below
-                    }
-                }
-            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sc_full[(it / R) & 1]);     // this warp's logits of the super-block are parked
         }
-    }
-    if (sum_heads && p.hist) {
-        named_bar_sync(1, consumer_threads);
-        for (int i = ctid; i < TIDAL_TOPK_BINS; i += consumer_threads)
-            if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
     }
 
     // ---------------------------------------------------------------- epilogue
@@ -442,7 +453,7 @@ template <typename T, int D>
 static int launch_one(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     auto kern = decode_attn_mma_kernel<T, D>;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 1) * 32), smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
+    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 2) * 32), smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
 }
