@@ -248,6 +248,15 @@ int tidal_merge_partials(const float* d_m, const float* d_l, const float* d_o, i
 int tidal_merge_partials_strided(const float* d_m, const float* d_l, const float* d_o, int64_t shard_stride, int shards,
                                  int batch, int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream);
 
+/* ------------------------------------------------------------------ RMSNorm
+ * y[r][:] = x[r][:] * rsqrt(mean(x[r]^2) + eps) * weight, fp32 statistics.  Stands in for
+ * rms_norm_forward (tidal/ops/csrc/rms_norm.cu:185-213); not part of the attention path, on the
+ * reference's operator surface next to it.  hidden must be a multiple of 8 (4 for fp32).
+ * round_before_weight = 1 rounds the normalised value to dtype before the weight, as the
+ * reference's PyTorch model does (src/models/llama_tidaldecoding.py:122-127). */
+int tidal_rms_norm(const void* d_x, const void* d_weight, void* d_y, int64_t rows, int hidden, float eps, int dtype,
+                   int round_before_weight, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

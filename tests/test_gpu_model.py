@@ -213,3 +213,24 @@ def test_batched_decode_equals_single_sequence_runs():
     with pytest.raises(RuntimeError):
         c._selection_valid = False
         U.decode_sparse_attn(qd, c, 0, c.topk_dindices_buffer, False)       # modify_llama.py:123-124
+
+
+@pytest.mark.parametrize("dtype,rows,hidden", [(torch.float16, 1, 4096), (torch.bfloat16, 7, 4096), (torch.float32, 3, 256),
+                                               (torch.float16, 2048, 1024), (torch.bfloat16, 2, 8192)])
+def test_rms_norm_matches_reference_model(K, dtype, rows, hidden):
+    """rms_norm_forward against the reference model's LlamaRMSNorm arithmetic (oracle restatement of
+    src/models/llama_tidaldecoding.py:122-127)."""
+    g = torch.Generator().manual_seed(hidden + rows)
+    x = (torch.randn(1, rows, hidden, generator=g) * 3).to(dtype)
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(dtype)
+    out = torch.empty_like(x, device="cuda")
+    K.rms_norm_forward(x.cuda(), w.cuda(), out, 1e-6)
+    want = O.rms_norm(x, w, 1e-6)
+    if dtype == torch.float32:
+        assert torch.allclose(out.cpu(), want, rtol=1e-5, atol=1e-6)
+    else:
+        ulp = 2 ** -7 if dtype == torch.bfloat16 else 2 ** -10
+        assert torch.allclose(out.cpu().float(), want.float(), rtol=2 * ulp, atol=1e-6)
+        assert (out.cpu() == want).float().mean() > 0.98
+    with pytest.raises(RuntimeError):
+        K.rms_norm_forward(x.cuda()[..., :-3].contiguous(), w.cuda()[:-3].contiguous(), out[..., :-3].contiguous(), 1e-6)

@@ -172,10 +172,13 @@ def prefill_with_paged_kv_cache(q, kv_data, kv_indices, kv_last_page_len, causal
 
 
 def rms_norm_forward(input: torch.Tensor, weight: torch.Tensor, output: torch.Tensor, epsilon: float) -> None:
-    """RMSNorm with fp32 statistics (tidal/ops/csrc/rms_norm.cu:185-213).  Not part of the
-    attention path; served by torch ops."""
-    x = input.float()
-    output.copy_((x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + epsilon) * weight.float()).to(output.dtype))
+    """RMSNorm with fp32 statistics into `output` (tidal/ops/csrc/rms_norm.cu:185-213).  The normalised
+    value is rounded to the storage type before the weight, as the reference's PyTorch model does."""
+    _check_input(input, "input")
+    _check_input(weight, "weight")
+    _check_input(output, "output")
+    _check(output.shape == input.shape and output.dtype == input.dtype, "output must match input")
+    _ops.rms_norm(input, weight, float(epsilon), out=output, round_before_weight=True)
 
 
 class BatchDecodeWithPagedKVCachePyTorchWrapper:

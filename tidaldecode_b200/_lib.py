@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm",
 )
 
 
@@ -99,6 +99,8 @@ def _load() -> C.CDLL:
     lib.tidal_merge_partials_strided.restype = C.c_int
     lib.tidal_merge_partials_strided.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
                                                  C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+    lib.tidal_rms_norm.restype = C.c_int
+    lib.tidal_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p]
     return lib
 
 

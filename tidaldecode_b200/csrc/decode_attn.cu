@@ -193,11 +193,6 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sc_empty[buf]);
             }
-            if (p.hist) {
-                __syncwarp();
-                for (int i = lane; i < TIDAL_TOPK_BINS; i += 32)
-                    if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
-            }
         }
     } else {
     // ================================================================= consumers
@@ -398,6 +393,12 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
         }
     }
     }   // consumers
+    if (sum_heads && p.hist) {
+        // every warp is done with its role: flush the CTA's digit counts with all threads
+        __syncthreads();
+        for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x)
+            if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
+    }
     store_attention_result<T>(p, cta_o, cta_ml, HC, G, D, qh0, b, chunk);
 }
 

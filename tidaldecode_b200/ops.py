@@ -274,3 +274,20 @@ def merge_partials(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, dtype: tor
         check(lib.tidal_merge_partials_strided(m.data_ptr(), l.data_ptr(), o.data_ptr(), stride, shards, B, Hq, D,
                                                out.data_ptr(), _DTYPES[dtype], _stream()), "tidal_merge_partials")
     return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+             round_before_weight: bool = True) -> torch.Tensor:
+    """RMSNorm over the last dimension; see tidal_rms_norm in include/tidal_b200.h."""
+    _need_cuda(x, weight, out)
+    if weight.dtype != x.dtype:
+        raise RuntimeError("input and weight must share a dtype")
+    hidden = x.shape[-1]
+    if weight.numel() != hidden:
+        raise RuntimeError("weight length differs from the last dimension of the input")
+    if out is None:
+        out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(lib.tidal_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.numel() // hidden, hidden, float(eps),
+                                 _dtype_code(x), 1 if round_before_weight else 0, _stream()), "tidal_rms_norm")
+    return out
