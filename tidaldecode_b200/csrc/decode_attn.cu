@@ -25,7 +25,7 @@ __host__ __device__ inline size_t attn_smem_bytes(int S, int T, int row_bytes, i
     size_t ep = (size_t)slots * hps * G * (D + 2) * sizeof(float) + cta_result_bytes(HC, G, D);
     size_t main_bytes = round16(stage > ep ? stage : ep);
     size_t sc = want_scores ? score_smem_bytes(T, HC) + sizeof(uint32_t) * TIDAL_TOPK_BINS : 0;
-    return main_bytes + sc + (2 * S + 4) * sizeof(uint64_t) + 64;
+    return main_bytes + sc + 2 * S * sizeof(uint64_t) + 64;
 }
 
 // Tokens one slot processes per stage (unrolled): fewer under wide GQA groups,
@@ -35,7 +35,7 @@ __host__ __device__ constexpr int attn_tps(int G) { return G >= 4 ? 2 : 4; }
 // T: storage type; D: head dim; G: q heads per KV head handled by one slot;
 // HPS: KV heads per slot.
 template <typename T, int D, int G, int HPS>
-__global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const AttnParams p) {
     using V = Vec16<T>;
     constexpr int VEC = V::N;
     constexpr int LPR = D / VEC;          // lanes per row
@@ -64,9 +64,7 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
     const int R = score_block_stages(TT, HC);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + main_bytes + sc_bytes);
     uint64_t* empty_bar = full_bar + S;
-    uint64_t* sc_full = empty_bar + S;        // [2] consumers -> reducer: a super-block of logits is parked
-    uint64_t* sc_empty = sc_full + 2;         // [2] reducer -> consumers: the buffer may be overwritten
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(sc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
 
     const int chunk = blockIdx.x, slice = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -99,10 +97,6 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
         for (int s = 0; s < S; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], p.CW);
-        }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&sc_full[i], p.CW);
-            mbar_init(&sc_empty[i], 1);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -167,36 +161,9 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
                     if (mbar_try_wait(&full_bar[s], (it / S) & 1)) break;
             }
         }
-    } else if (warp == 1) {
-        // ================================================================== reducer
-        // Sums the logits of each token over the CTA's heads (fixed order), stores them, counts their
-        // first radix digit — one super-block of R stages at a time, while the consumers stream on.
-        if (sum_heads) {
-            const int n_sb = (n_iters + R - 1) / R;
-            for (int sb = 0; sb < n_sb; ++sb) {
-                const int buf = sb & 1;
-                mbar_wait_bounded(&sc_full[buf], (sb >> 1) & 1, abort_flag, p.status);
-                const float* blk = sc_smem + (size_t)buf * R * TT * HC;
-                const int first = sb * R * TT;                       // token index (within the chunk) of row 0
-                const int rows = min(R * TT, ntok - first);
-                for (int r = lane; r < rows; r += 32) {
-                    float a = 0.f;
-                    for (int h = 0; h < HC; ++h) a += blk[r * HC + h];
-                    const int pos = tok0 + first + r;
-                    p.scores[(size_t)b * p.score_stride + pos] = a;
-                    if (p.hist) {
-                        uint32_t bin = ordered_key(a) >> kDigit0Shift;
-                        if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
-                        atomicAdd(&sh_hist[bin], 1u);               // flushed to the row's global histogram once, below
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sc_empty[buf]);
-            }
-        }
     } else {
     // ================================================================= consumers
-    const int cw = warp - 2;
+    const int cw = warp - 1;
     const int slot = cw * SPW + lane / LPR;
     const int sl = lane % LPR;                    // lane within the slot
     const unsigned slot_mask = (LPR == 32) ? 0xffffffffu : (((1u << LPR) - 1u) << ((lane / LPR) * LPR));
@@ -210,7 +177,7 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
     }
     const bool slot_active = head_local < HC;
     const int consumer_threads = p.CW * 32;
-    const int ctid = threadIdx.x - 64;
+    const int ctid = threadIdx.x - 32;
 
     float qf[HPS][G][VEC], of[HPS][G][VEC], mrun[HPS][G], lrun[HPS][G];
 #pragma unroll
@@ -236,8 +203,6 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
     for (int it = 0; it < n_iters; ++it) {
         const int s = it % S;
         mbar_wait_bounded(&full_bar[s], (it / S) & 1, abort_flag, p.status);
-        if (sum_heads && (it % R) == 0 && it >= 2 * R)               // the reducer is done with this buffer's previous use
-            mbar_wait_bounded(&sc_empty[(it / R) & 1], ((it / R) / 2 - 1) & 1, abort_flag, p.status);
         const int valid = min(TT, ntok - it * TT);
         const unsigned char* kst = stage_base + (size_t)s * 2 * TT * row_bytes;
         const unsigned char* vst = kst + (size_t)TT * row_bytes;
@@ -340,9 +305,38 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[s]);          // the stage is free: the logits wait in their own buffer
         if (sum_heads && ((it % R) == R - 1 || it == n_iters - 1)) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sc_full[(it / R) & 1]);     // this warp's logits of the super-block are parked
+            // head sum in a fixed order for the whole super-block: 8 lanes per token, each adds every 8th
+            // head, then a butterfly; one thread per token stores the logit and counts its first radix digit
+            named_bar_sync(1, consumer_threads);
+            const int sb = it / R;
+            const float* blk = sc_smem + (size_t)(sb & 1) * R * TT * HC;
+            const int rows = ((it % R) + 1) * TT;
+            const int first = sb * R * TT;                  // token index (within the chunk) of row 0
+            for (int base = 0; base < rows; base += consumer_threads / 8) {   // uniform per warp
+                const int r = base + (ctid >> 3), j = ctid & 7;
+                const bool in = r < rows && first + r < ntok;
+                float a = 0.f;
+                if (in)
+                    for (int h = j; h < HC; h += 8) a += blk[r * HC + h];
+                a += __shfl_xor_sync(0xffffffffu, a, 4);
+                a += __shfl_xor_sync(0xffffffffu, a, 2);
+                a += __shfl_xor_sync(0xffffffffu, a, 1);
+                if (j == 0 && in) {
+                    const int pos = tok0 + first + r;
+                    p.scores[(size_t)b * p.score_stride + pos] = a;
+                    if (p.hist) {
+                        uint32_t bin = ordered_key(a) >> kDigit0Shift;
+                        if (p.force_last && pos == last_index) bin = TIDAL_TOPK_BINS - 1;
+                        atomicAdd(&sh_hist[bin], 1u);       // flushed to the row's global histogram once, below
+                    }
+                }
+            }
         }
+    }
+    if (sum_heads && p.hist) {
+        named_bar_sync(1, consumer_threads);
+        for (int i = ctid; i < TIDAL_TOPK_BINS; i += consumer_threads)
+            if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
     }
 
     // ---------------------------------------------------------------- epilogue
@@ -393,12 +387,6 @@ __global__ void __launch_bounds__(G >= 4 ? 320 : 576) decode_attn_kernel(const A
         }
     }
     }   // consumers
-    if (sum_heads && p.hist) {
-        // every warp is done with its role: flush the CTA's digit counts with all threads
-        __syncthreads();
-        for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x)
-            if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
-    }
     store_attention_result<T>(p, cta_o, cta_ml, HC, G, D, qh0, b, chunk);
 }
 
@@ -577,7 +565,7 @@ static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t s
     auto kern = decode_attn_kernel<T, D, G, HPS>;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
     dim3 grid(plan.nchunks, plan.nslices, p.B);
-    dim3 block((plan.CW + 2) * 32);     // producer warp, reducer warp, consumers
+    dim3 block((plan.CW + 1) * 32);
     TIDAL_CUDA_OK(launch_pdl(kern, grid, block, plan.smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
