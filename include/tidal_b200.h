@@ -176,6 +176,10 @@ typedef struct tidal_topk_args {
                                       r*row_stride + j%seg_len); d_in_idx is addressed the same way.  This is how the
                                       per-rank candidate blocks of an all-gathered buffer are ranked in place.
                                       Needs k <= 2048 and n <= 2097152. */
+    const int32_t* d_row_len;   /* NULL, or [rows] int32 on the device: the length of each row; n is then only their
+                                   upper bound and force_last refers to the row's own last element.  For decode steps
+                                   replayed as a CUDA graph, where lengths grow without the host's involvement.
+                                   Same limits as seg_len. */
 } tidal_topk_args;
 int tidal_topk(const tidal_topk_args* args, void* d_ws, size_t ws_bytes, void* stream);
 

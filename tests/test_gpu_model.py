@@ -234,3 +234,46 @@ def test_rms_norm_matches_reference_model(K, dtype, rows, hidden):
         assert (out.cpu() == want).float().mean() > 0.98
     with pytest.raises(RuntimeError):
         K.rms_norm_forward(x.cuda()[..., :-3].contiguous(), w.cuda()[:-3].contiguous(), out[..., :-3].contiguous(), 1e-6)
+
+
+def test_graph_decoder_matches_eager_and_reference():
+    """The decode step captured as one CUDA graph (device-side lengths, positions and token feedback)
+    produces the reference model's greedy tokens on configuration 1."""
+    from tidaldecode_b200.runtime import GraphDecoder
+
+    z = load_golden("tiny_llama_cfg1.npz")
+    W = O.TinyLlamaWeights()
+    g = torch.Generator().manual_seed(int(z["prompt_seed"]))
+    prompt = torch.randint(0, W.vocab, (1, 2048), generator=g)
+    m = _tiny_model(W, torch.float32, (2, 3), "none", False, 1)
+    m.tidal_init(page_size=1, max_seq_len=2048 + 64, token_budget=128, dtype=torch.float32, device=torch.device("cuda"))
+    rt = GraphDecoder(m, max_seq_len=2048 + 64)
+    first = rt.prefill(prompt)
+    toks = [int(first)] + rt.decode(31).cpu()[0].tolist()
+    assert toks == z["tokens"].tolist()
+    assert rt.c.workspace.status() == 0
+    assert rt.c.kv_cache.seqlen == 2048 + 31
+    # a second prompt through the same decoder: graph and buffers are reused
+    first = rt.prefill(prompt[:, :700])
+    again = [int(first)] + rt.decode(5).cpu()[0].tolist()
+    with torch.no_grad():
+        want = O.tiny_llama_greedy(W, prompt[:, :700], 6, 128, 2, 3)
+    assert again == want
+
+
+def test_graph_decoder_gqa_head_sum_bf16():
+    from tidaldecode_b200.runtime import GraphDecoder
+
+    W = O.TinyLlamaWeights(vocab=512, hidden=512, layers=4, heads=8, kv_heads=2, ffn=344, seed=3, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, W.vocab, (1, 300), generator=g)
+    m = _tiny_model(W, torch.bfloat16, (2,), "sum", True, 1)
+    rt = GraphDecoder(m, max_seq_len=340, token_budget=32)
+    first = rt.prefill(prompt)
+    graph_toks = [int(first)] + rt.decode(6).cpu()[0].tolist()
+    m2 = _tiny_model(W, torch.bfloat16, (2,), "sum", True, 1)
+    m2.tidal_init(page_size=1, max_seq_len=340, token_budget=32, dtype=torch.bfloat16, device=torch.device("cuda"))
+    with torch.inference_mode():
+        eager_toks = m2.greedy_generate(prompt.cuda(), 7)
+    assert graph_toks == eager_toks, (graph_toks, eager_toks)
+    assert rt.c.workspace.status() == 0

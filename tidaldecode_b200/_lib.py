@@ -47,7 +47,7 @@ class TopkArgs(C.Structure):
         ("d_out_idx", C.c_void_p), ("d_out_val", C.c_void_p), ("out_stride", C.c_int64),
         ("idx_offset", C.c_int32), ("force_last", C.c_int32), ("own_lo", C.c_int32), ("own_hi", C.c_int32),
         ("d_out_count", C.c_void_p), ("d_hist", C.c_void_p),
-        ("seg_len", C.c_int32), ("seg_stride", C.c_int64),
+        ("seg_len", C.c_int32), ("seg_stride", C.c_int64), ("d_row_len", C.c_void_p),
     ]
 
 

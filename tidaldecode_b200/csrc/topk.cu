@@ -57,6 +57,7 @@ struct TopkParams {
     uint32_t* status;
     int32_t seg_len;      // 0, or rows are made of segments seg_stride elements apart (cluster kernel only)
     int64_t seg_stride;
+    const int32_t* row_len;  // nullptr, or per-row lengths on the device (cluster kernel only); n is then their bound
 };
 
 // Offset of element j of a row whose contiguous layout would start at row*stride.
@@ -453,8 +454,9 @@ __device__ __forceinline__ void for_each_cluster_candidate(const TopkParams& p, 
     }
 }
 
-__global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkParams p) {
+__global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkParams p_in) {
     extern __shared__ __align__(16) unsigned char csm[];
+    TopkParams p = p_in;
     uint32_t* h = reinterpret_cast<uint32_t*>(csm);                                   // [kBins]
     uint64_t* sel = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);      // [kClusterMaxK]
     // Candidates of the threshold bin: in shared memory for short rows; long rows can put thousands of
@@ -474,6 +476,16 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     const unsigned rank = cluster.block_rank();
     const int row = blockIdx.x / CS;
     const int t = threadIdx.x;
+    if (p.row_len) {
+        // the row's length lives on the device (a decode step replayed as a CUDA graph grows it every step)
+        const int64_t n_dev = max(0, p.row_len[row]);
+        p.n = min(p.n, n_dev);
+        p.k = (int32_t)min((int64_t)p.k, p.n);
+        if (p.n == 0) {                       // uniform over the cluster: nobody reaches a cluster barrier
+            if (rank == 0 && t == 0 && p.out_count) p.out_count[row] = 0;
+            return;
+        }
+    }
     const float* srow = p.seg_len ? nullptr : p.scores + (size_t)row * p.row_stride;   // contiguous rows only
     auto score_at = [&](int64_t j) -> float { return p.scores[elem_off(p, p.row_stride, row, j)]; };
     const uint32_t k = (uint32_t)p.k;
@@ -705,8 +717,10 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     p.sel = (uint64_t*)((char*)d_ws + L->sel_off);
     p.cand_cap = L->cand_cap;
     p.status = (uint32_t*)((char*)d_ws + L->status_off);
-    p.seg_len = a->seg_len; p.seg_stride = a->seg_stride;
+    p.seg_len = a->seg_len; p.seg_stride = a->seg_stride; p.row_len = a->d_row_len;
     TIDAL_REQUIRE(a->seg_len >= 0, TIDAL_ERR_ARG, "negative seg_len");
+    TIDAL_REQUIRE(a->d_row_len == nullptr || ((int64_t)a->k < a->n && k <= kClusterMaxK && a->n <= kClusterMaxN), TIDAL_ERR_ARG,
+                  "device-side row lengths need k < n (the bound), k <= %d and n <= %lld", kClusterMaxK, (long long)kClusterMaxN);
     TIDAL_REQUIRE(a->seg_len == 0 || ((int64_t)a->k < a->n && k <= kClusterMaxK && a->n <= kClusterMaxN), TIDAL_ERR_ARG,
                   "segmented rows need k < n, k <= %d and n <= %lld", kClusterMaxK, (long long)kClusterMaxN);
     cudaStream_t st = (cudaStream_t)stream;
@@ -827,7 +841,7 @@ extern "C" int tidal_topk_static(const tidal_topk_args* a, uint32_t* d_status, v
     p.sel = &sc->sel[0][0];
     p.cand_cap = kStaticCand;
     p.status = d_status ? d_status : &sc->status[0];
-    p.seg_len = 0; p.seg_stride = 0;
+    p.seg_len = 0; p.seg_stride = 0; p.row_len = nullptr;
     topk_finish_kernel<true><<<a->rows, kTopkThreads, 0, (cudaStream_t)stream>>>(p, (int64_t)a->k >= a->n ? 1 : 0);
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();

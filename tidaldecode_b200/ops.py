@@ -174,6 +174,7 @@ def topk(
     out_count: Optional[torch.Tensor] = None,
     hist: Optional[torch.Tensor] = None,
     segments: Optional[tuple] = None,     # (rows, seg_len, seg_stride, row_stride): rows scattered over equal blocks
+    row_len: Optional[torch.Tensor] = None,   # int32 [rows] on the device; n is then their upper bound
 ) -> torch.Tensor:
     """Row-wise top-k index sets; see tidal_topk in include/tidal_b200.h."""
     _need_cuda(out_idx, out_val, out_count, hist)
@@ -207,6 +208,7 @@ def topk(
     if own_range is not None:
         a.own_lo, a.own_hi = int(own_range[0]), int(own_range[1])
     a.d_out_count, a.d_hist = _ptr(out_count), _ptr(hist)
+    a.d_row_len = _ptr(row_len)
     with torch.cuda.device(scores.device):
         check(lib.tidal_topk(C.byref(a), ws.buf.data_ptr(), ws.nbytes, _stream()), "tidal_topk")
     return out_idx

@@ -52,10 +52,13 @@ class KvPool:
         return self._free.pop()
 
     def free_block(self, idx: int):
-        assert 0 <= idx < self.capacity
-        self._free.append(idx)
-        if len(self._free) > 1 and self._free[-2] < idx:
-            self._free.sort(reverse=True)
+        self.free_blocks([idx])
+
+    def free_blocks(self, ids):
+        for idx in ids:
+            assert 0 <= idx < self.capacity
+        self._free.extend(ids)
+        self._free.sort(reverse=True)
 
 
 class KvCache:
@@ -94,39 +97,47 @@ class KvCache:
 
     @property
     def indicies(self):
-        """Page ids of sequence 0 (the reference's only sequence)."""
-        return self._indicies[0]
+        """Page ids in use by sequence 0 (the reference's only sequence)."""
+        return self._indicies[0][: self.num_pages]
 
     @property
     def num_pages(self) -> int:
-        return len(self._indicies[0])
+        """Pages in use by the current sequence length (reserved pages beyond it are not counted)."""
+        return (self._seqlen + self._pool.block_len - 1) // self._pool.block_len
 
     def buf_layer(self, layer_idx: int):
         return self._pool.buf[layer_idx % self._pool.num_layers]
 
-    def append_seq(self, seq_len: int) -> int:
-        """Reserve space for seq_len more tokens per sequence; returns pages added per sequence."""
-        if seq_len <= 0:
-            return 0
+    def _ensure_pages(self, n_pages: int) -> int:
+        """Allocate until every sequence owns n_pages pages; extends the device page table by the new entries."""
         added = 0
-        for _ in range(seq_len):
-            if self._seqlen % self._pool.block_len == 0:
-                for b in range(self.batch_size):
-                    self._indicies[b].append(self._pool.alloc_block())
-                added += 1
-            self._seqlen += 1
+        while len(self._indicies[0]) < n_pages:
+            for b in range(self.batch_size):
+                self._indicies[b].append(self._pool.alloc_block())
+            added += 1
         if added:
-            n0, n1 = self._synced, self.num_pages
+            n0, n1 = self._synced, len(self._indicies[0])
             for b in range(self.batch_size):
                 self._stage[b, n0:n1] = torch.tensor(self._indicies[b][n0:n1], dtype=torch.int32)
             self.page_table[:, n0:n1].copy_(self._stage[:, n0:n1], non_blocking=True)
             self._synced = n1
         return added
 
+    def reserve(self, total_tokens: int) -> None:
+        """Own the pages for `total_tokens` tokens per sequence now, so that later appends touch neither the
+        allocator nor the page table (a decode step replayed as a CUDA graph needs exactly that)."""
+        self._ensure_pages((total_tokens + self._pool.block_len - 1) // self._pool.block_len)
+
+    def append_seq(self, seq_len: int) -> int:
+        """Make room for seq_len more tokens per sequence; returns pages added per sequence."""
+        if seq_len <= 0:
+            return 0
+        self._seqlen += seq_len
+        return self._ensure_pages(self.num_pages)
+
     def release(self):
         self._seqlen = 0
         for b in range(self.batch_size):
-            for idx in self._indicies[b]:
-                self._pool.free_block(idx)
+            self._pool.free_blocks(self._indicies[b])
             self._indicies[b].clear()
         self._synced = 0
