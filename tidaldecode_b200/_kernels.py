@@ -163,11 +163,14 @@ def prefill_with_paged_kv_cache(q, kv_data, kv_indices, kv_last_page_len, causal
     Hq = q.shape[1]
     qq = q.transpose(0, 1)[None]                                              # [1,Hq,seq,D]
     n_q = q.shape[0]
-    if causal and n_q > 1:
-        mask = torch.ones(n_q, seq_len, dtype=torch.bool, device=q.device).tril(diagonal=seq_len - n_q)
+    if causal and n_q > 1 and n_q == seq_len:
+        # the whole prompt at once: the fused causal kernel, no mask tensor
+        o = torch.nn.functional.scaled_dot_product_attention(qq, K, V, is_causal=True, enable_gqa=(Hq != Hkv))
     else:
         mask = None
-    o = torch.nn.functional.scaled_dot_product_attention(qq, K, V, attn_mask=mask, enable_gqa=(Hq != Hkv))
+        if causal and n_q > 1:      # a later chunk of a prompt: rows see the history and their own prefix
+            mask = torch.ones(n_q, seq_len, dtype=torch.bool, device=q.device).tril(diagonal=seq_len - n_q)
+        o = torch.nn.functional.scaled_dot_product_attention(qq, K, V, attn_mask=mask, enable_gqa=(Hq != Hkv))
     return o[0].transpose(0, 1).contiguous()
 
 
