@@ -52,8 +52,13 @@ class GraphDecoder:
         self.step_idx = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.out_tokens = torch.zeros(self.B, self.max_seq_len, dtype=torch.int64, device=self.device)
         self.graph = None
-        self._captured_steps = 0
         self.logits = None
+        # one GEMV for q,k,v and one for gate,up per layer (three and two in the module): fewer launches per token
+        self._wqkv, self._wgu = [], []
+        for layer in model.model.layers:
+            a, mlp = layer.self_attn, layer.mlp
+            self._wqkv.append(torch.cat((a.q_proj.weight, a.k_proj.weight, a.v_proj.weight), dim=0).contiguous())
+            self._wgu.append(torch.cat((mlp.gate_proj.weight, mlp.up_proj.weight), dim=0).contiguous())
 
     # ------------------------------------------------------------------ prefill
     @torch.inference_mode()
@@ -87,12 +92,15 @@ class GraphDecoder:
         ws = c.workspace
         h = m.model.embed_tokens(self.tok)                  # [B,1,hidden]
         cnt_shape = (B,) if c.score_rows == 1 else (B, c.num_heads)
-        for layer in m.model.layers:
+        F = torch.nn.functional
+        for li, layer in enumerate(m.model.layers):
             att = layer.self_attn
             x = layer.input_layernorm(h)
-            q = att.q_proj(x).view(B, att.num_heads, att.head_dim)
-            kk = att.k_proj(x).view(B, att.num_key_value_heads, att.head_dim)
-            vv = att.v_proj(x).view(B, att.num_key_value_heads, att.head_dim)
+            nq, nkv = att.num_heads * att.head_dim, att.num_key_value_heads * att.head_dim
+            qkv = F.linear(x, self._wqkv[li]).view(B, nq + 2 * nkv)
+            q = qkv[:, :nq].contiguous().view(B, att.num_heads, att.head_dim)
+            kk = qkv[:, nq:nq + nkv].contiguous().view(B, att.num_key_value_heads, att.head_dim)
+            vv = qkv[:, nq + nkv:].contiguous().view(B, att.num_key_value_heads, att.head_dim)
             pool = c.kv_cache.buf_layer(att.layer_idx)
             ops.rope_append(q, kk, vv, pool, batch=B, pos0_dev=self.pos, page_table=table, rope_theta=att.rope_theta,
                             rope_scale=att.rope_scale, rope_mode=att.rope_mode, inv_freq=att._inv_freq_on(self.device))
@@ -109,7 +117,9 @@ class GraphDecoder:
             else:
                 ops.decode_attention(q, pool, self.max_seq_len, ws, out=o, page_table=table, seq_lens=self.seq_lens)
             h = h + att.o_proj(o.view(B, 1, -1))
-            h = h + layer.mlp(layer.post_attention_layernorm(h))
+            gu = F.linear(layer.post_attention_layernorm(h), self._wgu[li])
+            ffn = gu.shape[-1] // 2
+            h = h + layer.mlp.down_proj(F.silu(gu[..., :ffn]) * gu[..., ffn:])
         logits = m.lm_head(m.model.norm(h))
         nxt = logits.argmax(-1)                             # [B,1]
         self.out_tokens.index_copy_(1, self.step_idx, nxt)
