@@ -350,6 +350,44 @@ def test_variable_lengths_and_counts(T):
     assert ws.status() == 0
 
 
+LONG_LIST_CASES = [
+    # dtype, B, Hq, Hkv, D, N, k, page_size, shuffle, kwargs  — lists long enough (two chunks) that every CTA looks
+    # up several blocks of pool rows, on every producer layout (1, 2 and 4 producer warps, stages of 16 and 32 tokens)
+    ("bf16", 2, 32, 8, 128, 6000, 3000, 1, False, dict(use_tensor_cores=-1, heads_per_cta=2)),   # 4 producers, 16-token stages
+    ("bf16", 2, 32, 8, 128, 6000, 3000, 1, False, dict(use_tensor_cores=-1, heads_per_cta=1)),   # 4 producers, 32-token stages
+    ("bf16", 2, 32, 8, 128, 6000, 3000, 1, False, dict(heads_per_cta=2)),                        # tensor cores, 2 producers
+    ("bf16", 2, 32, 8, 128, 6000, 3000, 1, False, dict()),                                       # tensor cores, K|V in one copy
+    ("bf16", 1, 32, 8, 128, 6000, 3000, 4, True, dict()),                                        # paged: 2 producers, 16-token stages
+    ("f16", 1, 32, 32, 128, 5000, 2500, 1, False, dict()),                                       # CUDA cores, whole rows
+    ("f16", 1, 32, 32, 128, 5000, 2500, 1, True, dict(heads_per_cta=1)),                          # 256-byte rows, page table
+    ("f16", 2, 8, 8, 64, 4000, 1999, 3, True, dict(heads_per_cta=2)),
+]
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,N,k,page,shuffle,kw", LONG_LIST_CASES)
+def test_long_selection_lists(T, dt, B, Hq, Hkv, D, N, k, page, shuffle, kw):
+    dtype = DT[dt]
+    q, K, V = make_qkv(23, B, Hq, Hkv, D, N, dtype)
+    pool, table, ppb = build_pool(K, V, page, shuffle_seed=5 if shuffle else None)
+    g = torch.Generator().manual_seed(3)
+    sel = torch.stack([torch.randperm(N, generator=g)[:k] for _ in range(B)]).to(torch.int32)
+    ws = _ws(T, B, Hq, D, B, N)
+    o = T.decode_attention(q[:, :, 0].contiguous().cuda(), pool.cuda(), N, ws, pages_per_seq=ppb,
+                           page_table=None if table is None else table.cuda(), sel_idx=sel.cuda(), num_chunks=2, **kw)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    for b in range(B):
+        want = O.gathered_attention(q[b:b + 1], K[b:b + 1], V[b:b + 1], sel[b:b + 1])
+        assert_close(o[b], want[0, :, 0], dtype, f"sequence {b}")
+    # the same list in a full layer's clothes: long paged sequences take the same lookups
+    if table is not None:
+        o_full = T.decode_attention(q[:, :, 0].contiguous().cuda(), pool.cuda(), N, ws, pages_per_seq=ppb, page_table=table.cuda(),
+                                    num_chunks=3, **kw)
+        want = O.gathered_attention(q, K, V, torch.arange(N, dtype=torch.int32)[None].expand(B, N))
+        assert_close(o_full, want[:, :, 0], dtype, "full layer through the page table")
+        assert ws.status() == 0
+
+
 def test_bad_index_is_flagged_not_followed(T):
     B, H, D, N = 1, 8, 128, 100
     q, K, V = make_qkv(1, B, H, H, D, N, torch.float16)

@@ -272,6 +272,37 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
+// Timeline stamps for debugging (compiled only with -DTIDAL_TRACE; nothing in a normal build).
+// Each translation unit that stamps has its own array [kTraceCtas][kTraceSlots][2] of
+// (%globaltimer ns, clock64) and exports a reader through TIDAL_TRACE_READER(name).
+#ifdef TIDAL_TRACE
+constexpr int kTraceSlots = 16, kTraceCtas = 2048;
+static __device__ unsigned long long g_trace[kTraceCtas * kTraceSlots * 2];
+__device__ __forceinline__ void trace_stamp(int slot) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (cta < kTraceCtas) {
+        g_trace[(cta * kTraceSlots + slot) * 2] = t;
+        g_trace[(cta * kTraceSlots + slot) * 2 + 1] = (unsigned long long)clock64();
+    }
+}
+#define TIDAL_STAMP(slot) ::tidal::trace_stamp(slot)
+#define TIDAL_TRACE_READER(name)                                                                              \
+    extern "C" int name(unsigned long long* host, int clear) {                                                 \
+        cudaError_t e = cudaMemcpyFromSymbol(host, ::tidal::g_trace, sizeof(::tidal::g_trace));                \
+        if (e == cudaSuccess && clear) {                                                                       \
+            void* d = nullptr;                                                                                 \
+            e = cudaGetSymbolAddress(&d, ::tidal::g_trace);                                                    \
+            if (e == cudaSuccess) e = cudaMemset(d, 0, sizeof(::tidal::g_trace));                              \
+        }                                                                                                      \
+        return e == cudaSuccess ? 0 : -3;                                                                      \
+    }
+#else
+#define TIDAL_STAMP(slot) ((void)0)
+#define TIDAL_TRACE_READER(name)
+#endif
+
 constexpr float kLog2e = 1.4426950408889634f;
 
 }  // namespace tidal

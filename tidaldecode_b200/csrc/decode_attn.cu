@@ -34,8 +34,10 @@ __host__ __device__ constexpr int attn_tps(int G) { return G >= 4 ? 2 : 4; }
 
 // T: storage type; D: head dim; G: q heads per KV head handled by one slot;
 // HPS: KV heads per slot.
-template <typename T, int D, int G, int HPS>
-__global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const AttnParams p) {
+// MPW: most producer warps the instance can be launched with (1 or kMaxProducerWarps); the instances
+// with one producer keep the tighter launch bound, which the long streaming layers are tuned for.
+template <typename T, int D, int G, int HPS, int MPW>
+__global__ void __launch_bounds__(((G >= 4 ? 8 : 16) + MPW) * 32) decode_attn_kernel(const __grid_constant__ AttnParams p) {
     using V = Vec16<T>;
     constexpr int VEC = V::N;
     constexpr int LPR = D / VEC;          // lanes per row
@@ -44,12 +46,15 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     static_assert(LPR <= 32 && (32 % LPR) == 0, "row must fit a warp");
 
     extern __shared__ __align__(128) unsigned char smem[];
-    pdl_wait();                 // ordered after the earlier kernels of the stream (see common.cuh)
-    pdl_launch_dependents();
+    __shared__ uint32_t src_row[2 * kAddrBlock];  // pool rows of the producers' current and next block of list entries
     const int row_bytes = p.HC * D * (int)sizeof(T);
     const int S = p.S, TT = p.T, TG = p.TG, HC = p.HC;
     const int slots = p.CW * SPW;
-    const size_t stage_bytes = (size_t)S * 2 * TT * row_bytes;
+    // K rows then V rows, or token-major K|V when both arrive in one copy
+    const int pitch = p.kv_fused ? 2 * row_bytes : row_bytes;
+    const int v_base = p.kv_fused ? row_bytes : TT * row_bytes;
+    const size_t stage_stride = (size_t)2 * TT * row_bytes;
+    const size_t stage_bytes = (size_t)S * stage_stride;
     const size_t ep_bytes = (size_t)slots * HPS * G * (D + 2) * sizeof(float);
     const size_t main_bytes = round16(stage_bytes > ep_bytes + cta_result_bytes(p.HC, G, D) ? stage_bytes
                                                                                              : ep_bytes + cta_result_bytes(p.HC, G, D));
@@ -69,6 +74,25 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     const int chunk = blockIdx.x, slice = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    if (threadIdx.x == 0) {
+        TIDAL_STAMP(0);
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], p.CW);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (sum_heads && p.hist)
+        for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x) sh_hist[i] = 0;
+    // the prologue above touched no global memory; from here on this kernel is ordered
+    // after the earlier kernels of the stream (see common.cuh)
+    // a cluster's CTAs write into each other's shared memory at the end: all of them must be running
+    if (p.cluster > 1) cooperative_groups::this_cluster().sync();
+    if (threadIdx.x == 0) TIDAL_STAMP(1);
+    pdl_wait();
+    if (threadIdx.x == 0) TIDAL_STAMP(2);
+    pdl_launch_dependents();
     // ---- token list of this CTA
     const int sel_row = p.sel_idx ? (p.sel_rows == 1 ? 0 : slice) : 0;
     int list_len;
@@ -93,77 +117,18 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     const int kvh0 = p.per_head ? slice / p.greal : slice * HC;   // first KV head of the CTA
     const int qh0 = p.per_head ? slice : kvh0 * G;                // first q head of the CTA
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], p.CW);
-        }
-        *abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (sum_heads && p.hist)
-        for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x) sh_hist[i] = 0;
+    const TokenList tl{b, sel_row, list_len, seq_len_b, tok0, ntok};
+    fill_first_rows(p, tl, src_row);
     __syncthreads();
+    if (threadIdx.x == 0) TIDAL_STAMP(3);
 
-    if (warp == 0) {
-        // =============================================================== producer
-        const size_t plane = (size_t)p.page_size * p.Hkv * D * sizeof(T);   // bytes of one K (or V) plane of a page
-        const size_t tok_bytes = (size_t)p.Hkv * D * sizeof(T);
-        for (int it = 0; it < n_iters; ++it) {
-            const int s = it % S;
-            if (it >= S) mbar_wait_bounded(&empty_bar[s], ((it / S) - 1) & 1, abort_flag, p.status);
-            const int valid = min(TT, ntok - it * TT);
-            if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(valid * 2 * row_bytes));
-            __syncwarp();
-            unsigned char* kdst = stage_base + (size_t)s * 2 * TT * row_bytes;
-            unsigned char* vdst = kdst + (size_t)TT * row_bytes;
-            for (int t = lane; t < valid; t += 32) {
-                const int li = tok0 + it * TT + t;   // index into the CTA's sequence-wide list
-                int64_t page;
-                int entry = 0;
-                bool ok = true;
-                if (p.sel_idx) {
-                    if (li >= list_len) {
-                        page = p.extra_page;           // the appended newest token
-                    } else {
-                        const int e = p.sel_idx[((size_t)b * p.sel_rows + sel_row) * p.sel_stride + li];
-                        if (p.sel_physical) {
-                            page = e;
-                        } else {
-                            ok = (e >= 0 && e < seq_len_b);
-                            const int pos = ok ? e : 0;
-                            const int pg = pos / p.page_size;
-                            entry = pos - pg * p.page_size;
-                            page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
-                        }
-                    }
-                } else {
-                    const int pg = li / p.page_size;
-                    entry = li - pg * p.page_size;
-                    page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
-                }
-                if (!ok || page < 0 || page >= p.num_pages) {
-                    atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
-                    page = 0;
-                    entry = 0;
-                }
-                const char* ksrc = p.kv + (size_t)page * 2 * plane + (size_t)entry * tok_bytes + (size_t)kvh0 * D * sizeof(T);
-                bulk_g2s(kdst + (size_t)t * row_bytes, ksrc, (uint32_t)row_bytes, &full_bar[s]);
-                bulk_g2s(vdst + (size_t)t * row_bytes, ksrc + plane, (uint32_t)row_bytes, &full_bar[s]);
-            }
-        }
-        // Nothing of this CTA may still be in flight when it retires: the consumers
-        // waited on every full barrier unless a wait ran out; cover that case here.
-        if (*abort_flag && lane == 0) {
-            for (int it = max(0, n_iters - S); it < n_iters; ++it) {
-                const int s = it % S;
-                for (uint32_t i = 0; i < kWaitSpinLimit; ++i)
-                    if (mbar_try_wait(&full_bar[s], (it / S) & 1)) break;
-            }
-        }
+    if (warp < p.PW) {
+        // ============================================================== producers
+        produce_stages<MPW>(p, tl, src_row, warp, lane, S, TT, n_iters, (uint32_t)row_bytes, (uint32_t)pitch, (uint32_t)v_base, stage_stride,
+                       (size_t)kvh0 * D * sizeof(T), (size_t)p.Hkv * D * sizeof(T), stage_base, full_bar, empty_bar, abort_flag);
     } else {
     // ================================================================= consumers
-    const int cw = warp - 1;
+    const int cw = warp - p.PW;
     const int slot = cw * SPW + lane / LPR;
     const int sl = lane % LPR;                    // lane within the slot
     const unsigned slot_mask = (LPR == 32) ? 0xffffffffu : (((1u << LPR) - 1u) << ((lane / LPR) * LPR));
@@ -177,7 +142,7 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     }
     const bool slot_active = head_local < HC;
     const int consumer_threads = p.CW * 32;
-    const int ctid = threadIdx.x - 32;
+    const int ctid = threadIdx.x - 32 * p.PW;
 
     float qf[HPS][G][VEC], of[HPS][G][VEC], mrun[HPS][G], lrun[HPS][G];
 #pragma unroll
@@ -203,9 +168,10 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
     for (int it = 0; it < n_iters; ++it) {
         const int s = it % S;
         mbar_wait_bounded(&full_bar[s], (it / S) & 1, abort_flag, p.status);
+        if (ctid == 0 && it == 0) TIDAL_STAMP(6);
         const int valid = min(TT, ntok - it * TT);
-        const unsigned char* kst = stage_base + (size_t)s * 2 * TT * row_bytes;
-        const unsigned char* vst = kst + (size_t)TT * row_bytes;
+        const unsigned char* kst = stage_base + (size_t)s * stage_stride;
+        const unsigned char* vst = kst + v_base;
         float* sc = sc_smem + ((size_t)((it / R) & 1) * R + (it % R)) * TT * HC;   // this stage's rows of the super-block
         if (slot_active) {
             // The slot's TPS tokens of this stage are processed together: independent dot
@@ -218,7 +184,7 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
                     float kf[TPS][VEC];
 #pragma unroll
                     for (int j = 0; j < TPS; ++j)
-                        V::to_float(*reinterpret_cast<const uint4*>(kst + (size_t)(tg + j * TG) * row_bytes + hoff), kf[j]);
+                        V::to_float(*reinterpret_cast<const uint4*>(kst + (size_t)(tg + j * TG) * pitch + hoff), kf[j]);
 #pragma unroll
                     for (int j = 0; j < TPS; ++j)
 #pragma unroll
@@ -239,7 +205,7 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
 #pragma unroll
                 for (int j = 0; j < TPS; ++j) {
                     if (tg + j * TG < valid) {
-                        V::to_float(*reinterpret_cast<const uint4*>(vst + (size_t)(tg + j * TG) * row_bytes + hoff), vf[j]);
+                        V::to_float(*reinterpret_cast<const uint4*>(vst + (size_t)(tg + j * TG) * pitch + hoff), vf[j]);
                     } else {
                         // rows beyond the stage's valid tokens hold stale bytes: their weight is 0, and 0 * NaN is NaN
 #pragma unroll
@@ -333,6 +299,7 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
             }
         }
     }
+    if (ctid == 0) TIDAL_STAMP(7);
     if (sum_heads && p.hist) {
         named_bar_sync(1, consumer_threads);
         for (int i = ctid; i < TIDAL_TOPK_BINS; i += consumer_threads)
@@ -386,8 +353,9 @@ __global__ void __launch_bounds__(G >= 4 ? 288 : 544) decode_attn_kernel(const A
             cta_ml[2 * hg + 1] = L;
         }
     }
+    if (ctid == 0) TIDAL_STAMP(8);
     }   // consumers
-    store_attention_result<T>(p, cta_o, cta_ml, HC, G, D, qh0, b, chunk);
+    store_attention_result<T>(p, cta_o, cta_ml, reinterpret_cast<float*>(smem + p.recv_off), HC, G, D, qh0, b, chunk);
 }
 
 // Merge the split-KV partials of one (sequence, q head): grid (Hq, B), 1024 threads as
@@ -517,10 +485,10 @@ static int sm_count_cached() {
     return n;
 }
 
-constexpr size_t kSmemBudget = 227 * 1024 - 512;   // per CTA (227 KB is the hardware limit)
+constexpr size_t kSmemBudget = 227 * 1024 - 512 - sizeof(uint32_t) * 2 * kAddrBlock;   // per CTA (227 KB is the hardware limit)
 
 // Pick the slot geometry for HC heads per CTA; false if HC cannot be mapped.
-static bool plan_slots(int HC, int lpr, bool allow_hps2, int max_cw, int* CW, int* HPS, int* TG) {
+static bool plan_slots(int HC, int lpr, bool allow_hps2, int max_cw, int tps, int* CW, int* HPS, int* TG) {
     const int spw = 32 / lpr;
     // more consumer warps hide the shuffle and shared-memory latency of the dot products better
     // than more heads per slot (measured: 16 warps x 1 head beats 8 warps x 2 heads by 16 %)
@@ -528,6 +496,7 @@ static bool plan_slots(int HC, int lpr, bool allow_hps2, int max_cw, int* CW, in
     for (int cw : order) {
         if (cw > max_cw) continue;
         const int slots = cw * spw;
+        if (slots % HC == 0 && (slots / HC) * tps > kAddrBlock) continue;    // a stage must fit a block of looked-up rows
         if (slots % HC == 0) {
             *CW = cw; *HPS = 1; *TG = slots / HC;
             return true;
@@ -560,15 +529,20 @@ extern "C" int tidal_plan_chunks(int batch, int head_slices, int tokens, int min
 
 namespace tidal {
 
-template <typename T, int D, int G, int HPS>
-static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t st) {
-    auto kern = decode_attn_kernel<T, D, G, HPS>;
+template <typename T, int D, int G, int HPS, int MPW>
+static int launch_attn_pw(const AttnParams& p, const AttnPlan& plan, cudaStream_t st) {
+    auto kern = decode_attn_kernel<T, D, G, HPS, MPW>;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
     dim3 grid(plan.nchunks, plan.nslices, p.B);
-    dim3 block((plan.CW + 1) * 32);
+    dim3 block((plan.CW + p.PW) * 32);
     TIDAL_CUDA_OK(launch_pdl(kern, grid, block, plan.smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
+}
+
+template <typename T, int D, int G, int HPS>
+static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t st) {
+    return p.PW == 1 ? launch_attn_pw<T, D, G, HPS, 1>(p, plan, st) : launch_attn_pw<T, D, G, HPS, kMaxProducerWarps>(p, plan, st);
 }
 
 template <typename T, int D>
@@ -626,6 +600,8 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
                   "num_qo_heads %d is not a multiple of num_kv_heads %d", a->num_qo_heads, a->num_kv_heads);
     TIDAL_REQUIRE(a->page_size >= 1 && a->num_pages >= 1, TIDAL_ERR_ARG, "bad page_size/num_pages");
     TIDAL_REQUIRE(a->seq_len >= 0, TIDAL_ERR_ARG, "negative seq_len");
+    TIDAL_REQUIRE(a->num_pages * 2 * a->page_size < ((int64_t)1 << 32), TIDAL_ERR_ARG,
+                  "the pool has more than 2^32 token rows (num_pages * 2 * page_size)");
     TIDAL_REQUIRE(a->dtype >= 0 && a->dtype <= 2, TIDAL_ERR_ARG, "unknown dtype %d", a->dtype);
     const int G = a->num_qo_heads / a->num_kv_heads;
     const int D = a->head_dim;
@@ -642,6 +618,12 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
                       "head-summed logits over per-head lists are undefined");
     } else {
         TIDAL_REQUIRE(a->extra_page < 0, TIDAL_ERR_ARG, "extra_page needs a selection list");
+        if (!a->d_page_table) {
+            // identity mapping: sequence b occupies pages [b * stride, b * stride + pages of seq_len)
+            const int64_t need = (int64_t)(a->batch - 1) * a->page_table_stride + (a->seq_len + a->page_size - 1) / a->page_size;
+            TIDAL_REQUIRE(a->page_table_stride >= 0 && need <= a->num_pages, TIDAL_ERR_ARG,
+                          "identity page mapping needs %lld pages, the pool has %lld", (long long)need, (long long)a->num_pages);
+        }
     }
     if (a->d_scores) {
         TIDAL_REQUIRE(a->score_rows == 1 || a->score_rows == a->num_qo_heads, TIDAL_ERR_ARG,
@@ -675,7 +657,7 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
             plan.CW = kMmaWarps; plan.HPS = 1; plan.TG = kMmaWarps / hc;
             plan.T = kMmaTile * plan.TG;
         } else {
-            if (!plan_slots(hc, lpr, kernel_G == 1, max_cw, &plan.CW, &plan.HPS, &plan.TG)) return false;
+            if (!plan_slots(hc, lpr, kernel_G == 1, max_cw, attn_tps(kernel_G), &plan.CW, &plan.HPS, &plan.TG)) return false;
             plan.T = plan.TG * attn_tps(kernel_G);
         }
         plan.HC = hc;
@@ -698,7 +680,8 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     if (!use_mma) {
         int hc = hc0 ? hc0 : a->num_kv_heads;
         // rows of 4 KB stream a little faster than rows of 8 KB (measured 88.7 vs 92.8 us at 32 x 128 fp16)
-        if (!hc0 && a->num_kv_heads % 2 == 0 && a->num_kv_heads * D * es >= 8192) hc = a->num_kv_heads / 2;
+        // — but a gathered list wants the longest rows it can get (fewer copies per byte: 172 vs 218 us for 1 GiB)
+        if (!hc0 && !sel && a->num_kv_heads % 2 == 0 && a->num_kv_heads * D * es >= 8192) hc = a->num_kv_heads / 2;
         TIDAL_REQUIRE(per_head || a->num_kv_heads % hc == 0, TIDAL_ERR_ARG, "heads_per_cta %d does not divide num_kv_heads %d", hc,
                       a->num_kv_heads);
         if (!set_heads(hc, false)) {
@@ -715,7 +698,11 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     int cluster = 1;
     const size_t list_bytes = (size_t)ntok * 2 * a->num_kv_heads * D * es;
     if (sel && a->num_chunks == 0 && ntok >= 1 && list_bytes <= ((size_t)8 << 20)) {
-        if (!hc0) {
+        // ... unless the CTA takes all KV heads of a token in one copy (tensor-core kernel, page_size 1):
+        // splitting the heads would double the copies per byte, which costs more than idle SMs
+        // (measured 7.0 vs 8.5 us at 4 sequences x 8 KV heads x 128 tokens).
+        const bool one_copy = use_mma && a->page_size == 1 && plan.HC == a->num_kv_heads;
+        if (!hc0 && !one_copy) {
             int hc = plan.HC;
             while (hc > 1 && a->batch * plan.nslices * 8 < 64 && set_heads(hc / 2, use_mma)) hc = plan.HC;
         }
@@ -733,10 +720,13 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
                   plan.nchunks, kMaxChunks);
     const int slots = plan.CW * (32 / lpr);
-    auto smem_of = [&](int S) {
-        return use_mma ? attn_mma_smem_bytes(S, plan.HC, kernel_G, D, sum_heads)
-                       : attn_smem_bytes(S, plan.T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads);
+    // a cluster CTA also holds a receive block for the merge, behind everything else
+    const size_t recv_bytes = cluster > 1 ? cluster_recv_bytes(plan.HC, kernel_G, D, cluster) : 0;
+    auto smem_base = [&](int S) {
+        return round16(use_mma ? attn_mma_smem_bytes(S, plan.HC, kernel_G, D, sum_heads)
+                               : attn_smem_bytes(S, plan.T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads));
     };
+    auto smem_of = [&](int S) { return smem_base(S) + recv_bytes; };
     int S = 8;
     while (S > 1 && smem_of(S) > kSmemBudget) --S;
     // no more stages than the longest chunk can use (short lists: less shared memory to set up)
@@ -744,7 +734,7 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     if (S > iters) S = iters < 1 ? 1 : iters;
     plan.S = S;
     plan.smem = smem_of(S);
-    TIDAL_REQUIRE(plan.smem <= 227 * 1024, TIDAL_ERR_ARG, "shared memory %zu exceeds 227 KB (row %d bytes)", plan.smem, row_bytes);
+    TIDAL_REQUIRE(plan.smem + sizeof(uint32_t) * 2 * kAddrBlock <= 227 * 1024, TIDAL_ERR_ARG, "shared memory %zu exceeds 227 KB (row %d bytes)", plan.smem, row_bytes);
 
     AttnParams p;
     p.q = a->d_q; p.o = a->d_o; p.kv = (const char*)a->d_kv;
@@ -764,6 +754,16 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     p.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)D);
     p.nchunks = plan.nchunks; p.HC = plan.HC; p.greal = G; p.per_head = per_head ? 1 : 0;
     p.T = plan.T; p.S = plan.S; p.TG = plan.TG; p.CW = plan.CW; p.cluster = cluster;
+    p.recv_off = (uint32_t)smem_base(plan.S);
+    p.kv_fused = (a->page_size == 1 && plan.HC == a->num_kv_heads && !per_head) ? 1 : 0;
+    // One warp gets a bulk copy accepted every ~70 cycles, so short rows want more producer warps.
+    // On the CUDA-core kernel that is a second instance of the kernel: with rows of 1 KB and more the
+    // single-producer instance is kept, because a step that alternates between two instances pays more
+    // in cold instruction fetches than the extra producers gain (measured: 119.8 vs 121.5 us per step of
+    // a selection and a sparse layer at 32 x 128 heads).
+    const int copy_bytes = (p.kv_fused ? 2 : 1) * row_bytes;
+    if (use_mma) p.PW = copy_bytes <= 2048 ? kMmaMaxProducers : 1;
+    else p.PW = copy_bytes <= 512 ? kMaxProducerWarps : 1;
     const size_t part_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * D;
     TIDAL_REQUIRE(plan.nchunks == 1 || cluster > 1 || L->part_o_off + part_need <= L->part_ml_off, TIDAL_ERR_WORKSPACE,
                   "workspace was sized for a smaller batch/heads/head_dim than this call");
@@ -816,3 +816,5 @@ extern "C" int tidal_merge_partials(const float* d_m, const float* d_l, const fl
                                     int num_qo_heads, int head_dim, void* d_out, int dtype, void* stream) {
     return tidal_merge_partials_strided(d_m, d_l, d_o, 0, shards, batch, num_qo_heads, head_dim, d_out, dtype, stream);
 }
+
+TIDAL_TRACE_READER(tidal_trace_read_cc)

@@ -72,16 +72,20 @@ size_t attn_mma_smem_bytes(int S, int HC, int G, int D, bool sum_heads) {
 }
 
 template <typename T, int D>
-__global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__((kMmaWarps + 1 + kMmaMaxProducers) * 32) decode_attn_mma_kernel(const __grid_constant__ AttnParams p) {
     constexpr int KS = D / 16;    // k-steps of Q K^T
     constexpr int NT = D / 8;     // n-tiles of P V
     using M = Mma16<T>;
 
     extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint32_t src_row[2 * kAddrBlock];  // pool rows of the producers' current and next block of list entries
     const int HC = p.HC, S = p.S, TG = kMmaWarps / HC, TT = kMmaTile * TG;
-    const int pitch = mma_pitch(HC, D);
     const int row_bytes = HC * D * 2;
-    const size_t stage_bytes = (size_t)S * 2 * TT * pitch;
+    // token rows carry a 16-byte pad; K rows then V rows, or token-major K|V when both arrive in one copy
+    const int pitch = p.kv_fused ? 2 * row_bytes + 16 : mma_pitch(HC, D);
+    const int v_base = p.kv_fused ? row_bytes : TT * pitch;
+    const size_t stage_stride = (size_t)2 * TT * mma_pitch(HC, D);
+    const size_t stage_bytes = (size_t)S * stage_stride;
     const int G = p.per_head ? 1 : p.greal;
     const size_t ep_bytes = (size_t)kMmaWarps * 16 * (D + 2) * sizeof(float);
     const size_t main_bytes = round16(stage_bytes > ep_bytes + cta_result_bytes(HC, G, D) ? stage_bytes
@@ -105,6 +109,7 @@ __global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
+        TIDAL_STAMP(0);
         for (int s = 0; s < S; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], kMmaWarps);
@@ -126,7 +131,11 @@ __global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(c
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // the prologue above touched no global memory; from here on this kernel is ordered
     // after the earlier kernels of the stream (see common.cuh)
+    // a cluster's CTAs write into each other's shared memory at the end: all of them must be running
+    if (p.cluster > 1) cooperative_groups::this_cluster().sync();
+    if (threadIdx.x == 0) TIDAL_STAMP(1);
     pdl_wait();
+    if (threadIdx.x == 0) TIDAL_STAMP(2);
     pdl_launch_dependents();
     // ---- token list of this CTA (same rules as the CUDA-core kernel)
     const int sel_row = p.sel_idx ? (p.sel_rows == 1 ? 0 : slice) : 0;
@@ -148,63 +157,16 @@ __global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(c
     const int kvh0 = p.per_head ? slice / p.greal : slice * HC;
     const int qh0 = p.per_head ? slice : kvh0 * G;
 
+    const TokenList tl{b, sel_row, list_len, seq_len_b, tok0, ntok};
+    fill_first_rows(p, tl, src_row);
     __syncthreads();
+    if (threadIdx.x == 0) TIDAL_STAMP(3);
 
-    if (warp == 0) {
-        // =============================================================== producer
-        const size_t plane = (size_t)p.page_size * p.Hkv * D * 2;
-        const size_t tok_bytes = (size_t)p.Hkv * D * 2;
-        for (int it = 0; it < n_iters; ++it) {
-            const int s = it % S;
-            if (it >= S) mbar_wait_bounded(&empty_bar[s], ((it / S) - 1) & 1, abort_flag, p.status);
-            const int valid = min(TT, ntok - it * TT);
-            if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(valid * 2 * row_bytes));
-            __syncwarp();
-            unsigned char* kdst = stage_base + (size_t)s * 2 * TT * pitch;
-            unsigned char* vdst = kdst + (size_t)TT * pitch;
-            for (int t = lane; t < valid; t += 32) {
-                const int li = tok0 + it * TT + t;
-                int64_t page;
-                int entry = 0;
-                bool ok = true;
-                if (p.sel_idx) {
-                    if (li >= list_len) {
-                        page = p.extra_page;
-                    } else {
-                        const int e = p.sel_idx[((size_t)b * p.sel_rows + sel_row) * p.sel_stride + li];
-                        if (p.sel_physical) {
-                            page = e;
-                        } else {
-                            ok = (e >= 0 && e < seq_len_b);
-                            const int pos = ok ? e : 0;
-                            const int pg = pos / p.page_size;
-                            entry = pos - pg * p.page_size;
-                            page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
-                        }
-                    }
-                } else {
-                    const int pg = li / p.page_size;
-                    entry = li - pg * p.page_size;
-                    page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
-                }
-                if (!ok || page < 0 || page >= p.num_pages) {
-                    atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
-                    page = 0;
-                    entry = 0;
-                }
-                const char* ksrc = p.kv + (size_t)page * 2 * plane + (size_t)entry * tok_bytes + (size_t)kvh0 * D * 2;
-                bulk_g2s(kdst + (size_t)t * pitch, ksrc, (uint32_t)row_bytes, &full_bar[s]);
-                bulk_g2s(vdst + (size_t)t * pitch, ksrc + plane, (uint32_t)row_bytes, &full_bar[s]);
-            }
-        }
-        if (*abort_flag && lane == 0) {
-            for (int it = max(0, n_iters - S); it < n_iters; ++it) {
-                const int s = it % S;
-                for (uint32_t i = 0; i < kWaitSpinLimit; ++i)
-                    if (mbar_try_wait(&full_bar[s], (it / S) & 1)) break;
-            }
-        }
-    } else if (warp == 1) {
+    if (warp < p.PW) {
+        // ============================================================== producers
+        produce_stages<kMmaMaxProducers>(p, tl, src_row, warp, lane, S, TT, n_iters, (uint32_t)row_bytes, (uint32_t)pitch, (uint32_t)v_base, stage_stride,
+                       (size_t)kvh0 * D * 2, (size_t)p.Hkv * D * 2, stage_base, full_bar, empty_bar, abort_flag);
+    } else if (warp == p.PW) {
         // ================================================================== reducer
         // Sums the logits of each token over the CTA's heads (fixed order), stores them, counts their
         // first radix digit — one super-block of R stages at a time, while the consumers stream on.
@@ -233,10 +195,10 @@ __global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(c
         }
     } else {
     // ================================================================= consumers
-    const int cw = warp - 2;
+    const int cw = warp - p.PW - 1;
     const int head_local = cw % HC, tg = cw / HC;
     const int consumer_threads = kMmaWarps * 32;
-    const int ctid = threadIdx.x - 64;
+    const int ctid = threadIdx.x - 32 * (p.PW + 1);
     const int r0 = lane >> 2;            // fragment row (query head within the group); the second row is r0 + 8
     const int cq = (lane & 3) * 2;       // fragment column pair
 
@@ -266,13 +228,14 @@ __global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(c
     for (int it = 0; it < n_iters; ++it) {
         const int s = it % S;
         mbar_wait_bounded(&full_bar[s], (it / S) & 1, abort_flag, p.status);
+        if (ctid == 0 && it == 0) TIDAL_STAMP(6);
         if (sum_heads && (it % R) == 0 && it >= 2 * R)               // the reducer is done with this buffer's previous use
             mbar_wait_bounded(&sc_empty[(it / R) & 1], ((it / R) / 2 - 1) & 1, abort_flag, p.status);
         const int valid = min(TT, ntok - it * TT);
         const int tbase = tg * kMmaTile;
         const int mine = min(kMmaTile, valid - tbase);          // valid tokens of this warp's tile (may be <= 0)
-        const uint32_t kst = smem_u32(stage_base + (size_t)s * 2 * TT * pitch);
-        const uint32_t vst = kst + (uint32_t)(TT * pitch);
+        const uint32_t kst = smem_u32(stage_base + (size_t)s * stage_stride);
+        const uint32_t vst = kst + (uint32_t)v_base;
         float* sc = sc_smem + ((size_t)((it / R) & 1) * R + (it % R)) * TT * HC;   // this stage's rows of the super-block
         if (mine > 0) {
             // ---- S = Q K^T for 16 tokens: two n-tiles of 8
@@ -399,47 +362,73 @@ __global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(c
     }
 
     // ---------------------------------------------------------------- epilogue
+    if (ctid == 0) TIDAL_STAMP(7);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         lrow[half] += __shfl_xor_sync(0xffffffffu, lrow[half], 1);
         lrow[half] += __shfl_xor_sync(0xffffffffu, lrow[half], 2);
     }
-    named_bar_sync(2, consumer_threads);
-    float* ep_o = reinterpret_cast<float*>(stage_base);                 // [warps][16][D]
-    float* ep_ml = ep_o + (size_t)kMmaWarps * 16 * D;                   // [warps][16][2]
+    named_bar_sync(2, consumer_threads);                 // every consumer is done with the stage ring
+    if (TG == 1) {
+        // one warp per KV head: its rows are the CTA's result as they are
+        const int hg0 = head_local * G;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        *reinterpret_cast<float2*>(ep_o + ((size_t)cw * 16 + r0) * D + nt * 8 + cq) = make_float2(o[nt][0], o[nt][1]);
-        *reinterpret_cast<float2*>(ep_o + ((size_t)cw * 16 + r0 + 8) * D + nt * 8 + cq) = make_float2(o[nt][2], o[nt][3]);
-    }
-    if ((lane & 3) == 0) {
-        ep_ml[((size_t)cw * 16 + r0) * 2] = mrow[0];
-        ep_ml[((size_t)cw * 16 + r0) * 2 + 1] = lrow[0];
-        ep_ml[((size_t)cw * 16 + r0 + 8) * 2] = mrow[1];
-        ep_ml[((size_t)cw * 16 + r0 + 8) * 2 + 1] = lrow[1];
-    }
-    named_bar_sync(2, consumer_threads);
-    const int nout = HC * G * D;
-    for (int idx = ctid; idx < nout; idx += consumer_threads) {
-        const int d = idx % D;
-        const int hg = idx / D;
-        const int hl = hg / G, g = hg % G;
-        float Mx = -INFINITY;
-        for (int j = 0; j < TG; ++j) Mx = fmaxf(Mx, ep_ml[((size_t)(hl + j * HC) * 16 + g) * 2]);
-        float acc = 0.f, L = 0.f;
-        for (int j = 0; j < TG; ++j) {
-            const size_t e = (size_t)(hl + j * HC) * 16 + g;
-            const float m = ep_ml[e * 2];
-            const float w = (m == -INFINITY) ? 0.f : fast_exp2(m - Mx);
-            acc = fmaf(w, ep_o[e * D + d], acc);
-            L = fmaf(w, ep_ml[e * 2 + 1], L);
+        for (int half = 0; half < 2; ++half) {
+            const int row = r0 + half * 8;
+            if (row < G) {
+                float* dst = cta_o + (size_t)(hg0 + row) * D + cq;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][half * 2], o[nt][half * 2 + 1]);
+                if ((lane & 3) == 0) {
+                    cta_ml[2 * (hg0 + row)] = mrow[half];
+                    cta_ml[2 * (hg0 + row) + 1] = lrow[half];
+                }
+            }
         }
-        cta_o[idx] = acc;
-        if (d == 0) {
-            cta_ml[2 * hg] = Mx;
-            cta_ml[2 * hg + 1] = L;
+    } else {
+        // TG warps hold parts of each head: park the fragments, then one warp per (head, query) row merges them
+        float* ep_o = reinterpret_cast<float*>(stage_base);                 // [warps][16][D]
+        float* ep_ml = ep_o + (size_t)kMmaWarps * 16 * D;                   // [warps][16][2]
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            *reinterpret_cast<float2*>(ep_o + ((size_t)cw * 16 + r0) * D + nt * 8 + cq) = make_float2(o[nt][0], o[nt][1]);
+            *reinterpret_cast<float2*>(ep_o + ((size_t)cw * 16 + r0 + 8) * D + nt * 8 + cq) = make_float2(o[nt][2], o[nt][3]);
+        }
+        if ((lane & 3) == 0) {
+            ep_ml[((size_t)cw * 16 + r0) * 2] = mrow[0];
+            ep_ml[((size_t)cw * 16 + r0) * 2 + 1] = lrow[0];
+            ep_ml[((size_t)cw * 16 + r0 + 8) * 2] = mrow[1];
+            ep_ml[((size_t)cw * 16 + r0 + 8) * 2 + 1] = lrow[1];
+        }
+        named_bar_sync(2, consumer_threads);
+        for (int hg = cw; hg < HC * G; hg += kMmaWarps) {
+            const int hl = hg / G, g = hg - hl * G;
+            float Mx = -INFINITY;
+            for (int j = 0; j < TG; ++j) Mx = fmaxf(Mx, ep_ml[((size_t)(hl + j * HC) * 16 + g) * 2]);
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int d = lane * 4;
+            for (int j = 0; j < TG; ++j) {
+                const size_t e = (size_t)(hl + j * HC) * 16 + g;
+                const float m = ep_ml[e * 2];
+                const float w = (m == -INFINITY) ? 0.f : fast_exp2(m - Mx);
+                L = fmaf(w, ep_ml[e * 2 + 1], L);
+                if (d < D) {
+                    const float4 v = *reinterpret_cast<const float4*>(ep_o + e * D + d);
+                    acc.x = fmaf(w, v.x, acc.x);
+                    acc.y = fmaf(w, v.y, acc.y);
+                    acc.z = fmaf(w, v.z, acc.z);
+                    acc.w = fmaf(w, v.w, acc.w);
+                }
+            }
+            if (d < D) *reinterpret_cast<float4*>(cta_o + (size_t)hg * D + d) = acc;
+            if (lane == 0) {
+                cta_ml[2 * hg] = Mx;
+                cta_ml[2 * hg + 1] = L;
+            }
         }
     }
+    if (ctid == 0) TIDAL_STAMP(8);
     }   // consumers
     if (sum_heads && p.hist) {
         // every warp is done with its role: flush the CTA's digit counts with all threads
@@ -447,14 +436,14 @@ __global__ void __launch_bounds__((kMmaWarps + 2) * 32) decode_attn_mma_kernel(c
         for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x)
             if (sh_hist[i]) atomicAdd(&p.hist[(size_t)b * TIDAL_TOPK_BINS + i], sh_hist[i]);
     }
-    store_attention_result<T>(p, cta_o, cta_ml, HC, G, D, qh0, b, chunk);
+    store_attention_result<T>(p, cta_o, cta_ml, reinterpret_cast<float*>(smem + p.recv_off), HC, G, D, qh0, b, chunk);
 }
 
 template <typename T, int D>
 static int launch_one(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t st) {
     auto kern = decode_attn_mma_kernel<T, D>;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 2) * 32), smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
+    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 1 + p.PW) * 32), smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
 }
@@ -472,3 +461,5 @@ int launch_attn_mma(const AttnParams& p, int D, int dtype, dim3 grid, size_t sme
 }
 
 }  // namespace tidal
+
+TIDAL_TRACE_READER(tidal_trace_read_mma)
