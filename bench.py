@@ -34,6 +34,9 @@ WORKLOADS = {
     "cfg4": dict(B=4, Hq=32, Hkv=8, D=128, dtype="bfloat16", N=131072, k=128, planted=64, layer_pairs=2),
     "cfg5": dict(B=8, Hq=64, Hkv=8, D=128, dtype="bfloat16", N=1048576, k=1024, planted=10486, layer_pairs=1),
 }
+# dram__bytes_read.sum + dram__bytes_write.sum of one selection-layer launch at one GPU, from the ncu captures
+# summarised under profiles/ (cfg5 holds 64 GiB and is not captured; its traffic is left null)
+NCU_TRAFFIC_BYTES = {"cfg2": 536.97e6 + 4.30e6, "cfg4": 2147.76e6 + 8.41e6}
 METRIC = "decode_attn_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -290,6 +293,10 @@ def run_ours(args, rank, world, device):
         roof = {"bound": "hbm", "kernel": "decode_attn_kernel (selection layer: K,V streamed once, fp32 logits written)",
                 "achieved": round(ach, 1), "peak": hbm, "peak_source": which, "unit": "GB/s", "frac": round(ach / hbm, 4),
                 "algorithmic_bytes": alg, "us_per_launch": round(sel_ms * 1e3, 2), "traffic": None}
+        if args.workload in NCU_TRAFFIC_BYTES:
+            # measured at one GPU; a shard's launch streams n_loc / N of the tokens and traffic follows the tokens
+            roof["traffic"] = int(NCU_TRAFFIC_BYTES[args.workload] * n_loc / N)
+            roof["traffic_source"] = "ncu capture of this launch at 1 GPU (profiles/), scaled by the tokens a shard holds"
     per_layer = None
     if sh is None:
         # steady-state device time of each layer type: 2*pairs back-to-back launches (distinct pools) replayed as a graph
