@@ -261,6 +261,33 @@ int tidal_merge_partials_strided(const float* d_m, const float* d_l, const float
 int tidal_rms_norm(const void* d_x, const void* d_weight, void* d_y, int64_t rows, int hidden, float eps, int dtype,
                    int round_before_weight, void* stream);
 
+/* ------------------------------------------------------- decode-step linear
+ * y[M][N] = x[M][K] * W[N][K]^T for M <= 8 rows of activations (one token per sequence), W in the
+ * layout of torch.nn.Linear.weight, fp32 accumulation.  Replaces, in one launch, what the
+ * reference's decoder layer issues as separate ops around each projection at decode time
+ * (tidal/models/llama.py:182-208: rms_norm_forward, the cuBLAS GEMV of nn.Linear, the residual
+ * add; tidal/models/llama.py:160-170: act_fn(gate_proj(x)) * up_proj(x)):
+ *   d_norm_weight != NULL   x is RMS-normalised first (weight [K], norm_eps, rounding as in tidal_rms_norm);
+ *   d_residual != NULL      y = round(x W^T) + residual ([M][N], may be d_y itself);
+ *   TIDAL_LINEAR_SILU_MUL   W stacks the gate rows over the up rows (N = 2 F): y[M][F] = silu(gate) * up,
+ *                           each factor rounded to dtype as the separate torch ops would.
+ * K must be a multiple of 8 (4 for fp32); x, W and the norm weight 16-byte aligned. */
+#define TIDAL_LINEAR_PLAIN 0
+#define TIDAL_LINEAR_SILU_MUL 1
+typedef struct {
+    const void* d_x;            /* [M][K] */
+    const void* d_w;            /* [N][K] */
+    void* d_y;                  /* [M][N], or [M][N/2] for TIDAL_LINEAR_SILU_MUL */
+    const void* d_residual;     /* optional */
+    const void* d_norm_weight;  /* optional [K] */
+    float norm_eps;
+    int32_t norm_round_before_weight;
+    int32_t M, N, K;
+    int32_t dtype;
+    int32_t epilogue;
+} tidal_linear_args;
+int tidal_decode_linear(const tidal_linear_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

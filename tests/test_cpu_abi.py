@@ -34,7 +34,8 @@ def test_every_declared_symbol_is_exported(L):
 
 
 def test_struct_layouts_match_header(L, tmp_path):
-    structs = {"tidal_attn_args": L.AttnArgs, "tidal_topk_args": L.TopkArgs, "tidal_rope_append_args": L.RopeAppendArgs}
+    structs = {"tidal_attn_args": L.AttnArgs, "tidal_topk_args": L.TopkArgs, "tidal_rope_append_args": L.RopeAppendArgs,
+               "tidal_linear_args": L.LinearArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for cname, st in structs.items():
         lines.append(f'printf("{cname} %zu\\n", sizeof({cname}));')
@@ -80,6 +81,15 @@ def test_argument_errors_without_gpu(L):
     assert L.lib.tidal_decode_attention(C.byref(a), 0x4000, 1 << 20, None) == L.ERR_WORKSPACE
     t = L.TopkArgs()
     assert L.lib.tidal_topk(C.byref(t), 0x4000, 1 << 20, None) == L.ERR_ARG
+    lin = L.LinearArgs()
+    assert L.lib.tidal_decode_linear(C.byref(lin), None) == L.ERR_ARG          # null pointers
+    lin.d_x = lin.d_w = lin.d_y = 256
+    lin.M, lin.N, lin.K, lin.dtype = 9, 16, 64, L.DTYPE_F16
+    assert L.lib.tidal_decode_linear(C.byref(lin), None) == L.ERR_ARG and "M 9" in L.last_error()
+    lin.M, lin.K = 1, 12
+    assert L.lib.tidal_decode_linear(C.byref(lin), None) == L.ERR_ARG and "multiple of 8" in L.last_error()
+    lin.K, lin.N, lin.epilogue = 64, 15, L.LINEAR_SILU_MUL
+    assert L.lib.tidal_decode_linear(C.byref(lin), None) == L.ERR_ARG and "even N" in L.last_error()
     r = L.RopeAppendArgs()
     assert L.lib.tidal_rope_append(C.byref(r), None) == L.ERR_ARG
     assert L.lib.tidal_ws_bytes(1, 32, 128, 32, 32768) > 0

@@ -503,3 +503,46 @@ def test_rope_append(T, dt, B, Hq, Hkv, D, page, tps):
         O.append_paged_kv(want_pool, table[b].tolist(), seq_len, kd.cpu()[b * tps:(b + 1) * tps], v[b * tps:(b + 1) * tps])
     assert torch.equal(pool.cpu(), want_pool), "pool contents differ from the CPU append"
     assert int(status) == 0
+
+
+LINEAR_CASES = [
+    # dtype, M, N, K, norm, residual, silu_mul
+    ("f16", 1, 4096, 4096, False, False, False),
+    ("f16", 1, 22016, 4096, True, False, True),          # gate|up of a 7B layer behind its RMSNorm
+    ("f16", 1, 4096, 11008, False, True, False),         # down projection into the residual stream
+    ("bf16", 4, 6144, 4096, True, False, False),         # q|k|v of an 8B layer, four sequences
+    ("bf16", 8, 512, 1024, False, True, False),
+    ("f16", 3, 1001, 512, True, True, False),            # odd N: the last row has no partner
+    ("f32", 1, 1024, 256, True, False, False),           # config 1: lm_head behind the final norm
+    ("f32", 2, 1376, 256, True, False, True),            # config 1: gate|up, F = 688
+    ("f32", 1, 256, 688, False, True, False),            # K not a multiple of a warp's stride
+]
+
+
+@pytest.mark.parametrize("dt,M,N,K,norm,res,silu", LINEAR_CASES)
+def test_decode_linear(T, dt, M, N, K, norm, res, silu):
+    """tidal_decode_linear against the same ops done one by one in torch (tidal/models/llama.py:160-208):
+    rms_norm -> linear -> (+ residual | silu(gate) * up), every intermediate rounded to the storage type."""
+    dtype = DT[dt]
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype)
+    nw = (1.0 + 0.1 * torch.randn(K, generator=g)).to(dtype) if norm else None
+    r = torch.randn(M, N // 2 if silu else N, generator=g).to(dtype) if res else None
+    xin = O.rms_norm(x, nw, 1e-6) if norm else x
+    y = (xin.double() @ w.double().t()).to(dtype)                      # fp32-or-better accumulation, one rounding
+    if silu:
+        F = N // 2
+        want = (torch.nn.functional.silu(y[:, :F].float()).to(dtype).float() * y[:, F:].float()).to(dtype)
+    elif res:
+        want = (y.float() + r.float()).to(dtype)
+    else:
+        want = y
+    got = T.linear(x.cuda(), w.cuda(), residual=None if r is None else r.cuda(), norm_weight=None if nw is None else nw.cuda(),
+                   eps=1e-6, silu_mul=silu)
+    assert got.shape == want.shape
+    assert_close(got, want, dtype, "decode linear")
+    if res:   # in place: the residual stream is the output
+        buf = r.cuda().clone()
+        T.linear(x.cuda(), w.cuda(), out=buf, residual=buf, norm_weight=None if nw is None else nw.cuda(), eps=1e-6)
+        assert torch.equal(buf, got)

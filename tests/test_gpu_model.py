@@ -236,7 +236,8 @@ def test_rms_norm_matches_reference_model(K, dtype, rows, hidden):
         K.rms_norm_forward(x.cuda()[..., :-3].contiguous(), w.cuda()[:-3].contiguous(), out[..., :-3].contiguous(), 1e-6)
 
 
-def test_graph_decoder_matches_eager_and_reference():
+@pytest.mark.parametrize("fused_linear", [True, False])
+def test_graph_decoder_matches_eager_and_reference(fused_linear):
     """The decode step captured as one CUDA graph (device-side lengths, positions and token feedback)
     produces the reference model's greedy tokens on configuration 1."""
     from tidaldecode_b200.runtime import GraphDecoder
@@ -247,7 +248,7 @@ def test_graph_decoder_matches_eager_and_reference():
     prompt = torch.randint(0, W.vocab, (1, 2048), generator=g)
     m = _tiny_model(W, torch.float32, (2, 3), "none", False, 1)
     m.tidal_init(page_size=1, max_seq_len=2048 + 64, token_budget=128, dtype=torch.float32, device=torch.device("cuda"))
-    rt = GraphDecoder(m, max_seq_len=2048 + 64)
+    rt = GraphDecoder(m, max_seq_len=2048 + 64, fused_linear=fused_linear)   # projections in one launch each, or torch ops
     first = rt.prefill(prompt)
     toks = [int(first)] + rt.decode(31).cpu()[0].tolist()
     assert toks == z["tokens"].tolist()

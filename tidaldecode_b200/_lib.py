@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear",
 )
 
 
@@ -63,6 +63,17 @@ class RopeAppendArgs(C.Structure):
     ]
 
 
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("d_x", C.c_void_p), ("d_w", C.c_void_p), ("d_y", C.c_void_p), ("d_residual", C.c_void_p), ("d_norm_weight", C.c_void_p),
+        ("norm_eps", C.c_float), ("norm_round_before_weight", C.c_int32),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("dtype", C.c_int32), ("epilogue", C.c_int32),
+    ]
+
+
+LINEAR_PLAIN, LINEAR_SILU_MUL = 0, 1
+
+
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -101,6 +112,8 @@ def _load() -> C.CDLL:
                                                  C.c_int, C.c_void_p, C.c_int, C.c_void_p]
     lib.tidal_rms_norm.restype = C.c_int
     lib.tidal_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p]
+    lib.tidal_decode_linear.restype = C.c_int
+    lib.tidal_decode_linear.argtypes = [C.POINTER(LinearArgs), C.c_void_p]
     return lib
 
 

@@ -51,11 +51,12 @@ def main():
     ap.add_argument("--head_reduce", choices=["none", "sum"], default="none")
     ap.add_argument("--full", action="store_true", help="full attention in every layer (budget = context)")
     ap.add_argument("--iteration", type=int, default=1)
+    ap.add_argument("--torch_linear", action="store_true", help="projections, norms and activations as separate torch/cuBLAS ops")
     a = ap.parse_args()
     sel = [] if a.full else a.selection_layers
     m, dtype = build(a.model, sel, a.head_reduce, True)
     max_len = a.context_len + a.decode_len + 8
-    rt = GraphDecoder(m, max_seq_len=max_len, token_budget=a.token_budget, dtype=dtype)
+    rt = GraphDecoder(m, max_seq_len=max_len, token_budget=a.token_budget, dtype=dtype, fused_linear=not a.torch_linear)
     g = torch.Generator().manual_seed(0)
     for it in range(a.iteration):
         prompt = torch.randint(0, m.vocab_size, (1, a.context_len), generator=g)
@@ -76,7 +77,7 @@ def main():
         n = a.decode_len - 2
         print(json.dumps({
             "model": a.model, "context_len": a.context_len, "decode_len": a.decode_len,
-            "token_budget": None if a.full else a.token_budget, "selection_layers": sel, "head_reduce": a.head_reduce,
+            "token_budget": None if a.full else a.token_budget, "selection_layers": sel, "head_reduce": a.head_reduce, "fused_linear": rt.fused_linear,
             "prefill_s": round(t_prefill, 3), "decode_ms_per_token_device": round(e0.elapsed_time(e1) / n, 4),
             "decode_ms_per_token_wall": round(wall * 1e3 / n, 4), "tokens_per_s": round(n / wall, 1),
             "status": rt.c.workspace.status(), "last_tokens": toks[0, -4:].tolist()}))

@@ -272,6 +272,17 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
+// SM count of the current device (148 if it cannot be read); looked up once.
+inline int sm_count_cached() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
 // Timeline stamps for debugging (compiled only with -DTIDAL_TRACE; nothing in a normal build).
 // Each translation unit that stamps has its own array [kTraceCtas][kTraceSlots][2] of
 // (%globaltimer ns, clock64) and exports a reader through TIDAL_TRACE_READER(name).

@@ -475,16 +475,6 @@ struct AttnPlan {
     size_t smem;
 };
 
-static int sm_count_cached() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
-    }
-    return n;
-}
-
 constexpr size_t kSmemBudget = 227 * 1024 - 512 - sizeof(uint32_t) * 2 * kAddrBlock;   // per CTA (227 KB is the hardware limit)
 
 // Pick the slot geometry for HC heads per CTA; false if HC cannot be mapped.

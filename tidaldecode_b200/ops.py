@@ -293,3 +293,39 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[to
         check(lib.tidal_rms_norm(x.data_ptr(), weight.data_ptr(), out.data_ptr(), x.numel() // hidden, hidden, float(eps),
                                  _dtype_code(x), 1 if round_before_weight else 0, _stream()), "tidal_rms_norm")
     return out
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, *, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+           norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6, round_before_weight: bool = True,
+           silu_mul: bool = False) -> torch.Tensor:
+    """Decode-step projection y = x W^T for up to 8 rows of x, with the optional RMSNorm of x, residual
+    add and SiLU(gate) * up folded in; see tidal_decode_linear in include/tidal_b200.h.
+    x [..., K] (at most 8 rows in all), weight [N, K]; returns [..., N] (or [..., N/2] with silu_mul)."""
+    _need_cuda(x, weight, out, residual, norm_weight)
+    if weight.dtype != x.dtype or weight.dim() != 2:
+        raise RuntimeError("weight must be a [N, K] matrix of the input's dtype")
+    N, K = weight.shape
+    if x.shape[-1] != K:
+        raise RuntimeError(f"input has {x.shape[-1]} features, the weight {K}")
+    M = x.numel() // K
+    if not (x.is_contiguous() and weight.is_contiguous()):
+        raise RuntimeError("input and weight must be contiguous")
+    n_out = N // 2 if silu_mul else N
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n_out, dtype=x.dtype, device=x.device)
+    elif out.numel() != M * n_out or out.dtype != x.dtype or not out.is_contiguous():
+        raise RuntimeError("out has the wrong size, dtype or layout")
+    if residual is not None and (residual.numel() != M * n_out or residual.dtype != x.dtype or not residual.is_contiguous()):
+        raise RuntimeError("residual has the wrong size, dtype or layout")
+    if norm_weight is not None and (norm_weight.numel() != K or norm_weight.dtype != x.dtype):
+        raise RuntimeError("norm weight must have K elements of the input's dtype")
+    a = _lib.LinearArgs()
+    a.d_x, a.d_w, a.d_y = x.data_ptr(), weight.data_ptr(), out.data_ptr()
+    a.d_residual = _ptr(residual)
+    a.d_norm_weight = _ptr(norm_weight)
+    a.norm_eps, a.norm_round_before_weight = float(eps), 1 if round_before_weight else 0
+    a.M, a.N, a.K, a.dtype = M, N, K, _dtype_code(x)
+    a.epilogue = _lib.LINEAR_SILU_MUL if silu_mul else _lib.LINEAR_PLAIN
+    with torch.cuda.device(x.device):
+        check(lib.tidal_decode_linear(C.byref(a), _stream()), "tidal_decode_linear")
+    return out

@@ -25,7 +25,7 @@ from .attention import FullAttention, SearchAttention, SparseAttention
 
 class GraphDecoder:
     def __init__(self, model, max_seq_len: int, token_budget: Optional[int] = None, dtype: Optional[torch.dtype] = None,
-                 device=None, batch_size: int = 1):
+                 device=None, batch_size: int = 1, fused_linear: bool = True):
         self.model = model
         p = next(model.parameters())
         self.dtype = dtype or p.dtype
@@ -53,6 +53,8 @@ class GraphDecoder:
         self.out_tokens = torch.zeros(self.B, self.max_seq_len, dtype=torch.int64, device=self.device)
         self.graph = None
         self.logits = None
+        # decode-step projections through tidal_decode_linear (norm, residual and SiLU*up folded in); False = torch ops
+        self.fused_linear = fused_linear and batch_size <= 8
         # one GEMV for q,k,v and one for gate,up per layer (three and two in the module): fewer launches per token
         self._wqkv, self._wgu = [], []
         for layer in model.model.layers:
@@ -90,14 +92,18 @@ class GraphDecoder:
         B, k = self.B, self.k
         table = c.kv_cache.page_table
         ws = c.workspace
-        h = m.model.embed_tokens(self.tok)                  # [B,1,hidden]
+        h = m.model.embed_tokens(self.tok).view(B, -1).contiguous()          # [B, hidden], the residual stream (updated in place)
         cnt_shape = (B,) if c.score_rows == 1 else (B, c.num_heads)
         F = torch.nn.functional
+        fused = self.fused_linear
         for li, layer in enumerate(m.model.layers):
             att = layer.self_attn
-            x = layer.input_layernorm(h)
             nq, nkv = att.num_heads * att.head_dim, att.num_key_value_heads * att.head_dim
-            qkv = F.linear(x, self._wqkv[li]).view(B, nq + 2 * nkv)
+            ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
+            if fused:
+                qkv = ops.linear(h, self._wqkv[li], norm_weight=ln1.weight, eps=ln1.variance_epsilon)
+            else:
+                qkv = F.linear(ln1(h), self._wqkv[li])
             q = qkv[:, :nq].contiguous().view(B, att.num_heads, att.head_dim)
             kk = qkv[:, nq:nq + nkv].contiguous().view(B, att.num_key_value_heads, att.head_dim)
             vv = qkv[:, nq + nkv:].contiguous().view(B, att.num_key_value_heads, att.head_dim)
@@ -116,11 +122,20 @@ class GraphDecoder:
                                      sel_idx=c._topk_indices_full, sel_counts=self.sel_counts.view(cnt_shape))
             else:
                 ops.decode_attention(q, pool, self.max_seq_len, ws, out=o, page_table=table, seq_lens=self.seq_lens)
-            h = h + att.o_proj(o.view(B, 1, -1))
-            gu = F.linear(layer.post_attention_layernorm(h), self._wgu[li])
-            ffn = gu.shape[-1] // 2
-            h = h + layer.mlp.down_proj(F.silu(gu[..., :ffn]) * gu[..., ffn:])
-        logits = m.lm_head(m.model.norm(h))
+            if fused:
+                # o_proj into the residual stream; gate|up behind the second norm with SiLU(gate)*up; down into the stream
+                ops.linear(o.view(B, -1), att.o_proj.weight, out=h, residual=h)
+                act = ops.linear(h, self._wgu[li], norm_weight=ln2.weight, eps=ln2.variance_epsilon, silu_mul=True)
+                ops.linear(act, layer.mlp.down_proj.weight, out=h, residual=h)
+            else:
+                h = h + att.o_proj(o.view(B, -1))
+                gu = F.linear(ln2(h), self._wgu[li])
+                ffn = gu.shape[-1] // 2
+                h = h + layer.mlp.down_proj(F.silu(gu[..., :ffn]) * gu[..., ffn:])
+        if fused:
+            logits = ops.linear(h, m.lm_head.weight, norm_weight=m.model.norm.weight, eps=m.model.norm.variance_epsilon).view(B, 1, -1)
+        else:
+            logits = m.lm_head(m.model.norm(h)).view(B, 1, -1)
         nxt = logits.argmax(-1)                             # [B,1]
         self.out_tokens.index_copy_(1, self.step_idx, nxt)
         self.tok.copy_(nxt)
