@@ -285,6 +285,9 @@ typedef struct {
     int32_t M, N, K;
     int32_t dtype;
     int32_t epilogue;
+    uint32_t* d_status;         /* optional: TIDAL_DEV_* bits are OR-ed in (a wait on the staging ring that ran out) */
+    int32_t static_weights;     /* 1: W was not written by the kernel that precedes this call in the stream (model
+                                 * weights): the kernel starts fetching W before it is ordered after that kernel */
 } tidal_linear_args;
 int tidal_decode_linear(const tidal_linear_args* args, void* stream);
 

@@ -512,6 +512,9 @@ LINEAR_CASES = [
     ("f16", 1, 4096, 11008, False, True, False),         # down projection into the residual stream
     ("bf16", 4, 6144, 4096, True, False, False),         # q|k|v of an 8B layer, four sequences
     ("bf16", 8, 512, 1024, False, True, False),
+    ("bf16", 4, 28672, 4096, True, False, True),         # gate|up of an 8B layer, four sequences (tensor-core kernel, tile pairs)
+    ("f16", 2, 1000, 4096, False, True, False),          # N not a multiple of the 16-row tile
+    ("bf16", 1, 688, 352, False, False, True),           # F = 344 is not a multiple of 16: CUDA-core kernel
     ("f16", 3, 1001, 512, True, True, False),            # odd N: the last row has no partner
     ("f32", 1, 1024, 256, True, False, False),           # config 1: lm_head behind the final norm
     ("f32", 2, 1376, 256, True, False, True),            # config 1: gate|up, F = 688
@@ -538,10 +541,15 @@ def test_decode_linear(T, dt, M, N, K, norm, res, silu):
         want = (y.float() + r.float()).to(dtype)
     else:
         want = y
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     got = T.linear(x.cuda(), w.cuda(), residual=None if r is None else r.cuda(), norm_weight=None if nw is None else nw.cuda(),
-                   eps=1e-6, silu_mul=silu)
+                   eps=1e-6, silu_mul=silu, status=status)
     assert got.shape == want.shape
     assert_close(got, want, dtype, "decode linear")
+    torch.cuda.synchronize()
+    again = T.linear(x.cuda(), w.cuda(), residual=None if r is None else r.cuda(), norm_weight=None if nw is None else nw.cuda(),
+                     eps=1e-6, silu_mul=silu, status=status, static_weights=True)       # weights fetched ahead of stream order
+    assert torch.equal(again, got) and int(status.item()) == 0
     if res:   # in place: the residual stream is the output
         buf = r.cuda().clone()
         T.linear(x.cuda(), w.cuda(), out=buf, residual=buf, norm_weight=None if nw is None else nw.cuda(), eps=1e-6)

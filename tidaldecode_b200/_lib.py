@@ -68,6 +68,7 @@ class LinearArgs(C.Structure):
         ("d_x", C.c_void_p), ("d_w", C.c_void_p), ("d_y", C.c_void_p), ("d_residual", C.c_void_p), ("d_norm_weight", C.c_void_p),
         ("norm_eps", C.c_float), ("norm_round_before_weight", C.c_int32),
         ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("dtype", C.c_int32), ("epilogue", C.c_int32),
+        ("d_status", C.c_void_p), ("static_weights", C.c_int32),
     ]
 
 

@@ -80,7 +80,7 @@ def main():
             "token_budget": None if a.full else a.token_budget, "selection_layers": sel, "head_reduce": a.head_reduce, "fused_linear": rt.fused_linear,
             "prefill_s": round(t_prefill, 3), "decode_ms_per_token_device": round(e0.elapsed_time(e1) / n, 4),
             "decode_ms_per_token_wall": round(wall * 1e3 / n, 4), "tokens_per_s": round(n / wall, 1),
-            "status": rt.c.workspace.status(), "last_tokens": toks[0, -4:].tolist()}))
+            "status": rt.c.workspace.status() | int(rt.lin_status.item()), "last_tokens": toks[0, -4:].tolist()}))
 
 
 if __name__ == "__main__":

@@ -4,10 +4,10 @@
 //   * RMSNorm of x on the way into shared memory (every CTA needs all of x anyway),
 //   * residual add on the way out,
 //   * SiLU(gate) * up when W stacks the gate and up projections.
-// One warp owns two rows of W at a time (for the gated form: gate row r and up row r + N/2), lanes
-// stride over K in 16-byte vectors with four vectors per row in flight, accumulate in fp32, and a
-// butterfly reduces the 2 M sums.  Before the kernel is ordered after its predecessor it already
-// asks L2 for its first rows: the weights do not depend on anything.
+// Two kernels.  16-bit weights go through mma.sync.m16n8k16 with a tile of 16 rows of W as the A
+// operand and the (up to 8) activation rows as the 8 columns of B, the tiles staged in shared memory
+// by bulk copies (see below).  Everything else (fp32, odd shapes) takes the CUDA-core kernel: one warp
+// owns two rows of W at a time, lanes stride over K in 16-byte vectors, a butterfly reduces the 2 M sums.
 #include "common.cuh"
 
 namespace tidal {
@@ -39,7 +39,7 @@ template <typename T, int M>
 __global__ void __launch_bounds__(kLinThreads, M <= 2 ? 2 : 1) decode_linear_kernel(const __grid_constant__ LinearParams p) {
     using V = Vec16<T>;
     constexpr int VEC = V::N;
-    extern __shared__ __align__(16) unsigned char lin_smem[];
+    extern __shared__ __align__(128) unsigned char lin_smem[];
     T* xs = reinterpret_cast<T*>(lin_smem);                  // [M][K], normalised if asked for
     __shared__ float s_part[M][kLinWarps];
     __shared__ float s_scale[M];
@@ -191,6 +191,272 @@ __global__ void __launch_bounds__(kLinThreads, M <= 2 ? 2 : 1) decode_linear_ker
     }
 }
 
+// ------------------------------------------------------------------ tensor-core kernel
+// Same data path as the attention kernels: a producer warp brings tiles of 16 rows of W into a ring of
+// shared-memory stages with one bulk copy per row (2-4 KB each, so DRAM sees long bursts and the SM
+// keeps up to ~190 KB in flight whatever the register budget), 8 consumer warps read them with
+// ldmatrix and multiply by the activation rows kept in shared memory.  The warps of a CTA split the
+// K range of a stage between them and add their partial tiles up through shared memory once per
+// tile (pair), while the producer is already filling stages of the next one.  The first stages are
+// requested before the kernel is ordered after its predecessor: weights do not depend on anything.
+constexpr int kLinConsumers = 8;
+constexpr int kLinProducers = 2;      // a warp gets a bulk copy accepted every ~70 cycles: two of them for 16 rows of 2 KB
+constexpr int kLinMmaThreads = (kLinConsumers + kLinProducers) * 32;
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_a(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+struct LinearMmaGeom {
+    int M, tiles, units, tpu, t0_stride, tile1_off;
+    int KC;        // elements of K per stage
+    int S;         // stages
+    uint32_t* status;
+    int static_weights;   // the weights were not written by the stream's preceding kernel: fetch them before stream order
+};
+
+__host__ __device__ inline size_t lin_x_bytes(int M, int K) { return ((size_t)M * (K * 2 + 16) + 127) & ~(size_t)127; }
+__host__ __device__ inline size_t lin_stage_bytes(int KC) { return (size_t)16 * (KC * 2 + 16); }
+
+template <typename T>
+__global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const __grid_constant__ LinearParams p,
+                                                                           const __grid_constant__ LinearMmaGeom gm) {
+    using V = Vec16<T>;
+    extern __shared__ __align__(128) unsigned char lin_smem[];
+    const int K = p.K, M = gm.M, KC = gm.KC, S = gm.S;
+    const int xpitch = K * 2 + 16;                            // bytes; the 8 x 4 lanes of a B fragment then hit 32 distinct banks
+    const int pitch = KC * 2 + 16;                            // bytes between the 16 rows of a stage
+    unsigned char* xs = lin_smem;                             // [M] rows of x, normalised if asked for
+    unsigned char* stages = lin_smem + lin_x_bytes(M, K);     // [S][16][pitch]
+    float* red = reinterpret_cast<float*>(stages + (size_t)S * lin_stage_bytes(KC));        // [2][8 warps][2 tiles][128]
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(red + 2 * kLinConsumers * 256);
+    uint64_t* empty_bar = full_bar + S;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
+    __shared__ float s_part[8][kLinConsumers];
+    __shared__ float s_scale[8];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* W = reinterpret_cast<const T*>(p.w);
+    const int nkc = (K + KC - 1) / KC;                        // stages per tile
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], kLinConsumers);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp >= kLinConsumers) {
+        // ============================================================== producers
+        const int pw = warp - kLinConsumers;                  // rows 8 pw .. 8 pw + 7 of every tile
+        if (!gm.static_weights) pdl_wait();      // else never ordered after the predecessor: it reads nothing but weights
+        int it = 0;
+        for (int u = blockIdx.x; u < gm.units; u += gridDim.x) {
+            for (int t = 0; t < gm.tpu; ++t) {
+                const int tile = u * gm.t0_stride + (t ? gm.tile1_off : 0);
+                if (tile >= gm.tiles) break;
+                const int trow = pw * 8 + (lane & 7);
+                const int row = min(tile * 16 + trow, p.N - 1);             // a short last tile reads the last row again
+                const char* src = reinterpret_cast<const char*>(W + (size_t)row * K);
+                for (int kc = 0; kc < nkc; ++kc, ++it) {
+                    const int s = it % S;
+                    if (it >= S && !mbar_wait_bounded(&empty_bar[s], ((it / S) - 1) & 1, abort_flag, gm.status)) break;
+                    const uint32_t len = (uint32_t)min(KC, K - kc * KC) * 2u;
+                    if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&full_bar[s], 16u * len);   // (the other warp's copies may land first)
+                    __syncwarp();
+                    if (lane < 8)
+                        bulk_g2s(stages + (size_t)s * lin_stage_bytes(KC) + (size_t)trow * pitch, src + (size_t)kc * KC * 2, len, &full_bar[s]);
+                }
+            }
+        }
+        // nothing of this CTA may still be in flight when it retires: after a wait that ran out, outlast the copies
+        if (*abort_flag)
+            for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    } else {
+        // ============================================================== consumers
+        pdl_wait();
+        pdl_launch_dependents();
+        const int ctid = threadIdx.x;                         // consumers are warps 0..7
+        constexpr int CT = kLinConsumers * 32;
+        // ---- activations into shared memory, RMS-normalised on the way if a norm weight is given
+        {
+            const int nvec = K / 8;
+            const uint4* xg = reinterpret_cast<const uint4*>(p.x);
+            if (p.norm_w) {
+                for (int m = 0; m < M; ++m) {
+                    float ss = 0.f;
+                    for (int i = ctid; i < nvec; i += CT) {
+                        float f[8];
+                        V::to_float(xg[(size_t)m * nvec + i], f);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+                    }
+#pragma unroll
+                    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                    if (lane == 0) s_part[m][warp] = ss;
+                }
+                named_bar_sync(1, CT);
+                if (ctid < M) {
+                    float tot = 0.f;
+                    for (int i = 0; i < kLinConsumers; ++i) tot += s_part[ctid][i];
+                    s_scale[ctid] = rsqrtf(tot / (float)K + p.eps);
+                }
+                named_bar_sync(1, CT);
+                const uint4* wn = reinterpret_cast<const uint4*>(p.norm_w);
+                for (int i = ctid; i < nvec; i += CT) {
+                    float gw[8];
+                    V::to_float(wn[i], gw);
+                    for (int m = 0; m < M; ++m) {
+                        float f[8], o[8];
+                        V::to_float(xg[(size_t)m * nvec + i], f);
+                        const float sc = s_scale[m];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float n = f[e] * sc;
+                            o[e] = p.round_before_weight ? __fmul_rn(V::round(n), gw[e]) : n * gw[e];
+                        }
+                        *reinterpret_cast<uint4*>(xs + (size_t)m * xpitch + (size_t)i * 16) = V::from_float(o);
+                    }
+                }
+            } else {
+                for (int i = ctid; i < M * nvec; i += CT) {
+                    const int m = i / nvec, j = i - m * nvec;
+                    *reinterpret_cast<uint4*>(xs + (size_t)m * xpitch + (size_t)j * 16) = xg[i];
+                }
+            }
+        }
+        named_bar_sync(1, CT);
+
+        const int g = lane >> 2, c = lane & 3;
+        const bool has_x = g < M;
+        const unsigned char* xrow = xs + (size_t)g * xpitch + c * 4;      // B fragment: x[g][k0 + 2c, +1] and [k0 + 8 + 2c, +1]
+        const int kslice = KC / kLinConsumers;                           // K elements of a stage per warp (a multiple of 16)
+        const uint32_t a_lane = (uint32_t)((lane & 15) * pitch + (lane >> 4) * 16);
+        int it = 0, round = 0;
+        for (int u = blockIdx.x; u < gm.units; u += gridDim.x, ++round) {
+            const int t0 = u * gm.t0_stride, t1 = t0 + gm.tile1_off;
+            const int ntile = (gm.tpu == 2 && t1 < gm.tiles) ? 2 : 1;
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 1
+            for (int t = 0; t < ntile; ++t) {
+                float cur[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+                for (int kc = 0; kc < nkc; ++kc, ++it) {
+                    const int s = it % S;
+                    mbar_wait_bounded(&full_bar[s], (it / S) & 1, abort_flag, gm.status);
+                    const int len = min(KC, K - kc * KC);                // elements of this stage
+                    const int k_lo = warp * kslice, k_hi = min(len, k_lo + kslice);
+                    const uint32_t st = smem_u32(stages + (size_t)s * lin_stage_bytes(KC)) + a_lane;
+                    const unsigned char* xk = xrow + (size_t)kc * KC * 2;
+#pragma unroll 4
+                    for (int k0 = k_lo; k0 < k_hi; k0 += 16) {
+                        uint32_t a[4];
+                        ldsm_a(a, st + (uint32_t)k0 * 2);
+                        uint32_t b0 = 0, b1 = 0;
+                        if (has_x) {
+                            b0 = *reinterpret_cast<const uint32_t*>(xk + (size_t)k0 * 2);
+                            b1 = *reinterpret_cast<const uint32_t*>(xk + (size_t)k0 * 2 + 16);
+                        }
+                        mma16816<T>(cur, a, b0, b1);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty_bar[s]);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (t == 0) acc[0][i] = cur[i];
+                    else acc[1][i] = cur[i];
+                }
+            }
+            // ---- add the 8 warps' partial tiles up (double-buffered: one barrier per round)
+            float* rbuf = red + (size_t)(round & 1) * kLinConsumers * 256;
+            float4* myred = reinterpret_cast<float4*>(rbuf) + (size_t)warp * 64 + lane;
+            myred[0] = make_float4(acc[0][0], acc[0][1], acc[0][2], acc[0][3]);
+            myred[32] = make_float4(acc[1][0], acc[1][1], acc[1][2], acc[1][3]);
+            named_bar_sync(1, CT);
+            if (ctid < 128) {
+                // element e of tile 0 and of tile 1: fragment of lane el, register i
+                const int e = ctid, el = e >> 2, i = e & 3;
+                float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                for (int w = 0; w < kLinConsumers; ++w) {
+                    s0 += rbuf[(size_t)w * 256 + e];
+                    s1 += rbuf[(size_t)w * 256 + 128 + e];
+                }
+                const int rr = (el >> 2) + (i >= 2 ? 8 : 0);              // row within the tile
+                const int m = (el & 3) * 2 + (i & 1);                     // batch row
+                if (m < M) {
+                    T* y = reinterpret_cast<T*>(p.y);
+                    const int ra = t0 * 16 + rr;
+                    if (p.epilogue == TIDAL_LINEAR_SILU_MUL) {
+                        const float gt = V::round(s0), up = V::round(s1);
+                        const float sg = V::round(gt / (1.f + __expf(-gt)));
+                        y[(size_t)m * (p.N / 2) + ra] = from_f32<T>(sg * up);
+                    } else {
+                        const T* res = reinterpret_cast<const T*>(p.residual);
+                        if (ra < p.N) y[(size_t)m * p.N + ra] = from_f32<T>(res ? V::round(s0) + to_f32(res[(size_t)m * p.N + ra]) : s0);
+                        const int rb = t1 * 16 + rr;
+                        if (ntile == 2 && rb < p.N) y[(size_t)m * p.N + rb] = from_f32<T>(res ? V::round(s1) + to_f32(res[(size_t)m * p.N + rb]) : s1);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// false: the shapes do not fit (the caller takes the CUDA-core kernel).  One CTA per SM with all of its
+// shared memory: stages as long as they come (4 KB per row) and at least three of them.  (Half-SM CTAs,
+// two per SM or one next to the next launch's, measured no better: the kernel streams at the copy rate
+// either way and pays ~5 us per launch for ramp-up and tail.)
+static bool plan_linear_mma(const LinearParams& p, int M, LinearMmaGeom* gm, size_t* smem, int* per_sm) {
+    const size_t fixed = lin_x_bytes(M, p.K) + (size_t)2 * kLinConsumers * 256 * sizeof(float) + 2 * 8 * sizeof(uint64_t) + 64;
+    const size_t budget = 225 * 1024;
+    for (int KC : {2048, 1024, 512, 256, 128}) {
+        if (KC > p.K && KC > 128) continue;                   // no stage longer than a row (but at least 128: 16 per warp)
+        if (fixed + 3 * lin_stage_bytes(KC) > budget) continue;
+        int S = (int)((budget - fixed) / lin_stage_bytes(KC));
+        if (S > 8) S = 8;
+        gm->KC = KC; gm->S = S;
+        *smem = fixed + (size_t)S * lin_stage_bytes(KC);
+        *per_sm = 1;
+        return true;
+    }
+    return false;
+}
+
+template <typename T>
+static int launch_linear_mma(const LinearParams& p, LinearMmaGeom gm, size_t smem, int per_sm, cudaStream_t st) {
+    auto kern = decode_linear_mma_kernel<T>;
+    const int sms = sm_count_cached();
+    if (p.epilogue == TIDAL_LINEAR_SILU_MUL) {
+        const int F = p.N / 2;
+        gm.tiles = p.N / 16; gm.units = F / 16; gm.tpu = 2; gm.t0_stride = 1; gm.tile1_off = F / 16;
+    } else {
+        gm.tiles = (p.N + 15) / 16;
+        gm.tpu = gm.tiles >= 8 * sms ? 2 : 1;       // small matrices: one tile per round, so that every CTA gets some
+        gm.units = (gm.tiles + gm.tpu - 1) / gm.tpu; gm.t0_stride = gm.tpu; gm.tile1_off = 1;
+    }
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int grid = gm.units < sms * per_sm ? gm.units : sms * per_sm;
+    TIDAL_CUDA_OK(launch_pdl(kern, dim3(grid), dim3(kLinMmaThreads), smem, st, 1, p, gm));
+    count_launch();
+    return TIDAL_OK;
+}
+
 template <typename T, int M>
 static int launch_linear(const LinearParams& p, cudaStream_t st) {
     auto kern = decode_linear_kernel<T, M>;
@@ -251,6 +517,19 @@ extern "C" int tidal_decode_linear(const tidal_linear_args* a, void* stream) {
         p.up_off = a->K;
     }
     cudaStream_t st = (cudaStream_t)stream;
+    // tensor cores: 16-bit weights, whole 16-element k steps, 16-byte row starts, whole gate/up tiles
+    const bool mma_ok = a->dtype != TIDAL_DTYPE_F32 && a->K % 16 == 0 && a->K >= 128 && a->N >= 16 &&
+                        (a->epilogue != TIDAL_LINEAR_SILU_MUL || (a->N / 2) % 16 == 0);
+    if (mma_ok) {
+        LinearMmaGeom gm;
+        size_t smem = 0;
+        gm.M = a->M; gm.status = (uint32_t*)a->d_status; gm.static_weights = a->static_weights;
+        int per_sm = 1;
+        if (plan_linear_mma(p, a->M, &gm, &smem, &per_sm)) {
+            if (a->dtype == TIDAL_DTYPE_F16) return launch_linear_mma<__half>(p, gm, smem, per_sm, st);
+            return launch_linear_mma<__nv_bfloat16>(p, gm, smem, per_sm, st);
+        }
+    }
     switch (a->dtype) {
         case TIDAL_DTYPE_F16: return dispatch_m<__half>(p, a->M, st);
         case TIDAL_DTYPE_BF16: return dispatch_m<__nv_bfloat16>(p, a->M, st);

@@ -297,7 +297,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[to
 
 def linear(x: torch.Tensor, weight: torch.Tensor, *, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
            norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6, round_before_weight: bool = True,
-           silu_mul: bool = False) -> torch.Tensor:
+           silu_mul: bool = False, static_weights: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Decode-step projection y = x W^T for up to 8 rows of x, with the optional RMSNorm of x, residual
     add and SiLU(gate) * up folded in; see tidal_decode_linear in include/tidal_b200.h.
     x [..., K] (at most 8 rows in all), weight [N, K]; returns [..., N] (or [..., N/2] with silu_mul)."""
@@ -326,6 +326,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, out: Optional[torch.Tensor]
     a.norm_eps, a.norm_round_before_weight = float(eps), 1 if round_before_weight else 0
     a.M, a.N, a.K, a.dtype = M, N, K, _dtype_code(x)
     a.epilogue = _lib.LINEAR_SILU_MUL if silu_mul else _lib.LINEAR_PLAIN
+    a.static_weights = 1 if static_weights else 0       # model weights: may be fetched ahead of stream order
+    a.d_status = _ptr(status)                           # uint32 [1], fault bits are OR-ed in
     with torch.cuda.device(x.device):
         check(lib.tidal_decode_linear(C.byref(a), _stream()), "tidal_decode_linear")
     return out

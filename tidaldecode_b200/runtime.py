@@ -55,6 +55,7 @@ class GraphDecoder:
         self.logits = None
         # decode-step projections through tidal_decode_linear (norm, residual and SiLU*up folded in); False = torch ops
         self.fused_linear = fused_linear and batch_size <= 8
+        self.lin_status = torch.zeros(1, dtype=torch.int32, device=self.device)      # fault bits of the linear kernels
         # one GEMV for q,k,v and one for gate,up per layer (three and two in the module): fewer launches per token
         self._wqkv, self._wgu = [], []
         for layer in model.model.layers:
@@ -96,12 +97,13 @@ class GraphDecoder:
         cnt_shape = (B,) if c.score_rows == 1 else (B, c.num_heads)
         F = torch.nn.functional
         fused = self.fused_linear
+        lin = dict(static_weights=True, status=self.lin_status)
         for li, layer in enumerate(m.model.layers):
             att = layer.self_attn
             nq, nkv = att.num_heads * att.head_dim, att.num_key_value_heads * att.head_dim
             ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
             if fused:
-                qkv = ops.linear(h, self._wqkv[li], norm_weight=ln1.weight, eps=ln1.variance_epsilon)
+                qkv = ops.linear(h, self._wqkv[li], norm_weight=ln1.weight, eps=ln1.variance_epsilon, **lin)
             else:
                 qkv = F.linear(ln1(h), self._wqkv[li])
             q = qkv[:, :nq].contiguous().view(B, att.num_heads, att.head_dim)
@@ -124,16 +126,16 @@ class GraphDecoder:
                 ops.decode_attention(q, pool, self.max_seq_len, ws, out=o, page_table=table, seq_lens=self.seq_lens)
             if fused:
                 # o_proj into the residual stream; gate|up behind the second norm with SiLU(gate)*up; down into the stream
-                ops.linear(o.view(B, -1), att.o_proj.weight, out=h, residual=h)
-                act = ops.linear(h, self._wgu[li], norm_weight=ln2.weight, eps=ln2.variance_epsilon, silu_mul=True)
-                ops.linear(act, layer.mlp.down_proj.weight, out=h, residual=h)
+                ops.linear(o.view(B, -1), att.o_proj.weight, out=h, residual=h, **lin)
+                act = ops.linear(h, self._wgu[li], norm_weight=ln2.weight, eps=ln2.variance_epsilon, silu_mul=True, **lin)
+                ops.linear(act, layer.mlp.down_proj.weight, out=h, residual=h, **lin)
             else:
                 h = h + att.o_proj(o.view(B, -1))
                 gu = F.linear(ln2(h), self._wgu[li])
                 ffn = gu.shape[-1] // 2
                 h = h + layer.mlp.down_proj(F.silu(gu[..., :ffn]) * gu[..., ffn:])
         if fused:
-            logits = ops.linear(h, m.lm_head.weight, norm_weight=m.model.norm.weight, eps=m.model.norm.variance_epsilon).view(B, 1, -1)
+            logits = ops.linear(h, m.lm_head.weight, norm_weight=m.model.norm.weight, eps=m.model.norm.variance_epsilon, **lin).view(B, 1, -1)
         else:
             logits = m.lm_head(m.model.norm(h)).view(B, 1, -1)
         nxt = logits.argmax(-1)                             # [B,1]
