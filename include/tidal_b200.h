@@ -291,6 +291,15 @@ typedef struct {
 } tidal_linear_args;
 int tidal_decode_linear(const tidal_linear_args* args, void* stream);
 
+/* The q|k|v projection of a decoder layer with tidal_rope_append folded in: W stacks the Hq query
+ * heads, the Hkv key heads and the Hkv value heads ((Hq + 2 Hkv) * D rows); q comes out rotated in
+ * rope->d_q ([M][Hq][D]), k (rotated) and v go straight into the slot of each sequence's newest token
+ * in the paged KV pool.  `lin` gives x, W, M, K and the optional RMSNorm (d_y, d_residual and epilogue
+ * are ignored); `rope` gives the destinations and the RoPE as for tidal_rope_append (batch = M,
+ * tokens_per_seq = 1; d_k and d_v are ignored).  f16/bf16 only. */
+#define TIDAL_LINEAR_QKV_ROPE 2
+int tidal_decode_qkv(const tidal_linear_args* lin, const tidal_rope_append_args* rope, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -554,3 +554,42 @@ def test_decode_linear(T, dt, M, N, K, norm, res, silu):
         buf = r.cuda().clone()
         T.linear(x.cuda(), w.cuda(), out=buf, residual=buf, norm_weight=None if nw is None else nw.cuda(), eps=1e-6)
         assert torch.equal(buf, got)
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,K,page,mode", [
+    ("f16", 1, 32, 32, 128, 4096, 1, 1), ("bf16", 4, 32, 8, 128, 4096, 1, 2), ("bf16", 2, 8, 2, 64, 512, 4, 1),
+    ("f16", 3, 4, 4, 64, 256, 1, 0),
+])
+def test_fused_qkv_projection_rope_append(T, dt, B, Hq, Hkv, D, K, page, mode):
+    """tidal_decode_qkv = RMSNorm + q|k|v projection + RoPE + KV append in one launch, against the same
+    steps as separate calls (tidal_decode_linear, tidal_rope_append), which have their own parity tests."""
+    dtype = DT[dt]
+    g = torch.Generator().manual_seed(5)
+    N = (Hq + 2 * Hkv) * D
+    x = torch.randn(B, K, generator=g).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(dtype).cuda()
+    nw = (1.0 + 0.1 * torch.randn(K, generator=g)).to(dtype).cuda()
+    ppb = 6
+    pages = B * ppb + 3
+    table = torch.randperm(pages, generator=g)[:B * ppb].view(B, ppb).to(torch.int32).cuda()    # distinct pages per sequence
+    pos = torch.tensor([(7 * b + 5) % (ppb * page) for b in range(B)], dtype=torch.int32).cuda()
+    inv = (1.0 / (10000.0 ** (torch.arange(0, D, 2).float() / D))).cuda()
+    rope = dict(pos0_dev=pos, page_table=table, rope_theta=1e4, rope_scale=1.0, rope_mode=mode, inv_freq=inv)
+    # separate calls
+    pool_a = torch.zeros(pages, 2, page, Hkv, D, dtype=dtype, device="cuda")
+    qkv = T.linear(x, w, norm_weight=nw, eps=1e-6)
+    q_a = qkv[:, :Hq * D].contiguous().view(B, Hq, D)
+    k_a = qkv[:, Hq * D:(Hq + Hkv) * D].contiguous().view(B, Hkv, D)
+    v_a = qkv[:, (Hq + Hkv) * D:].contiguous().view(B, Hkv, D)
+    T.rope_append(q_a, k_a, v_a, pool_a, batch=B, **rope)
+    # one call
+    pool_b = torch.zeros_like(pool_a)
+    q_b = torch.empty(B, Hq, D, dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    T.qkv_rope_append(x, w, q_b, pool_b, num_kv_heads=Hkv, norm_weight=nw, eps=1e-6, status=status, **rope)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    tol = dict(rtol=0, atol=0) if mode != 2 else dict(rtol=2 ** -7 if dtype == torch.bfloat16 else 2 ** -10, atol=1e-6)
+    assert torch.allclose(q_b.float(), q_a.float(), **tol)
+    assert torch.allclose(pool_b.float(), pool_a.float(), **tol)
+    assert float(pool_b.float().abs().sum()) > 0

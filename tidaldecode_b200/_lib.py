@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv",
 )
 
 
@@ -115,6 +115,8 @@ def _load() -> C.CDLL:
     lib.tidal_rms_norm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_int, C.c_int, C.c_void_p]
     lib.tidal_decode_linear.restype = C.c_int
     lib.tidal_decode_linear.argtypes = [C.POINTER(LinearArgs), C.c_void_p]
+    lib.tidal_decode_qkv.restype = C.c_int
+    lib.tidal_decode_qkv.argtypes = [C.POINTER(LinearArgs), C.POINTER(RopeAppendArgs), C.c_void_p]
     return lib
 
 

@@ -219,12 +219,30 @@ __device__ __forceinline__ void ldsm_a(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
 
+// Where the q, k and v rows of a fused q|k|v projection go: q (rotated) to q_out, k (rotated) and v into
+// the slot of the sequence's newest token in the paged KV pool — what tidal_rope_append does in a
+// launch of its own.
+struct QkvEpilogue {
+    void* q_out;                 // [M][Hq][D]
+    char* kv;
+    const int32_t* page_table;
+    int64_t pt_stride;
+    const int32_t* pos_dev;
+    int32_t pos;
+    const float* inv_freq;
+    float theta, scale;
+    int32_t rope_mode, Hq, Hkv, D, page_size;
+    int64_t num_pages;
+};
+
 struct LinearMmaGeom {
-    int M, tiles, units, tpu, t0_stride, tile1_off;
+    // unit u covers tile t0 = (u / upg) * tpg + u % upg and, with tpu == 2, tile t0 + tile1_off
+    int M, tiles, units, tpu, upg, tpg, tile1_off;
     int KC;        // elements of K per stage
     int S;         // stages
     uint32_t* status;
     int static_weights;   // the weights were not written by the stream's preceding kernel: fetch them before stream order
+    QkvEpilogue qkv;      // TIDAL_LINEAR_QKV_ROPE only
 };
 
 __host__ __device__ inline size_t lin_x_bytes(int M, int K) { return ((size_t)M * (K * 2 + 16) + 127) & ~(size_t)127; }
@@ -267,7 +285,7 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
         int it = 0;
         for (int u = blockIdx.x; u < gm.units; u += gridDim.x) {
             for (int t = 0; t < gm.tpu; ++t) {
-                const int tile = u * gm.t0_stride + (t ? gm.tile1_off : 0);
+                const int tile = (u / gm.upg) * gm.tpg + u % gm.upg + (t ? gm.tile1_off : 0);
                 if (tile >= gm.tiles) break;
                 const int trow = pw * 8 + (lane & 7);
                 const int row = min(tile * 16 + trow, p.N - 1);             // a short last tile reads the last row again
@@ -348,7 +366,7 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
         const uint32_t a_lane = (uint32_t)((lane & 15) * pitch + (lane >> 4) * 16);
         int it = 0, round = 0;
         for (int u = blockIdx.x; u < gm.units; u += gridDim.x, ++round) {
-            const int t0 = u * gm.t0_stride, t1 = t0 + gm.tile1_off;
+            const int t0 = (u / gm.upg) * gm.tpg + u % gm.upg, t1 = t0 + gm.tile1_off;
             const int ntile = (gm.tpu == 2 && t1 < gm.tiles) ? 2 : 1;
             float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll 1
@@ -402,7 +420,50 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
                 if (m < M) {
                     T* y = reinterpret_cast<T*>(p.y);
                     const int ra = t0 * 16 + rr;
-                    if (p.epilogue == TIDAL_LINEAR_SILU_MUL) {
+                    if (p.epilogue == TIDAL_LINEAR_QKV_ROPE) {
+                        // s0, s1: elements i and i + D/2 of head h of sequence m's q|k|v row
+                        const QkvEpilogue& e = gm.qkv;
+                        const int tph = e.D / 16;                            // tiles per head
+                        const int h = t0 / tph, i0 = (t0 - h * tph) * 16 + rr;
+                        const int pos = e.pos_dev ? e.pos_dev[m] : e.pos;
+                        float x0 = V::round(s0), x1 = V::round(s1);          // what a separate projection would have stored
+                        if (h < e.Hq + e.Hkv && e.rope_mode != 0) {
+                            const float inv = e.inv_freq ? e.inv_freq[i0] : 1.0f / powf(e.theta, (float)(2 * i0) / (float)e.D);
+                            const float ang = ((float)pos / e.scale) * inv;
+                            float cs = cosf(ang), sn = sinf(ang);
+                            float r0, r1;
+                            if (e.rope_mode == 1) {    // the reference model's order: cos, sin and each product rounded to T
+                                cs = V::round(cs);
+                                sn = V::round(sn);
+                                r0 = V::round(__fadd_rn(V::round(__fmul_rn(x0, cs)), V::round(__fmul_rn(-x1, sn))));
+                                r1 = V::round(__fadd_rn(V::round(__fmul_rn(x1, cs)), V::round(__fmul_rn(x0, sn))));
+                            } else {
+                                r0 = x0 * cs - x1 * sn;
+                                r1 = x1 * cs + x0 * sn;
+                            }
+                            x0 = r0;
+                            x1 = r1;
+                        }
+                        if (h < e.Hq) {
+                            T* q = reinterpret_cast<T*>(e.q_out) + ((size_t)m * e.Hq + h) * e.D + i0;
+                            q[0] = from_f32<T>(x0);
+                            q[e.D / 2] = from_f32<T>(x1);
+                        } else {
+                            const int pg = pos / e.page_size, entry = pos - pg * e.page_size;
+                            const int64_t page = e.page_table ? e.page_table[(size_t)m * e.pt_stride + pg] : (int64_t)m * e.pt_stride + pg;
+                            if (pos < 0 || page < 0 || page >= e.num_pages) {
+                                if (gm.status) atomicOr(gm.status, TIDAL_DEV_BAD_INDEX);
+                            } else {
+                                const size_t plane = (size_t)e.page_size * e.Hkv * e.D;           // elements of a page's K (or V) plane
+                                const bool is_v = h >= e.Hq + e.Hkv;
+                                const int hk = h - e.Hq - (is_v ? e.Hkv : 0);
+                                T* dst = reinterpret_cast<T*>(e.kv) + (size_t)page * 2 * plane + (is_v ? plane : 0) +
+                                         ((size_t)entry * e.Hkv + hk) * e.D + i0;
+                                dst[0] = from_f32<T>(x0);
+                                dst[e.D / 2] = from_f32<T>(x1);
+                            }
+                        }
+                    } else if (p.epilogue == TIDAL_LINEAR_SILU_MUL) {
                         const float gt = V::round(s0), up = V::round(s1);
                         const float sg = V::round(gt / (1.f + __expf(-gt)));
                         y[(size_t)m * (p.N / 2) + ra] = from_f32<T>(sg * up);
@@ -444,11 +505,14 @@ static int launch_linear_mma(const LinearParams& p, LinearMmaGeom gm, size_t sme
     const int sms = sm_count_cached();
     if (p.epilogue == TIDAL_LINEAR_SILU_MUL) {
         const int F = p.N / 2;
-        gm.tiles = p.N / 16; gm.units = F / 16; gm.tpu = 2; gm.t0_stride = 1; gm.tile1_off = F / 16;
+        gm.tiles = p.N / 16; gm.units = F / 16; gm.tpu = 2; gm.upg = gm.units; gm.tpg = gm.units; gm.tile1_off = F / 16;
+    } else if (p.epilogue == TIDAL_LINEAR_QKV_ROPE) {
+        const int D = gm.qkv.D;                     // pairs of tiles half a head apart
+        gm.tiles = p.N / 16; gm.units = p.N / 32; gm.tpu = 2; gm.upg = D / 32; gm.tpg = D / 16; gm.tile1_off = D / 32;
     } else {
         gm.tiles = (p.N + 15) / 16;
         gm.tpu = gm.tiles >= 8 * sms ? 2 : 1;       // small matrices: one tile per round, so that every CTA gets some
-        gm.units = (gm.tiles + gm.tpu - 1) / gm.tpu; gm.t0_stride = gm.tpu; gm.tile1_off = 1;
+        gm.units = (gm.tiles + gm.tpu - 1) / gm.tpu; gm.upg = 1; gm.tpg = gm.tpu; gm.tile1_off = 1;
     }
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int grid = gm.units < sms * per_sm ? gm.units : sms * per_sm;
@@ -535,4 +599,42 @@ extern "C" int tidal_decode_linear(const tidal_linear_args* a, void* stream) {
         case TIDAL_DTYPE_BF16: return dispatch_m<__nv_bfloat16>(p, a->M, st);
         default: return dispatch_m<float>(p, a->M, st);
     }
+}
+
+extern "C" int tidal_decode_qkv(const tidal_linear_args* a, const tidal_rope_append_args* r, void* stream) {
+    TIDAL_REQUIRE(a != nullptr && r != nullptr, TIDAL_ERR_ARG, "args is NULL");
+    TIDAL_REQUIRE(a->d_x && a->d_w, TIDAL_ERR_ARG, "x and w must be given");
+    TIDAL_REQUIRE(r->d_q && r->d_kv, TIDAL_ERR_ARG, "the q output and the KV pool must be given");
+    TIDAL_REQUIRE(a->M >= 1 && a->M <= 8 && r->batch == a->M && r->tokens_per_seq == 1, TIDAL_ERR_ARG,
+                  "one new token for each of 1..8 sequences (M %d, batch %d, tokens_per_seq %d)", a->M, r->batch, r->tokens_per_seq);
+    TIDAL_REQUIRE((a->dtype == TIDAL_DTYPE_F16 || a->dtype == TIDAL_DTYPE_BF16) && r->dtype == a->dtype, TIDAL_ERR_ARG,
+                  "the fused q|k|v projection is built for f16/bf16");
+    TIDAL_REQUIRE(r->head_dim == 64 || r->head_dim == 128, TIDAL_ERR_ARG, "unsupported head_dim %d (built: 64, 128)", r->head_dim);
+    TIDAL_REQUIRE(r->num_qo_heads >= 1 && r->num_kv_heads >= 1 && a->N == (r->num_qo_heads + 2 * r->num_kv_heads) * r->head_dim,
+                  TIDAL_ERR_ARG, "W must have (Hq + 2 Hkv) * D = %d rows, got %d", (r->num_qo_heads + 2 * r->num_kv_heads) * r->head_dim, a->N);
+    TIDAL_REQUIRE(a->K % 16 == 0 && a->K >= 128, TIDAL_ERR_ARG, "K %d must be a multiple of 16, at least 128", a->K);
+    TIDAL_REQUIRE(r->rope_mode >= 0 && r->rope_mode <= 2, TIDAL_ERR_ARG, "rope_mode must be 0, 1 or 2");
+    TIDAL_REQUIRE(r->rope_mode == 0 || r->rope_scale > 0.f, TIDAL_ERR_ARG, "rope_scale must be positive");
+    TIDAL_REQUIRE(r->rope_mode == 0 || r->d_inv_freq || r->rope_theta > 0.f, TIDAL_ERR_ARG, "rope_theta must be positive");
+    TIDAL_REQUIRE(r->page_size >= 1 && r->num_pages >= 1, TIDAL_ERR_ARG, "bad page_size/num_pages");
+    TIDAL_REQUIRE((((uintptr_t)a->d_x | (uintptr_t)a->d_w | (uintptr_t)a->d_norm_weight) & 15) == 0, TIDAL_ERR_ARG,
+                  "x, w and the norm weight must be 16-byte aligned");
+    LinearParams p;
+    p.x = a->d_x; p.w = a->d_w; p.y = nullptr; p.residual = nullptr; p.norm_w = a->d_norm_weight;
+    p.eps = a->norm_eps; p.round_before_weight = a->norm_round_before_weight;
+    p.N = a->N; p.K = a->K; p.epilogue = TIDAL_LINEAR_QKV_ROPE;
+    p.items = 0; p.up_off = 0;
+    LinearMmaGeom gm;
+    gm.M = a->M; gm.status = r->d_status ? (uint32_t*)r->d_status : (uint32_t*)a->d_status; gm.static_weights = a->static_weights;
+    QkvEpilogue& e = gm.qkv;
+    e.q_out = r->d_q; e.kv = (char*)r->d_kv; e.page_table = r->d_page_table; e.pt_stride = r->page_table_stride;
+    e.pos_dev = r->d_pos0; e.pos = r->pos0; e.inv_freq = r->d_inv_freq; e.theta = r->rope_theta; e.scale = r->rope_scale;
+    e.rope_mode = r->rope_mode; e.Hq = r->num_qo_heads; e.Hkv = r->num_kv_heads; e.D = r->head_dim; e.page_size = r->page_size;
+    e.num_pages = r->num_pages;
+    size_t smem = 0;
+    int per_sm = 1;
+    TIDAL_REQUIRE(plan_linear_mma(p, a->M, &gm, &smem, &per_sm), TIDAL_ERR_ARG, "activations of %d x %d do not fit shared memory", a->M, a->K);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a->dtype == TIDAL_DTYPE_F16) return launch_linear_mma<__half>(p, gm, smem, per_sm, st);
+    return launch_linear_mma<__nv_bfloat16>(p, gm, smem, per_sm, st);
 }

@@ -331,3 +331,41 @@ def linear(x: torch.Tensor, weight: torch.Tensor, *, out: Optional[torch.Tensor]
     with torch.cuda.device(x.device):
         check(lib.tidal_decode_linear(C.byref(a), _stream()), "tidal_decode_linear")
     return out
+
+
+def qkv_rope_append(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, kv: torch.Tensor, *,
+                    num_kv_heads: int, norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6,
+                    round_before_weight: bool = True, pos0: int = 0, pos0_dev: Optional[torch.Tensor] = None,
+                    page_table: Optional[torch.Tensor] = None, pages_per_seq: Optional[int] = None, rope_theta: float = 1e4,
+                    rope_scale: float = 1.0, rope_mode: int = 1, inv_freq: Optional[torch.Tensor] = None,
+                    static_weights: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The q|k|v projection of one new token per sequence with RoPE and the KV append folded in; see
+    tidal_decode_qkv in include/tidal_b200.h.  x [B, K]; weight [(Hq + 2 Hkv) D, K] (q heads, k heads, v
+    heads); q_out [B, Hq, D] receives the rotated queries; k and v land in the pool."""
+    _need_cuda(x, weight, q_out, kv, norm_weight, pos0_dev, page_table, inv_freq, status)
+    B, Hq, D = q_out.shape
+    N, K = weight.shape
+    if x.numel() != B * K or weight.dtype != x.dtype or q_out.dtype != x.dtype or kv.dtype != x.dtype:
+        raise RuntimeError("x must be [B, K] and share its dtype with the weight, q_out and the pool")
+    a = _lib.LinearArgs()
+    a.d_x, a.d_w = x.data_ptr(), weight.data_ptr()
+    a.d_norm_weight = _ptr(norm_weight)
+    a.norm_eps, a.norm_round_before_weight = float(eps), 1 if round_before_weight else 0
+    a.M, a.N, a.K, a.dtype = B, N, K, _dtype_code(x)
+    a.static_weights = 1 if static_weights else 0
+    r = RopeAppendArgs()
+    r.d_q, r.d_kv = q_out.data_ptr(), kv.data_ptr()
+    if page_table is not None:
+        r.d_page_table, r.page_table_stride = page_table.data_ptr(), page_table.shape[1]
+    else:
+        r.page_table_stride = pages_per_seq if pages_per_seq is not None else kv.shape[0] // B
+    r.d_pos0, r.pos0, r.d_inv_freq = _ptr(pos0_dev), int(pos0), _ptr(inv_freq)
+    r.rope_theta, r.rope_scale, r.rope_mode = float(rope_theta), float(rope_scale), int(rope_mode)
+    r.batch, r.tokens_per_seq = B, 1
+    r.num_qo_heads, r.num_kv_heads, r.head_dim = Hq, int(num_kv_heads), D
+    r.page_size, r.num_pages = kv.shape[2], kv.shape[0]
+    r.dtype = _dtype_code(x)
+    r.d_status = _ptr(status)
+    with torch.cuda.device(x.device):
+        check(lib.tidal_decode_qkv(C.byref(a), C.byref(r), _stream()), "tidal_decode_qkv")
+    return q_out

@@ -102,16 +102,23 @@ class GraphDecoder:
             att = layer.self_attn
             nq, nkv = att.num_heads * att.head_dim, att.num_key_value_heads * att.head_dim
             ln1, ln2 = layer.input_layernorm, layer.post_attention_layernorm
-            if fused:
-                qkv = ops.linear(h, self._wqkv[li], norm_weight=ln1.weight, eps=ln1.variance_epsilon, **lin)
-            else:
-                qkv = F.linear(ln1(h), self._wqkv[li])
-            q = qkv[:, :nq].contiguous().view(B, att.num_heads, att.head_dim)
-            kk = qkv[:, nq:nq + nkv].contiguous().view(B, att.num_key_value_heads, att.head_dim)
-            vv = qkv[:, nq + nkv:].contiguous().view(B, att.num_key_value_heads, att.head_dim)
             pool = c.kv_cache.buf_layer(att.layer_idx)
-            ops.rope_append(q, kk, vv, pool, batch=B, pos0_dev=self.pos, page_table=table, rope_theta=att.rope_theta,
-                            rope_scale=att.rope_scale, rope_mode=att.rope_mode, inv_freq=att._inv_freq_on(self.device))
+            rope = dict(pos0_dev=self.pos, page_table=table, rope_theta=att.rope_theta, rope_scale=att.rope_scale,
+                        rope_mode=att.rope_mode, inv_freq=att._inv_freq_on(self.device))
+            if fused and h.dtype != torch.float32:
+                # norm, q|k|v projection, RoPE and the KV append in one launch
+                q = torch.empty(B, att.num_heads, att.head_dim, dtype=h.dtype, device=h.device)
+                ops.qkv_rope_append(h, self._wqkv[li], q, pool, num_kv_heads=att.num_key_value_heads, norm_weight=ln1.weight,
+                                    eps=ln1.variance_epsilon, **rope, **lin)
+            else:
+                if fused:
+                    qkv = ops.linear(h, self._wqkv[li], norm_weight=ln1.weight, eps=ln1.variance_epsilon, **lin)
+                else:
+                    qkv = F.linear(ln1(h), self._wqkv[li])
+                q = qkv[:, :nq].contiguous().view(B, att.num_heads, att.head_dim)
+                kk = qkv[:, nq:nq + nkv].contiguous().view(B, att.num_key_value_heads, att.head_dim)
+                vv = qkv[:, nq + nkv:].contiguous().view(B, att.num_key_value_heads, att.head_dim)
+                ops.rope_append(q, kk, vv, pool, batch=B, **rope)
             o = torch.empty_like(q)
             if isinstance(att, SearchAttention):
                 ops.decode_attention(q, pool, self.max_seq_len, ws, out=o, page_table=table, seq_lens=self.seq_lens,
