@@ -513,6 +513,8 @@ LINEAR_CASES = [
     ("bf16", 4, 6144, 4096, True, False, False),         # q|k|v of an 8B layer, four sequences
     ("bf16", 8, 512, 1024, False, True, False),
     ("bf16", 4, 28672, 4096, True, False, True),         # gate|up of an 8B layer, four sequences (tensor-core kernel, tile pairs)
+    ("bf16", 4, 4096, 14336, False, True, False),        # activations too large to keep resident: they travel with the weights
+    ("f16", 8, 1024, 8192, False, False, False),
     ("f16", 2, 1000, 4096, False, True, False),          # N not a multiple of the 16-row tile
     ("bf16", 1, 688, 352, False, False, True),           # F = 344 is not a multiple of 16: CUDA-core kernel
     ("f16", 3, 1001, 512, True, True, False),            # odd N: the last row has no partner

@@ -51,18 +51,28 @@ def main():
     ap.add_argument("--head_reduce", choices=["none", "sum"], default="none")
     ap.add_argument("--full", action="store_true", help="full attention in every layer (budget = context)")
     ap.add_argument("--iteration", type=int, default=1)
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoded in lockstep; more than one implies --random_cache")
+    ap.add_argument("--random_cache", action="store_true",
+                    help="skip prefill: decode from KV caches filled with random values (prefill takes one sequence at a time)")
     ap.add_argument("--torch_linear", action="store_true", help="projections, norms and activations as separate torch/cuBLAS ops")
     a = ap.parse_args()
     sel = [] if a.full else a.selection_layers
     m, dtype = build(a.model, sel, a.head_reduce, True)
     max_len = a.context_len + a.decode_len + 8
-    rt = GraphDecoder(m, max_seq_len=max_len, token_budget=a.token_budget, dtype=dtype, fused_linear=not a.torch_linear)
+    rt = GraphDecoder(m, max_seq_len=max_len, token_budget=a.token_budget, dtype=dtype, fused_linear=not a.torch_linear,
+                      batch_size=a.batch)
     g = torch.Generator().manual_seed(0)
     for it in range(a.iteration):
-        prompt = torch.randint(0, m.vocab_size, (1, a.context_len), generator=g)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        rt.prefill(prompt)
+        if a.batch > 1 or a.random_cache:
+            rt.start_from_cache(a.context_len, torch.randint(0, m.vocab_size, (a.batch,), generator=g))
+            kv = rt.c.kv_cache
+            for layer in range(kv.pool.num_layers):              # N(0,1) keys and values, a layer at a time
+                kv.pool.buf[layer].normal_()
+        else:
+            prompt = torch.randint(0, m.vocab_size, (1, a.context_len), generator=g)
+            rt.prefill(prompt)
         torch.cuda.synchronize()
         t_prefill = time.perf_counter() - t0
         rt.decode(2)                                            # eager step + capture + one replay
@@ -76,10 +86,10 @@ def main():
         wall = time.perf_counter() - t0
         n = a.decode_len - 2
         print(json.dumps({
-            "model": a.model, "context_len": a.context_len, "decode_len": a.decode_len,
+            "model": a.model, "batch": a.batch, "context_len": a.context_len, "decode_len": a.decode_len,
             "token_budget": None if a.full else a.token_budget, "selection_layers": sel, "head_reduce": a.head_reduce, "fused_linear": rt.fused_linear,
             "prefill_s": round(t_prefill, 3), "decode_ms_per_token_device": round(e0.elapsed_time(e1) / n, 4),
-            "decode_ms_per_token_wall": round(wall * 1e3 / n, 4), "tokens_per_s": round(n / wall, 1),
+            "decode_ms_per_token_wall": round(wall * 1e3 / n, 4), "tokens_per_s": round(a.batch * n / wall, 1),
             "status": rt.c.workspace.status() | int(rt.lin_status.item()), "last_tokens": toks[0, -4:].tolist()}))
 
 

@@ -242,11 +242,12 @@ struct LinearMmaGeom {
     int S;         // stages
     uint32_t* status;
     int static_weights;   // the weights were not written by the stream's preceding kernel: fetch them before stream order
+    int stream_x;         // the activations travel with the weights, M more rows per stage (no norm; for x too large to keep resident)
     QkvEpilogue qkv;      // TIDAL_LINEAR_QKV_ROPE only
 };
 
 __host__ __device__ inline size_t lin_x_bytes(int M, int K) { return ((size_t)M * (K * 2 + 16) + 127) & ~(size_t)127; }
-__host__ __device__ inline size_t lin_stage_bytes(int KC) { return (size_t)16 * (KC * 2 + 16); }
+__host__ __device__ inline size_t lin_stage_bytes(int KC, int rows) { return (size_t)rows * (KC * 2 + 16); }
 
 template <typename T>
 __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const __grid_constant__ LinearParams p,
@@ -256,9 +257,11 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
     const int K = p.K, M = gm.M, KC = gm.KC, S = gm.S;
     const int xpitch = K * 2 + 16;                            // bytes; the 8 x 4 lanes of a B fragment then hit 32 distinct banks
     const int pitch = KC * 2 + 16;                            // bytes between the 16 rows of a stage
-    unsigned char* xs = lin_smem;                             // [M] rows of x, normalised if asked for
-    unsigned char* stages = lin_smem + lin_x_bytes(M, K);     // [S][16][pitch]
-    float* red = reinterpret_cast<float*>(stages + (size_t)S * lin_stage_bytes(KC));        // [2][8 warps][2 tiles][128]
+    const int srows = gm.stream_x ? 16 + M : 16;              // rows of a stage: the tile, then (streamed) the x rows
+    const size_t sbytes = lin_stage_bytes(KC, srows);
+    unsigned char* xs = lin_smem;                             // [M] rows of x, normalised if asked for (resident mode)
+    unsigned char* stages = lin_smem + (gm.stream_x ? 0 : lin_x_bytes(M, K));     // [S][srows][pitch]
+    float* red = reinterpret_cast<float*>(stages + (size_t)S * sbytes);             // [2][8 warps][2 tiles][128]
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(red + 2 * kLinConsumers * 256);
     uint64_t* empty_bar = full_bar + S;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty_bar + S);
@@ -281,7 +284,8 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
     if (warp >= kLinConsumers) {
         // ============================================================== producers
         const int pw = warp - kLinConsumers;                  // rows 8 pw .. 8 pw + 7 of every tile
-        if (!gm.static_weights) pdl_wait();      // else never ordered after the predecessor: it reads nothing but weights
+        // with static weights and resident x never ordered after the predecessor: it reads nothing but weights
+        if (!gm.static_weights || gm.stream_x) pdl_wait();
         int it = 0;
         for (int u = blockIdx.x; u < gm.units; u += gridDim.x) {
             for (int t = 0; t < gm.tpu; ++t) {
@@ -294,10 +298,13 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
                     const int s = it % S;
                     if (it >= S && !mbar_wait_bounded(&empty_bar[s], ((it / S) - 1) & 1, abort_flag, gm.status)) break;
                     const uint32_t len = (uint32_t)min(KC, K - kc * KC) * 2u;
-                    if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&full_bar[s], 16u * len);   // (the other warp's copies may land first)
+                    if (pw == 0 && lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)srows * len);   // (the other warp's copies may land first)
                     __syncwarp();
                     if (lane < 8)
-                        bulk_g2s(stages + (size_t)s * lin_stage_bytes(KC) + (size_t)trow * pitch, src + (size_t)kc * KC * 2, len, &full_bar[s]);
+                        bulk_g2s(stages + (size_t)s * sbytes + (size_t)trow * pitch, src + (size_t)kc * KC * 2, len, &full_bar[s]);
+                    else if (gm.stream_x && pw == 0 && lane < 8 + M)
+                        bulk_g2s(stages + (size_t)s * sbytes + (size_t)(16 + lane - 8) * pitch,
+                                 reinterpret_cast<const char*>(p.x) + ((size_t)(lane - 8) * K + (size_t)kc * KC) * 2, len, &full_bar[s]);
                 }
             }
         }
@@ -311,7 +318,7 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
         const int ctid = threadIdx.x;                         // consumers are warps 0..7
         constexpr int CT = kLinConsumers * 32;
         // ---- activations into shared memory, RMS-normalised on the way if a norm weight is given
-        {
+        if (!gm.stream_x) {
             const int nvec = K / 8;
             const uint4* xg = reinterpret_cast<const uint4*>(p.x);
             if (p.norm_w) {
@@ -361,7 +368,9 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
 
         const int g = lane >> 2, c = lane & 3;
         const bool has_x = g < M;
-        const unsigned char* xrow = xs + (size_t)g * xpitch + c * 4;      // B fragment: x[g][k0 + 2c, +1] and [k0 + 8 + 2c, +1]
+        // B fragment: x[g][k0 + 2c, +1] and [k0 + 8 + 2c, +1], from the resident rows or from the stage
+        const unsigned char* xrow = xs + (size_t)g * xpitch + c * 4;
+        const size_t xstage = (size_t)(16 + g) * pitch + c * 4;
         const int kslice = KC / kLinConsumers;                           // K elements of a stage per warp (a multiple of 16)
         const uint32_t a_lane = (uint32_t)((lane & 15) * pitch + (lane >> 4) * 16);
         int it = 0, round = 0;
@@ -378,8 +387,8 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
                     mbar_wait_bounded(&full_bar[s], (it / S) & 1, abort_flag, gm.status);
                     const int len = min(KC, K - kc * KC);                // elements of this stage
                     const int k_lo = warp * kslice, k_hi = min(len, k_lo + kslice);
-                    const uint32_t st = smem_u32(stages + (size_t)s * lin_stage_bytes(KC)) + a_lane;
-                    const unsigned char* xk = xrow + (size_t)kc * KC * 2;
+                    const uint32_t st = smem_u32(stages + (size_t)s * sbytes) + a_lane;
+                    const unsigned char* xk = gm.stream_x ? stages + (size_t)s * sbytes + xstage : xrow + (size_t)kc * KC * 2;
 #pragma unroll 4
                     for (int k0 = k_lo; k0 < k_hi; k0 += 16) {
                         uint32_t a[4];
@@ -484,18 +493,28 @@ __global__ void __launch_bounds__(kLinMmaThreads) decode_linear_mma_kernel(const
 // two per SM or one next to the next launch's, measured no better: the kernel streams at the copy rate
 // either way and pays ~5 us per launch for ramp-up and tail.)
 static bool plan_linear_mma(const LinearParams& p, int M, LinearMmaGeom* gm, size_t* smem, int* per_sm) {
-    const size_t fixed = lin_x_bytes(M, p.K) + (size_t)2 * kLinConsumers * 256 * sizeof(float) + 2 * 8 * sizeof(uint64_t) + 64;
+    const size_t other = (size_t)2 * kLinConsumers * 256 * sizeof(float) + 2 * 8 * sizeof(uint64_t) + 64;
     const size_t budget = 225 * 1024;
-    for (int KC : {2048, 1024, 512, 256, 128}) {
-        if (KC > p.K && KC > 128) continue;                   // no stage longer than a row (but at least 128: 16 per warp)
-        if (fixed + 3 * lin_stage_bytes(KC) > budget) continue;
-        int S = (int)((budget - fixed) / lin_stage_bytes(KC));
-        if (S > 8) S = 8;
-        gm->KC = KC; gm->S = S;
-        *smem = fixed + (size_t)S * lin_stage_bytes(KC);
-        *per_sm = 1;
+    *per_sm = 1;
+    auto try_plan = [&](int KC, bool stream) {
+        if (KC > p.K && KC > 128) return false;               // no stage longer than a row (but at least 128: 16 per warp)
+        const size_t fixed = other + (stream ? 0 : lin_x_bytes(M, p.K));
+        const size_t stage = lin_stage_bytes(KC, stream ? 16 + M : 16);
+        if (fixed + 3 * stage > budget) return false;
+        const int S = (int)((budget - fixed) / stage);
+        gm->KC = KC; gm->S = S > 8 ? 8 : S; gm->stream_x = stream ? 1 : 0;
+        *smem = fixed + (size_t)gm->S * stage;
         return true;
-    }
+    };
+    // x resident in shared memory (needed for the fused norm; lets the producers run ahead of stream order) with
+    // rows of at least 2 KB per copy; else x travelling with the weights; else resident with shorter stages
+    for (int KC : {2048, 1024})
+        if (try_plan(KC, false)) return true;
+    if (!p.norm_w)
+        for (int KC : {2048, 1024})
+            if (try_plan(KC, true)) return true;
+    for (int KC : {512, 256, 128})
+        if (try_plan(KC, false)) return true;
     return false;
 }
 

@@ -87,6 +87,26 @@ class GraphDecoder:
         self._prefill_len = P
         return first
 
+    @torch.inference_mode()
+    def start_from_cache(self, seq_len: int, first_tokens: torch.Tensor) -> None:
+        """Begin decoding with KV caches the caller has filled: every sequence holds `seq_len` tokens in the
+        controller's cache (pages reserved here, to be written through `self.c.kv_cache.buf_layer(l)` and
+        `self.c.kv_cache.page_table` before the first `decode`), and `first_tokens` [B] are fed first.
+        The latency benchmark uses it for batches: the reference times decode steps on random data as well
+        (scripts/bench_textgen.py:78-89), and prefill takes one sequence at a time."""
+        c = self.c
+        if seq_len + 1 > self.max_seq_len:
+            raise RuntimeError("seq_len does not leave room for a decoded token")
+        c.clean_states()
+        c.kv_cache.reserve(self.max_seq_len)
+        c.kv_cache._seqlen = seq_len
+        self.seq_lens.fill_(seq_len + 1)
+        self.pos.fill_(seq_len)
+        self.row_lens.fill_(seq_len + 1)
+        self.tok.copy_(first_tokens.view(self.B, 1).to(self.device))
+        self.step_idx.zero_()
+        self._prefill_len = seq_len
+
     # --------------------------------------------------------------- one step
     def _step(self):
         m, c = self.model, self.c
