@@ -22,6 +22,7 @@ MODELS = {
     # name: (hidden, ffn, layers, heads, kv_heads, vocab, theta, dtype)
     "llama2-7b": (4096, 11008, 32, 32, 32, 32000, 1e4, torch.float16),
     "llama3-8b": (4096, 14336, 32, 32, 8, 128256, 5e5, torch.bfloat16),
+    "llama-1b": (2048, 5632, 22, 32, 4, 32000, 1e4, torch.float16),       # small enough to profile (2.2 GB of weights)
     "tiny": (256, 688, 4, 4, 4, 1024, 1e4, torch.float32),
 }
 

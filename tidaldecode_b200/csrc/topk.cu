@@ -600,9 +600,25 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     uint32_t need = k - above;
     if (sh.nsel != above && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
 
+    // Few candidates in shared memory (the usual case: a 12-bit first digit leaves a few dozen keys in the
+    // threshold bin): rank them directly — keys are distinct, so the `need` largest are those with fewer
+    // than `need` larger ones — instead of up to seven more radix passes with four barriers each.
+    const bool few = !overflow && !cand_global && ncand_total <= 256u && need <= ncand_total;
+    if (few) {
+        if ((uint32_t)t < ncand_total) {
+            const uint64_t key = cand[t];
+            uint32_t larger = 0;
+            for (uint32_t i = 0; i < ncand_total; ++i) larger += cand[i] > key ? 1u : 0u;
+            if (larger < need) {
+                const uint32_t at = nsel + atomicAdd(&sh.cnt, 1u);
+                if (at < (uint32_t)kClusterMaxK) sel[at] = key;
+            }
+        }
+        __syncthreads();
+    }
     uint64_t prefix = (uint64_t)bstar << 52;
     uint64_t known_mask = 0xFFFull << 52;
-    bool done = (need == ncand_total);
+    bool done = few || (need == ncand_total);
     for (int shift = 44; !done && shift >= -4; shift -= 8) {
         const int sft = shift < 0 ? 0 : shift;
         const int nb = shift < 0 ? 16 : 256;
@@ -624,13 +640,15 @@ __global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkPa
     const uint64_t thr = prefix;
 
     // winners: sel[0, nsel) plus the candidates at or above the threshold, appended behind them
-    for_each_cluster_candidate(p, row, bstar, cand, ncand_total, overflow, [&](uint64_t key) {
-        if (key >= thr) {
-            const uint32_t at = nsel + atomicAdd(&sh.cnt, 1u);
-            if (at < (uint32_t)kClusterMaxK) sel[at] = key;
-        }
-    });
-    __syncthreads();
+    if (!few) {
+        for_each_cluster_candidate(p, row, bstar, cand, ncand_total, overflow, [&](uint64_t key) {
+            if (key >= thr) {
+                const uint32_t at = nsel + atomicAdd(&sh.cnt, 1u);
+                if (at < (uint32_t)kClusterMaxK) sel[at] = key;
+            }
+        });
+        __syncthreads();
+    }
     const uint32_t got = min(nsel + sh.cnt, k);
     if (nsel + sh.cnt != k && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
     // order by position: a key's low word is 0xFFFFFFFF - position, so rank by descending low word
