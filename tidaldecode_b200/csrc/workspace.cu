@@ -33,7 +33,7 @@ const WsLayout* find_ws(const void* d_ws) {
 
 using namespace tidal;
 
-extern "C" int tidal_version(void) { return 100; }
+extern "C" int tidal_version(void) { return 101; }   // 101: tidal_decode_linear, tidal_decode_qkv
 
 extern "C" const char* tidal_last_error(void) { return g_err; }
 
