@@ -90,6 +90,14 @@ def test_argument_errors_without_gpu(L):
     assert L.lib.tidal_decode_linear(C.byref(lin), None) == L.ERR_ARG and "multiple of 8" in L.last_error()
     lin.K, lin.N, lin.epilogue = 64, 15, L.LINEAR_SILU_MUL
     assert L.lib.tidal_decode_linear(C.byref(lin), None) == L.ERR_ARG and "even N" in L.last_error()
+    rq = L.RopeAppendArgs()
+    assert L.lib.tidal_decode_qkv(C.byref(lin), C.byref(rq), None) == L.ERR_ARG            # no q output, no pool
+    lin.K, lin.N, lin.epilogue, lin.M = 256, (8 + 2 * 2) * 64, L.LINEAR_PLAIN, 2
+    rq.d_q = rq.d_kv = 256
+    rq.batch, rq.tokens_per_seq, rq.num_qo_heads, rq.num_kv_heads, rq.head_dim, rq.dtype = 2, 1, 8, 2, 64, L.DTYPE_F32
+    assert L.lib.tidal_decode_qkv(C.byref(lin), C.byref(rq), None) == L.ERR_ARG and "f16/bf16" in L.last_error()
+    rq.dtype, rq.num_kv_heads = L.DTYPE_F16, 4
+    assert L.lib.tidal_decode_qkv(C.byref(lin), C.byref(rq), None) == L.ERR_ARG and "rows" in L.last_error()
     r = L.RopeAppendArgs()
     assert L.lib.tidal_rope_append(C.byref(r), None) == L.ERR_ARG
     assert L.lib.tidal_ws_bytes(1, 32, 128, 32, 32768) > 0

@@ -278,3 +278,31 @@ def test_graph_decoder_gqa_head_sum_bf16():
         eager_toks = m2.greedy_generate(prompt.cuda(), 7)
     assert graph_toks == eager_toks, (graph_toks, eager_toks)
     assert rt.c.workspace.status() == 0
+
+
+def test_graph_decoder_batch_from_filled_caches():
+    """Sequences decoded in lockstep from caches the caller filled (GraphDecoder.start_from_cache): two
+    sequences with the same cache content and first token produce the same tokens as one sequence alone."""
+    from tidaldecode_b200.runtime import GraphDecoder
+
+    W = O.TinyLlamaWeights(vocab=512, hidden=512, layers=4, heads=8, kv_heads=2, ffn=352, seed=5, dtype=torch.bfloat16)
+    ctx, steps = 200, 6
+    outs = []
+    ref_pool = None
+    for B in (1, 2):
+        m = _tiny_model(W, torch.bfloat16, (2,), "sum", True, 1)
+        rt = GraphDecoder(m, max_seq_len=ctx + steps + 4, token_budget=32, batch_size=B)
+        rt.start_from_cache(ctx, torch.full((B,), 7))
+        kv = rt.c.kv_cache
+        g = torch.Generator(device="cuda").manual_seed(3)
+        for layer in range(kv.pool.num_layers):
+            buf = kv.pool.buf[layer]
+            t0 = kv.page_table[0, :ctx].long()
+            buf[t0] = torch.randn(ctx, *buf.shape[1:], generator=g, device="cuda").to(buf.dtype)
+            for b in range(1, B):
+                buf[kv.page_table[b, :ctx].long()] = buf[t0]
+        toks = rt.decode(steps).cpu()
+        assert rt.c.workspace.status() == 0 and int(rt.lin_status.item()) == 0
+        outs.append(toks)
+    assert torch.equal(outs[1][0], outs[1][1])
+    assert torch.equal(outs[1][0], outs[0][0])
