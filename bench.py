@@ -164,7 +164,7 @@ def run_ours(args, rank, world, device):
 
     sh = None
     if world > 1:
-        sh = ShardedDecodeAttention(B, Hq, Hkv, D, dtype, plan, rank, k, "sum", device=device)
+        sh = ShardedDecodeAttention(B, Hq, Hkv, D, dtype, plan, rank, k, "sum", device=device, exchange=args.exchange)
     ws = T.Workspace(B, Hq, D, B, max(n_loc, 1), device=device)
     scores = torch.empty(B, max(n_loc, 1), dtype=torch.float32, device=device)
     idx = torch.zeros(B, k, dtype=torch.int32, device=device)
@@ -274,7 +274,7 @@ def run_ours(args, rank, world, device):
         step(i)
         step(i, e2e=True)
     torch.cuda.synchronize()
-    assert ws.status() == 0 and (sh is None or sh.ws.status() == 0), "device-side fault bits set during warm-up"
+    assert ws.status() == 0 and (sh is None or (sh.ws.status() | sh.exchange_status()) == 0), "device-side fault bits set during warm-up"
     if use_graph:
         block_graph().replay()
         for i in range(pairs):
@@ -303,7 +303,7 @@ def run_ours(args, rank, world, device):
         # launches (measured in the eager pass) times the steps
         launches = int(round(launches_eager / min(args.steps, 4 * pairs) * args.steps))
     ms_e2e = timed(args.steps, e2e=True)
-    assert ws.status() == 0 and (sh is None or sh.ws.status() == 0), "device-side fault bits set"
+    assert ws.status() == 0 and (sh is None or (sh.ws.status() | sh.exchange_status()) == 0), "device-side fault bits set"
 
     ms_step = ms / args.steps
     value = B / (ms_step * 1e-3)
@@ -367,7 +367,7 @@ def run_ours(args, rank, world, device):
         "dtype": {"float16": "f16", "bfloat16": "bf16"}[w["dtype"]], "data": "synthetic",
         "config": {"workload": f"{args.workload}: selection layer + sparse layer, B={B}, {Hq}q/{Hkv}kv heads x {D}, "
                                f"context {N}, top_k {k}, head-summed scores",
-                   "kv_sharding": f"sequence-sharded over {world} GPU(s)", "l2": l2_note},
+                   "kv_sharding": f"sequence-sharded over {world} GPU(s)" + (("; per-layer exchange: " + ("peer stores (tidal_peer_all_gather)" if sh.peer is not None else "NCCL all-gather")) if sh is not None else ""), "l2": l2_note},
         "e2e": {"value": round(B / (ms_e2e / args.steps * 1e-3), 2), "unit": UNIT,
                 "h2d_bytes_per_step": 2 * B * Hq * D * es, "d2h_bytes_per_step": 2 * B * Hq * D * es},
         "gpu_launches": int(launches),
@@ -432,6 +432,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--exchange", choices=["auto", "nccl", "peer"], default="auto",
+                    help="per-layer exchange of sharded KV: this library's peer-store all-gather, or NCCL")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--graph", type=int, default=-1, help="replay each step as one CUDA graph (default); 0: issue every launch from the host")

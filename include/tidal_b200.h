@@ -300,6 +300,31 @@ int tidal_decode_linear(const tidal_linear_args* args, void* stream);
 #define TIDAL_LINEAR_QKV_ROPE 2
 int tidal_decode_qkv(const tidal_linear_args* lin, const tidal_rope_append_args* rope, void* stream);
 
+/* ------------------------------------------------------- peer all-gather
+ * All-gather of one block per rank over NVLink peer stores, for the per-layer exchange of
+ * sequence-sharded KV (no reference counterpart; stands where a library all-gather would).  Every
+ * rank runs one process per GPU and calls this with the same `bytes`; when the kernel has finished,
+ * d_recv holds rank r's block at byte r * slot_bytes.  Memory the caller sets up once:
+ *   staging   per rank 2 * world * slot_bytes bytes, mapped on every rank (CUDA IPC / fabric handles);
+ *             d_peer_stage[r] is rank r's staging buffer as addressed from this GPU (r = rank: its own);
+ *   counters  per rank 2 * world uint32, zeroed, mapped the same way: d_peer_count[r];
+ *   d_state   2 uint32 of this rank's own memory, zeroed.
+ * d_peer_stage and d_peer_count are device arrays of `world` pointers.  Nothing is reset between
+ * calls.  A rank that never arrives makes the others' bounded waits run out: TIDAL_DEV_WAIT_TIMEOUT is
+ * OR-ed into *d_status (if given) and the call completes with incomplete data. */
+typedef struct {
+    const void* d_send;
+    void* d_recv;
+    int64_t bytes;               /* multiple of 16, <= slot_bytes */
+    int64_t slot_bytes;          /* multiple of 16 */
+    void* const* d_peer_stage;
+    uint32_t* const* d_peer_count;
+    uint32_t* d_state;
+    uint32_t* d_status;
+    int32_t rank, world;
+} tidal_exchange_args;
+int tidal_peer_all_gather(const tidal_exchange_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

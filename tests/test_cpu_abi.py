@@ -35,7 +35,7 @@ def test_every_declared_symbol_is_exported(L):
 
 def test_struct_layouts_match_header(L, tmp_path):
     structs = {"tidal_attn_args": L.AttnArgs, "tidal_topk_args": L.TopkArgs, "tidal_rope_append_args": L.RopeAppendArgs,
-               "tidal_linear_args": L.LinearArgs}
+               "tidal_linear_args": L.LinearArgs, "tidal_exchange_args": L.ExchangeArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for cname, st in structs.items():
         lines.append(f'printf("{cname} %zu\\n", sizeof({cname}));')
@@ -98,6 +98,13 @@ def test_argument_errors_without_gpu(L):
     assert L.lib.tidal_decode_qkv(C.byref(lin), C.byref(rq), None) == L.ERR_ARG and "f16/bf16" in L.last_error()
     rq.dtype, rq.num_kv_heads = L.DTYPE_F16, 4
     assert L.lib.tidal_decode_qkv(C.byref(lin), C.byref(rq), None) == L.ERR_ARG and "rows" in L.last_error()
+    x = L.ExchangeArgs()
+    assert L.lib.tidal_peer_all_gather(C.byref(x), None) == L.ERR_ARG
+    x.d_send = x.d_recv = x.d_peer_stage = x.d_peer_count = x.d_state = 256
+    x.world, x.rank, x.bytes, x.slot_bytes = 1, 0, 64, 64
+    assert L.lib.tidal_peer_all_gather(C.byref(x), None) == L.ERR_ARG and "world" in L.last_error()
+    x.world, x.bytes = 2, 72
+    assert L.lib.tidal_peer_all_gather(C.byref(x), None) == L.ERR_ARG and "multiples of 16" in L.last_error()
     r = L.RopeAppendArgs()
     assert L.lib.tidal_rope_append(C.byref(r), None) == L.ERR_ARG
     assert L.lib.tidal_ws_bytes(1, 32, 128, 32, 32768) > 0

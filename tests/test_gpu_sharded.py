@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, result_dir, reduce):
+def _worker(rank, world, port, result_dir, reduce, exchange):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
@@ -35,10 +35,12 @@ def _worker(rank, world, port, result_dir, reduce):
         pool[:, 0, 0] = K[:, :, lo:hi].permute(0, 2, 1, 3).reshape(B * n, Hkv, D)
         pool[:, 1, 0] = V[:, :, lo:hi].permute(0, 2, 1, 3).reshape(B * n, Hkv, D)
         pool = pool.cuda()
-        sh = ShardedDecodeAttention(B, Hq, Hkv, D, dtype, plan, rank, k, reduce, device=torch.device("cuda", rank))
+        sh = ShardedDecodeAttention(B, Hq, Hkv, D, dtype, plan, rank, k, reduce, device=torch.device("cuda", rank),
+                                    exchange=exchange)
+        assert (sh.peer is not None) == (exchange == "peer")
         qd = q[:, :, 0].contiguous().cuda()
         res = {}
-        for rep in range(2):                       # twice: buffers and counters must be reusable
+        for rep in range(3):                       # several times: buffers and counters must be reusable
             o_sel = sh.selection_layer(qd, pool, pages_per_seq=n, want_global=True).float().cpu()
             sel = sh.selected_global().cpu()
             o_sp = sh.sparse_layer(qd, pool, pages_per_seq=n).float().cpu()
@@ -49,19 +51,20 @@ def _worker(rank, world, port, result_dir, reduce):
         ok, why = O.topk_sets_match(O.scores_fp32(q, K, reduce).reshape(rows, N), sel.reshape(rows, -1), k, tie_band=1e-4)
         want_sp = O.gathered_attention(q, K, V, sel)[:, :, 0]
         res = dict(sel_err=float((o_sel - want_sel).abs().max()), topk_ok=ok, why=why,
-                   sp_err=float((o_sp - want_sp).abs().max()), sel=sel, status=sh.ws.status())
+                   sp_err=float((o_sp - want_sp).abs().max()), sel=sel, status=sh.ws.status() | sh.exchange_status())
         torch.save(res, os.path.join(result_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
 @pytest.mark.parametrize("reduce", ["sum", "none"])
-def test_sharded_two_gpus(tmp_path, reduce):
+def test_sharded_two_gpus(tmp_path, reduce, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = min(torch.cuda.device_count(), 4)
     port = 29700 + (os.getpid() % 2000)
-    mp.spawn(_worker, args=(world, port, str(tmp_path), reduce), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, str(tmp_path), reduce, exchange), nprocs=world, join=True)
     res = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
     for r in res:
         assert r["status"] == 0

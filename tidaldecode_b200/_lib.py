@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather",
 )
 
 
@@ -75,6 +75,14 @@ class LinearArgs(C.Structure):
 LINEAR_PLAIN, LINEAR_SILU_MUL = 0, 1
 
 
+class ExchangeArgs(C.Structure):
+    _fields_ = [
+        ("d_send", C.c_void_p), ("d_recv", C.c_void_p), ("bytes", C.c_int64), ("slot_bytes", C.c_int64),
+        ("d_peer_stage", C.c_void_p), ("d_peer_count", C.c_void_p), ("d_state", C.c_void_p), ("d_status", C.c_void_p),
+        ("rank", C.c_int32), ("world", C.c_int32),
+    ]
+
+
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -117,6 +125,8 @@ def _load() -> C.CDLL:
     lib.tidal_decode_linear.argtypes = [C.POINTER(LinearArgs), C.c_void_p]
     lib.tidal_decode_qkv.restype = C.c_int
     lib.tidal_decode_qkv.argtypes = [C.POINTER(LinearArgs), C.POINTER(RopeAppendArgs), C.c_void_p]
+    lib.tidal_peer_all_gather.restype = C.c_int
+    lib.tidal_peer_all_gather.argtypes = [C.POINTER(ExchangeArgs), C.c_void_p]
     return lib
 
 

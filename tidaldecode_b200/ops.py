@@ -369,3 +369,48 @@ def qkv_rope_append(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, 
     with torch.cuda.device(x.device):
         check(lib.tidal_decode_qkv(C.byref(a), C.byref(r), _stream()), "tidal_decode_qkv")
     return q_out
+
+
+class PeerExchange:
+    """Buffers and peer mappings of tidal_peer_all_gather for one process group: staging and arrival
+    counters live in symmetric memory (torch.distributed._symmetric_memory: CUDA memory mapped on every
+    rank of the group), the pointer tables on the device.  One object per (group, slot size); every rank
+    must construct it at the same point of the program (the constructor is a collective)."""
+
+    def __init__(self, slot_bytes: int, group, device):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if slot_bytes % 16:
+            raise RuntimeError("slot_bytes must be a multiple of 16")
+        self.slot_bytes = int(slot_bytes)
+        stage_bytes = 2 * self.world * self.slot_bytes
+        count_off = (stage_bytes + 255) // 256 * 256
+        with torch.cuda.device(device):
+            self.buf = symm_mem.empty(count_off + 256, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            hdl = symm_mem.rendezvous(self.buf, group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            i64 = dict(dtype=torch.int64, device=device)
+            self.peer_stage = torch.tensor(ptrs, **i64)
+            self.peer_count = torch.tensor([p + count_off for p in ptrs], **i64)
+            self.state = torch.zeros(2, dtype=torch.int32, device=device)
+            self._hdl = hdl
+            torch.cuda.synchronize()
+        dist.barrier(group)                      # every rank's counters are zero before anyone adds to them
+
+    def all_gather(self, send: torch.Tensor, recv: torch.Tensor, nbytes: Optional[int] = None,
+                   status: Optional[torch.Tensor] = None) -> None:
+        """recv [world, slot] (any dtype, slot_bytes per row) <- the first nbytes of every rank's `send`."""
+        _need_cuda(send, recv, status)
+        nbytes = send.numel() * send.element_size() if nbytes is None else int(nbytes)
+        if recv.numel() * recv.element_size() < self.world * self.slot_bytes:
+            raise RuntimeError("recv is smaller than world x slot_bytes")
+        a = _lib.ExchangeArgs()
+        a.d_send, a.d_recv, a.bytes, a.slot_bytes = send.data_ptr(), recv.data_ptr(), nbytes, self.slot_bytes
+        a.d_peer_stage, a.d_peer_count = self.peer_stage.data_ptr(), self.peer_count.data_ptr()
+        a.d_state, a.d_status = self.state.data_ptr(), _ptr(status)
+        a.rank, a.world = self.rank, self.world
+        with torch.cuda.device(send.device):
+            check(lib.tidal_peer_all_gather(C.byref(a), _stream()), "tidal_peer_all_gather")

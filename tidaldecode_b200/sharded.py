@@ -70,7 +70,10 @@ class ShardedDecodeAttention:
 
     def __init__(self, batch: int, hq: int, hkv: int, d: int, dtype: torch.dtype, plan: ShardPlan, rank: int,
                  top_k: int, head_reduce: str = "sum", group: Optional[dist.ProcessGroup] = None, device="cuda",
-                 ops=None):
+                 ops=None, exchange: str = "auto"):
+        """exchange: "peer" = tidal_peer_all_gather (NVLink peer stores from this library's own kernel),
+        "nccl" = one all_gather_into_tensor per layer, "auto" = peer where symmetric memory can be set up
+        (CUDA ranks of one node), else nccl."""
         if ops is None:
             from . import ops  # the CUDA library; raises if it is missing (tests of the exchange logic inject a stand-in)
 
@@ -87,6 +90,7 @@ class ShardedDecodeAttention:
         self.k_local = min(top_k, max(self.local_len, 1))
         self.k_global = min(top_k, plan.seq_len)
         L = pack_layout(batch, hq, d, self.rows, top_k)
+        L["total"] = (L["total"] + 3) // 4 * 4             # blocks start on 16-byte boundaries in the receive buffer
         self.layout = L
         self.ws = ops.Workspace(batch, hq, d, self.rows, max(self.local_len, self.world * top_k, 1), device=device)
         f32 = dict(dtype=torch.float32, device=device)
@@ -109,6 +113,15 @@ class ShardedDecodeAttention:
         if self.world == 1:
             self._rcs = self._rcs[: self.rows * top_k].view(self.rows, top_k)
             self._rci = self._rci[: self.rows * top_k].view(self.rows, top_k)
+        self.peer = None
+        if self.world > 1 and exchange in ("peer", "auto") and hasattr(ops, "PeerExchange") and torch.device(device).type == "cuda":
+            try:
+                self.peer = ops.PeerExchange(L["total"] * 4, group if group is not None else dist.group.WORLD, torch.device(device))
+                self._xstatus = torch.zeros(1, dtype=torch.int32, device=device)
+            except Exception:
+                if exchange == "peer":
+                    raise
+                self.peer = None
         if self.local_len < top_k:
             # fewer local tokens than candidates: the unused slots stay at -inf / 0 for good
             _, _, _, cs, ci = self._send_views()
@@ -122,11 +135,20 @@ class ShardedDecodeAttention:
         return (s[L["m"]:L["l"]].view(B, Hq), s[L["l"]:L["o"]].view(B, Hq), s[L["o"]:L["cs"]].view(B, Hq, D),
                 s[L["cs"]:L["ci"]].view(R, k), s[L["ci"]:L["total"]].view(torch.int32).view(R, k))
 
-    def _all_gather(self):
+    def _all_gather(self, words: Optional[int] = None):
+        """Every rank's packed block into recv; `words`: only the leading fp32 words are needed (sparse layers
+        exchange the partials, not the candidate lists)."""
         if self.world == 1:
             self.recv[0].copy_(self.send)
+        elif self.peer is not None:
+            n = self.layout["total"] if words is None else (words + 3) // 4 * 4
+            self.peer.all_gather(self.send, self.recv, nbytes=n * 4, status=self._xstatus)
         else:
             dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
+
+    def exchange_status(self) -> int:
+        """Fault bits of the peer exchange (0 when the library all-gather is in use)."""
+        return int(self._xstatus.item()) if self.peer is not None else 0
 
     def selection_layer(self, q: torch.Tensor, kv_local: torch.Tensor, pages_per_seq: Optional[int] = None,
                         page_table: Optional[torch.Tensor] = None, want_global: bool = False,
@@ -171,7 +193,7 @@ class ShardedDecodeAttention:
         cnt = self.sel_count.view(self.B) if self.rows_per_seq == 1 else self.sel_count.view(self.B, self.Hq)
         ops.decode_attention(q, kv_local, max(self.local_len, 1), self.ws, page_table=page_table, pages_per_seq=pages_per_seq,
                              sel_idx=sel, sel_counts=cnt, partials=(m, l, o), want_out=False)
-        self._all_gather()
+        self._all_gather(words=self.layout["cs"])
         return ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
 
     def selected_global(self) -> torch.Tensor:
