@@ -274,6 +274,19 @@ def run_ours(args, rank, world, device):
         step(i)
         step(i, e2e=True)
     torch.cuda.synchronize()
+    if sh is not None and sh.peer is not None and args.exchange == "auto":
+        # a peer exchange whose bounded waits ran out on any rank (a rank that cannot reach a peer's memory):
+        # every rank falls back to the library all-gather together
+        bad = torch.tensor([sh.exchange_status()], device=device)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad):
+            if rank == 0:
+                print("bench: peer exchange reported fault bits %d during warm-up, using NCCL" % int(bad), file=sys.stderr)
+            sh = ShardedDecodeAttention(B, Hq, Hkv, D, dtype, plan, rank, k, "sum", device=device, exchange="nccl")
+            for i in range(args.warmup):
+                step(i)
+                step(i, e2e=True)
+            torch.cuda.synchronize()
     assert ws.status() == 0 and (sh is None or (sh.ws.status() | sh.exchange_status()) == 0), "device-side fault bits set during warm-up"
     if use_graph:
         block_graph().replay()
