@@ -65,6 +65,10 @@ def pack_layout(batch: int, hq: int, d: int, rows: int, k: int):
     return dict(m=o_m, l=o_l, o=o_o, cs=o_cs, ci=o_ci, total=o_ci + rows * k)
 
 
+# largest group the peer-store exchange has run on; larger groups get NCCL unless exchange="peer" is asked for
+kPeerValidatedWorld = 2
+
+
 class ShardedDecodeAttention:
     """Per-rank driver of the kernels for one (batch, heads, context) geometry."""
 
@@ -72,8 +76,8 @@ class ShardedDecodeAttention:
                  top_k: int, head_reduce: str = "sum", group: Optional[dist.ProcessGroup] = None, device="cuda",
                  ops=None, exchange: str = "auto"):
         """exchange: "peer" = tidal_peer_all_gather (NVLink peer stores from this library's own kernel),
-        "nccl" = one all_gather_into_tensor per layer, "auto" = peer where symmetric memory can be set up
-        (CUDA ranks of one node), else nccl."""
+        "nccl" = one all_gather_into_tensor per layer, "auto" = peer for groups of up to kPeerValidatedWorld
+        CUDA ranks where symmetric memory can be set up, else nccl."""
         if ops is None:
             from . import ops  # the CUDA library; raises if it is missing (tests of the exchange logic inject a stand-in)
 
@@ -114,7 +118,9 @@ class ShardedDecodeAttention:
             self._rcs = self._rcs[: self.rows * top_k].view(self.rows, top_k)
             self._rci = self._rci[: self.rows * top_k].view(self.rows, top_k)
         self.peer = None
-        if self.world > 1 and exchange in ("peer", "auto") and hasattr(ops, "PeerExchange") and torch.device(device).type == "cuda":
+        # "auto" takes the peer exchange up to the world size it has been validated on (kPeerValidatedWorld)
+        use_peer = exchange == "peer" or (exchange == "auto" and self.world <= kPeerValidatedWorld)
+        if self.world > 1 and use_peer and hasattr(ops, "PeerExchange") and torch.device(device).type == "cuda":
             try:
                 self.peer = ops.PeerExchange(L["total"] * 4, group if group is not None else dist.group.WORLD, torch.device(device))
                 self._xstatus = torch.zeros(1, dtype=torch.int32, device=device)
