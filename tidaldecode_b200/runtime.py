@@ -60,8 +60,15 @@ class GraphDecoder:
         self._wqkv, self._wgu = [], []
         for layer in model.model.layers:
             a, mlp = layer.self_attn, layer.mlp
-            self._wqkv.append(torch.cat((a.q_proj.weight, a.k_proj.weight, a.v_proj.weight), dim=0).contiguous())
-            self._wgu.append(torch.cat((mlp.gate_proj.weight, mlp.up_proj.weight), dim=0).contiguous())
+            wqkv = torch.cat((a.q_proj.weight, a.k_proj.weight, a.v_proj.weight), dim=0).contiguous()
+            wgu = torch.cat((mlp.gate_proj.weight, mlp.up_proj.weight), dim=0).contiguous()
+            # the modules keep working (prefill runs through them) on row ranges of the stacked matrices: no second copy
+            nq, nk = a.q_proj.weight.shape[0], a.k_proj.weight.shape[0]
+            a.q_proj.weight.data, a.k_proj.weight.data, a.v_proj.weight.data = wqkv[:nq], wqkv[nq:nq + nk], wqkv[nq + nk:]
+            f = mlp.gate_proj.weight.shape[0]
+            mlp.gate_proj.weight.data, mlp.up_proj.weight.data = wgu[:f], wgu[f:]
+            self._wqkv.append(wqkv)
+            self._wgu.append(wgu)
 
     # ------------------------------------------------------------------ prefill
     @torch.inference_mode()
