@@ -304,7 +304,7 @@ int tidal_decode_qkv(const tidal_linear_args* lin, const tidal_rope_append_args*
  * All-gather of one block per rank over NVLink peer stores, for the per-layer exchange of
  * sequence-sharded KV (no reference counterpart; stands where a library all-gather would).  Every
  * rank runs one process per GPU and calls this with the same `bytes`; when the kernel has finished,
- * d_recv holds rank r's block at byte r * slot_bytes.  Memory the caller sets up once:
+ * d_recv (if given) holds rank r's block at byte r * slot_bytes.  Memory the caller sets up once:
  *   staging   per rank 2 * world * slot_bytes bytes, mapped on every rank (CUDA IPC / fabric handles);
  *             d_peer_stage[r] is rank r's staging buffer as addressed from this GPU (r = rank: its own);
  *   counters  per rank 2 * world uint32, zeroed, mapped the same way: d_peer_count[r];
@@ -322,6 +322,12 @@ typedef struct {
     uint32_t* d_state;
     uint32_t* d_status;
     int32_t rank, world;
+    /* optional: the blocks hold softmax partials of sequence-sharded attention — m [rows], l [rows],
+     * o [rows][head_dim] fp32 at these word offsets — and the kernel also writes their exact merge (as
+     * tidal_merge_partials would) to d_merge_out [rows][head_dim] of merge_dtype; d_recv may then be NULL */
+    void* d_merge_out;
+    int64_t merge_m_off, merge_l_off, merge_o_off;
+    int32_t merge_rows, merge_head_dim, merge_dtype;
 } tidal_exchange_args;
 int tidal_peer_all_gather(const tidal_exchange_args* args, void* stream);
 

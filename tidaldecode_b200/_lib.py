@@ -80,6 +80,8 @@ class ExchangeArgs(C.Structure):
         ("d_send", C.c_void_p), ("d_recv", C.c_void_p), ("bytes", C.c_int64), ("slot_bytes", C.c_int64),
         ("d_peer_stage", C.c_void_p), ("d_peer_count", C.c_void_p), ("d_state", C.c_void_p), ("d_status", C.c_void_p),
         ("rank", C.c_int32), ("world", C.c_int32),
+        ("d_merge_out", C.c_void_p), ("merge_m_off", C.c_int64), ("merge_l_off", C.c_int64), ("merge_o_off", C.c_int64),
+        ("merge_rows", C.c_int32), ("merge_head_dim", C.c_int32), ("merge_dtype", C.c_int32),
     ]
 
 

@@ -7,7 +7,9 @@
 //   3. waits — with an iteration limit — until every rank's counter on this GPU shows all CTAs of the
 //      current exchange, and
 //   4. copies the staged blocks into the caller's receive buffer, which the kernels that follow in the
-//      stream read with fixed addresses (the same graph can be replayed).
+//      stream read with fixed addresses (the same graph can be replayed), and — if asked — merges the
+//      ranks' softmax partials (m, l, o) found in the blocks into the attention output on the spot, so
+//      that the exchange of a sparse layer is followed by no merge launch at all.
 // Staging and counters are double-buffered by the parity of an exchange counter kept in device memory
 // and advanced by the last CTA to finish, so nothing is reset between exchanges: a rank can be at most
 // one exchange ahead of another, because it needs the other's arrivals to finish the one in between.
@@ -32,6 +34,10 @@ struct ExchangeParams {
     uint32_t* fin;                // local: CTAs of the current exchange that are done
     uint32_t* status;
     int rank, world;
+    // optional merge of the ranks' softmax partials: fp32 word offsets of m [rows], l [rows], o [rows][D] in a block
+    void* merge_out;
+    int64_t m_off, l_off, o_off;
+    int merge_rows, merge_dim, merge_dtype;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -79,8 +85,32 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
 
     // 4. staged blocks into the receive buffer
     const uint4* stage = p.peer_stage[p.rank] + (int64_t)par * p.world * p.slot_vec;
-    for (int r = 0; r < p.world; ++r)
-        for (int64_t i = first; i < p.nvec; i += stride) p.out[(int64_t)r * p.slot_vec + i] = stage[(int64_t)r * p.slot_vec + i];
+    if (p.out)
+        for (int r = 0; r < p.world; ++r)
+            for (int64_t i = first; i < p.nvec; i += stride) p.out[(int64_t)r * p.slot_vec + i] = stage[(int64_t)r * p.slot_vec + i];
+    //    and the merge of the ranks' partials, in rank order (the arithmetic of merge_shards_kernel)
+    if (p.merge_out) {
+        const float* st = reinterpret_cast<const float*>(stage);
+        const int64_t slot_words = p.slot_vec * 4;
+        const int64_t total = (int64_t)p.merge_rows * p.merge_dim;
+        for (int64_t idx = first; idx < total; idx += stride) {
+            const int64_t r = idx / p.merge_dim;
+            const int d = (int)(idx - r * p.merge_dim);
+            float M = -INFINITY;
+            for (int s = 0; s < p.world; ++s) M = fmaxf(M, st[s * slot_words + p.m_off + r]);
+            float acc = 0.f, L = 0.f;
+            for (int s = 0; s < p.world; ++s) {
+                const float ms = st[s * slot_words + p.m_off + r];
+                const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+                acc = fmaf(w, st[s * slot_words + p.o_off + r * p.merge_dim + d], acc);
+                L = fmaf(w, st[s * slot_words + p.l_off + r], L);
+            }
+            const float v = L > 0.f ? acc / L : 0.f;
+            if (p.merge_dtype == TIDAL_DTYPE_F16) reinterpret_cast<__half*>(p.merge_out)[idx] = __float2half_rn(v);
+            else if (p.merge_dtype == TIDAL_DTYPE_BF16) reinterpret_cast<__nv_bfloat16*>(p.merge_out)[idx] = __float2bfloat16_rn(v);
+            else reinterpret_cast<float*>(p.merge_out)[idx] = v;
+        }
+    }
 
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -98,7 +128,17 @@ using namespace tidal;
 
 extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream) {
     TIDAL_REQUIRE(a != nullptr, TIDAL_ERR_ARG, "args is NULL");
-    TIDAL_REQUIRE(a->d_send && a->d_recv && a->d_peer_stage && a->d_peer_count && a->d_state, TIDAL_ERR_ARG, "null pointer");
+    TIDAL_REQUIRE(a->d_send && a->d_peer_stage && a->d_peer_count && a->d_state, TIDAL_ERR_ARG, "null pointer");
+    TIDAL_REQUIRE(a->d_recv || a->d_merge_out, TIDAL_ERR_ARG, "neither a receive buffer nor a merge output given");
+    if (a->d_merge_out) {
+        TIDAL_REQUIRE(a->merge_rows >= 1 && a->merge_head_dim >= 1 && a->merge_dtype >= 0 && a->merge_dtype <= 2, TIDAL_ERR_ARG,
+                      "bad merge geometry");
+        const int64_t words = a->bytes / 4;
+        TIDAL_REQUIRE(a->merge_m_off >= 0 && a->merge_m_off + a->merge_rows <= words && a->merge_l_off >= 0 &&
+                          a->merge_l_off + a->merge_rows <= words && a->merge_o_off >= 0 &&
+                          a->merge_o_off + (int64_t)a->merge_rows * a->merge_head_dim <= words,
+                      TIDAL_ERR_ARG, "the partials lie outside the exchanged bytes");
+    }
     TIDAL_REQUIRE(a->world >= 2 && a->world <= kXchgMaxWorld && a->rank >= 0 && a->rank < a->world, TIDAL_ERR_ARG,
                   "bad rank %d / world %d (2..%d ranks)", a->rank, a->world, kXchgMaxWorld);
     TIDAL_REQUIRE(a->bytes > 0 && a->bytes % 16 == 0 && a->slot_bytes % 16 == 0 && a->bytes <= a->slot_bytes, TIDAL_ERR_ARG,
@@ -117,6 +157,10 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
     p.status = a->d_status;
     p.rank = a->rank;
     p.world = a->world;
+    p.merge_out = a->d_merge_out;
+    p.m_off = a->merge_m_off; p.l_off = a->merge_l_off; p.o_off = a->merge_o_off;
+    p.merge_rows = a->merge_rows; p.merge_dim = a->merge_head_dim; p.merge_dtype = a->merge_dtype;
+    // (the CTA count follows from the byte count alone: every rank must use the same)
     int64_t ctas = (p.nvec + kXchgThreads - 1) / kXchgThreads;
     if (ctas > kXchgMaxCtas) ctas = kXchgMaxCtas;
     TIDAL_CUDA_OK(launch_pdl(peer_all_gather_kernel, dim3((unsigned)ctas), dim3(kXchgThreads), 0, (cudaStream_t)stream, 1, p));

@@ -400,15 +400,23 @@ class PeerExchange:
             torch.cuda.synchronize()
         dist.barrier(group)                      # every rank's counters are zero before anyone adds to them
 
-    def all_gather(self, send: torch.Tensor, recv: torch.Tensor, nbytes: Optional[int] = None,
-                   status: Optional[torch.Tensor] = None) -> None:
-        """recv [world, slot] (any dtype, slot_bytes per row) <- the first nbytes of every rank's `send`."""
+    def all_gather(self, send: torch.Tensor, recv: Optional[torch.Tensor], nbytes: Optional[int] = None,
+                   status: Optional[torch.Tensor] = None, merge: Optional[tuple] = None) -> None:
+        """recv [world, slot] (any dtype, slot_bytes per row) <- the first nbytes of every rank's `send`.
+        merge = (out [rows, D], m_off, l_off, o_off): the blocks hold softmax partials at these fp32 word offsets
+        and their merge goes to `out` in the same launch; recv may then be None."""
         _need_cuda(send, recv, status)
         nbytes = send.numel() * send.element_size() if nbytes is None else int(nbytes)
-        if recv.numel() * recv.element_size() < self.world * self.slot_bytes:
+        if recv is not None and recv.numel() * recv.element_size() < self.world * self.slot_bytes:
             raise RuntimeError("recv is smaller than world x slot_bytes")
         a = _lib.ExchangeArgs()
-        a.d_send, a.d_recv, a.bytes, a.slot_bytes = send.data_ptr(), recv.data_ptr(), nbytes, self.slot_bytes
+        a.d_send, a.d_recv, a.bytes, a.slot_bytes = send.data_ptr(), _ptr(recv), nbytes, self.slot_bytes
+        if merge is not None:
+            out, m_off, l_off, o_off = merge
+            _need_cuda(out)
+            a.d_merge_out, a.merge_m_off, a.merge_l_off, a.merge_o_off = out.data_ptr(), int(m_off), int(l_off), int(o_off)
+            a.merge_head_dim = out.shape[-1]
+            a.merge_rows, a.merge_dtype = out.numel() // out.shape[-1], _dtype_code(out)
         a.d_peer_stage, a.d_peer_count = self.peer_stage.data_ptr(), self.peer_count.data_ptr()
         a.d_state, a.d_status = self.state.data_ptr(), _ptr(status)
         a.rank, a.world = self.rank, self.world

@@ -141,16 +141,21 @@ class ShardedDecodeAttention:
         return (s[L["m"]:L["l"]].view(B, Hq), s[L["l"]:L["o"]].view(B, Hq), s[L["o"]:L["cs"]].view(B, Hq, D),
                 s[L["cs"]:L["ci"]].view(R, k), s[L["ci"]:L["total"]].view(torch.int32).view(R, k))
 
-    def _all_gather(self, words: Optional[int] = None):
+    def _all_gather(self, words: Optional[int] = None) -> bool:
         """Every rank's packed block into recv; `words`: only the leading fp32 words are needed (sparse layers
-        exchange the partials, not the candidate lists)."""
+        exchange the partials, not the candidate lists, and need no receive buffer).  True if the exchange also
+        merged the partials into self.out (the peer-store kernel does)."""
         if self.world == 1:
             self.recv[0].copy_(self.send)
         elif self.peer is not None:
-            n = self.layout["total"] if words is None else (words + 3) // 4 * 4
-            self.peer.all_gather(self.send, self.recv, nbytes=n * 4, status=self._xstatus)
+            L = self.layout
+            n = L["total"] if words is None else (words + 3) // 4 * 4
+            self.peer.all_gather(self.send, self.recv if words is None else None, nbytes=n * 4, status=self._xstatus,
+                                 merge=(self.out.view(-1, self.D), L["m"], L["l"], L["o"]))
+            return True
         else:
             dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
+        return False
 
     def exchange_status(self) -> int:
         """Fault bits of the peer exchange (0 when the library all-gather is in use)."""
@@ -178,8 +183,8 @@ class ShardedDecodeAttention:
             m.fill_(-float("inf"))
             l.zero_()
             o.zero_()
-        self._all_gather()
-        ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
+        if not self._all_gather():
+            ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
         # global top-k of the world*k candidates, read in place; keep the positions this rank owns
         n_cand = self.world * k
         if want_global:
@@ -199,8 +204,9 @@ class ShardedDecodeAttention:
         cnt = self.sel_count.view(self.B) if self.rows_per_seq == 1 else self.sel_count.view(self.B, self.Hq)
         ops.decode_attention(q, kv_local, max(self.local_len, 1), self.ws, page_table=page_table, pages_per_seq=pages_per_seq,
                              sel_idx=sel, sel_counts=cnt, partials=(m, l, o), want_out=False)
-        self._all_gather(words=self.layout["cs"])
-        return ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
+        if not self._all_gather(words=self.layout["cs"]):
+            ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
+        return self.out
 
     def selected_global(self) -> torch.Tensor:
         """[B, k] or [B, Hq, k] global positions chosen by the last selection layer."""
