@@ -331,6 +331,27 @@ typedef struct {
 } tidal_exchange_args;
 int tidal_peer_all_gather(const tidal_exchange_args* args, void* stream);
 
+/* ------------------------------------------------------------------ prefill
+ * Causal attention of n_q new query rows of ONE sequence over its paged KV, which already holds
+ * the new rows' K,V (row i of q sits at position kv_len - n_q + i and sees tokens 0..that position;
+ * causal = 0: every row sees all kv_len tokens).  Replaces prefill_with_paged_kv_cache
+ * (tidal/ops/csrc/bsk_ops.h:78-86, tidal/ops/csrc/batch_prefill.cu:27-117, kernel
+ * kernels/include/prefill/prefill.cuh:688-870); RoPE is applied beforehand (tidal_rope_append), as
+ * the reference's modules do (tidal/models/SearchAttention.py:154-163).  f16/bf16, head_dim 64 or
+ * 128, NHD pool [pages][2][page_size][num_kv_heads][head_dim]; d_page_table lists the sequence's
+ * pages in order.  sm_scale <= 0 means 1/sqrt(head_dim).  Allocates nothing, needs no workspace. */
+typedef struct {
+    const void* d_q;             /* [n_q][num_qo_heads][head_dim] */
+    void* d_o;                   /* [n_q][num_qo_heads][head_dim] */
+    const void* d_kv;
+    const int32_t* d_page_table; /* [ceil(kv_len / page_size)] */
+    uint32_t* d_status;          /* optional: TIDAL_DEV_* bits are OR-ed in */
+    int64_t kv_len;
+    int32_t n_q, num_qo_heads, num_kv_heads, head_dim, page_size, dtype, causal;
+    float sm_scale;
+} tidal_prefill_args;
+int tidal_prefill(const tidal_prefill_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -145,6 +145,25 @@ def sparse_layer(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, mask: torch.
     return softmax_pv(S, Vr, q.dtype)
 
 
+def causal_prefill(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, causal: bool = True) -> torch.Tensor:
+    """Attention of qo_len new rows q [qo_len,Hq,D] over kv_len cached tokens K,V [kv_len,Hkv,D] of one
+    sequence, fp32 arithmetic on the stored values: row i sees kv_idx <= kv_len + i - qo_len
+    (kernels/src/include/cpu_reference.h:56-160, mask at :127; scale 1/sqrt(D), no rotary here because
+    the modules rotate before they append: tidal/models/SearchAttention.py:121-163)."""
+    n_q, Hq, D = q.shape
+    kv_len, Hkv, _ = K.shape
+    G = Hq // Hkv
+    qq = q.float().transpose(0, 1)
+    kk = K.float().transpose(0, 1).repeat_interleave(G, 0)
+    vv = V.float().transpose(0, 1).repeat_interleave(G, 0)
+    S = qq @ kk.transpose(1, 2) / math.sqrt(D)
+    if causal:
+        q_idx = torch.arange(n_q, device=q.device)[:, None]
+        kv_idx = torch.arange(kv_len, device=q.device)[None, :]
+        S = S.masked_fill(kv_idx > kv_len + q_idx - n_q, float("-inf"))
+    return (torch.softmax(S, -1) @ vv).transpose(0, 1).contiguous()
+
+
 def full_layer(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor) -> torch.Tensor:
     """Layers below sparse_layer_start: plain SDPA (modify_llama.py:84-98)."""
     G = q.shape[1] // K.shape[1]

@@ -35,7 +35,7 @@ def test_every_declared_symbol_is_exported(L):
 
 def test_struct_layouts_match_header(L, tmp_path):
     structs = {"tidal_attn_args": L.AttnArgs, "tidal_topk_args": L.TopkArgs, "tidal_rope_append_args": L.RopeAppendArgs,
-               "tidal_linear_args": L.LinearArgs, "tidal_exchange_args": L.ExchangeArgs}
+               "tidal_linear_args": L.LinearArgs, "tidal_exchange_args": L.ExchangeArgs, "tidal_prefill_args": L.PrefillArgs}
     lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{HEADER}"', "int main(void){"]
     for cname, st in structs.items():
         lines.append(f'printf("{cname} %zu\\n", sizeof({cname}));')
@@ -105,6 +105,17 @@ def test_argument_errors_without_gpu(L):
     assert L.lib.tidal_peer_all_gather(C.byref(x), None) == L.ERR_ARG and "world" in L.last_error()
     x.world, x.bytes = 2, 72
     assert L.lib.tidal_peer_all_gather(C.byref(x), None) == L.ERR_ARG and "multiples of 16" in L.last_error()
+    pf = L.PrefillArgs()
+    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG
+    pf.d_q = pf.d_o = pf.d_kv = pf.d_page_table = 256
+    pf.dtype, pf.head_dim, pf.num_qo_heads, pf.num_kv_heads, pf.page_size, pf.n_q, pf.kv_len = L.DTYPE_F32, 128, 8, 2, 1, 4, 4
+    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "fp16 or bf16" in L.last_error()
+    pf.dtype, pf.head_dim = L.DTYPE_BF16, 96
+    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "head_dim" in L.last_error()
+    pf.head_dim, pf.num_kv_heads = 128, 3
+    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "multiple" in L.last_error()
+    pf.num_kv_heads, pf.kv_len = 2, 3          # the cache must already hold the new rows
+    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "kv_len" in L.last_error()
     r = L.RopeAppendArgs()
     assert L.lib.tidal_rope_append(C.byref(r), None) == L.ERR_ARG
     assert L.lib.tidal_ws_bytes(1, 32, 128, 32, 32768) > 0

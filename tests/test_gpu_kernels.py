@@ -595,3 +595,52 @@ def test_fused_qkv_projection_rope_append(T, dt, B, Hq, Hkv, D, K, page, mode):
     assert torch.allclose(q_b.float(), q_a.float(), **tol)
     assert torch.allclose(pool_b.float(), pool_a.float(), **tol)
     assert float(pool_b.float().abs().sum()) > 0
+
+
+PREFILL_CASES = [
+    # dtype, n_q, kv_len, Hq, Hkv, D, page_size, causal
+    ("f16", 128, 128, 1, 1, 128, 1, True),
+    ("bf16", 300, 300, 8, 2, 128, 16, True),          # GQA, ragged last tile, pages of 16 in shuffled order
+    ("f16", 63, 2047, 4, 4, 128, 1, True),            # a later chunk of a prompt (kernels/src/test/test_prefill.cu:305)
+    ("bf16", 513, 513, 4, 1, 64, 3, True),            # head_dim 64, page size that divides nothing
+    ("f16", 200, 200, 2, 2, 64, 1, False),            # non-causal
+    ("f16", 2048, 2048, 4, 2, 128, 1, True),
+    ("bf16", 1, 65, 2, 1, 128, 1, True),              # a single row
+    ("f16", 17, 17, 32, 8, 128, 31, True),            # shortest length of the reference's sweep, one partial page
+]
+
+
+@pytest.mark.parametrize("dt,n_q,kv_len,Hq,Hkv,D,page,causal", PREFILL_CASES)
+def test_prefill(T, dt, n_q, kv_len, Hq, Hkv, D, page, causal):
+    """tidal_prefill (tcgen05 kernel) against the oracle's causal attention over the same stored values;
+    shapes follow kernels/src/test/test_prefill.cu:408-491 (GQA 4/8/32 kv heads, ragged lengths)."""
+    dtype = DT[dt]
+    g = torch.Generator().manual_seed(n_q * 7 + kv_len)
+    n_pages = (kv_len + page - 1) // page
+    pool = torch.randn(n_pages + 5, 2, page, Hkv, D, generator=g).to(dtype)
+    table = torch.randperm(n_pages + 5, generator=g)[:n_pages].to(torch.int32)
+    q = torch.randn(n_q, Hq, D, generator=g).to(dtype)
+    sel = pool[table.long()]
+    K = sel[:, 0].reshape(-1, Hkv, D)[:kv_len]
+    V = sel[:, 1].reshape(-1, Hkv, D)[:kv_len]
+    want = O.causal_prefill(q, K, V, causal)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = T.prefill(q.cuda(), pool.cuda(), table.cuda(), kv_len, causal=causal, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert_close(got, want, dtype, "prefill")
+    # the last row is what a decode step over the same cache computes
+    if causal:
+        ws = T.Workspace(1, Hq, D, Hq, kv_len)
+        dec = T.decode_attention(q[-1:].cuda().contiguous(), pool.cuda(), kv_len, ws, page_table=table.cuda().view(1, -1))
+        assert_close(got[-1:], dec, dtype, "prefill last row vs decode")
+
+
+def test_prefill_rejects_what_it_does_not_compute(T):
+    q = torch.zeros(4, 2, 128, device="cuda")
+    pool = torch.zeros(4, 2, 1, 2, 128, device="cuda")
+    table = torch.arange(4, dtype=torch.int32, device="cuda")
+    with pytest.raises(RuntimeError, match="fp16 or bf16"):
+        T.prefill(q, pool, table, 4)
+    with pytest.raises(RuntimeError, match="kv_len"):
+        T.prefill(q.half(), pool.half(), table, 3)

@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather", "tidal_prefill",
 )
 
 
@@ -85,6 +85,15 @@ class ExchangeArgs(C.Structure):
     ]
 
 
+class PrefillArgs(C.Structure):
+    _fields_ = [
+        ("d_q", C.c_void_p), ("d_o", C.c_void_p), ("d_kv", C.c_void_p), ("d_page_table", C.c_void_p), ("d_status", C.c_void_p),
+        ("kv_len", C.c_int64),
+        ("n_q", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("page_size", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
+    ]
+
+
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -129,6 +138,8 @@ def _load() -> C.CDLL:
     lib.tidal_decode_qkv.argtypes = [C.POINTER(LinearArgs), C.POINTER(RopeAppendArgs), C.c_void_p]
     lib.tidal_peer_all_gather.restype = C.c_int
     lib.tidal_peer_all_gather.argtypes = [C.POINTER(ExchangeArgs), C.c_void_p]
+    lib.tidal_prefill.restype = C.c_int
+    lib.tidal_prefill.argtypes = [C.POINTER(PrefillArgs), C.c_void_p]
     return lib
 
 

@@ -1,0 +1,365 @@
+// Causal attention of a block of new query rows over one sequence's paged KV ("prefill"), on the
+// 5th-generation tensor cores: tcgen05.mma with both operands in shared memory and the accumulators in
+// tensor memory.  Takes the place of prefill_with_paged_kv_cache (tidal/ops/csrc/batch_prefill.cu:27-117,
+// kernels/include/prefill/prefill.cuh:688-870, an mma.sync kernel).
+//
+// One CTA = 128 query rows of one query head; it walks the KV tokens its rows may see in tiles of 64.
+// Per tile:
+//   S = Q K^T     8 (D=128) MMAs of 128x64x16, Q and K as K-major operands with the 128-byte swizzle,
+//                 S in tensor-memory columns [0,64)
+//   softmax       thread t owns row t (tcgen05.ld 32x32b: lane = row), running max / sum in registers,
+//                 P rounded to the storage type and written to shared memory as the next A operand
+//   PV = P V      4 MMAs of 128xDx16, V rows as they lie in the cache (MN-major B operand),
+//                 result in tensor-memory columns [64,64+D), added to the fp32 output row in registers
+// K of the next tile is fetched (cp.async, 16 bytes per request, page lookup per row) as soon as S is
+// complete, V of the next tile as soon as PV is complete; two CTAs share an SM (80 KB of shared memory,
+// 256 of the 512 tensor-memory columns each), so one CTA's softmax overlaps the other's MMAs.
+// Every wait on an mbarrier has an iteration limit; a CTA that gives up sets TIDAL_DEV_WAIT_TIMEOUT,
+// still frees its tensor memory and returns.
+#include <cmath>
+#include <cstdlib>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace tidal {
+
+constexpr int kPfRows = 128;     // query rows per CTA = MMA M = TMEM lanes
+constexpr int kPfTile = 64;      // KV tokens per tile
+constexpr int kPfThreads = 128;
+constexpr int kPfTmemCols = 256;
+
+struct PrefillParams {
+    const void* q;        // [n_q][Hq][D]
+    void* o;              // [n_q][Hq][D]
+    const void* kv;       // [pages][2][page_size][Hkv][D]
+    const int32_t* pages; // page ids of this sequence, in order
+    uint32_t* status;
+    int64_t kv_len;
+    int n_q, Hq, Hkv, page_size;
+    int causal;
+    float scale_log2;     // softmax scale x log2(e)
+};
+
+// ------------------------------------------------------------------ tcgen05 wrappers
+__device__ __forceinline__ void tc_alloc(uint32_t* slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tc_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Shared-memory operand descriptor, 128-byte swizzle, atoms of 8 rows x 128 bytes (1024-byte aligned).
+//   K-major operand (rows = M or N, 64 elements of K per row): `sbo` = bytes between 8-row groups.
+//   MN-major operand (rows = K, 64 elements of M/N per row): `sbo` = bytes between 8-row (K) groups,
+//   `lbo` = bytes between blocks of 64 elements along M/N.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;   // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor for kind::f16: fp32 accumulator, A K-major, B K- or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int dtype_bf16, int b_mn_major, int M, int N) {
+    return (1u << 4) | ((uint32_t)dtype_bf16 << 7) | ((uint32_t)dtype_bf16 << 10) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// Byte offset of the 16-byte chunk `c16` of row `r` in an operand tile of `rows` rows: blocks of 64
+// elements (8 chunks) are stored one after the other, each [rows][128 bytes] with the chunk index
+// XOR-ed with the row's low 3 bits (what the 128-byte swizzle of the descriptor expects).
+__device__ __forceinline__ uint32_t sw128_offset(int rows, int r, int c16) {
+    return (uint32_t)((c16 >> 3) * rows * 128 + r * 128 + (((c16 & 7) ^ (r & 7)) << 4));
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
+    constexpr int kChunks = D / 8;                    // 16-byte chunks per row
+    constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + kQBytes;
+    uint8_t* sV = sK + kKBytes;
+    uint8_t* sP = sV + kKBytes;
+    __shared__ uint64_t bar_s, bar_o;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int n_qt = (p.n_q + kPfRows - 1) / kPfRows;
+    const int qt = n_qt - 1 - (int)blockIdx.x;        // longest rows first
+    const int h = blockIdx.y, kvh = h / (p.Hq / p.Hkv);
+    const int q0 = qt * kPfRows;
+    const int64_t pos0 = p.kv_len - p.n_q + q0;       // position of row 0 of this CTA
+    const int rows_here = min(kPfRows, p.n_q - q0);
+    int64_t kv_end = p.causal ? min(p.kv_len, pos0 + rows_here) : p.kv_len;   // tokens any row of the CTA sees
+    const int n_tiles = (int)((kv_end + kPfTile - 1) / kPfTile);
+
+    if (tid == 0) {
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_o, 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        tc_alloc(&tmem_slot, kPfTmemCols);
+        tc_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    pdl_wait();
+    pdl_launch_dependents();
+
+    const T* q = reinterpret_cast<const T*>(p.q);
+    const T* kv = reinterpret_cast<const T*>(p.kv);
+    const int64_t row_elems = (int64_t)p.Hkv * D;
+    const int64_t v_off = (int64_t)p.page_size * row_elems;
+
+    // K or V rows [t0, t0+64) of this KV head into a swizzled tile; rows past the sequence are zero
+    auto stage_kv = [&](uint8_t* dst, int64_t t0, int which) {
+        const uint32_t base = smem_u32(dst);
+        for (int i = tid; i < kPfTile * kChunks; i += kPfThreads) {
+            const int r = i / kChunks, c = i % kChunks;
+            const int64_t t = t0 + r;
+            const bool ok = t < p.kv_len;
+            const T* src = kv;
+            if (ok) {
+                const int64_t pg = p.pages[t / p.page_size];
+                const int slot = (int)(t % p.page_size);
+                src = kv + (pg * 2 * p.page_size + slot) * row_elems + (which ? v_off : 0) + (int64_t)kvh * D + c * 8;
+            }
+            cp_async16(base + sw128_offset(kPfTile, r, c), src, ok ? 16u : 0u);
+        }
+    };
+
+    // Q tile, K and V of tile 0
+    {
+        const uint32_t base = smem_u32(sQ);
+        for (int i = tid; i < kPfRows * kChunks; i += kPfThreads) {
+            const int r = i / kChunks, c = i % kChunks;
+            const bool ok = r < rows_here;
+            const T* src = ok ? q + ((int64_t)(q0 + r) * p.Hq + h) * D + c * 8 : q;
+            cp_async16(base + sw128_offset(kPfRows, r, c), src, ok ? 16u : 0u);
+        }
+        stage_kv(sK, 0, 0);
+        cp_async_commit();
+        stage_kv(sV, 0, 1);
+        cp_async_commit();
+    }
+
+    constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
+    constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
+    constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
+
+    float o_acc[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o_acc[d] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    const int64_t my_pos = pos0 + tid;
+    bool alive = true;
+
+    for (int j = 0; j < n_tiles; ++j) {
+        const uint32_t phase = (uint32_t)(j & 1);
+        // ---- S = Q K^T
+        cp_async_wait<1>();           // K of this tile (and Q) have landed; V may still be in flight
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(!alive)) break;      // every thread leaves in the same iteration
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+                const uint32_t a = smem_u32(sQ) + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
+                const uint32_t b = smem_u32(sK) + (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
+                tc_mma_f16(tmem, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, 16, 1024), idesc_qk, k > 0);
+            }
+            tc_commit(&bar_s);
+        }
+        alive = mbar_wait_bounded(&bar_s, phase, &abort_flag, p.status);
+        tc_fence_after();
+        // K's buffer is free: fetch K of the next tile
+        if (j + 1 < n_tiles) stage_kv(sK, (int64_t)(j + 1) * kPfTile, 0);
+        cp_async_commit();
+
+        // ---- softmax of this thread's row
+        float s[kPfTile];
+        __syncwarp();
+        tc_ld32(t_lane, s);
+        tc_ld32(t_lane + 32, s + 32);
+        tc_wait_ld();
+        const int64_t t0 = (int64_t)j * kPfTile;
+        const int64_t lim = p.causal ? min(p.kv_len - 1, my_pos) : p.kv_len - 1;   // last visible token
+        float mx = m_run;
+        if (t0 + kPfTile - 1 > lim) {
+#pragma unroll
+            for (int c = 0; c < kPfTile; ++c) s[c] = (t0 + c <= lim) ? s[c] : -INFINITY;
+        }
+#pragma unroll
+        for (int c = 0; c < kPfTile; ++c) mx = fmaxf(mx, s[c]);
+        const float m_use = (mx == -INFINITY) ? 0.f : mx;
+        const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);   // m_run = -inf gives 0
+        const float mb = m_use * p.scale_log2;
+        float sum = 0.f;
+        {
+            const uint32_t prow = smem_u32(sP) + tid * 128;
+#pragma unroll
+            for (int c8 = 0; c8 < kPfTile / 8; ++c8) {
+                float e[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    e[u] = Vec16<T>::round(fast_exp2(fmaf(s[c8 * 8 + u], p.scale_log2, -mb)));
+                    sum += e[u];
+                }
+                const uint4 v = Vec16<T>::from_float(e);
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (tid & 7)) << 4)), "r"(v.x),
+                             "r"(v.y), "r"(v.z), "r"(v.w)
+                             : "memory");
+            }
+        }
+        l_run = l_run * alpha + sum;
+        m_run = mx;
+#pragma unroll
+        for (int d = 0; d < D; ++d) o_acc[d] *= alpha;
+
+        // ---- PV = P V
+        cp_async_wait<1>();           // V of this tile has landed (K of the next may be in flight)
+        fence_async_smem();
+        tc_fence_before();
+        if (__syncthreads_or(!alive)) break;
+        if (tid == 0) {
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < kPfTile / 16; ++k) {
+                const uint32_t a = smem_u32(sP) + k * 32;
+                const uint32_t b = smem_u32(sV) + k * (16 * 128);
+                tc_mma_f16(tmem + kPfTile, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, v_lbo, v_sbo), idesc_pv, k > 0);
+            }
+            tc_commit(&bar_o);
+        }
+        alive = mbar_wait_bounded(&bar_o, phase, &abort_flag, p.status) && alive;
+        tc_fence_after();
+        if (j + 1 < n_tiles) stage_kv(sV, (int64_t)(j + 1) * kPfTile, 1);
+        cp_async_commit();
+#pragma unroll
+        for (int d0 = 0; d0 < D; d0 += 32) {
+            float t[32];
+            __syncwarp();
+            tc_ld32(t_lane + kPfTile + d0, t);
+            tc_wait_ld();
+#pragma unroll
+            for (int u = 0; u < 32; ++u) o_acc[d0 + u] += t[u];
+        }
+    }
+    cp_async_wait<0>();
+    alive = !__syncthreads_or(!alive);
+
+    if (tid < rows_here && alive) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.o) + ((int64_t)(q0 + tid) * p.Hq + h) * D);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            float e[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) e[u] = o_acc[c * 8 + u] * inv;
+            dst[c] = Vec16<T>::from_float(e);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tc_dealloc(tmem, kPfTmemCols);
+}
+
+template <typename T, int D>
+static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
+    const size_t smem = 1024 + (size_t)kPfRows * D * 2 + 2 * (size_t)kPfTile * D * 2 + (size_t)kPfRows * kPfTile * 2;
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int n_qt = (p.n_q + kPfRows - 1) / kPfRows;
+    TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(kPfThreads), smem, st, 1, p));
+    count_launch();
+    return TIDAL_OK;
+}
+
+}  // namespace tidal
+
+using namespace tidal;
+
+extern "C" int tidal_prefill(const tidal_prefill_args* a, void* stream) {
+    TIDAL_REQUIRE(a != nullptr, TIDAL_ERR_ARG, "args is NULL");
+    TIDAL_REQUIRE(a->d_q && a->d_o && a->d_kv && a->d_page_table, TIDAL_ERR_ARG, "null pointer");
+    TIDAL_REQUIRE(a->dtype == TIDAL_DTYPE_F16 || a->dtype == TIDAL_DTYPE_BF16, TIDAL_ERR_ARG,
+                  "tidal_prefill computes in fp16 or bf16 (dtype %d given)", a->dtype);
+    TIDAL_REQUIRE(a->head_dim == 64 || a->head_dim == 128, TIDAL_ERR_ARG, "head_dim %d not supported (64, 128)", a->head_dim);
+    TIDAL_REQUIRE(a->num_qo_heads >= 1 && a->num_kv_heads >= 1 && a->num_qo_heads % a->num_kv_heads == 0, TIDAL_ERR_ARG,
+                  "num_qo_heads (%d) must be a multiple of num_kv_heads (%d)", a->num_qo_heads, a->num_kv_heads);
+    TIDAL_REQUIRE(a->num_qo_heads <= 65535, TIDAL_ERR_ARG, "too many heads");
+    TIDAL_REQUIRE(a->page_size >= 1 && a->n_q >= 1 && a->kv_len >= a->n_q, TIDAL_ERR_ARG,
+                  "need page_size >= 1, n_q >= 1 and kv_len (%lld) >= n_q (%d): the cache already holds the new rows",
+                  (long long)a->kv_len, a->n_q);
+    TIDAL_REQUIRE((((uintptr_t)a->d_q | (uintptr_t)a->d_o | (uintptr_t)a->d_kv) & 15) == 0, TIDAL_ERR_ARG,
+                  "q, o and the pool must be 16-byte aligned");
+    PrefillParams p;
+    p.q = a->d_q;
+    p.o = a->d_o;
+    p.kv = a->d_kv;
+    p.pages = a->d_page_table;
+    p.status = a->d_status;
+    p.kv_len = a->kv_len;
+    p.n_q = a->n_q;
+    p.Hq = a->num_qo_heads;
+    p.Hkv = a->num_kv_heads;
+    p.page_size = a->page_size;
+    p.causal = a->causal ? 1 : 0;
+    const float sc = a->sm_scale > 0.f ? a->sm_scale : 1.f / sqrtf((float)a->head_dim);
+    p.scale_log2 = sc * kLog2e;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (a->dtype == TIDAL_DTYPE_F16)
+        return a->head_dim == 128 ? launch_prefill<__half, 128>(p, st) : launch_prefill<__half, 64>(p, st);
+    return a->head_dim == 128 ? launch_prefill<__nv_bfloat16, 128>(p, st) : launch_prefill<__nv_bfloat16, 64>(p, st);
+}

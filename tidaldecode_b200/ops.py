@@ -295,6 +295,36 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: Optional[to
     return out
 
 
+def prefill(q: torch.Tensor, kv_pool: torch.Tensor, page_table: torch.Tensor, kv_len: int, *, causal: bool = True,
+            sm_scale: float = 0.0, out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of the new rows q [n_q, Hq, D] of one sequence over its paged KV (which already
+    holds their K,V); see tidal_prefill in include/tidal_b200.h.  kv_pool [pages, 2, page_size, Hkv, D],
+    page_table int32 [>= ceil(kv_len / page_size)]; f16/bf16, D 64 or 128."""
+    _need_cuda(q, kv_pool, page_table, out, status)
+    if q.dim() != 3 or kv_pool.dim() != 5 or kv_pool.shape[1] != 2:
+        raise RuntimeError("q must be [n_q, Hq, D] and kv_pool [pages, 2, page_size, Hkv, D]")
+    if kv_pool.dtype != q.dtype or page_table.dtype != torch.int32:
+        raise RuntimeError("q and kv_pool must share a dtype, page_table must be int32")
+    if not (q.is_contiguous() and kv_pool.is_contiguous() and page_table.is_contiguous()):
+        raise RuntimeError("q, kv_pool and page_table must be contiguous")
+    n_q, Hq, D = q.shape
+    page_size, Hkv = kv_pool.shape[2], kv_pool.shape[3]
+    if kv_pool.shape[4] != D:
+        raise RuntimeError("q and kv_pool disagree on head_dim")
+    if page_table.numel() * page_size < kv_len:
+        raise RuntimeError("page_table does not cover kv_len tokens")
+    if out is None:
+        out = torch.empty_like(q)
+    a = _lib.PrefillArgs()
+    a.d_q, a.d_o, a.d_kv, a.d_page_table = q.data_ptr(), out.data_ptr(), kv_pool.data_ptr(), page_table.data_ptr()
+    a.d_status = status.data_ptr() if status is not None else None
+    a.kv_len, a.n_q, a.num_qo_heads, a.num_kv_heads, a.head_dim = int(kv_len), n_q, Hq, Hkv, D
+    a.page_size, a.dtype, a.causal, a.sm_scale = page_size, _dtype_code(q), 1 if causal else 0, float(sm_scale)
+    with torch.cuda.device(q.device):
+        check(lib.tidal_prefill(C.byref(a), _stream()), "tidal_prefill")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, *, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
            norm_weight: Optional[torch.Tensor] = None, eps: float = 1e-6, round_before_weight: bool = True,
            silu_mul: bool = False, static_weights: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
