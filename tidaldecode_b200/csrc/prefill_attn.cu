@@ -77,6 +77,18 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
+    const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -115,19 +127,30 @@ __device__ __forceinline__ uint32_t sw128_offset(int rows, int r, int c16) {
     return (uint32_t)((c16 >> 3) * rows * 128 + r * 128 + (((c16 & 7) ^ (r & 7)) << 4));
 }
 
+// Wait for an MMA commit: the tensor core answers within microseconds, so poll without sleeping
+// (try_wait itself suspends the thread for a while); past ~64 K polls something is wrong and the
+// wait backs off, then gives up like mbar_wait_bounded.
+__device__ __forceinline__ bool mma_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+    for (uint32_t i = 0; i < (1u << 16); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_bounded(bar, parity, abort_flag, status);
+}
+
 template <typename T, int D>
 __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
     constexpr int kChunks = D / 8;                    // 16-byte chunks per row
     constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
+    // operand tiles need, and two CTAs (112 KB + 64 bytes each) fit on one SM.
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + kQBytes;
-    uint8_t* sV = sK + kKBytes;
-    uint8_t* sP = sV + kKBytes;
-    __shared__ uint64_t bar_s, bar_o;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int abort_flag;
+    uint8_t* sK = sQ + kQBytes;          // two buffers
+    uint8_t* sV = sK + 2 * kKBytes;      // two buffers
+    uint8_t* sP = sV + 2 * kKBytes;
+    uint64_t& bar_s = *reinterpret_cast<uint64_t*>(sP + kPfRows * kPfTile * 2);
+    uint64_t& bar_o = *(&bar_s + 1);
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(&bar_s + 2);
+    int& abort_flag = *reinterpret_cast<int*>(&tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int n_qt = (p.n_q + kPfRows - 1) / kPfRows;
@@ -160,72 +183,83 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     const T* q = reinterpret_cast<const T*>(p.q);
     const T* kv = reinterpret_cast<const T*>(p.kv);
     const int64_t row_elems = (int64_t)p.Hkv * D;
-    const int64_t v_off = (int64_t)p.page_size * row_elems;
 
-    // K or V rows [t0, t0+64) of this KV head into a swizzled tile; rows past the sequence are zero
-    auto stage_kv = [&](uint8_t* dst, int64_t t0, int which) {
+    // K or V rows [t0, t0+64) of this KV head into a swizzled tile; rows past the sequence are zero.
+    // kChunks consecutive threads share a row (one page lookup, one division per row and thread).
+    const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
+    const int my_c = tid % kChunks, my_r0 = tid / kChunks;
+    const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
+    auto stage_kv = [&](uint8_t* dst, uint32_t t0, int which) {
         const uint32_t base = smem_u32(dst);
-        for (int i = tid; i < kPfTile * kChunks; i += kPfThreads) {
-            const int r = i / kChunks, c = i % kChunks;
-            const int64_t t = t0 + r;
-            const bool ok = t < p.kv_len;
+#pragma unroll
+        for (int r = my_r0; r < kPfTile; r += kPfThreads / kChunks) {
+            const uint32_t t = t0 + r;
+            const bool ok = t < kv_len32;
             const T* src = kv;
             if (ok) {
-                const int64_t pg = p.pages[t / p.page_size];
-                const int slot = (int)(t % p.page_size);
-                src = kv + (pg * 2 * p.page_size + slot) * row_elems + (which ? v_off : 0) + (int64_t)kvh * D + c * 8;
+                const uint32_t pi = ps == 1 ? t : t / ps;
+                const uint32_t slot = ps == 1 ? 0u : t - pi * ps;
+                const int64_t pg = p.pages[pi];
+                src = kv_head + ((pg * 2 + which) * ps + slot) * row_elems;
             }
-            cp_async16(base + sw128_offset(kPfTile, r, c), src, ok ? 16u : 0u);
+            cp_async16(base + sw128_offset(kPfTile, r, my_c), src, ok ? 16u : 0u);
         }
     };
 
-    // Q tile, K and V of tile 0
+    // Q tile, K of tiles 0 and 1, V of tile 0
     {
         const uint32_t base = smem_u32(sQ);
-        for (int i = tid; i < kPfRows * kChunks; i += kPfThreads) {
-            const int r = i / kChunks, c = i % kChunks;
+#pragma unroll 4
+        for (int r = my_r0; r < kPfRows; r += kPfThreads / kChunks) {
             const bool ok = r < rows_here;
-            const T* src = ok ? q + ((int64_t)(q0 + r) * p.Hq + h) * D + c * 8 : q;
-            cp_async16(base + sw128_offset(kPfRows, r, c), src, ok ? 16u : 0u);
+            const T* src = ok ? q + ((int64_t)(q0 + r) * p.Hq + h) * D + my_c * 8 : q;
+            cp_async16(base + sw128_offset(kPfRows, r, my_c), src, ok ? 16u : 0u);
         }
         stage_kv(sK, 0, 0);
-        cp_async_commit();
         stage_kv(sV, 0, 1);
+        if (n_tiles > 1) stage_kv(sK + kKBytes, kPfTile, 0);
         cp_async_commit();
     }
 
     constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
     constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
     constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
+    const uint32_t t_s = tmem, t_o = tmem + kPfTile;          // S in columns [0,64), O in [64,64+D)
 
-    float o_acc[D];
+    auto issue_qk = [&](int j) {     // one thread: S = Q K_j^T, arrival on bar_s
+        const uint32_t kb = smem_u32(sK) + (uint32_t)(j & 1) * kKBytes;
 #pragma unroll
-    for (int d = 0; d < D; ++d) o_acc[d] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+        for (int k = 0; k < D / 16; ++k) {
+            const uint32_t a = smem_u32(sQ) + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
+            const uint32_t b = kb + (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
+            tc_mma_f16(t_s, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, 16, 1024), idesc_qk, k > 0);
+        }
+        tc_commit(&bar_s);
+    };
+
+    cp_async_wait<0>();
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+        tc_fence_after();
+        issue_qk(0);
+    }
+
+    // The output row stays in tensor memory, scaled by 2^(-m_ref * scale); m_ref follows the running
+    // maximum only when that has grown by more than 2^8, so that most tiles need no rescaling pass.
+    float m_ref = -INFINITY, l_run = 0.f;
     const int64_t my_pos = pos0 + tid;
     bool alive = true;
 
     for (int j = 0; j < n_tiles; ++j) {
-        const uint32_t phase = (uint32_t)(j & 1);
-        // ---- S = Q K^T
-        cp_async_wait<1>();           // K of this tile (and Q) have landed; V may still be in flight
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(!alive)) break;      // every thread leaves in the same iteration
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int k = 0; k < D / 16; ++k) {
-                const uint32_t a = smem_u32(sQ) + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
-                const uint32_t b = smem_u32(sK) + (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
-                tc_mma_f16(tmem, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, 16, 1024), idesc_qk, k > 0);
-            }
-            tc_commit(&bar_s);
-        }
-        alive = mbar_wait_bounded(&bar_s, phase, &abort_flag, p.status);
+        // ---- S_j is complete; so is PV of the previous tile (commits arrive in issue order)
+        alive = mma_wait(&bar_s, (uint32_t)(j & 1), &abort_flag, p.status) && alive;
         tc_fence_after();
-        // K's buffer is free: fetch K of the next tile
-        if (j + 1 < n_tiles) stage_kv(sK, (int64_t)(j + 1) * kPfTile, 0);
+        // S_j complete: K_j's buffer takes K of tile j+2; PV_(j-1) complete: its V buffer takes V of tile j+1.
+        // Both are first read one tile from now, so their latency is covered by a whole iteration.
+        if (j + 2 < n_tiles) stage_kv(sK + (uint32_t)(j & 1) * kKBytes, (uint32_t)(j + 2) * kPfTile, 0);
+        if (j + 1 < n_tiles) stage_kv(sV + (uint32_t)((j + 1) & 1) * kKBytes, (uint32_t)(j + 1) * kPfTile, 1);
         cp_async_commit();
 
         // ---- softmax of this thread's row
@@ -236,16 +270,21 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
         tc_wait_ld();
         const int64_t t0 = (int64_t)j * kPfTile;
         const int64_t lim = p.causal ? min(p.kv_len - 1, my_pos) : p.kv_len - 1;   // last visible token
-        float mx = m_run;
         if (t0 + kPfTile - 1 > lim) {
 #pragma unroll
             for (int c = 0; c < kPfTile; ++c) s[c] = (t0 + c <= lim) ? s[c] : -INFINITY;
         }
+        float mx = m_ref;
 #pragma unroll
         for (int c = 0; c < kPfTile; ++c) mx = fmaxf(mx, s[c]);
-        const float m_use = (mx == -INFINITY) ? 0.f : mx;
-        const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);   // m_run = -inf gives 0
-        const float mb = m_use * p.scale_log2;
+        const bool grow = (mx - m_ref) * p.scale_log2 > 8.f;      // also true while m_ref = -inf
+        float alpha = 1.f;
+        if (grow) {
+            alpha = fast_exp2((m_ref - mx) * p.scale_log2);       // 0 for m_ref = -inf
+            l_run *= alpha;
+            m_ref = mx;
+        }
+        const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
         float sum = 0.f;
         {
             const uint32_t prow = smem_u32(sP) + tid * 128;
@@ -254,8 +293,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
                 float e[8];
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    e[u] = Vec16<T>::round(fast_exp2(fmaf(s[c8 * 8 + u], p.scale_log2, -mb)));
-                    sum += e[u];
+                    e[u] = fast_exp2(fmaf(s[c8 * 8 + u], p.scale_log2, -mb));
+                    sum += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
                 }
                 const uint4 v = Vec16<T>::from_float(e);
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (tid & 7)) << 4)), "r"(v.x),
@@ -263,52 +302,62 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
                              : "memory");
             }
         }
-        l_run = l_run * alpha + sum;
-        m_run = mx;
+        l_run += sum;
+        // O row *= alpha in the warps where some row's reference moved (tile 0: PV overwrites O anyway)
+        if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll
-        for (int d = 0; d < D; ++d) o_acc[d] *= alpha;
+            for (int d0 = 0; d0 < D; d0 += 32) {
+                float t[32];
+                tc_ld32(t_lane + kPfTile + d0, t);
+                tc_wait_ld();
+#pragma unroll
+                for (int u = 0; u < 32; ++u) t[u] *= alpha;
+                tc_st32(t_lane + kPfTile + d0, t);
+            }
+            tc_wait_st();
+        }
 
-        // ---- PV = P V
-        cp_async_wait<1>();           // V of this tile has landed (K of the next may be in flight)
+        // ---- PV_j accumulates into O; S of the next tile follows at once
+        cp_async_wait<1>();           // everything but this iteration's fetches has landed
         fence_async_smem();
         tc_fence_before();
-        if (__syncthreads_or(!alive)) break;
+        if (__syncthreads_or(!alive)) break;      // every thread leaves in the same iteration
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < kPfTile / 16; ++k) {
                 const uint32_t a = smem_u32(sP) + k * 32;
-                const uint32_t b = smem_u32(sV) + k * (16 * 128);
-                tc_mma_f16(tmem + kPfTile, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, v_lbo, v_sbo), idesc_pv, k > 0);
+                const uint32_t b = smem_u32(sV) + (uint32_t)(j & 1) * kKBytes + k * (16 * 128);
+                tc_mma_f16(t_o, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, v_lbo, v_sbo), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
             }
-            tc_commit(&bar_o);
+            if (j + 1 < n_tiles) issue_qk(j + 1);
+            else tc_commit(&bar_o);
         }
-        alive = mbar_wait_bounded(&bar_o, phase, &abort_flag, p.status) && alive;
-        tc_fence_after();
-        if (j + 1 < n_tiles) stage_kv(sV, (int64_t)(j + 1) * kPfTile, 1);
-        cp_async_commit();
+    }
+    cp_async_wait<0>();
+    alive = !__syncthreads_or(!alive);
+    if (alive) alive = mma_wait(&bar_o, 0, &abort_flag, p.status);
+    tc_fence_after();
+    alive = !__syncthreads_or(!alive);
+
+    if (alive) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.o) + ((int64_t)(q0 + tid) * p.Hq + h) * D);
 #pragma unroll
         for (int d0 = 0; d0 < D; d0 += 32) {
             float t[32];
             __syncwarp();
             tc_ld32(t_lane + kPfTile + d0, t);
             tc_wait_ld();
+            if (tid < rows_here) {
 #pragma unroll
-            for (int u = 0; u < 32; ++u) o_acc[d0 + u] += t[u];
-        }
-    }
-    cp_async_wait<0>();
-    alive = !__syncthreads_or(!alive);
-
-    if (tid < rows_here && alive) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.o) + ((int64_t)(q0 + tid) * p.Hq + h) * D);
+                for (int c = 0; c < 4; ++c) {
+                    float e[8];
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-            float e[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) e[u] = o_acc[c * 8 + u] * inv;
-            dst[c] = Vec16<T>::from_float(e);
+                    for (int u = 0; u < 8; ++u) e[u] = t[c * 8 + u] * inv;
+                    dst[d0 / 8 + c] = Vec16<T>::from_float(e);
+                }
+            }
         }
     }
     tc_fence_before();
@@ -318,7 +367,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
 
 template <typename T, int D>
 static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
-    const size_t smem = 1024 + (size_t)kPfRows * D * 2 + 2 * (size_t)kPfTile * D * 2 + (size_t)kPfRows * kPfTile * 2;
+    const size_t smem = (size_t)kPfRows * D * 2 + 4 * (size_t)kPfTile * D * 2 + (size_t)kPfRows * kPfTile * 2 + 64;   // Q, K x2, V x2, P, barriers
     TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int n_qt = (p.n_q + kPfRows - 1) / kPfRows;
     TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(kPfThreads), smem, st, 1, p));
@@ -339,6 +388,7 @@ extern "C" int tidal_prefill(const tidal_prefill_args* a, void* stream) {
     TIDAL_REQUIRE(a->num_qo_heads >= 1 && a->num_kv_heads >= 1 && a->num_qo_heads % a->num_kv_heads == 0, TIDAL_ERR_ARG,
                   "num_qo_heads (%d) must be a multiple of num_kv_heads (%d)", a->num_qo_heads, a->num_kv_heads);
     TIDAL_REQUIRE(a->num_qo_heads <= 65535, TIDAL_ERR_ARG, "too many heads");
+    TIDAL_REQUIRE(a->kv_len < ((int64_t)1 << 31) - kPfTile, TIDAL_ERR_ARG, "kv_len too large");
     TIDAL_REQUIRE(a->page_size >= 1 && a->n_q >= 1 && a->kv_len >= a->n_q, TIDAL_ERR_ARG,
                   "need page_size >= 1, n_q >= 1 and kv_len (%lld) >= n_q (%d): the cache already holds the new rows",
                   (long long)a->kv_len, a->n_q);
