@@ -184,27 +184,37 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     const T* kv = reinterpret_cast<const T*>(p.kv);
     const int64_t row_elems = (int64_t)p.Hkv * D;
 
-    // K or V rows [t0, t0+64) of this KV head into a swizzled tile; rows past the sequence are zero.
-    // kChunks consecutive threads share a row (one page lookup, one division per row and thread).
+    // K or V rows of one tile of this KV head into a swizzled tile; rows past the sequence are zero.
+    // kChunks consecutive threads share a row.  The rows' places in the pool (page lookup) are read a
+    // whole iteration before the copies that use them are issued, so no copy waits for its address.
+    constexpr int kRowsPerThread = kPfTile / (kPfThreads / kChunks);
     const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
     const int my_c = tid % kChunks, my_r0 = tid / kChunks;
     const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
-    auto stage_kv = [&](uint8_t* dst, uint32_t t0, int which) {
-        const uint32_t base = smem_u32(dst);
+    const int64_t v_off = (int64_t)ps * row_elems;
+    auto lookup_rows = [&](uint32_t t0, int64_t* off) {      // element offset of each of this thread's K rows, -1 past the end
 #pragma unroll
-        for (int r = my_r0; r < kPfTile; r += kPfThreads / kChunks) {
-            const uint32_t t = t0 + r;
-            const bool ok = t < kv_len32;
-            const T* src = kv;
-            if (ok) {
+        for (int i = 0; i < kRowsPerThread; ++i) {
+            const uint32_t t = t0 + my_r0 + i * (kPfThreads / kChunks);
+            off[i] = -1;
+            if (t < kv_len32) {
                 const uint32_t pi = ps == 1 ? t : t / ps;
                 const uint32_t slot = ps == 1 ? 0u : t - pi * ps;
-                const int64_t pg = p.pages[pi];
-                src = kv_head + ((pg * 2 + which) * ps + slot) * row_elems;
+                off[i] = (((int64_t)p.pages[pi] * 2) * ps + slot) * row_elems;
             }
+        }
+    };
+    auto stage_kv = [&](uint8_t* dst, const int64_t* off, int which) {
+        const uint32_t base = smem_u32(dst);
+#pragma unroll
+        for (int i = 0; i < kRowsPerThread; ++i) {
+            const int r = my_r0 + i * (kPfThreads / kChunks);
+            const bool ok = off[i] >= 0;
+            const T* src = ok ? kv_head + off[i] + (which ? v_off : 0) : kv;
             cp_async16(base + sw128_offset(kPfTile, r, my_c), src, ok ? 16u : 0u);
         }
     };
+    int64_t off_a[kRowsPerThread], off_b[kRowsPerThread];   // rows of tile j+2 and of tile j+1 at the top of iteration j
 
     // Q tile, K of tiles 0 and 1, V of tile 0
     {
@@ -215,10 +225,13 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
             const T* src = ok ? q + ((int64_t)(q0 + r) * p.Hq + h) * D + my_c * 8 : q;
             cp_async16(base + sw128_offset(kPfRows, r, my_c), src, ok ? 16u : 0u);
         }
-        stage_kv(sK, 0, 0);
-        stage_kv(sV, 0, 1);
-        if (n_tiles > 1) stage_kv(sK + kKBytes, kPfTile, 0);
+        lookup_rows(0, off_a);
+        lookup_rows(kPfTile, off_b);
+        stage_kv(sK, off_a, 0);
+        stage_kv(sV, off_a, 1);
+        if (n_tiles > 1) stage_kv(sK + kKBytes, off_b, 0);
         cp_async_commit();
+        lookup_rows(2 * kPfTile, off_a);
     }
 
     constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
@@ -226,13 +239,16 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
     const uint32_t t_s = tmem, t_o = tmem + kPfTile;          // S in columns [0,64), O in [64,64+D)
 
+    // operand descriptors of the tile origins; a step along K adds a constant to the address field
+    const uint64_t dq = smem_desc_sw128(smem_u32(sQ), 16, 1024), dk = smem_desc_sw128(smem_u32(sK), 16, 1024);
+    const uint64_t dp = smem_desc_sw128(smem_u32(sP), 16, 1024), dv = smem_desc_sw128(smem_u32(sV), v_lbo, v_sbo);
     auto issue_qk = [&](int j) {     // one thread: S = Q K_j^T, arrival on bar_s
-        const uint32_t kb = smem_u32(sK) + (uint32_t)(j & 1) * kKBytes;
+        const uint64_t dkj = dk + (uint64_t)(((uint32_t)(j & 1) * kKBytes) >> 4);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-            const uint32_t a = smem_u32(sQ) + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
-            const uint32_t b = kb + (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
-            tc_mma_f16(t_s, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, 16, 1024), idesc_qk, k > 0);
+            const uint32_t a = (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
+            const uint32_t b = (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
+            tc_mma_f16(t_s, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
         }
         tc_commit(&bar_s);
     };
@@ -258,9 +274,12 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
         tc_fence_after();
         // S_j complete: K_j's buffer takes K of tile j+2; PV_(j-1) complete: its V buffer takes V of tile j+1.
         // Both are first read one tile from now, so their latency is covered by a whole iteration.
-        if (j + 2 < n_tiles) stage_kv(sK + (uint32_t)(j & 1) * kKBytes, (uint32_t)(j + 2) * kPfTile, 0);
-        if (j + 1 < n_tiles) stage_kv(sV + (uint32_t)((j + 1) & 1) * kKBytes, (uint32_t)(j + 1) * kPfTile, 1);
+        if (j + 2 < n_tiles) stage_kv(sK + (uint32_t)(j & 1) * kKBytes, off_a, 0);
+        if (j + 1 < n_tiles) stage_kv(sV + (uint32_t)((j + 1) & 1) * kKBytes, off_b, 1);
         cp_async_commit();
+#pragma unroll
+        for (int i = 0; i < kRowsPerThread; ++i) off_b[i] = off_a[i];
+        lookup_rows((uint32_t)(j + 3) * kPfTile, off_a);       // used at the top of the next iteration
 
         // ---- softmax of this thread's row
         float s[kPfTile];
@@ -274,9 +293,10 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
 #pragma unroll
             for (int c = 0; c < kPfTile; ++c) s[c] = (t0 + c <= lim) ? s[c] : -INFINITY;
         }
-        float mx = m_ref;
+        float mx4[4] = {m_ref, -INFINITY, -INFINITY, -INFINITY};   // four chains: nothing else hides the latency
 #pragma unroll
-        for (int c = 0; c < kPfTile; ++c) mx = fmaxf(mx, s[c]);
+        for (int c = 0; c < kPfTile; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const bool grow = (mx - m_ref) * p.scale_log2 > 8.f;      // also true while m_ref = -inf
         float alpha = 1.f;
         if (grow) {
@@ -285,7 +305,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
             m_ref = mx;
         }
         const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         {
             const uint32_t prow = smem_u32(sP) + tid * 128;
 #pragma unroll
@@ -294,7 +314,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     e[u] = fast_exp2(fmaf(s[c8 * 8 + u], p.scale_log2, -mb));
-                    sum += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
+                    sum4[u & 3] += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
                 }
                 const uint4 v = Vec16<T>::from_float(e);
                 asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (tid & 7)) << 4)), "r"(v.x),
@@ -302,7 +322,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
                              : "memory");
             }
         }
-        l_run += sum;
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         // O row *= alpha in the warps where some row's reference moved (tile 0: PV overwrites O anyway)
         if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll
@@ -325,11 +345,10 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < kPfTile / 16; ++k) {
-                const uint32_t a = smem_u32(sP) + k * 32;
-                const uint32_t b = smem_u32(sV) + (uint32_t)(j & 1) * kKBytes + k * (16 * 128);
-                tc_mma_f16(t_o, smem_desc_sw128(a, 16, 1024), smem_desc_sw128(b, v_lbo, v_sbo), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-            }
+            const uint64_t dvj = dv + (uint64_t)(((uint32_t)(j & 1) * kKBytes) >> 4);
+#pragma unroll
+            for (int k = 0; k < kPfTile / 16; ++k)
+                tc_mma_f16(t_o, dp + (uint64_t)((k * 32) >> 4), dvj + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
             if (j + 1 < n_tiles) issue_qk(j + 1);
             else tc_commit(&bar_o);
         }
