@@ -26,8 +26,6 @@ namespace tidal {
 
 constexpr int kPfRows = 128;     // query rows per CTA = MMA M = TMEM lanes
 constexpr int kPfTile = 64;      // KV tokens per tile
-constexpr int kPfThreads = 128;
-constexpr int kPfTmemCols = 256;
 
 struct PrefillParams {
     const void* q;        // [n_q][Hq][D]
@@ -136,29 +134,33 @@ __device__ __forceinline__ bool mma_wait(uint64_t* bar, uint32_t parity, volatil
     return mbar_wait_bounded(bar, parity, abort_flag, status);
 }
 
-template <typename T, int D>
-__global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
+template <typename T, int D, int SUB>
+__global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
+    // SUB row blocks of 128 queries share every K/V tile (SUB = 2: half the L2 traffic per flop, one CTA per SM).
+    constexpr int kThreads = 128 * SUB, kRows = kPfRows * SUB;
     constexpr int kChunks = D / 8;                    // 16-byte chunks per row
-    constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2;
+    constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2, kPBytes = kPfRows * kPfTile * 2;
+    constexpr uint32_t kSubCols = kPfTile + D;        // tensor-memory columns of one row block: S, then O
+    constexpr uint32_t kTmemCols = SUB * kSubCols <= 256 ? 256 : 512;
     // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
     // operand tiles need, and two CTAs (112 KB + 64 bytes each) fit on one SM.
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + kQBytes;          // two buffers
+    uint8_t* sK = sQ + SUB * kQBytes;    // two buffers
     uint8_t* sV = sK + 2 * kKBytes;      // two buffers
     uint8_t* sP = sV + 2 * kKBytes;
-    uint64_t& bar_s = *reinterpret_cast<uint64_t*>(sP + kPfRows * kPfTile * 2);
+    uint64_t& bar_s = *reinterpret_cast<uint64_t*>(sP + SUB * kPBytes);
     uint64_t& bar_o = *(&bar_s + 1);
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(&bar_s + 2);
     int& abort_flag = *reinterpret_cast<int*>(&tmem_slot + 1);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
-    const int n_qt = (p.n_q + kPfRows - 1) / kPfRows;
+    const int tid = threadIdx.x, warp = tid >> 5, sub = warp >> 2, row = tid & 127;
+    const int n_qt = (p.n_q + kRows - 1) / kRows;
     const int qt = n_qt - 1 - (int)blockIdx.x;        // longest rows first
     const int h = blockIdx.y, kvh = h / (p.Hq / p.Hkv);
-    const int q0 = qt * kPfRows;
+    const int q0 = qt * kRows;
     const int64_t pos0 = p.kv_len - p.n_q + q0;       // position of row 0 of this CTA
-    const int rows_here = min(kPfRows, p.n_q - q0);
+    const int rows_here = min(kRows, p.n_q - q0);
     int64_t kv_end = p.causal ? min(p.kv_len, pos0 + rows_here) : p.kv_len;   // tokens any row of the CTA sees
     const int n_tiles = (int)((kv_end + kPfTile - 1) / kPfTile);
 
@@ -169,14 +171,14 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
-        tc_alloc(&tmem_slot, kPfTmemCols);
+        tc_alloc(&tmem_slot, kTmemCols);
         tc_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)sub * kSubCols;   // this thread's lane, its row block's columns
     pdl_wait();
     pdl_launch_dependents();
 
@@ -187,7 +189,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     // K or V rows of one tile of this KV head into a swizzled tile; rows past the sequence are zero.
     // kChunks consecutive threads share a row.  The rows' places in the pool (page lookup) are read a
     // whole iteration before the copies that use them are issued, so no copy waits for its address.
-    constexpr int kRowsPerThread = kPfTile / (kPfThreads / kChunks);
+    constexpr int kRowsPerThread = kPfTile / (kThreads / kChunks);
     const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
     const int my_c = tid % kChunks, my_r0 = tid / kChunks;
     const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
@@ -195,7 +197,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     auto lookup_rows = [&](uint32_t t0, int64_t* off) {      // element offset of each of this thread's K rows, -1 past the end
 #pragma unroll
         for (int i = 0; i < kRowsPerThread; ++i) {
-            const uint32_t t = t0 + my_r0 + i * (kPfThreads / kChunks);
+            const uint32_t t = t0 + my_r0 + i * (kThreads / kChunks);
             off[i] = -1;
             if (t < kv_len32) {
                 const uint32_t pi = ps == 1 ? t : t / ps;
@@ -208,7 +210,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
         const uint32_t base = smem_u32(dst);
 #pragma unroll
         for (int i = 0; i < kRowsPerThread; ++i) {
-            const int r = my_r0 + i * (kPfThreads / kChunks);
+            const int r = my_r0 + i * (kThreads / kChunks);
             const bool ok = off[i] >= 0;
             const T* src = ok ? kv_head + off[i] + (which ? v_off : 0) : kv;
             cp_async16(base + sw128_offset(kPfTile, r, my_c), src, ok ? 16u : 0u);
@@ -220,10 +222,10 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     {
         const uint32_t base = smem_u32(sQ);
 #pragma unroll 4
-        for (int r = my_r0; r < kPfRows; r += kPfThreads / kChunks) {
+        for (int r = my_r0; r < kRows; r += kThreads / kChunks) {
             const bool ok = r < rows_here;
             const T* src = ok ? q + ((int64_t)(q0 + r) * p.Hq + h) * D + my_c * 8 : q;
-            cp_async16(base + sw128_offset(kPfRows, r, my_c), src, ok ? 16u : 0u);
+            cp_async16(base + (r >> 7) * kQBytes + sw128_offset(kPfRows, r & 127, my_c), src, ok ? 16u : 0u);
         }
         lookup_rows(0, off_a);
         lookup_rows(kPfTile, off_b);
@@ -237,7 +239,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
     constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
     constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
-    const uint32_t t_s = tmem, t_o = tmem + kPfTile;          // S in columns [0,64), O in [64,64+D)
+    const uint32_t t_s = tmem, t_o = tmem + kPfTile;          // per row block: S in columns [0,64), O in [64,64+D)
 
     // operand descriptors of the tile origins; a step along K adds a constant to the address field
     const uint64_t dq = smem_desc_sw128(smem_u32(sQ), 16, 1024), dk = smem_desc_sw128(smem_u32(sK), 16, 1024);
@@ -245,11 +247,13 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     auto issue_qk = [&](int j) {     // one thread: S = Q K_j^T, arrival on bar_s
         const uint64_t dkj = dk + (uint64_t)(((uint32_t)(j & 1) * kKBytes) >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-            const uint32_t a = (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
-            const uint32_t b = (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
-            tc_mma_f16(t_s, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
-        }
+        for (int sb = 0; sb < SUB; ++sb)
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {
+                const uint32_t a = sb * kQBytes + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
+                const uint32_t b = (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
+                tc_mma_f16(t_s + sb * kSubCols, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
+            }
         tc_commit(&bar_s);
     };
 
@@ -307,7 +311,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
         const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         {
-            const uint32_t prow = smem_u32(sP) + tid * 128;
+            const uint32_t prow = smem_u32(sP) + sub * kPBytes + row * 128;
 #pragma unroll
             for (int c8 = 0; c8 < kPfTile / 8; ++c8) {
                 float e[8];
@@ -317,7 +321,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
                     sum4[u & 3] += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
                 }
                 const uint4 v = Vec16<T>::from_float(e);
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (tid & 7)) << 4)), "r"(v.x),
+                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (row & 7)) << 4)), "r"(v.x),
                              "r"(v.y), "r"(v.z), "r"(v.w)
                              : "memory");
             }
@@ -347,8 +351,11 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
 #pragma unroll
             const uint64_t dvj = dv + (uint64_t)(((uint32_t)(j & 1) * kKBytes) >> 4);
 #pragma unroll
-            for (int k = 0; k < kPfTile / 16; ++k)
-                tc_mma_f16(t_o, dp + (uint64_t)((k * 32) >> 4), dvj + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            for (int sb = 0; sb < SUB; ++sb)
+#pragma unroll
+                for (int k = 0; k < kPfTile / 16; ++k)
+                    tc_mma_f16(t_o + sb * kSubCols, dp + (uint64_t)((sb * kPBytes + k * 32) >> 4), dvj + (uint64_t)((k * 16 * 128) >> 4),
+                               idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
             if (j + 1 < n_tiles) issue_qk(j + 1);
             else tc_commit(&bar_o);
         }
@@ -381,17 +388,23 @@ __global__ void __launch_bounds__(kPfThreads, 2) prefill_attn_kernel(const __gri
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tc_dealloc(tmem, kPfTmemCols);
+    if (warp == 0) tc_dealloc(tmem, kTmemCols);
 }
 
-template <typename T, int D>
-static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
-    const size_t smem = (size_t)kPfRows * D * 2 + 4 * (size_t)kPfTile * D * 2 + (size_t)kPfRows * kPfTile * 2 + 64;   // Q, K x2, V x2, P, barriers
-    TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int n_qt = (p.n_q + kPfRows - 1) / kPfRows;
-    TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(kPfThreads), smem, st, 1, p));
+template <typename T, int D, int SUB>
+static int launch_prefill_sub(const PrefillParams& p, cudaStream_t st) {
+    // Q, K x2, V x2, P, barriers
+    const size_t smem = (size_t)SUB * kPfRows * D * 2 + 4 * (size_t)kPfTile * D * 2 + (size_t)SUB * kPfRows * kPfTile * 2 + 64;
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel<T, D, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int n_qt = (p.n_q + kPfRows * SUB - 1) / (kPfRows * SUB);
+    TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D, SUB>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(128 * SUB), smem, st, 1, p));
     count_launch();
     return TIDAL_OK;
+}
+template <typename T, int D>
+static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
+    // one row block per CTA when there are no more rows than that (a late chunk of a prompt, a short prompt)
+    return p.n_q > kPfRows ? launch_prefill_sub<T, D, 2>(p, st) : launch_prefill_sub<T, D, 1>(p, st);
 }
 
 }  // namespace tidal
