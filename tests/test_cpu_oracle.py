@@ -106,3 +106,30 @@ def test_paged_append_roundtrip():
     assert O.kv_elem_offset(2, 1, 3, 1, 5, page, H, D) == (((2 * 2 + 1) * page + 3) * H + 1) * D + 5
     flat = pool.view(-1)
     assert flat[O.kv_elem_offset(9, 0, 0, 2, 7, page, H, D)] == k[8, 2, 7]
+
+
+def test_causal_prefill_matches_the_reference_paths():
+    """The prefill restatement against (a) the fused causal attention the reference's PyTorch path
+    runs below the sparse layers (src/tidal_build/modify_llama.py:84-98) and (b), for a later chunk of
+    a prompt, one decode-style full_layer call per row over that row's prefix — the mask of
+    kernels/src/include/cpu_reference.h:127."""
+    g = torch.Generator().manual_seed(3)
+    n, Hq, Hkv, D = 37, 4, 2, 32
+    q = torch.randn(n, Hq, D, generator=g)
+    K = torch.randn(n, Hkv, D, generator=g)
+    V = torch.randn(n, Hkv, D, generator=g)
+    got = O.causal_prefill(q, K, V)
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(0, 1)[None], O.repeat_kv(K.transpose(0, 1)[None], Hq // Hkv), O.repeat_kv(V.transpose(0, 1)[None], Hq // Hkv),
+        is_causal=True)[0].transpose(0, 1)
+    assert torch.allclose(got, ref, rtol=1e-5, atol=1e-6)
+    # a chunk: the last 5 rows over all 37 cached tokens
+    chunk = O.causal_prefill(q[-5:], K, V)
+    for i in range(5):
+        upto = n - 5 + i + 1
+        row = O.full_layer(q[-5 + i][None, :, None, :], K[:upto].transpose(0, 1)[None], V[:upto].transpose(0, 1)[None])
+        assert torch.allclose(chunk[i], row[0, :, 0], rtol=1e-5, atol=1e-6)
+    # non-causal: every row sees everything
+    full = O.causal_prefill(q[:3], K, V, causal=False)
+    row = O.full_layer(q[:3].transpose(0, 1)[None], K.transpose(0, 1)[None], V.transpose(0, 1)[None])
+    assert torch.allclose(full, row[0].transpose(0, 1), rtol=1e-5, atol=1e-6)
