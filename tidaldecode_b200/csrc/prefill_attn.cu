@@ -135,22 +135,22 @@ __device__ __forceinline__ bool mma_wait(uint64_t* bar, uint32_t parity, volatil
 }
 
 template <typename T, int D, int SUB>
-__global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
+__global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
     // SUB row blocks of 128 queries share every K/V tile (SUB = 2: half the L2 traffic per flop, one CTA per SM).
     constexpr int kThreads = 128 * SUB, kRows = kPfRows * SUB;
     constexpr int kChunks = D / 8;                    // 16-byte chunks per row
     constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2, kPBytes = kPfRows * kPfTile * 2;
-    constexpr uint32_t kSubCols = kPfTile + D;        // tensor-memory columns of one row block: S, then O
+    constexpr uint32_t kSubCols = 2 * kPfTile + D;    // tensor-memory columns of one row block: S (two buffers), then O
     constexpr uint32_t kTmemCols = SUB * kSubCols <= 256 ? 256 : 512;
     // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
     // operand tiles need, and two CTAs (112 KB + 64 bytes each) fit on one SM.
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + SUB * kQBytes;    // two buffers
-    uint8_t* sV = sK + 2 * kKBytes;      // two buffers
-    uint8_t* sP = sV + 2 * kKBytes;
-    uint64_t& bar_s = *reinterpret_cast<uint64_t*>(sP + SUB * kPBytes);
-    uint64_t& bar_o = *(&bar_s + 1);
+    uint8_t* sK = sQ + SUB * kQBytes;    // three buffers
+    uint8_t* sV = sK + 3 * kKBytes;      // three buffers
+    uint8_t* sP = sV + 3 * kKBytes;      // two buffers per row block
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sP + 2 * SUB * kPBytes);   // two barriers, used alternately
+    uint64_t& bar_s = bar[0];
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(&bar_s + 2);
     int& abort_flag = *reinterpret_cast<int*>(&tmem_slot + 1);
 
@@ -165,8 +165,8 @@ __global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kern
     const int n_tiles = (int)((kv_end + kPfTile - 1) / kPfTile);
 
     if (tid == 0) {
-        mbar_init(&bar_s, 1);
-        mbar_init(&bar_o, 1);
+        mbar_init(&bar[0], 1);
+        mbar_init(&bar[1], 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -232,29 +232,30 @@ __global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kern
         stage_kv(sK, off_a, 0);
         stage_kv(sV, off_a, 1);
         if (n_tiles > 1) stage_kv(sK + kKBytes, off_b, 0);
-        cp_async_commit();
         lookup_rows(2 * kPfTile, off_a);
+        if (n_tiles > 2) stage_kv(sK + 2 * kKBytes, off_a, 0);
+        cp_async_commit();
+        lookup_rows(3 * kPfTile, off_a);      // K of tile 3 and V of tile 1 are fetched in iteration 0
     }
 
     constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
     constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
     constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
-    const uint32_t t_s = tmem, t_o = tmem + kPfTile;          // per row block: S in columns [0,64), O in [64,64+D)
+    const uint32_t t_s = tmem, t_o = tmem + 2 * kPfTile;      // per row block: S buffers in columns [0,64) and [64,128), O after them
 
     // operand descriptors of the tile origins; a step along K adds a constant to the address field
     const uint64_t dq = smem_desc_sw128(smem_u32(sQ), 16, 1024), dk = smem_desc_sw128(smem_u32(sK), 16, 1024);
     const uint64_t dp = smem_desc_sw128(smem_u32(sP), 16, 1024), dv = smem_desc_sw128(smem_u32(sV), v_lbo, v_sbo);
-    auto issue_qk = [&](int j) {     // one thread: S = Q K_j^T, arrival on bar_s
-        const uint64_t dkj = dk + (uint64_t)(((uint32_t)(j & 1) * kKBytes) >> 4);
+    auto issue_qk = [&](int j, int kbuf) {     // one thread: S_j = Q K_j^T into S buffer j & 1
+        const uint64_t dkj = dk + (uint64_t)(((uint32_t)kbuf * kKBytes) >> 4);
 #pragma unroll
         for (int sb = 0; sb < SUB; ++sb)
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
                 const uint32_t a = sb * kQBytes + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
                 const uint32_t b = (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
-                tc_mma_f16(t_s + sb * kSubCols, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
+                tc_mma_f16(t_s + sb * kSubCols + (uint32_t)(j & 1) * kPfTile, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
             }
-        tc_commit(&bar_s);
     };
 
     cp_async_wait<0>();
@@ -263,33 +264,39 @@ __global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kern
     __syncthreads();
     if (tid == 0) {
         tc_fence_after();
-        issue_qk(0);
+        issue_qk(0, 0);
+        tc_commit(&bar[0]);
+        if (n_tiles > 1) issue_qk(1, 1);
+        tc_commit(&bar[1]);
     }
 
+    // Software pipeline: at the barrier that ends iteration j one thread issues PV_j and QK_(j+2) and commits
+    // them to bar[j & 1]; iteration j itself only needs QK_j and PV_(j-2), issued two barriers earlier, so the
+    // tensor core has a whole iteration to run while the threads are in the softmax of the tile in between.
+    // (Two barriers because a wait may find its batch and the next one both complete: one barrier's parity
+    // could not tell that from "not yet".)  Batch b is phase (b >> 1) + 1 of bar[b & 1]; phase 0 is the prologue's.
     // The output row stays in tensor memory, scaled by 2^(-m_ref * scale); m_ref follows the running
     // maximum only when that has grown by more than 2^8, so that most tiles need no rescaling pass.
     float m_ref = -INFINITY, l_run = 0.f;
     const int64_t my_pos = pos0 + tid;
     bool alive = true;
 
-    for (int j = 0; j < n_tiles; ++j) {
-        // ---- S_j is complete; so is PV of the previous tile (commits arrive in issue order)
-        alive = mma_wait(&bar_s, (uint32_t)(j & 1), &abort_flag, p.status) && alive;
+    int k3 = 0;     // j % 3
+    for (int j = 0; j < n_tiles; ++j, k3 = (k3 == 2 ? 0 : k3 + 1)) {
+        // ---- S_j and PV_(j-2) are complete: K_j's buffer takes K of tile j+3, V_(j-2)'s buffer V of tile j+1
+        alive = mma_wait(&bar[j & 1], (uint32_t)((j >> 1) & 1), &abort_flag, p.status) && alive;
         tc_fence_after();
-        // S_j complete: K_j's buffer takes K of tile j+2; PV_(j-1) complete: its V buffer takes V of tile j+1.
-        // Both are first read one tile from now, so their latency is covered by a whole iteration.
-        if (j + 2 < n_tiles) stage_kv(sK + (uint32_t)(j & 1) * kKBytes, off_a, 0);
-        if (j + 1 < n_tiles) stage_kv(sV + (uint32_t)((j + 1) & 1) * kKBytes, off_b, 1);
+        if (j + 3 < n_tiles) stage_kv(sK + (uint32_t)k3 * kKBytes, off_a, 0);
+        if (j + 1 < n_tiles) stage_kv(sV + (uint32_t)(k3 == 2 ? 0 : k3 + 1) * kKBytes, off_b, 1);
         cp_async_commit();
-#pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) off_b[i] = off_a[i];
-        lookup_rows((uint32_t)(j + 3) * kPfTile, off_a);       // used at the top of the next iteration
+        lookup_rows((uint32_t)(j + 4) * kPfTile, off_a);       // both used at the top of the next iteration
+        lookup_rows((uint32_t)(j + 2) * kPfTile, off_b);
 
         // ---- softmax of this thread's row
         float s[kPfTile];
         __syncwarp();
-        tc_ld32(t_lane, s);
-        tc_ld32(t_lane + 32, s + 32);
+        tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile, s);
+        tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile + 32, s + 32);
         tc_wait_ld();
         const int64_t t0 = (int64_t)j * kPfTile;
         const int64_t lim = p.causal ? min(p.kv_len - 1, my_pos) : p.kv_len - 1;   // last visible token
@@ -311,7 +318,7 @@ __global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kern
         const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         {
-            const uint32_t prow = smem_u32(sP) + sub * kPBytes + row * 128;
+            const uint32_t prow = smem_u32(sP) + ((j & 1) * SUB + sub) * kPBytes + row * 128;
 #pragma unroll
             for (int c8 = 0; c8 < kPfTile / 8; ++c8) {
                 float e[8];
@@ -329,40 +336,42 @@ __global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kern
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         // O row *= alpha in the warps where some row's reference moved (tile 0: PV overwrites O anyway)
         if (j > 0 && __any_sync(0xffffffffu, grow)) {
+            // PV_(j-1) may still be adding into O: its batch is the one iteration j+1 would wait for
+            alive = mma_wait(&bar[(j - 1) & 1], (uint32_t)((((j - 1) >> 1) + 1) & 1), &abort_flag, p.status) && alive;
+            tc_fence_after();
 #pragma unroll
             for (int d0 = 0; d0 < D; d0 += 32) {
                 float t[32];
-                tc_ld32(t_lane + kPfTile + d0, t);
+                tc_ld32(t_lane + 2 * kPfTile + d0, t);
                 tc_wait_ld();
 #pragma unroll
                 for (int u = 0; u < 32; ++u) t[u] *= alpha;
-                tc_st32(t_lane + kPfTile + d0, t);
+                tc_st32(t_lane + 2 * kPfTile + d0, t);
             }
             tc_wait_st();
         }
 
-        // ---- PV_j accumulates into O; S of the next tile follows at once
+        // ---- PV_j accumulates into O; QK of tile j+2 refills the S buffer this iteration has just read
         cp_async_wait<1>();           // everything but this iteration's fetches has landed
         fence_async_smem();
         tc_fence_before();
         if (__syncthreads_or(!alive)) break;      // every thread leaves in the same iteration
         if (tid == 0) {
             tc_fence_after();
-#pragma unroll
-            const uint64_t dvj = dv + (uint64_t)(((uint32_t)(j & 1) * kKBytes) >> 4);
+            const uint64_t dvj = dv + (uint64_t)(((uint32_t)k3 * kKBytes) >> 4);
 #pragma unroll
             for (int sb = 0; sb < SUB; ++sb)
 #pragma unroll
                 for (int k = 0; k < kPfTile / 16; ++k)
-                    tc_mma_f16(t_o + sb * kSubCols, dp + (uint64_t)((sb * kPBytes + k * 32) >> 4), dvj + (uint64_t)((k * 16 * 128) >> 4),
-                               idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-            if (j + 1 < n_tiles) issue_qk(j + 1);
-            else tc_commit(&bar_o);
+                    tc_mma_f16(t_o + sb * kSubCols, dp + (uint64_t)((((j & 1) * SUB + sb) * kPBytes + k * 32) >> 4),
+                               dvj + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+            if (j + 2 < n_tiles) issue_qk(j + 2, k3 == 0 ? 2 : k3 - 1);      // (j + 2) % 3
+            tc_commit(&bar[j & 1]);
         }
     }
     cp_async_wait<0>();
     alive = !__syncthreads_or(!alive);
-    if (alive) alive = mma_wait(&bar_o, 0, &abort_flag, p.status);
+    if (alive) alive = mma_wait(&bar[(n_tiles - 1) & 1], (uint32_t)((((n_tiles - 1) >> 1) + 1) & 1), &abort_flag, p.status);
     tc_fence_after();
     alive = !__syncthreads_or(!alive);
 
@@ -373,7 +382,7 @@ __global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kern
         for (int d0 = 0; d0 < D; d0 += 32) {
             float t[32];
             __syncwarp();
-            tc_ld32(t_lane + kPfTile + d0, t);
+            tc_ld32(t_lane + 2 * kPfTile + d0, t);
             tc_wait_ld();
             if (tid < rows_here) {
 #pragma unroll
@@ -393,8 +402,8 @@ __global__ void __launch_bounds__(128 * SUB, SUB == 1 ? 2 : 1) prefill_attn_kern
 
 template <typename T, int D, int SUB>
 static int launch_prefill_sub(const PrefillParams& p, cudaStream_t st) {
-    // Q, K x2, V x2, P, barriers
-    const size_t smem = (size_t)SUB * kPfRows * D * 2 + 4 * (size_t)kPfTile * D * 2 + (size_t)SUB * kPfRows * kPfTile * 2 + 64;
+    // Q, K x3, V x3, P x2, barriers
+    const size_t smem = (size_t)SUB * kPfRows * D * 2 + 6 * (size_t)kPfTile * D * 2 + 2 * (size_t)SUB * kPfRows * kPfTile * 2 + 64;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel<T, D, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int n_qt = (p.n_q + kPfRows * SUB - 1) / (kPfRows * SUB);
     TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D, SUB>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(128 * SUB), smem, st, 1, p));
