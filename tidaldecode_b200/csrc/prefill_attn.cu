@@ -3,17 +3,19 @@
 // tensor memory.  Takes the place of prefill_with_paged_kv_cache (tidal/ops/csrc/batch_prefill.cu:27-117,
 // kernels/include/prefill/prefill.cuh:688-870, an mma.sync kernel).
 //
-// One CTA = 128 query rows of one query head; it walks the KV tokens its rows may see in tiles of 64.
-// Per tile:
+// A row block = 128 query rows of one query head = the 128 lanes of tensor memory; a CTA holds one row
+// block (short calls) or two that share every K/V tile.  It walks the KV tokens its rows may see in
+// tiles of 64.  Per row block and tile:
 //   S = Q K^T     8 (D=128) MMAs of 128x64x16, Q and K as K-major operands with the 128-byte swizzle,
-//                 S in tensor-memory columns [0,64)
-//   softmax       thread t owns row t (tcgen05.ld 32x32b: lane = row), running max / sum in registers,
+//                 S in one of two 64-column buffers of tensor memory
+//   softmax       thread t owns row t (tcgen05.ld 32x32b: lane = row), running sum in registers,
 //                 P rounded to the storage type and written to shared memory as the next A operand
-//   PV = P V      4 MMAs of 128xDx16, V rows as they lie in the cache (MN-major B operand),
-//                 result in tensor-memory columns [64,64+D), added to the fp32 output row in registers
-// K of the next tile is fetched (cp.async, 16 bytes per request, page lookup per row) as soon as S is
-// complete, V of the next tile as soon as PV is complete; two CTAs share an SM (80 KB of shared memory,
-// 256 of the 512 tensor-memory columns each), so one CTA's softmax overlaps the other's MMAs.
+//   O += P V      4 MMAs of 128xDx16, V rows as they lie in the cache (MN-major B operand); O stays in
+//                 tensor memory and is rescaled only when a row's maximum has grown by more than 2^8
+// The loop is software-pipelined: the barrier that ends iteration j is followed by one thread issuing
+// PV of tile j and QK of tile j+2, so the MMAs run under the softmax of tile j+1.  K and V tiles live in
+// three-deep rings, fetched at least one tile ahead (cp.async, 16 bytes per request, page lookup per
+// row, itself one iteration ahead of the copies).
 // Every wait on an mbarrier has an iteration limit; a CTA that gives up sets TIDAL_DEV_WAIT_TIMEOUT,
 // still frees its tensor memory and returns.
 #include <cmath>
@@ -136,22 +138,21 @@ __device__ __forceinline__ bool mma_wait(uint64_t* bar, uint32_t parity, volatil
 
 template <typename T, int D, int SUB>
 __global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
-    // SUB row blocks of 128 queries share every K/V tile (SUB = 2: half the L2 traffic per flop, one CTA per SM).
+    // SUB row blocks of 128 queries share every K/V tile (SUB = 2: half the L2 traffic per flop); one CTA per SM.
     constexpr int kThreads = 128 * SUB, kRows = kPfRows * SUB;
     constexpr int kChunks = D / 8;                    // 16-byte chunks per row
     constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2, kPBytes = kPfRows * kPfTile * 2;
     constexpr uint32_t kSubCols = 2 * kPfTile + D;    // tensor-memory columns of one row block: S (two buffers), then O
     constexpr uint32_t kTmemCols = SUB * kSubCols <= 256 ? 256 : 512;
     // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
-    // operand tiles need, and two CTAs (112 KB + 64 bytes each) fit on one SM.
+    // operand tiles need (224 KB + 64 bytes with two row blocks at D = 128).
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + SUB * kQBytes;    // three buffers
     uint8_t* sV = sK + 3 * kKBytes;      // three buffers
     uint8_t* sP = sV + 3 * kKBytes;      // two buffers per row block
     uint64_t* bar = reinterpret_cast<uint64_t*>(sP + 2 * SUB * kPBytes);   // two barriers, used alternately
-    uint64_t& bar_s = bar[0];
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(&bar_s + 2);
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bar + 2);
     int& abort_flag = *reinterpret_cast<int*>(&tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, sub = warp >> 2, row = tid & 127;
