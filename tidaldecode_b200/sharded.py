@@ -66,7 +66,7 @@ def pack_layout(batch: int, hq: int, d: int, rows: int, k: int):
 
 
 # largest group the peer-store exchange has run on; larger groups get NCCL unless exchange="peer" is asked for
-kPeerValidatedWorld = 2
+kPeerValidatedWorld = 4
 
 
 class ShardedDecodeAttention:
