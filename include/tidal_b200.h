@@ -194,7 +194,8 @@ int tidal_topk(const tidal_topk_args* args, void* d_ws, size_t ws_bytes, void* s
  * loads the library keeps that array until the process exits.
  *
  * Limits (anything beyond is refused with TIDAL_ERR_ARG and a message): at most 8 rows
- * per call, rows of at most 262144 scores, k at most 16384; d_hist must be NULL.
+ * per call, rows of at most 262144 scores, k at most 16384; d_hist and d_row_len must be
+ * NULL and seg_len, seg_stride 0 (contiguous rows whose length is n).
  * The call itself allocates nothing and frees nothing.  Its first use on a device
  * looks up the array's device address (cudaGetSymbolAddress, with that device
  * current) and caches it, so make that first call outside any stream capture.
@@ -205,6 +206,11 @@ int tidal_topk(const tidal_topk_args* args, void* d_ws, size_t ws_bytes, void* s
  * d_status: NULL, or a device word of the caller's that receives TIDAL_DEV_* bits
  * instead of the internal fault word. */
 int tidal_topk_static(const tidal_topk_args* args, uint32_t* d_status, void* stream);
+/* Blocking: the TIDAL_DEV_* bits that calls with d_status == NULL have left in the internal fault
+ * word of the current device since it was last cleared (>= 0), or a negative TIDAL_ERR_*; clear != 0
+ * zeroes the word afterwards (on `stream`, ordered after the read).  Has no counterpart in the
+ * reference either; allocates nothing. */
+int tidal_topk_static_status(int clear, void* stream);
 
 /* ------------------------------------------------------ RoPE + KV append
  * Rotates q (in place) and the new k, then writes k,v into their pool slots.
@@ -236,6 +242,12 @@ typedef struct tidal_rope_append_args {
     int32_t batch, tokens_per_seq, num_qo_heads, num_kv_heads, head_dim, page_size, dtype;
     int64_t num_pages;
     uint32_t* d_status;          /* NULL or a device word that receives TIDAL_DEV_* bits */
+    const void* d_q_src;         /* NULL, or [n_tokens][Hq][D]: the queries are read from here and their rotated
+                                    rows written to d_q, so the source survives (a projection's output buffer that
+                                    is reused, a benchmark's resident inputs) */
+    int32_t kv_pos_base;         /* position that the first slot of each sequence in this pool holds (0 unless the pool
+                                    is one rank's shard [lo, hi) of a sequence-sharded context: then lo); the token at
+                                    position p is rotated by p and written to slot p - kv_pos_base */
 } tidal_rope_append_args;
 
 int tidal_rope_append(const tidal_rope_append_args* args, void* stream);
@@ -310,8 +322,16 @@ int tidal_decode_qkv(const tidal_linear_args* lin, const tidal_rope_append_args*
  *   counters  per rank 2 * world uint32, zeroed, mapped the same way: d_peer_count[r];
  *   d_state   2 uint32 of this rank's own memory, zeroed.
  * d_peer_stage and d_peer_count are device arrays of `world` pointers.  Nothing is reset between
- * calls.  A rank that never arrives makes the others' bounded waits run out: TIDAL_DEV_WAIT_TIMEOUT is
- * OR-ed into *d_status (if given) and the call completes with incomplete data. */
+ * calls.  Contract across calls on one set of buffers: slot_bytes, world and rank never change (the
+ * number of CTAs, and with it the arrivals a rank expects per exchange, follows from slot_bytes:
+ * tidal_peer_exchange_ctas); `bytes` may differ from call to call as long as every rank passes the
+ * same value in the same call; the ranks issue their calls in the same order.
+ * A rank that never arrives makes the others' bounded waits run out (wait_limit polls, 0 = the
+ * default of about half a second): TIDAL_DEV_WAIT_TIMEOUT is OR-ed into *d_status (if given) and the
+ * call completes with incomplete data.  After that the arrival counters and the exchange count of the
+ * ranks no longer agree, and every later call on these buffers would time out or read stale blocks:
+ * tidal_peer_exchange_reset must run on EVERY rank, with no exchange in flight anywhere (a host-side
+ * barrier before and after), before the buffers are used again. */
 typedef struct {
     const void* d_send;
     void* d_recv;
@@ -328,8 +348,14 @@ typedef struct {
     void* d_merge_out;
     int64_t merge_m_off, merge_l_off, merge_o_off;
     int32_t merge_rows, merge_head_dim, merge_dtype;
+    int32_t wait_limit;          /* polls before a CTA gives up on the other ranks; 0 = default */
 } tidal_exchange_args;
 int tidal_peer_all_gather(const tidal_exchange_args* args, void* stream);
+/* CTAs every exchange on buffers with this slot size runs with (host arithmetic). */
+int tidal_peer_exchange_ctas(int64_t slot_bytes);
+/* Zeroes this rank's arrival counters (d_count = d_peer_count[rank], 2 * world words) and d_state on
+ * the stream.  See tidal_peer_all_gather for when and how: every rank, nothing in flight. */
+int tidal_peer_exchange_reset(uint32_t* d_count, uint32_t* d_state, int world, void* stream);
 
 /* ------------------------------------------------------------------ prefill
  * Causal attention of n_q new query rows of ONE sequence over its paged KV, which already holds
@@ -349,6 +375,8 @@ typedef struct {
     int64_t kv_len;
     int32_t n_q, num_qo_heads, num_kv_heads, head_dim, page_size, dtype, causal;
     float sm_scale;
+    int64_t num_pages;           /* pages in the pool: a table entry outside [0, num_pages) is not followed (its
+                                    tokens read as zeros) and TIDAL_DEV_BAD_INDEX is OR-ed into *d_status */
 } tidal_prefill_args;
 int tidal_prefill(const tidal_prefill_args* args, void* stream);
 

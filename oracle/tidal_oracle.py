@@ -197,6 +197,51 @@ def gathered_attention(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, idx: t
     return torch.matmul(torch.softmax(S, dim=-1), Vg)
 
 
+def attention_chunked(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, head_reduce: Optional[str] = None,
+                      chunk: int = 32768, return_partials: bool = False):
+    """The same fp32 arithmetic as `scores_fp32` + `gathered_attention` over ALL positions, for contexts
+    where materialising the G-fold repeated K,V (modify_llama.py:82-83) in fp32 would not fit the host:
+    query heads are grouped on their KV head instead of repeating K,V, and the context is walked in
+    chunks whose partials are merged by log-sum-exp (`merge_partials`).  q [B,Hq,1,D]; K,V [B,Hkv,N,D].
+    Returns (o [B,Hq,D] fp32, scores: None, [B,N] ("sum") or [B,Hq,N] ("none") fp32); with
+    return_partials the first item is the un-normalised (m [B,Hq], l [B,Hq], o [B,Hq,D]) of
+    `partial_attention` instead (natural-log domain)."""
+    B, Hq, _, D = q.shape
+    Hkv, N = K.shape[1], K.shape[2]
+    G = Hq // Hkv
+    qg = q.float().view(B, Hkv, G, D)
+    parts, sc = [], []
+    for lo in range(0, N, chunk):
+        Kc, Vc = K[:, :, lo:lo + chunk].float(), V[:, :, lo:lo + chunk].float()
+        S = torch.matmul(qg, Kc.transpose(2, 3)) / math.sqrt(D)          # [B,Hkv,G,n]
+        if head_reduce is not None:
+            Sh = S.reshape(B, Hq, -1)
+            sc.append(Sh.sum(dim=1) if head_reduce == "sum" else Sh)
+        m = S.max(dim=-1).values
+        p = torch.exp(S - m[..., None])
+        parts.append((m.reshape(B, Hq), p.sum(-1).reshape(B, Hq), torch.matmul(p, Vc).reshape(B, Hq, D)))
+    scores = torch.cat(sc, dim=-1) if sc else None
+    if not parts:
+        parts = [(torch.full((B, Hq), -float("inf")), torch.zeros(B, Hq), torch.zeros(B, Hq, D))]
+    if return_partials:
+        m = torch.stack([p[0] for p in parts]).max(dim=0).values
+        wts = [torch.where(torch.isfinite(p[0]), torch.exp(p[0] - m), torch.zeros_like(m)) for p in parts]
+        return (m, sum(w * p[1] for w, p in zip(wts, parts)), sum(w[..., None] * p[2] for w, p in zip(wts, parts))), scores
+    return merge_partials(parts), scores
+
+
+def gathered_attention_gqa(q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """`gathered_attention` for a list shared by all heads of a sequence (idx [B,k]) without repeating
+    K,V: the rows are gathered first, then the query heads of a group share them.  [B,Hq,D] fp32."""
+    B, Hq, _, D = q.shape
+    Hkv = K.shape[1]
+    G = Hq // Hkv
+    gi = idx.long()[:, None, :, None].expand(B, Hkv, idx.shape[-1], D)
+    Kg, Vg = torch.gather(K, 2, gi).float(), torch.gather(V, 2, gi).float()
+    S = torch.matmul(q.float().view(B, Hkv, G, D), Kg.transpose(2, 3)) / math.sqrt(D)
+    return torch.matmul(torch.softmax(S, dim=-1), Vg).reshape(B, Hq, D)
+
+
 def topk_sets_match(scores: torch.Tensor, got_idx: torch.Tensor, k: int, tie_band: float = 1e-4,
                     force_last: bool = False) -> Tuple[bool, str]:
     """Set equality of a row's top-k up to ties: every index whose score is more
@@ -373,7 +418,7 @@ def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 
 def tiny_llama_greedy(W: TinyLlamaWeights, prompt: torch.Tensor, steps: int, top_k: int,
                       sparse_layer_start: int, correction_layer: int, head_reduce: str = "none",
-                      force_last: bool = False, return_trace: bool = False):
+                      force_last: bool = False, return_trace: bool = False, return_logits: bool = False):
     """Prefill + greedy decode with path-A attention per layer
     (src/models/llama_tidaldecoding.py:914-1019 for the layer loop and pos_dict
     threading; modify_llama.py:19-148 for the attention).  prompt [1,P] int64."""
@@ -382,7 +427,7 @@ def tiny_llama_greedy(W: TinyLlamaWeights, prompt: torch.Tensor, steps: int, top
     H, Hkv, D = W.heads, W.kv_heads, W.head_dim
     Ks = [None] * W.layers
     Vs = [None] * W.layers
-    out_tokens, trace = [], []
+    out_tokens, trace, step_logits = [], [], []
 
     def forward(ids, pos0):
         n = ids.shape[1]
@@ -415,13 +460,16 @@ def tiny_llama_greedy(W: TinyLlamaWeights, prompt: torch.Tensor, steps: int, top
             x = rms_norm(h, L["ln2"], W.eps)
             h = h + F.linear(F.silu(F.linear(x, L["gate"])) * F.linear(x, L["up"]), L["down"])
         h = rms_norm(h, W.norm, W.eps)
-        return F.linear(h[:, -1:], W.lm_head)
+        return F.linear(h, W.lm_head)[:, -1:]               # logits of every position, as the reference computes them
 
     logit = forward(prompt, 0)
+    step_logits.append(logit[0, -1].clone())
     tok = logit.argmax(-1)
     out_tokens.append(int(tok))
     for s in range(steps - 1):
         logit = forward(tok.view(1, 1), P + s)
+        step_logits.append(logit[0, -1].clone())
         tok = logit.argmax(-1)
         out_tokens.append(int(tok))
-    return (out_tokens, trace) if return_trace else out_tokens
+    res = (out_tokens,) + ((trace,) if return_trace else ()) + ((torch.stack(step_logits),) if return_logits else ())
+    return res if len(res) > 1 else out_tokens

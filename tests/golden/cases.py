@@ -43,4 +43,7 @@ ATTN_CASES = [
     ("f16_gqa8_d128", 15, 1, 16, 2, 128, 515, 128, torch.float16, 8),
     ("f32_k_ge_n", 16, 1, 4, 4, 64, 20, 128, torch.float32, 0),
     ("f16_mha_d64", 17, 1, 4, 4, 64, 777, 48, torch.float16, 4),
+    # the single-layer benchmark configuration verbatim: Llama-2-7B attention shape, context 32768,
+    # 64 planted keys 3*q/|q| + N(0,0.1), top_k 256 (per-q-head sets, as the reference selects)
+    ("cfg2_f16_mha_32k", 2, 1, 32, 32, 128, 32768, 256, torch.float16, 64),
 ]

@@ -172,26 +172,39 @@ def gen_tiny_model(lt, mod, outdir):
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, W.vocab, (1, 2048), generator=g)
     steps = 32
-    toks, sets = [], []
+    toks, sets, sets2, logits = [], [], [], []
+
+    def sets_of(layer):
+        pd = model.model.layers[layer].self_attn.pos_dict
+        return torch.nonzero(pd[0, :, 0, :])[:, 1].view(W.heads, -1).to(torch.int32)
+
     with torch.no_grad():
         cache = DynamicCache()
         out = model(prompt, past_key_values=cache, use_cache=True)
+        logits.append(out.logits[0, -1].clone())
         tok = out.logits[:, -1:].argmax(-1)
         toks.append(int(tok))
         for s in range(steps - 1):
             out = model(tok.view(1, 1), past_key_values=cache, use_cache=True)
-            pd = model.model.layers[3].self_attn.pos_dict
-            sets.append(torch.nonzero(pd[0, :, 0, :])[:, 1].view(W.heads, -1).to(torch.int32))
+            sets2.append(sets_of(2))
+            sets.append(sets_of(3))
+            logits.append(out.logits[0, -1].clone())
             tok = out.logits[:, -1:].argmax(-1)
             toks.append(int(tok))
     with torch.no_grad():
-        toks2, trace = O.tiny_llama_greedy(W, prompt, steps, 128, 2, 3, return_trace=True)
+        toks2, trace, logits2 = O.tiny_llama_greedy(W, prompt, steps, 128, 2, 3, return_trace=True, return_logits=True)
     assert toks2 == toks, (toks, toks2)
-    l3 = [t[2] for t in trace if t[1] == 3]
-    for a, b in zip(sets, l3):
-        assert torch.equal(a, torch.sort(b[0, :, 0, :], dim=-1).values.to(torch.int32))
+    assert torch.equal(logits2, torch.stack(logits)), "the restatement's per-step logits differ from the reference model's"
+    for layer, got in ((2, sets2), (3, sets)):
+        mine = [t[2] for t in trace if t[1] == layer]
+        assert len(mine) == len(got)
+        for a, b in zip(got, mine):
+            assert torch.equal(a, torch.sort(b[0, :, 0, :], dim=-1).values.to(torch.int32))
+    # tokens, the last-position logits of every step (the prefill's first) and the sets selected at
+    # layers 2 and 3 in every decode step, each sorted by position
     np.savez_compressed(os.path.join(outdir, "tiny_llama_cfg1.npz"), prompt_seed=0, tokens=np.array(toks, np.int64),
-                        layer3_sets=torch.stack(sets).numpy())
+                        layer3_sets=torch.stack(sets).numpy(), layer2_sets=torch.stack(sets2).numpy(),
+                        logits=torch.stack(logits).numpy())
     print("tiny model ok; tokens", toks)
 
 

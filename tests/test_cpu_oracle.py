@@ -41,12 +41,15 @@ def test_oracle_reproduces_reference_tiny_model():
     g = torch.Generator().manual_seed(int(z["prompt_seed"]))
     prompt = torch.randint(0, W.vocab, (1, 2048), generator=g)
     with torch.no_grad():
-        toks, trace = O.tiny_llama_greedy(W, prompt, 8, 128, 2, 3, return_trace=True)
+        toks, trace, logits = O.tiny_llama_greedy(W, prompt, 8, 128, 2, 3, return_trace=True, return_logits=True)
     assert toks == z["tokens"][:8].tolist()
-    l3 = [t[2] for t in trace if t[1] == 3]
-    for step, got in enumerate(l3):
-        want = torch.from_numpy(z["layer3_sets"][step])
-        assert torch.equal(torch.sort(got[0, :, 0, :], dim=-1).values.to(torch.int32), want)
+    assert torch.equal(logits, torch.from_numpy(z["logits"][:8])), "last-position logits of every step, bit for bit"
+    for layer, key in ((2, "layer2_sets"), (3, "layer3_sets")):
+        mine = [t[2] for t in trace if t[1] == layer]
+        assert len(mine) == 7
+        for step, got in enumerate(mine):
+            want = torch.from_numpy(z[key][step])
+            assert torch.equal(torch.sort(got[0, :, 0, :], dim=-1).values.to(torch.int32), want)
 
 
 def test_gathered_attention_equals_masked_dense():

@@ -161,3 +161,98 @@ def test_sharded_exchange_two_gloo_ranks(tmp_path):
         assert r["sp_ok"], "merged sparse-layer output differs from the unsharded oracle"
     assert torch.equal(res[0]["sel"], res[1]["sel"]), "ranks disagree on the selected set"
     assert res[0]["owned"] + res[1]["owned"] == 2 * 24, "every selected position has exactly one owner"
+
+
+def _leaving_worker(rank, world, port, result_dir):
+    """Rank 1 leaves between steps; rank 0 learns of it on the host before its next launch, and — when it
+    skips that check — its next collective ends with an error instead of hanging."""
+    import datetime
+    import time
+
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from tidaldecode_b200.sharded import GroupHealth, RankLost, ShardedDecodeAttention, ShardPlan
+    from tests.helpers import make_qkv
+
+    store = dist.distributed_c10d._get_default_store()
+    health = GroupHealth(store, rank, world)
+    B, Hq, Hkv, D, N, k = 1, 4, 2, 64, 90, 8
+    q, K, V = make_qkv(3, B, Hq, Hkv, D, N, torch.float32)
+    plan = ShardPlan.contiguous(N, world)
+    lo, hi = plan.range_of(rank)
+    n = hi - lo
+    pool = torch.zeros(B * n, 2, 1, Hkv, D)
+    pool[:, 0, 0] = K[:, :, lo:hi].permute(0, 2, 1, 3).reshape(B * n, Hkv, D)
+    pool[:, 1, 0] = V[:, :, lo:hi].permute(0, 2, 1, 3).reshape(B * n, Hkv, D)
+    sh = ShardedDecodeAttention(B, Hq, Hkv, D, torch.float32, plan, rank, k, "sum", device="cpu", ops=_OracleOps, health=health)
+    qd = q[:, :, 0].contiguous()
+    sh.selection_layer(qd, pool, pages_per_seq=n)              # step 0: everybody is there
+    sh.sparse_layer(qd, pool, pages_per_seq=n)
+    if rank == 1:
+        health.leave()                                         # between steps, nothing in flight
+        dist.destroy_process_group()
+        return
+    res = dict(noticed=False, collective_failed=False, seconds=None)
+    deadline = time.time() + 20
+    while time.time() < deadline:
+        try:
+            health.check()
+            time.sleep(0.05)
+        except RankLost:
+            res["noticed"] = True
+            break
+    try:
+        sh.selection_layer(qd, pool, pages_per_seq=n)          # with the check in place the launch never happens
+    except RankLost:
+        res["raised_before_launch"] = True
+    sh.health = None                                           # a caller without the check: the collective must fail, not hang
+    t0 = time.time()
+    try:
+        sh.selection_layer(qd, pool, pages_per_seq=n)
+    except RankLost:
+        raise
+    except Exception as e:                                     # gloo: peer closed the connection, or the group timeout
+        res["collective_failed"] = True
+        res["error"] = type(e).__name__
+    res["seconds"] = time.time() - t0
+    torch.save(res, os.path.join(result_dir, "r0.pt"))
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+def test_rank_leaving_between_steps_is_noticed_on_the_host(tmp_path):
+    world = 2
+    port = 29300 + (os.getpid() % 2000)
+    mp.spawn(_leaving_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    res = torch.load(tmp_path / "r0.pt")
+    assert res["noticed"] and res.get("raised_before_launch"), res
+    assert res["collective_failed"], res
+    assert res["seconds"] < 30, res
+
+
+def test_peer_exchange_arrival_accounting_is_independent_of_payload():
+    """The arrivals a rank expects per exchange follow from the slot size alone, so exchanges of different
+    payloads (selection layers send partials and candidates, sparse layers only partials) can follow each
+    other in any order on one set of buffers: a model of the counters over sel, sparse, sparse, sel, ..."""
+    from tidaldecode_b200 import _lib as L
+    from tidaldecode_b200.sharded import pack_layout
+
+    lay = pack_layout(4, 32, 128, 4 * 32, 128)                   # per-head candidate rows: the payloads differ most
+    slot = (lay["total"] + 3) // 4 * 4 * 4
+    ctas = L.lib.tidal_peer_exchange_ctas(slot)
+    assert 1 <= ctas <= 32
+    assert L.lib.tidal_peer_exchange_ctas(15) == L.ERR_ARG
+    world = 4
+    count = [[0] * world for _ in range(2)]                      # one rank's counters [parity][source rank]
+    epoch = 0
+    for payload in ("sel", "sparse", "sparse", "sel", "sparse", "sel", "sel", "sparse", "sparse", "sparse"):
+        e = epoch + 1
+        par = e & 1
+        target = ((e + 1) // 2) * ctas                           # what the kernel waits for
+        for r in range(world):
+            count[par][r] += ctas                                # every CTA of every rank arrives once, whatever it carried
+        assert all(c == target for c in count[par]), (payload, e, count, target)
+        epoch = e

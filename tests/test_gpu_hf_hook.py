@@ -25,17 +25,21 @@ def _hf_model(W, dtype):
     return m.to(dtype).cuda()
 
 
-def _greedy(model, prompt, steps):
+def _greedy(model, prompt, steps, logits_out=None):
     from transformers.cache_utils import DynamicCache
 
     toks = []
     with torch.inference_mode():
         cache = DynamicCache()
         out = model(prompt, past_key_values=cache, use_cache=True)
+        if logits_out is not None:
+            logits_out.append(out.logits[0, -1].float().cpu())
         tok = out.logits[:, -1:].argmax(-1)
         toks.append(int(tok))
         for _ in range(steps - 1):
             out = model(tok.view(1, 1), past_key_values=cache, use_cache=True)
+            if logits_out is not None:
+                logits_out.append(out.logits[0, -1].float().cpu())
             tok = out.logits[:, -1:].argmax(-1)
             toks.append(int(tok))
     return toks
@@ -52,8 +56,12 @@ def test_enable_tidal_on_hf_llama_matches_reference_tokens():
     enable_tidal(model, attn_type="tidal", top_k=128, sparse_layer_start=2, correction_layer=3, max_seq_len=2048 + 64)
     attn = model.model.layers[0].self_attn
     assert hasattr(attn, "flash_forward")                       # the original forward is kept (modify_llama.py:366)
-    toks = _greedy(model, prompt, 32)
+    step_logits = []
+    toks = _greedy(model, prompt, 32, step_logits)
     assert toks == z["tokens"].tolist()
+    want_logits = torch.from_numpy(z["logits"])
+    err = (torch.stack(step_logits) - want_logits).abs().max().item()
+    assert torch.allclose(torch.stack(step_logits), want_logits, rtol=1e-4, atol=1e-5), f"per-step logits differ by {err:.3e}"
     c = model._tidal_state.controller
     assert c.workspace.status() == 0
     sets = torch.sort(c.topk_dindices_buffer[0].cpu(), dim=-1).values

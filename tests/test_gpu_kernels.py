@@ -644,3 +644,87 @@ def test_prefill_rejects_what_it_does_not_compute(T):
         T.prefill(q, pool, table, 4)
     with pytest.raises(RuntimeError, match="kv_len"):
         T.prefill(q.half(), pool.half(), table, 3)
+
+
+def test_prefill_bad_page_entry_is_flagged_not_followed(T):
+    """A page-table entry outside the pool reads as zeros and sets TIDAL_DEV_BAD_INDEX; nothing is fetched
+    through it (the decode kernels treat their lists the same way)."""
+    from tidaldecode_b200 import _lib as L
+
+    g = torch.Generator().manual_seed(3)
+    n, Hq, Hkv, D = 200, 4, 2, 128
+    pool = torch.randn(n, 2, 1, Hkv, D, generator=g).half()
+    q = torch.randn(n, Hq, D, generator=g).half()
+    table = torch.arange(n, dtype=torch.int32)
+    bad = table.clone()
+    bad[57] = n + 1000
+    bad[58] = -4
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = T.prefill(q.cuda(), pool.cuda(), bad.cuda(), n, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == L.DEV_BAD_INDEX
+    # tokens 57 and 58 read as zero rows: logit 0 and value 0 for the rows that see them
+    K = pool[:, 0, 0].clone()
+    V = pool[:, 1, 0].clone()
+    K[57:59] = 0
+    V[57:59] = 0
+    assert_close(got, O.causal_prefill(q, K, V, True), torch.float16, "prefill with two unreadable pages")
+
+
+def test_rope_append_out_of_place_queries(T):
+    """q_src: the queries are read from one buffer and written, rotated, to another; the source survives."""
+    g = torch.Generator().manual_seed(8)
+    B, Hq, Hkv, D = 3, 8, 2, 128
+    q = torch.randn(B, Hq, D, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(B, Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn(B, Hkv, D, generator=g).to(torch.bfloat16).cuda()
+    pool_a = torch.zeros(B * 8, 2, 1, Hkv, D, dtype=torch.bfloat16, device="cuda")
+    pool_b = torch.zeros_like(pool_a)
+    q_in_place, k_in_place = q.clone(), k.clone()
+    T.rope_append(q_in_place, k_in_place, v, pool_a, batch=B, pos0=5, rope_theta=5e5, rope_mode=2)
+    q_out, q_keep, k_keep = torch.zeros_like(q), q.clone(), k.clone()
+    T.rope_append(q_out, k_keep, v, pool_b, batch=B, pos0=5, rope_theta=5e5, rope_mode=2, q_src=q_keep, rotate_k_in_place=False)
+    torch.cuda.synchronize()
+    assert torch.equal(q_out, q_in_place) and torch.equal(pool_a, pool_b)
+    assert torch.equal(q_keep, q) and torch.equal(k_keep, k), "sources must be left as they were"
+
+
+def test_peer_exchange_wait_runs_out_and_reset_recovers(T):
+    """Rank 0 of a two-rank exchange whose peer never calls: the bounded wait runs out, the status word says
+    so and the kernel returns (the context stays usable).  After tidal_peer_exchange_reset the same buffers
+    carry a complete exchange again — the missing rank's block and arrivals are written by the host before
+    the launch, so no kernel ever waits on another one."""
+    from tidaldecode_b200 import _lib as L
+
+    dev = torch.device("cuda", 0)
+    words = 4 * 8 * (64 + 2)                                     # m, l, o of 4 x 8 heads x 64
+    px = T.PeerExchange.loopback(words * 4, 2, dev, wait_limit=2000)
+    send = torch.arange(words, dtype=torch.float32, device=dev)
+    recv = torch.zeros(2, words, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    px.all_gather(send, recv, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == L.DEV_WAIT_TIMEOUT
+    assert torch.equal(recv[0], send), "its own block still arrives"
+    # without a reset the counters stay skewed: the next exchange of this parity would pass on stale arrivals
+    px.reset()
+    status.zero_()
+    torch.cuda.synchronize()
+    assert int(px.counters.abs().sum()) == 0 and int(px.state.abs().sum()) == 0
+    # the peer's part of exchange 1 (parity 1), as its kernel would have left it: block in slot [1][1], arrivals
+    other = torch.full((words,), 7.0, dtype=torch.float32, device=dev)
+    px.stage[1, 1].copy_(other.view(torch.uint8))
+    px.counters[1, 1] = px.ctas
+    px.all_gather(send, recv, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(recv[0], send) and torch.equal(recv[1], other)
+    # and exchange 2 (parity 0) with another payload size on the same buffers
+    half = words // 2 // 4 * 4
+    px.stage[0, 1, : half * 4].copy_(other[:half].view(torch.uint8))
+    px.counters[0, 1] = px.ctas
+    recv.zero_()
+    px.all_gather(send, recv, nbytes=half * 4, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(recv[0, :half], send[:half]) and torch.equal(recv[1, :half], other[:half])

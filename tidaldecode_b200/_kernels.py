@@ -42,17 +42,46 @@ def _check_layout(layout: int) -> None:
                            "tidal/utils/controller.py:40)")
 
 
-_ws_cache = {}
+_ws_cache = {}          # device index -> the Workspace per-token calls on that device use
 
 
-def _workspace(device: torch.device, batch: int, hq: int, d: int, rows: int, n: int) -> _ops.Workspace:
-    """One workspace per (device, geometry class), grown on demand, kept for the process."""
-    key = (device.index, hq, d)
-    ws = _ws_cache.get(key)
-    if ws is None or ws.geometry[0] < batch or ws.geometry[3] < rows or ws.geometry[4] < n:
-        g = ws.geometry if ws is not None else (1, hq, d, 1, 1)
-        ws = _ops.Workspace(max(batch, g[0]), hq, d, max(rows, g[3]), max(n, g[4]), device=device)
-        _ws_cache[key] = ws
+def _fits(ws: _ops.Workspace, batch: int, hq: int, d: int, rows: int, n: int) -> bool:
+    g = ws.geometry
+    return batch * hq * d <= g[0] * g[1] * g[2] and batch * hq <= g[0] * g[1] and rows <= g[3] and n <= g[4]
+
+
+def adopt_workspace(ws: _ops.Workspace) -> None:
+    """Let `forward` and `topk_filtering` on ws's device use a workspace the caller owns already
+    (an InferenceController's) instead of reserving a second one."""
+    _ws_cache[ws.buf.device.index] = ws
+
+
+def reserve_workspace(device, num_qo_heads: int, head_dim: int, rows: int, n: int, batch: int = 1) -> _ops.Workspace:
+    """Make sure scratch for this geometry exists on `device`: split-KV partials for `batch` x `num_qo_heads` x
+    `head_dim`, top-k lists for `rows` rows of up to `n` scores.  This is the only place of this module that
+    allocates device memory, and only when what is there does not fit; `begin_forward` calls it, as the
+    reference's handler allocates in BeginForward (decode_handler.cuh:104-117), so that the per-token calls
+    find everything in place."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    ws = _ws_cache.get(device.index)
+    if ws is None or not _fits(ws, batch, num_qo_heads, head_dim, rows, n):
+        g = ws.geometry if ws is not None else (1, 1, 1, 1, 1)
+        ws = _ops.Workspace(max(batch, g[0]), max(num_qo_heads, g[1]), max(head_dim, g[2]), max(rows, g[3]), max(n, g[4]),
+                            device=device)
+        _ws_cache[device.index] = ws
+    return ws
+
+
+def _reserved(device: torch.device, batch: int, hq: int, d: int, rows: int, n: int, first_use_reserves: bool = False) -> _ops.Workspace:
+    """The scratch for a per-token call; never allocates once a workspace exists on the device."""
+    ws = _ws_cache.get(device.index)
+    if ws is None and first_use_reserves:
+        return reserve_workspace(device, hq, d, rows, n, batch)
+    _check(ws is not None and _fits(ws, batch, hq, d, rows, n),
+           f"no scratch reserved for {batch} x {hq} heads x {d}, {rows} rows of {n} scores on {device}: call begin_forward "
+           "(or tidaldecode_b200._kernels.reserve_workspace) with this geometry first; per-token calls do not allocate")
     return ws
 
 
@@ -128,7 +157,9 @@ def topk_filtering(estimated_value: torch.Tensor, estimated_indices: torch.Tenso
         _check(estimated_indices.is_contiguous(), "estimated_indices must be contiguous or row-broadcast")
         _check(estimated_indices.shape[1] == width, "value and indices disagree on columns")
         in_idx = estimated_indices
-    ws = _workspace(val.device, 1, 1, 64, rows, width)
+    # scratch: reserved by the first call for this row count and width (the reference's callers pass rows of
+    # max_seq_len columns, so the width never changes afterwards); later calls find it and allocate nothing
+    ws = _reserved(val.device, 1, 1, 64, rows, width, first_use_reserves=True)
     out_val = d_out if d_out.dtype == torch.float32 else torch.empty(d_out.shape, dtype=torch.float32, device=d_out.device)
     _ops.topk(val, int(page_budget), ws, n=n, in_idx=in_idx, out_idx=indices_out, out_val=out_val)
     if out_val is not d_out:
@@ -195,14 +226,29 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
         self._layout = layout
         self._begun = False
         self._geom = None
+        self._ws = None
+        self._max_list = 4096          # shortest list the scratch is sized for
 
     def begin_forward(self, indptr: torch.Tensor, num_qo_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                      empty_data: torch.Tensor) -> None:
-        """Plans nothing on the host and allocates nothing (the reference allocates and
-        uploads a partition plan here: decode_handler.cuh:73-121); it only records the geometry."""
+                      empty_data: torch.Tensor, max_pages: int = 0, device=None) -> None:
+        """Records the geometry and makes sure the scratch for it exists, so that `forward` allocates
+        nothing (the reference allocates two buffers and uploads a partition plan here on every call:
+        decode_handler.cuh:73-121; this allocates only when the geometry outgrows what is reserved).
+        `indptr` ([0, pages listed per head], as the reference passes it) gives the list length when it
+        is a host tensor or a list; a device tensor is not read back (no sync) and `max_pages` — or the
+        longest list seen so far — is used instead."""
         if num_qo_heads % num_kv_heads != 0:
             raise ValueError(f"num_qo_heads {num_qo_heads} is not a multiple of num_kv_heads {num_kv_heads}")
         self._geom = (int(num_qo_heads), int(num_kv_heads), int(head_dim), int(page_size), empty_data.dtype)
+        n = int(max_pages)
+        if indptr is not None and not (isinstance(indptr, torch.Tensor) and indptr.is_cuda):
+            ip = [int(x) for x in (indptr.tolist() if isinstance(indptr, torch.Tensor) else indptr)]
+            if len(ip) >= 2:
+                n = max(n, max(b - a for a, b in zip(ip[:-1], ip[1:])))
+        self._max_list = max(self._max_list, n)
+        dev = device if device is not None else (indptr.device if isinstance(indptr, torch.Tensor) and indptr.is_cuda
+                                                 else torch.device("cuda", torch.cuda.current_device()))
+        self._ws = reserve_workspace(dev, num_qo_heads, head_dim, num_qo_heads, self._max_list + 1)
         self._begun = True
 
     def end_forward(self) -> None:
@@ -235,7 +281,7 @@ class BatchDecodeWithPagedKVCachePyTorchWrapper:
             else:
                 tmp = torch.empty(1, Hq, n + 1, dtype=torch.float32, device=q.device)
                 scores = tmp
-        ws = _workspace(q.device, 1, Hq, D, Hq, max(n + 1, 1))
+        ws = _reserved(q.device, 1, Hq, D, 1, 1)          # the attention call needs the split-KV partials only
         _ops.decode_attention(q, paged_kv_data, n + 1, ws, out=o, sel_idx=paged_kv_indices.view(1, Hq, n),
                               sel_physical=True, extra_page=int(paged_kv_last_page_idx), scores=scores)
         if tmp is not None:

@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather", "tidal_prefill",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_topk_static_status", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather", "tidal_peer_exchange_ctas", "tidal_peer_exchange_reset", "tidal_prefill",
 )
 
 
@@ -59,7 +59,7 @@ class RopeAppendArgs(C.Structure):
         ("rope_theta", C.c_float), ("rope_scale", C.c_float), ("rope_mode", C.c_int32), ("rotate_k_in_place", C.c_int32),
         ("batch", C.c_int32), ("tokens_per_seq", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32),
         ("head_dim", C.c_int32), ("page_size", C.c_int32), ("dtype", C.c_int32),
-        ("num_pages", C.c_int64), ("d_status", C.c_void_p),
+        ("num_pages", C.c_int64), ("d_status", C.c_void_p), ("d_q_src", C.c_void_p), ("kv_pos_base", C.c_int32),
     ]
 
 
@@ -82,6 +82,7 @@ class ExchangeArgs(C.Structure):
         ("rank", C.c_int32), ("world", C.c_int32),
         ("d_merge_out", C.c_void_p), ("merge_m_off", C.c_int64), ("merge_l_off", C.c_int64), ("merge_o_off", C.c_int64),
         ("merge_rows", C.c_int32), ("merge_head_dim", C.c_int32), ("merge_dtype", C.c_int32),
+        ("wait_limit", C.c_int32),
     ]
 
 
@@ -91,6 +92,7 @@ class PrefillArgs(C.Structure):
         ("kv_len", C.c_int64),
         ("n_q", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
         ("page_size", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32), ("sm_scale", C.c_float),
+        ("num_pages", C.c_int64),
     ]
 
 
@@ -122,6 +124,8 @@ def _load() -> C.CDLL:
     lib.tidal_topk.argtypes = [C.POINTER(TopkArgs), C.c_void_p, C.c_size_t, C.c_void_p]
     lib.tidal_topk_static.restype = C.c_int
     lib.tidal_topk_static.argtypes = [C.POINTER(TopkArgs), C.c_void_p, C.c_void_p]
+    lib.tidal_topk_static_status.restype = C.c_int
+    lib.tidal_topk_static_status.argtypes = [C.c_int, C.c_void_p]
     lib.tidal_rope_append.restype = C.c_int
     lib.tidal_rope_append.argtypes = [C.POINTER(RopeAppendArgs), C.c_void_p]
     lib.tidal_merge_partials.restype = C.c_int
@@ -138,6 +142,10 @@ def _load() -> C.CDLL:
     lib.tidal_decode_qkv.argtypes = [C.POINTER(LinearArgs), C.POINTER(RopeAppendArgs), C.c_void_p]
     lib.tidal_peer_all_gather.restype = C.c_int
     lib.tidal_peer_all_gather.argtypes = [C.POINTER(ExchangeArgs), C.c_void_p]
+    lib.tidal_peer_exchange_ctas.restype = C.c_int
+    lib.tidal_peer_exchange_ctas.argtypes = [C.c_int64]
+    lib.tidal_peer_exchange_reset.restype = C.c_int
+    lib.tidal_peer_exchange_reset.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     lib.tidal_prefill.restype = C.c_int
     lib.tidal_prefill.argtypes = [C.POINTER(PrefillArgs), C.c_void_p]
     return lib

@@ -755,8 +755,10 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     if (use_mma) p.PW = copy_bytes <= 2048 ? kMmaMaxProducers : 1;
     else p.PW = copy_bytes <= 512 ? kMaxProducerWarps : 1;
     const size_t part_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * D;
-    TIDAL_REQUIRE(plan.nchunks == 1 || cluster > 1 || L->part_o_off + part_need <= L->part_ml_off, TIDAL_ERR_WORKSPACE,
-                  "workspace was sized for a smaller batch/heads/head_dim than this call");
+    const size_t ml_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * 2;
+    TIDAL_REQUIRE(plan.nchunks == 1 || cluster > 1 ||
+                      (L->part_o_off + part_need <= L->part_ml_off && L->part_ml_off + ml_need <= L->hist_off),
+                  TIDAL_ERR_WORKSPACE, "workspace was sized for a smaller batch/heads/head_dim than this call");
 
     cudaStream_t st = (cudaStream_t)stream;
     int rc;

@@ -633,6 +633,8 @@ extern "C" int tidal_decode_qkv(const tidal_linear_args* a, const tidal_rope_app
                   TIDAL_ERR_ARG, "W must have (Hq + 2 Hkv) * D = %d rows, got %d", (r->num_qo_heads + 2 * r->num_kv_heads) * r->head_dim, a->N);
     TIDAL_REQUIRE(a->K % 16 == 0 && a->K >= 128, TIDAL_ERR_ARG, "K %d must be a multiple of 16, at least 128", a->K);
     TIDAL_REQUIRE(r->rope_mode >= 0 && r->rope_mode <= 2, TIDAL_ERR_ARG, "rope_mode must be 0, 1 or 2");
+    TIDAL_REQUIRE(r->kv_pos_base == 0 && r->d_q_src == nullptr, TIDAL_ERR_ARG,
+                  "tidal_decode_qkv writes whole-sequence pools and produces q itself: kv_pos_base must be 0, d_q_src NULL");
     TIDAL_REQUIRE(r->rope_mode == 0 || r->rope_scale > 0.f, TIDAL_ERR_ARG, "rope_scale must be positive");
     TIDAL_REQUIRE(r->rope_mode == 0 || r->d_inv_freq || r->rope_theta > 0.f, TIDAL_ERR_ARG, "rope_theta must be positive");
     TIDAL_REQUIRE(r->page_size >= 1 && r->num_pages >= 1, TIDAL_ERR_ARG, "bad page_size/num_pages");

@@ -13,7 +13,10 @@
 // Staging and counters are double-buffered by the parity of an exchange counter kept in device memory
 // and advanced by the last CTA to finish, so nothing is reset between exchanges: a rank can be at most
 // one exchange ahead of another, because it needs the other's arrivals to finish the one in between.
-// Every rank must call with the same byte count (the number of CTAs follows from it).
+// The number of CTAs follows from slot_bytes alone — a property of the buffers, not of the call — so
+// that the arrivals expected per exchange are the same whatever each exchange carries: calls that move
+// fewer bytes than a slot holds (a sparse layer sends only partials, a selection layer also its
+// candidates) may be mixed freely on one set of buffers.
 #include "common.cuh"
 
 namespace tidal {
@@ -21,7 +24,13 @@ namespace tidal {
 constexpr int kXchgThreads = 256;
 constexpr int kXchgMaxCtas = 32;
 constexpr int kXchgMaxWorld = 16;
-constexpr uint32_t kXchgSpinLimit = 1u << 22;
+constexpr uint32_t kXchgSpinLimit = 1u << 22;    // default wait limit (about half a second)
+
+// CTAs of every exchange on buffers with slots of slot_vec 16-byte vectors
+__host__ __device__ inline int exchange_ctas(int64_t slot_vec) {
+    int64_t c = (slot_vec + kXchgThreads - 1) / kXchgThreads;
+    return (int)(c < 1 ? 1 : (c > kXchgMaxCtas ? kXchgMaxCtas : c));
+}
 
 struct ExchangeParams {
     const uint4* send;
@@ -33,6 +42,7 @@ struct ExchangeParams {
     uint32_t* epoch;              // local: exchanges completed
     uint32_t* fin;                // local: CTAs of the current exchange that are done
     uint32_t* status;
+    uint32_t spin_limit;          // iterations a CTA polls for the other ranks before it gives up
     int rank, world;
     // optional merge of the ranks' softmax partials: fp32 word offsets of m [rows], l [rows], o [rows][D] in a block
     void* merge_out;
@@ -71,7 +81,7 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
     if ((int)threadIdx.x < p.world) {
         const uint32_t* c = &p.peer_count[p.rank][par * p.world + threadIdx.x];
         bool ok = false;
-        for (uint32_t it = 0; it < kXchgSpinLimit; ++it) {
+        for (uint32_t it = 0; it < p.spin_limit; ++it) {
             if ((int32_t)(ld_acquire_sys(c) - target) >= 0) {
                 ok = true;
                 break;
@@ -145,6 +155,7 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
                   "bytes (%lld) and slot_bytes (%lld) must be multiples of 16, bytes <= slot_bytes", (long long)a->bytes,
                   (long long)a->slot_bytes);
     TIDAL_REQUIRE((((uintptr_t)a->d_send | (uintptr_t)a->d_recv) & 15) == 0, TIDAL_ERR_ARG, "send and recv must be 16-byte aligned");
+    TIDAL_REQUIRE(a->wait_limit >= 0, TIDAL_ERR_ARG, "negative wait_limit");
     ExchangeParams p;
     p.send = (const uint4*)a->d_send;
     p.nvec = a->bytes / 16;
@@ -155,15 +166,28 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
     p.epoch = a->d_state;
     p.fin = a->d_state + 1;
     p.status = a->d_status;
+    p.spin_limit = a->wait_limit > 0 ? (uint32_t)a->wait_limit : kXchgSpinLimit;
     p.rank = a->rank;
     p.world = a->world;
     p.merge_out = a->d_merge_out;
     p.m_off = a->merge_m_off; p.l_off = a->merge_l_off; p.o_off = a->merge_o_off;
     p.merge_rows = a->merge_rows; p.merge_dim = a->merge_head_dim; p.merge_dtype = a->merge_dtype;
-    // (the CTA count follows from the byte count alone: every rank must use the same)
-    int64_t ctas = (p.nvec + kXchgThreads - 1) / kXchgThreads;
-    if (ctas > kXchgMaxCtas) ctas = kXchgMaxCtas;
+    // the CTA count follows from the slot size alone: the same for every call on these buffers, on every rank
+    const int ctas = exchange_ctas(p.slot_vec);
     TIDAL_CUDA_OK(launch_pdl(peer_all_gather_kernel, dim3((unsigned)ctas), dim3(kXchgThreads), 0, (cudaStream_t)stream, 1, p));
     count_launch();
+    return TIDAL_OK;
+}
+
+extern "C" int tidal_peer_exchange_ctas(int64_t slot_bytes) {
+    if (slot_bytes <= 0 || slot_bytes % 16) return TIDAL_ERR_ARG;
+    return exchange_ctas(slot_bytes / 16);
+}
+
+extern "C" int tidal_peer_exchange_reset(uint32_t* d_count, uint32_t* d_state, int world, void* stream) {
+    TIDAL_REQUIRE(d_count && d_state, TIDAL_ERR_ARG, "null pointer");
+    TIDAL_REQUIRE(world >= 2 && world <= kXchgMaxWorld, TIDAL_ERR_ARG, "bad world %d (2..%d ranks)", world, kXchgMaxWorld);
+    TIDAL_CUDA_OK(cudaMemsetAsync(d_count, 0, sizeof(uint32_t) * 2 * world, (cudaStream_t)stream));
+    TIDAL_CUDA_OK(cudaMemsetAsync(d_state, 0, sizeof(uint32_t) * 2, (cudaStream_t)stream));
     return TIDAL_OK;
 }

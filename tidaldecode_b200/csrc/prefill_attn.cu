@@ -36,6 +36,7 @@ struct PrefillParams {
     const int32_t* pages; // page ids of this sequence, in order
     uint32_t* status;
     int64_t kv_len;
+    int64_t num_pages;    // pages in the pool: a table entry outside [0, num_pages) is skipped (zero rows) and reported
     int n_q, Hq, Hkv, page_size;
     int causal;
     float scale_log2;     // softmax scale x log2(e)
@@ -195,6 +196,7 @@ __global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid
     const int my_c = tid % kChunks, my_r0 = tid / kChunks;
     const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
     const int64_t v_off = (int64_t)ps * row_elems;
+    bool bad_page = false;
     auto lookup_rows = [&](uint32_t t0, int64_t* off) {      // element offset of each of this thread's K rows, -1 past the end
 #pragma unroll
         for (int i = 0; i < kRowsPerThread; ++i) {
@@ -203,7 +205,9 @@ __global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid
             if (t < kv_len32) {
                 const uint32_t pi = ps == 1 ? t : t / ps;
                 const uint32_t slot = ps == 1 ? 0u : t - pi * ps;
-                off[i] = (((int64_t)p.pages[pi] * 2) * ps + slot) * row_elems;
+                const int64_t page = p.pages[pi];
+                if (page >= 0 && page < p.num_pages) off[i] = ((page * 2) * ps + slot) * row_elems;
+                else bad_page = true;                    // reads as a row past the end; reported once at the exit
             }
         }
     };
@@ -396,6 +400,7 @@ __global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid
             }
         }
     }
+    if (bad_page && p.status) atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tc_dealloc(tmem, kTmemCols);
@@ -436,6 +441,7 @@ extern "C" int tidal_prefill(const tidal_prefill_args* a, void* stream) {
                   (long long)a->kv_len, a->n_q);
     TIDAL_REQUIRE((((uintptr_t)a->d_q | (uintptr_t)a->d_o | (uintptr_t)a->d_kv) & 15) == 0, TIDAL_ERR_ARG,
                   "q, o and the pool must be 16-byte aligned");
+    TIDAL_REQUIRE(a->num_pages >= 1, TIDAL_ERR_ARG, "num_pages (pages in the pool) must be given");
     PrefillParams p;
     p.q = a->d_q;
     p.o = a->d_o;
@@ -443,6 +449,7 @@ extern "C" int tidal_prefill(const tidal_prefill_args* a, void* stream) {
     p.pages = a->d_page_table;
     p.status = a->d_status;
     p.kv_len = a->kv_len;
+    p.num_pages = a->num_pages;
     p.n_q = a->n_q;
     p.Hq = a->num_qo_heads;
     p.Hkv = a->num_kv_heads;

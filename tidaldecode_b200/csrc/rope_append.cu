@@ -8,6 +8,7 @@ namespace tidal {
 
 struct RopeParams {
     void* q;
+    const void* q_src;   // rows of q are read from here (q itself when rotating in place)
     void* k;
     const void* v;
     char* kv;
@@ -15,6 +16,7 @@ struct RopeParams {
     int64_t pt_stride;
     const int32_t* pos0_dev;
     int32_t pos0;
+    int32_t kv_pos_base;   // position held by the pool's first slot of every sequence (a shard of the context)
     const float* inv_freq;
     float theta, scale;
     int32_t rope_mode, rotate_k_in_place;
@@ -76,9 +78,11 @@ __global__ void rope_append_kernel(const RopeParams p) {
     char* kdst = nullptr;
     size_t plane = 0;
     if (p.kv) {
-        const int pg = tpos / p.page_size;
-        const int entry = tpos - pg * p.page_size;
-        int64_t page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
+        const int spos = tpos - p.kv_pos_base;           // slot index within the sequence's part of the pool
+        const int pg = spos / p.page_size;
+        const int entry = spos - pg * p.page_size;
+        int64_t page = -1;
+        if (spos >= 0) page = p.page_table ? p.page_table[(size_t)b * p.pt_stride + pg] : (int64_t)b * p.pt_stride + pg;
         if (page < 0 || page >= p.num_pages) {
             if (threadIdx.x == 0 && p.status) atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
         } else {
@@ -100,7 +104,7 @@ __global__ void rope_append_kernel(const RopeParams p) {
         const bool is_q = idx < nq;
         const int j = is_q ? idx : idx - nq;
         const int h = j / VPR, d0 = (j % VPR) * VEC;
-        const T* row = is_q ? reinterpret_cast<const T*>(p.q) + ((size_t)tok * p.Hq + h) * D
+        const T* row = is_q ? reinterpret_cast<const T*>(p.q_src) + ((size_t)tok * p.Hq + h) * D
                             : reinterpret_cast<const T*>(p.k) + ((size_t)tok * p.Hkv + h) * D;
         if (p.rope_mode != 0) {
             rotate_vec<T, D>(row, d0, cs, p.rope_mode, res[cnt]);
@@ -118,7 +122,7 @@ __global__ void rope_append_kernel(const RopeParams p) {
         const int h = j / VPR, d0 = (j % VPR) * VEC;
         const uint4 packed = V::from_float(res[c]);
         if (is_q) {
-            if (p.rope_mode != 0)
+            if (p.rope_mode != 0 || p.q_src != p.q)
                 *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.q) + ((size_t)tok * p.Hq + h) * D + d0) = packed;
         } else {
             if (p.rope_mode != 0 && p.rotate_k_in_place)
@@ -162,8 +166,9 @@ extern "C" int tidal_rope_append(const tidal_rope_append_args* a, void* stream) 
     TIDAL_REQUIRE(a->d_kv == nullptr || a->d_v != nullptr, TIDAL_ERR_ARG, "appending needs v");
     TIDAL_REQUIRE(a->rope_mode == 0 || a->rope_scale > 0.f, TIDAL_ERR_ARG, "rope_scale must be positive");
     TIDAL_REQUIRE(a->rope_mode == 0 || a->d_inv_freq || a->rope_theta > 0.f, TIDAL_ERR_ARG, "rope_theta must be positive");
-    TIDAL_REQUIRE((((uintptr_t)a->d_q | (uintptr_t)a->d_k | (uintptr_t)a->d_v | (uintptr_t)a->d_kv) & 15) == 0, TIDAL_ERR_ARG,
-                  "q, k, v and kv must be 16-byte aligned");
+    TIDAL_REQUIRE((((uintptr_t)a->d_q | (uintptr_t)a->d_k | (uintptr_t)a->d_v | (uintptr_t)a->d_kv | (uintptr_t)a->d_q_src) & 15) == 0,
+                  TIDAL_ERR_ARG, "q, q_src, k, v and kv must be 16-byte aligned");
+    TIDAL_REQUIRE(a->d_q_src == nullptr || a->d_q != nullptr, TIDAL_ERR_ARG, "q_src needs q as its destination");
     const int es = a->dtype == TIDAL_DTYPE_F32 ? 4 : 2;
     const int vec = 16 / es;
     const int vpr = a->head_dim / vec;
@@ -174,9 +179,9 @@ extern "C" int tidal_rope_append(const tidal_rope_append_args* a, void* stream) 
     TIDAL_REQUIRE(threads <= 1024, TIDAL_ERR_ARG, "too many heads for one CTA per token (%d vectors)", items);
 
     RopeParams p;
-    p.q = a->d_q; p.k = a->d_k; p.v = a->d_v; p.kv = (char*)a->d_kv;
+    p.q = a->d_q; p.q_src = a->d_q_src ? a->d_q_src : a->d_q; p.k = a->d_k; p.v = a->d_v; p.kv = (char*)a->d_kv;
     p.page_table = a->d_page_table; p.pt_stride = a->page_table_stride;
-    p.pos0_dev = a->d_pos0; p.pos0 = a->pos0; p.inv_freq = a->d_inv_freq;
+    p.pos0_dev = a->d_pos0; p.pos0 = a->pos0; p.kv_pos_base = a->kv_pos_base; p.inv_freq = a->d_inv_freq;
     p.theta = a->rope_theta; p.scale = a->rope_scale;
     p.rope_mode = a->rope_mode; p.rotate_k_in_place = a->rotate_k_in_place;
     p.B = a->batch; p.tokens_per_seq = a->tokens_per_seq; p.Hq = a->num_qo_heads; p.Hkv = a->num_kv_heads;

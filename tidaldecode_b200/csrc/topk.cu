@@ -249,7 +249,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
     pdl_launch_dependents();
     const int row = blockIdx.x;
     const int t = threadIdx.x;
-    uint32_t* st = p.row_state + (size_t)row * 8;
+    uint32_t* st = FUSED ? nullptr : p.row_state + (size_t)row * 8;     // the fused form keeps its counters in shared memory
     const float* srow = p.scores + (size_t)row * p.row_stride;
     const uint32_t k = (uint32_t)p.k;
     int32_t* out_idx = p.out_idx + (size_t)row * p.out_stride;
@@ -752,11 +752,9 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
         // one cluster per row; 8 CTAs unless the row is short
         int cs = 8;
         while (cs > 1 && a->n < (int64_t)cs * 2048) cs >>= 1;
-        static bool attr_set = false;
-        if (!attr_set) {
-            TIDAL_CUDA_OK(cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kClusterSmem));
-            attr_set = true;
-        }
+        // per launch, like every other kernel here: the attribute belongs to the current device, and a process
+        // may drive several
+        TIDAL_CUDA_OK(cudaFuncSetAttribute(topk_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kClusterSmem));
         TIDAL_CUDA_OK(launch_pdl(topk_cluster_kernel, dim3((unsigned)(a->rows * cs)), dim3(kTopkThreads), kClusterSmem, st,
                                  (unsigned)cs, p));
         count_launch();
@@ -840,6 +838,9 @@ extern "C" int tidal_topk_static(const tidal_topk_args* a, uint32_t* d_status, v
     TIDAL_REQUIRE(a->d_in_idx == nullptr || a->in_idx_stride == 0 || a->in_idx_stride >= a->n, TIDAL_ERR_ARG,
                   "in_idx_stride must be 0 (shared row) or at least n");
     TIDAL_REQUIRE(a->d_hist == nullptr, TIDAL_ERR_ARG, "tidal_topk_static builds its own histogram: d_hist must be NULL");
+    TIDAL_REQUIRE(a->seg_len == 0 && a->seg_stride == 0, TIDAL_ERR_ARG,
+                  "tidal_topk_static takes contiguous rows only: seg_len and seg_stride must be 0");
+    TIDAL_REQUIRE(a->d_row_len == nullptr, TIDAL_ERR_ARG, "tidal_topk_static takes the row length from n: d_row_len must be NULL");
     const int k = (int64_t)a->k < a->n ? a->k : (int)a->n;
     TIDAL_REQUIRE(k <= kStaticMaxK || (int64_t)a->k >= a->n, TIDAL_ERR_ARG, "tidal_topk_static takes k of at most %d, got %d",
                   kStaticMaxK, k);
@@ -864,4 +865,16 @@ extern "C" int tidal_topk_static(const tidal_topk_args* a, uint32_t* d_status, v
     TIDAL_CUDA_OK(cudaGetLastError());
     count_launch();
     return TIDAL_OK;
+}
+
+extern "C" int tidal_topk_static_status(int clear, void* stream) {
+    StaticTopkScratch* sc = nullptr;
+    const int rc = static_scratch_for_current_device(&sc);
+    if (rc != TIDAL_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t bits = 0;
+    TIDAL_CUDA_OK(cudaMemcpyAsync(&bits, &sc->status[0], sizeof(bits), cudaMemcpyDeviceToHost, st));
+    TIDAL_CUDA_OK(cudaStreamSynchronize(st));
+    if (clear && bits) TIDAL_CUDA_OK(cudaMemsetAsync(&sc->status[0], 0, sizeof(uint32_t), st));
+    return (int)(bits & 0x7fffffffu);
 }

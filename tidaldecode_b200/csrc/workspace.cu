@@ -33,7 +33,8 @@ const WsLayout* find_ws(const void* d_ws) {
 
 using namespace tidal;
 
-extern "C" int tidal_version(void) { return 101; }   // 101: tidal_decode_linear, tidal_decode_qkv
+extern "C" int tidal_version(void) { return 102; }   // 102: q_src in tidal_rope_append_args, num_pages in tidal_prefill_args,
+                                                     //      wait_limit in tidal_exchange_args, reset / status entry points
 
 extern "C" const char* tidal_last_error(void) { return g_err; }
 

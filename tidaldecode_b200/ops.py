@@ -231,9 +231,13 @@ def rope_append(
     inv_freq: Optional[torch.Tensor] = None,
     rotate_k_in_place: bool = True,
     status: Optional[torch.Tensor] = None,
+    q_src: Optional[torch.Tensor] = None,         # [n_tokens, Hq, D]: read the queries here, write them rotated to q
+    kv_pos_base: int = 0,                         # position held by the pool's first slot per sequence (a shard's lo)
 ) -> None:
     """RoPE on q and k fused with the KV append; see tidal_rope_append in include/tidal_b200.h."""
-    _need_cuda(q, k, v, kv, pos0_dev, page_table, inv_freq, status)
+    _need_cuda(q, k, v, kv, pos0_dev, page_table, inv_freq, status, q_src)
+    if q_src is not None and (q is None or q_src.shape != q.shape or q_src.dtype != q.dtype):
+        raise RuntimeError("q_src must have the shape and dtype of q")
     if k.dim() != 3:
         raise RuntimeError("k must be [n_tokens, Hkv, D]")
     n_tokens, Hkv, D = k.shape
@@ -255,6 +259,8 @@ def rope_append(
     a.num_pages = kv.shape[0] if kv is not None else 1
     a.dtype = _dtype_code(k)
     a.d_status = _ptr(status)
+    a.d_q_src = _ptr(q_src)
+    a.kv_pos_base = int(kv_pos_base)
     with torch.cuda.device(k.device):
         check(lib.tidal_rope_append(C.byref(a), _stream()), "tidal_rope_append")
 
@@ -320,6 +326,7 @@ def prefill(q: torch.Tensor, kv_pool: torch.Tensor, page_table: torch.Tensor, kv
     a.d_status = status.data_ptr() if status is not None else None
     a.kv_len, a.n_q, a.num_qo_heads, a.num_kv_heads, a.head_dim = int(kv_len), n_q, Hq, Hkv, D
     a.page_size, a.dtype, a.causal, a.sm_scale = page_size, _dtype_code(q), 1 if causal else 0, float(sm_scale)
+    a.num_pages = kv_pool.shape[0]
     with torch.cuda.device(q.device):
         check(lib.tidal_prefill(C.byref(a), _stream()), "tidal_prefill")
     return out
@@ -407,28 +414,72 @@ class PeerExchange:
     rank of the group), the pointer tables on the device.  One object per (group, slot size); every rank
     must construct it at the same point of the program (the constructor is a collective)."""
 
-    def __init__(self, slot_bytes: int, group, device):
+    def __init__(self, slot_bytes: int, group, device, wait_limit: int = 0):
         import torch.distributed as dist
         import torch.distributed._symmetric_memory as symm_mem
 
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        if slot_bytes % 16:
-            raise RuntimeError("slot_bytes must be a multiple of 16")
-        self.slot_bytes = int(slot_bytes)
-        stage_bytes = 2 * self.world * self.slot_bytes
-        count_off = (stage_bytes + 255) // 256 * 256
+        self.group = group
+        stage_bytes, count_off = self._geometry(slot_bytes, self.world)
         with torch.cuda.device(device):
             self.buf = symm_mem.empty(count_off + 256, dtype=torch.uint8, device=device)
             self.buf.zero_()
             hdl = symm_mem.rendezvous(self.buf, group)
-            ptrs = [int(p) for p in hdl.buffer_ptrs]
-            i64 = dict(dtype=torch.int64, device=device)
-            self.peer_stage = torch.tensor(ptrs, **i64)
-            self.peer_count = torch.tensor([p + count_off for p in ptrs], **i64)
-            self.state = torch.zeros(2, dtype=torch.int32, device=device)
             self._hdl = hdl
+            self._tables([int(p) for p in hdl.buffer_ptrs], count_off, device)
             torch.cuda.synchronize()
+        self.wait_limit = int(wait_limit)
         dist.barrier(group)                      # every rank's counters are zero before anyone adds to them
+
+    def _geometry(self, slot_bytes: int, world: int):
+        if slot_bytes % 16:
+            raise RuntimeError("slot_bytes must be a multiple of 16")
+        self.slot_bytes = int(slot_bytes)
+        stage_bytes = 2 * world * self.slot_bytes
+        return stage_bytes, (stage_bytes + 255) // 256 * 256
+
+    def _tables(self, ptrs, count_off: int, device) -> None:
+        i64 = dict(dtype=torch.int64, device=device)
+        self.peer_stage = torch.tensor(ptrs, **i64)
+        self.peer_count = torch.tensor([p + count_off for p in ptrs], **i64)
+        self._own_count = ptrs[self.rank] + count_off
+        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+
+    @classmethod
+    def loopback(cls, slot_bytes: int, world: int, device, wait_limit: int = 0) -> "PeerExchange":
+        """Rank 0 of a `world`-rank exchange whose every table entry is this GPU's own buffer: no other
+        rank exists, so an exchange completes only if the missing ranks' arrivals were written by the
+        host beforehand (`counters`, `stage`), and otherwise runs into its wait limit.  For tests of the
+        timeout and reset behaviour on one GPU; nothing in it waits on another kernel."""
+        self = cls.__new__(cls)
+        self.world, self.rank, self.group, self._hdl = int(world), 0, None, None
+        stage_bytes, count_off = self._geometry(slot_bytes, self.world)
+        with torch.cuda.device(device):
+            self.buf = torch.zeros(count_off + 256, dtype=torch.uint8, device=device)
+            self._tables([self.buf.data_ptr()] * self.world, count_off, device)
+        self.wait_limit = int(wait_limit)
+        self.stage = self.buf[:stage_bytes].view(2, self.world, self.slot_bytes)       # [parity][rank][slot]
+        self.counters = self.buf[count_off:count_off + 8 * self.world].view(torch.int32).view(2, self.world)
+        return self
+
+    @property
+    def ctas(self) -> int:
+        return lib.tidal_peer_exchange_ctas(self.slot_bytes)
+
+    def reset(self) -> None:
+        """Arrival counters and exchange count back to zero after a timed-out exchange.  A collective in
+        effect: every rank calls it, with none of the group's exchanges in flight."""
+        import torch.distributed as dist
+
+        if self.group is not None:
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+        with torch.cuda.device(self.state.device):
+            check(lib.tidal_peer_exchange_reset(self._own_count, self.state.data_ptr(), self.world, _stream()),
+                  "tidal_peer_exchange_reset")
+        if self.group is not None:
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
 
     def all_gather(self, send: torch.Tensor, recv: Optional[torch.Tensor], nbytes: Optional[int] = None,
                    status: Optional[torch.Tensor] = None, merge: Optional[tuple] = None) -> None:
@@ -450,5 +501,6 @@ class PeerExchange:
         a.d_peer_stage, a.d_peer_count = self.peer_stage.data_ptr(), self.peer_count.data_ptr()
         a.d_state, a.d_status = self.state.data_ptr(), _ptr(status)
         a.rank, a.world = self.rank, self.world
+        a.wait_limit = self.wait_limit
         with torch.cuda.device(send.device):
             check(lib.tidal_peer_all_gather(C.byref(a), _stream()), "tidal_peer_all_gather")

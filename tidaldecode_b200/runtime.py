@@ -184,7 +184,9 @@ class GraphDecoder:
     # ------------------------------------------------------------------ decode
     @torch.inference_mode()
     def decode(self, steps: int, use_graph: bool = True) -> torch.Tensor:
-        """`steps` greedy tokens after the one `prefill` returned; returns [B, steps] (device)."""
+        """`steps` more greedy tokens (the first call continues after the token `prefill` returned);
+        returns those `steps` tokens, [B, steps] on the device."""
+        asked = steps
         if self._prefill_len + 1 + steps > self.max_seq_len:
             raise RuntimeError("max_seq_len too small for this many steps")
         if not use_graph:
@@ -205,4 +207,4 @@ class GraphDecoder:
                 self.graph.replay()
         done = int(self.step_idx.item())
         self.c.kv_cache._seqlen = self._prefill_len + done      # host bookkeeping catches up with the device
-        return self.out_tokens[:, :done]
+        return self.out_tokens[:, done - asked:done]

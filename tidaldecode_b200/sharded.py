@@ -65,6 +65,34 @@ def pack_layout(batch: int, hq: int, d: int, rows: int, k: int):
     return dict(m=o_m, l=o_l, o=o_o, cs=o_cs, ci=o_ci, total=o_ci + rows * k)
 
 
+class RankLost(RuntimeError):
+    """A rank of the sharded group announced that it is leaving; its shard of the KV is gone."""
+
+
+class GroupHealth:
+    """Host-side liveness of a sharded group over the process group's key-value store.
+
+    A rank leaves only between steps, with none of its kernels or collectives in flight: it calls
+    `leave()`; the others call `check()` before they launch their next step and get `RankLost`
+    instead of a collective that can never complete.  (A rank that dies without saying so is caught
+    by the next collective's timeout: the process-group timeout for NCCL/gloo, the bounded device-side
+    wait — TIDAL_DEV_WAIT_TIMEOUT — for the peer-store exchange.)"""
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "tidal/health"):
+        self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+
+    def _key(self, r: int) -> str:
+        return f"{self.prefix}/left/{r}"
+
+    def leave(self) -> None:
+        self.store.set(self._key(self.rank), b"1")
+
+    def check(self) -> None:
+        for r in range(self.world):
+            if r != self.rank and self.store.check([self._key(r)]):
+                raise RankLost(f"rank {r} has left the group")
+
+
 # largest group the peer-store exchange has run on; larger groups get NCCL unless exchange="peer" is asked for
 kPeerValidatedWorld = 4
 
@@ -74,7 +102,7 @@ class ShardedDecodeAttention:
 
     def __init__(self, batch: int, hq: int, hkv: int, d: int, dtype: torch.dtype, plan: ShardPlan, rank: int,
                  top_k: int, head_reduce: str = "sum", group: Optional[dist.ProcessGroup] = None, device="cuda",
-                 ops=None, exchange: str = "auto"):
+                 ops=None, exchange: str = "auto", health: Optional[GroupHealth] = None):
         """exchange: "peer" = tidal_peer_all_gather (NVLink peer stores from this library's own kernel),
         "nccl" = one all_gather_into_tensor per layer, "auto" = peer for groups of up to kPeerValidatedWorld
         CUDA ranks where symmetric memory can be set up, else nccl."""
@@ -82,6 +110,7 @@ class ShardedDecodeAttention:
             from . import ops  # the CUDA library; raises if it is missing (tests of the exchange logic inject a stand-in)
 
         self.ops = ops
+        self.health = health           # checked on the host before every layer's launches, if given
         self.B, self.Hq, self.Hkv, self.D, self.dtype = batch, hq, hkv, d, dtype
         self.plan, self.rank, self.k, self.group = plan, rank, top_k, group
         self.world = plan.world
@@ -167,6 +196,8 @@ class ShardedDecodeAttention:
         """q [B,Hq,D]; kv_local: this rank's pool holding positions [lo, hi) of every sequence.
         timing: a list that receives a (start, end) CUDA-event pair around the local attention."""
         ops, k = self.ops, self.k
+        if self.health is not None:
+            self.health.check()
         m, l, o, cs, ci = self._send_views()
         if self.local_len > 0:
             if timing is not None:
@@ -199,6 +230,8 @@ class ShardedDecodeAttention:
     def sparse_layer(self, q: torch.Tensor, kv_local: torch.Tensor, pages_per_seq: Optional[int] = None,
                      page_table: Optional[torch.Tensor] = None) -> torch.Tensor:
         ops = self.ops
+        if self.health is not None:
+            self.health.check()
         m, l, o, _, _ = self._send_views()
         sel = self.sel_local.view(self.B, self.k) if self.rows_per_seq == 1 else self.sel_local.view(self.B, self.Hq, self.k)
         cnt = self.sel_count.view(self.B) if self.rows_per_seq == 1 else self.sel_count.view(self.B, self.Hq)

@@ -120,28 +120,11 @@ def decode_sparse_attn(q: torch.Tensor, iController: InferenceController, layer_
             raise RuntimeError("sparse layer before a selection layer of this step")   # modify_llama.py:123-124
         if output_qk_product:
             raise RuntimeError("logits are written by selection layers only")
-        k = c.inference_token_budget
         ops.decode_attention(q, pool, n, c.workspace, out=o, page_table=c.kv_cache.page_table,
-                             sel_idx=c._topk_indices_full, sel_counts=_counts(c, k))
+                             sel_idx=c._topk_indices_full, sel_counts=c._counts_full)
     else:
-        c._decode_handler._wrapper._begun = True
         c._decode_handler.forward(q, o, pool, topk_indices, None, c.kv_cache.last_page_len, c.kv_last_page_idx,
                                   c.qk_product.view(c.num_heads, -1) if (output_qk_product and c.head_reduce == "none"
                                                                          and c.batch_size == 1) else None,
                                   rope_scale, rope_theta)
     return o
-
-
-_count_cache = {}
-
-
-def _counts(c: InferenceController, k: int) -> torch.Tensor:
-    """Device tensor of per-list valid counts (= k for every list), cached per (controller, k)."""
-    key = (id(c), k)
-    t = _count_cache.get(key)
-    if t is None:
-        rows = c.batch_size * c.score_rows
-        t = torch.full((rows,), k, dtype=torch.int32, device=c.device)
-        _count_cache.clear()
-        _count_cache[key] = t
-    return t

@@ -21,7 +21,7 @@ from typing import Optional
 
 import torch
 
-from .. import ops
+from .. import _kernels, ops
 from .decode_wrapper import BatchDecodeWithPagedKVCacheWrapper
 from .kv_cache import KvCache
 from .utils import TensorLayout
@@ -64,6 +64,8 @@ class InferenceController:
         self.score_rows = rows_per_seq
         rows = batch_size * rows_per_seq
         self.workspace = ops.Workspace(batch_size, num_heads, head_dim, rows, max_seq_len, device=device)
+        # the per-head page-list form of the attention call (BatchDecodeWithPagedKVCacheWrapper) shares it
+        _kernels.adopt_workspace(self.workspace)
         shape = (batch_size, max_seq_len) if head_reduce == "sum" else (batch_size, num_heads, max_seq_len)
         # fp32 logits of the last selection layer; column = token position
         self.qk_product = torch.empty(shape, dtype=torch.float32, device=device)
@@ -71,6 +73,9 @@ class InferenceController:
         idx_shape = (batch_size, self._max_budget) if head_reduce == "sum" else (batch_size, num_heads, self._max_budget)
         self._topk_indices_full = torch.zeros(idx_shape, dtype=torch.int32, device=device)
         self._topk_values_full = torch.zeros(idx_shape, dtype=torch.float32, device=device)
+        # valid entries per selection list (= the step's budget for every list), refilled when the budget changes
+        self._counts_full = torch.full((rows,), self._max_budget, dtype=torch.int32, device=device)
+        self._counts_value = self._max_budget
         self.topk_buf = None                       # the reference's RAFT scratch; the workspace replaces it
 
         self.kv_indices_with_last = None
@@ -114,6 +119,13 @@ class InferenceController:
         b = self.inference_token_budget
         self.topk_dindices_buffer = self._topk_indices_full[..., :b]
         self.topk_dout_buffer = self._topk_values_full[..., :b]
+        if b != self._counts_value:
+            self._counts_full.fill_(b)
+            self._counts_value = b
+        # as the reference does every step (controller.py:170-177); the scratch is in place already unless
+        # another controller's smaller workspace was adopted on this device since
+        self._decode_handler.begin_forward(None, self.num_heads, self.num_kv_heads, self.head_dim, self.page_size, self.dtype,
+                                           max_pages=0, device=self.device)
 
     def end_forward(self):
         self._decode_handler.end_forward()
