@@ -314,18 +314,20 @@ int tidal_decode_qkv(const tidal_linear_args* lin, const tidal_rope_append_args*
 
 /* ------------------------------------------------------- peer all-gather
  * All-gather of one block per rank over NVLink peer stores, for the per-layer exchange of
- * sequence-sharded KV (no reference counterpart; stands where a library all-gather would).  Every
- * rank runs one process per GPU and calls this with the same `bytes`; when the kernel has finished,
- * d_recv (if given) holds rank r's block at byte r * slot_bytes.  Memory the caller sets up once:
+ * sequence-sharded KV (no reference counterpart; stands where a library all-gather would), with the
+ * work that follows the exchange done in the same launch: the merge of the ranks' softmax partials
+ * and the ranking of their top-k candidates.  Every rank runs one process per GPU and calls this
+ * with the same `bytes`; when the kernel has finished, d_recv (if given) holds rank r's block at
+ * byte r * slot_bytes.  Memory the caller sets up once:
  *   staging   per rank 2 * world * slot_bytes bytes, mapped on every rank (CUDA IPC / fabric handles);
  *             d_peer_stage[r] is rank r's staging buffer as addressed from this GPU (r = rank: its own);
  *   counters  per rank 2 * world uint32, zeroed, mapped the same way: d_peer_count[r];
- *   d_state   2 uint32 of this rank's own memory, zeroed.
+ *   d_state   4 uint32 of this rank's own memory, zeroed.
  * d_peer_stage and d_peer_count are device arrays of `world` pointers.  Nothing is reset between
- * calls.  Contract across calls on one set of buffers: slot_bytes, world and rank never change (the
- * number of CTAs, and with it the arrivals a rank expects per exchange, follows from slot_bytes:
- * tidal_peer_exchange_ctas); `bytes` may differ from call to call as long as every rank passes the
- * same value in the same call; the ranks issue their calls in the same order.
+ * calls.  Contract across calls on one set of buffers: slot_bytes, world and rank never change; `bytes`
+ * and the optional parts may differ from call to call (a rank posts ONE arrival per exchange whatever
+ * the call carries) as long as every rank passes the same values in the same call; the ranks issue their
+ * calls in the same order.
  * A rank that never arrives makes the others' bounded waits run out (wait_limit polls, 0 = the
  * default of about half a second): TIDAL_DEV_WAIT_TIMEOUT is OR-ed into *d_status (if given) and the
  * call completes with incomplete data.  After that the arrival counters and the exchange count of the
@@ -334,7 +336,7 @@ int tidal_decode_qkv(const tidal_linear_args* lin, const tidal_rope_append_args*
  * barrier before and after), before the buffers are used again. */
 typedef struct {
     const void* d_send;
-    void* d_recv;
+    void* d_recv;                /* NULL when only the merge / the ranking are wanted */
     int64_t bytes;               /* multiple of 16, <= slot_bytes */
     int64_t slot_bytes;          /* multiple of 16 */
     void* const* d_peer_stage;
@@ -344,15 +346,26 @@ typedef struct {
     int32_t rank, world;
     /* optional: the blocks hold softmax partials of sequence-sharded attention — m [rows], l [rows],
      * o [rows][head_dim] fp32 at these word offsets — and the kernel also writes their exact merge (as
-     * tidal_merge_partials would) to d_merge_out [rows][head_dim] of merge_dtype; d_recv may then be NULL */
+     * tidal_merge_partials would) to d_merge_out [rows][head_dim] of merge_dtype */
     void* d_merge_out;
     int64_t merge_m_off, merge_l_off, merge_o_off;
     int32_t merge_rows, merge_head_dim, merge_dtype;
     int32_t wait_limit;          /* polls before a CTA gives up on the other ranks; 0 = default */
+    /* optional (cand_rows > 0): the blocks also hold every rank's top-k candidates — scores
+     * [cand_rows][cand_k] fp32 and global positions [cand_rows][cand_k] int32 at these word offsets, each
+     * rank's in ascending position order, ranks holding ascending position ranges — and the kernel ranks,
+     * per row, the world * cand_k candidates as tidal_topk would (k = cand_select, ties towards the lower
+     * position): the selected positions p with own_lo <= p < own_hi are written as p - own_lo, ascending,
+     * to d_sel_out[row * sel_stride ...] and their number to d_sel_count[row] (own_hi <= own_lo: all of
+     * them, unshifted).  Limits: cand_select <= 2048, world * cand_k <= 65536, cand_select < world * cand_k. */
+    int32_t cand_rows, cand_k, cand_select;
+    int64_t cand_score_off, cand_idx_off;
+    int32_t own_lo, own_hi;
+    int32_t* d_sel_out;
+    int64_t sel_stride;
+    int32_t* d_sel_count;
 } tidal_exchange_args;
 int tidal_peer_all_gather(const tidal_exchange_args* args, void* stream);
-/* CTAs every exchange on buffers with this slot size runs with (host arithmetic). */
-int tidal_peer_exchange_ctas(int64_t slot_bytes);
 /* Zeroes this rank's arrival counters (d_count = d_peer_count[rank], 2 * world words) and d_state on
  * the stream.  See tidal_peer_all_gather for when and how: every rank, nothing in flight. */
 int tidal_peer_exchange_reset(uint32_t* d_count, uint32_t* d_state, int world, void* stream);

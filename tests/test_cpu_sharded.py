@@ -234,25 +234,24 @@ def test_rank_leaving_between_steps_is_noticed_on_the_host(tmp_path):
 
 
 def test_peer_exchange_arrival_accounting_is_independent_of_payload():
-    """The arrivals a rank expects per exchange follow from the slot size alone, so exchanges of different
-    payloads (selection layers send partials and candidates, sparse layers only partials) can follow each
-    other in any order on one set of buffers: a model of the counters over sel, sparse, sparse, sel, ..."""
-    from tidaldecode_b200 import _lib as L
-    from tidaldecode_b200.sharded import pack_layout
-
-    lay = pack_layout(4, 32, 128, 4 * 32, 128)                   # per-head candidate rows: the payloads differ most
-    slot = (lay["total"] + 3) // 4 * 4 * 4
-    ctas = L.lib.tidal_peer_exchange_ctas(slot)
-    assert 1 <= ctas <= 32
-    assert L.lib.tidal_peer_exchange_ctas(15) == L.ERR_ARG
+    """A rank posts ONE arrival per exchange (its last CTA to have stored does), so the count a rank waits for
+    follows from the number of exchanges alone and exchanges of different payloads and grids (selection layers
+    send partials and candidates and rank them, sparse layers only partials) can follow each other in any order
+    on one set of buffers: a model of the counters over sel, sparse, sparse, sel, ..."""
     world = 4
+    grids = {"sel": 25, "sparse": 9}                             # CTAs of the two kinds of call differ
     count = [[0] * world for _ in range(2)]                      # one rank's counters [parity][source rank]
+    stored = 0                                                   # the rank's own "CTAs that stored" word
     epoch = 0
     for payload in ("sel", "sparse", "sparse", "sel", "sparse", "sel", "sel", "sparse", "sparse", "sparse"):
         e = epoch + 1
         par = e & 1
-        target = ((e + 1) // 2) * ctas                           # what the kernel waits for
+        target = (e + 1) // 2                                    # what the kernel waits for
         for r in range(world):
-            count[par][r] += ctas                                # every CTA of every rank arrives once, whatever it carried
+            for cta in range(grids[payload]):
+                stored += 1
+                if stored == grids[payload]:                     # the last CTA to have stored posts the arrival and clears the word
+                    stored = 0
+                    count[par][r] += 1
         assert all(c == target for c in count[par]), (payload, e, count, target)
         epoch = e

@@ -714,7 +714,7 @@ def test_peer_exchange_wait_runs_out_and_reset_recovers(T):
     # the peer's part of exchange 1 (parity 1), as its kernel would have left it: block in slot [1][1], arrivals
     other = torch.full((words,), 7.0, dtype=torch.float32, device=dev)
     px.stage[1, 1].copy_(other.view(torch.uint8))
-    px.counters[1, 1] = px.ctas
+    px.counters[1, 1] = 1
     px.all_gather(send, recv, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
@@ -722,7 +722,7 @@ def test_peer_exchange_wait_runs_out_and_reset_recovers(T):
     # and exchange 2 (parity 0) with another payload size on the same buffers
     half = words // 2 // 4 * 4
     px.stage[0, 1, : half * 4].copy_(other[:half].view(torch.uint8))
-    px.counters[0, 1] = px.ctas
+    px.counters[0, 1] = 1
     recv.zero_()
     px.all_gather(send, recv, nbytes=half * 4, status=status)
     torch.cuda.synchronize()

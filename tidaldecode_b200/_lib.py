@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_topk_static_status", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather", "tidal_peer_exchange_ctas", "tidal_peer_exchange_reset", "tidal_prefill",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_topk_static_status", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather", "tidal_peer_exchange_reset", "tidal_prefill",
 )
 
 
@@ -83,6 +83,9 @@ class ExchangeArgs(C.Structure):
         ("d_merge_out", C.c_void_p), ("merge_m_off", C.c_int64), ("merge_l_off", C.c_int64), ("merge_o_off", C.c_int64),
         ("merge_rows", C.c_int32), ("merge_head_dim", C.c_int32), ("merge_dtype", C.c_int32),
         ("wait_limit", C.c_int32),
+        ("cand_rows", C.c_int32), ("cand_k", C.c_int32), ("cand_select", C.c_int32),
+        ("cand_score_off", C.c_int64), ("cand_idx_off", C.c_int64), ("own_lo", C.c_int32), ("own_hi", C.c_int32),
+        ("d_sel_out", C.c_void_p), ("sel_stride", C.c_int64), ("d_sel_count", C.c_void_p),
     ]
 
 
@@ -142,8 +145,6 @@ def _load() -> C.CDLL:
     lib.tidal_decode_qkv.argtypes = [C.POINTER(LinearArgs), C.POINTER(RopeAppendArgs), C.c_void_p]
     lib.tidal_peer_all_gather.restype = C.c_int
     lib.tidal_peer_all_gather.argtypes = [C.POINTER(ExchangeArgs), C.c_void_p]
-    lib.tidal_peer_exchange_ctas.restype = C.c_int
-    lib.tidal_peer_exchange_ctas.argtypes = [C.c_int64]
     lib.tidal_peer_exchange_reset.restype = C.c_int
     lib.tidal_peer_exchange_reset.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     lib.tidal_prefill.restype = C.c_int

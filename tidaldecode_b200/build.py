@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtidal_b200.so")
 SOURCES = ["decode_attn.cu", "decode_attn_mma.cu", "topk.cu", "rope_append.cu", "rms_norm.cu", "decode_linear.cu", "peer_exchange.cu", "prefill_attn.cu", "workspace.cu"]
-HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "attn_params.cuh"), os.path.join(os.path.dirname(HERE), "include", "tidal_b200.h")]
+HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "attn_params.cuh"), os.path.join(CSRC, "topk_common.cuh"), os.path.join(os.path.dirname(HERE), "include", "tidal_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -261,9 +261,10 @@ __host__ __device__ inline size_t cta_result_bytes(int HC, int G, int D) { retur
 // distributed shared memory, no round trip — and after one cluster barrier each CTA merges what it
 // received from local shared memory and writes final values: no partials in global memory, no merge
 // kernel.  `recv` is that receive block (cluster_recv_bytes() bytes, touched by nothing else); the
-// kernel must have passed a cluster barrier since its start so that every CTA is running.
+// kernel must have ARRIVED at the cluster barrier at its start (cluster_arrive_relaxed, every thread); the
+// matching wait is here, before the first store into another CTA, so that every CTA is known to be running.
 // A thread owns four consecutive output elements; every thread of the CTA must call this.
-constexpr int kMaxCluster = 8;
+constexpr int kMaxCluster = 16;        // 8 is the portable limit; 16 needs the non-portable-size attribute
 template <typename T>
 struct alignas(sizeof(T) * 4) Pack4 {
     T v[4];
@@ -320,6 +321,7 @@ __device__ __forceinline__ void store_attention_result(const AttnParams& p, cons
     const int per = (units + CS - 1) / CS;            // float4 units each CTA finishes
     float2* recv_ml = reinterpret_cast<float2*>(recv + (size_t)CS * per * 4);     // [CS][HG], after [CS][per] float4
     __syncthreads();                                  // this CTA's block is complete
+    cluster_wait();                                   // every CTA of the cluster has started (arrived at its top)
     for (int u = threadIdx.x; u < units; u += blockDim.x) {
         const int dest = u / per, local = u - dest * per;
         float* dst = cluster.map_shared_rank(recv, dest) + ((size_t)rank * per + local) * 4;
@@ -359,6 +361,6 @@ constexpr int kMmaWarps = 8;
 constexpr int kMmaTile = 16;            // tokens one warp takes from a stage
 constexpr int kMmaMaxProducers = 2;
 size_t attn_mma_smem_bytes(int S, int HC, int G, int D, bool sum_heads);
-int launch_attn_mma(const AttnParams& p, int D, int dtype, dim3 grid, size_t smem, cudaStream_t st);
+int launch_attn_mma(const AttnParams& p, int D, int dtype, dim3 grid, size_t smem, cudaStream_t st, int* query);
 
 }  // namespace tidal

@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 #include <utility>
 
 #include "../../include/tidal_b200.h"
@@ -232,6 +233,13 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// Split cluster barrier: every thread of every CTA of the cluster arrives once and waits once per phase.
+// The arrive at the top of a kernel only says "this CTA is running" (no memory to publish: relaxed); the
+// matching wait sits right before the first store into another CTA's shared memory, so the prologue and
+// the whole streaming loop run without waiting for the slowest CTA of the cluster to start.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -270,6 +278,49 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     cfg.attrs = at;
     cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
+// How many clusters of `cluster_x` CTAs of this launch geometry the current device can hold at the same time
+// (a cluster lives inside one GPC).  Asked once per (kernel, geometry, device) and remembered: planners use it
+// to decide whether a non-portable cluster size would run all its clusters side by side.
+template <typename... KArgs>
+inline int max_resident_clusters(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x, int* out) {
+    struct Entry { const void* fn; size_t smem; unsigned threads; int cluster, dev, result; };
+    static Entry cache[32];
+    static int n_cached = 0;
+    static std::mutex mu;
+    int dev = 0;
+    TIDAL_CUDA_OK(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < n_cached; ++i) {
+        const Entry& e = cache[i];
+        if (e.fn == (const void*)kern && e.smem == smem && e.threads == block.x && e.cluster == cluster_x && e.dev == dev) {
+            *out = e.result;
+            return TIDAL_OK;
+        }
+    }
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (cluster_x > 8) TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = (unsigned)cluster_x;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();          // not launchable in this shape: report none, the caller keeps the portable size
+        n = 0;
+    }
+    if (n_cached < 32) cache[n_cached++] = Entry{(const void*)kern, smem, block.x, cluster_x, dev, n};
+    *out = n;
+    return TIDAL_OK;
 }
 
 // SM count of the current device (148 if it cannot be read); looked up once.

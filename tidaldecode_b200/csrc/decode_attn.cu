@@ -87,8 +87,9 @@ __global__ void __launch_bounds__(((G >= 4 ? 8 : 16) + MPW) * 32) decode_attn_ke
         for (int i = threadIdx.x; i < TIDAL_TOPK_BINS; i += blockDim.x) sh_hist[i] = 0;
     // the prologue above touched no global memory; from here on this kernel is ordered
     // after the earlier kernels of the stream (see common.cuh)
-    // a cluster's CTAs write into each other's shared memory at the end: all of them must be running
-    if (p.cluster > 1) cooperative_groups::this_cluster().sync();
+    // a cluster's CTAs write into each other's shared memory at the end: all of them must be running by then.
+    // Arrive now, wait only before the first such store (store_attention_result).
+    if (p.cluster > 1) cluster_arrive_relaxed();
     if (threadIdx.x == 0) TIDAL_STAMP(1);
     pdl_wait();
     if (threadIdx.x == 0) TIDAL_STAMP(2);
@@ -519,34 +520,39 @@ extern "C" int tidal_plan_chunks(int batch, int head_slices, int tokens, int min
 
 namespace tidal {
 
+// query != nullptr: nothing is launched; *query receives how many clusters of this launch's geometry can be
+// resident on the device at once (cudaOccupancyMaxActiveClusters)
 template <typename T, int D, int G, int HPS, int MPW>
-static int launch_attn_pw(const AttnParams& p, const AttnPlan& plan, cudaStream_t st) {
+static int launch_attn_pw(const AttnParams& p, const AttnPlan& plan, cudaStream_t st, int* query) {
     auto kern = decode_attn_kernel<T, D, G, HPS, MPW>;
-    TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
     dim3 grid(plan.nchunks, plan.nslices, p.B);
     dim3 block((plan.CW + p.PW) * 32);
+    if (query) return max_resident_clusters(kern, grid, block, plan.smem, p.cluster, query);
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.smem));
+    if (p.cluster > 8) TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     TIDAL_CUDA_OK(launch_pdl(kern, grid, block, plan.smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
 }
 
 template <typename T, int D, int G, int HPS>
-static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t st) {
-    return p.PW == 1 ? launch_attn_pw<T, D, G, HPS, 1>(p, plan, st) : launch_attn_pw<T, D, G, HPS, kMaxProducerWarps>(p, plan, st);
+static int launch_attn(const AttnParams& p, const AttnPlan& plan, cudaStream_t st, int* query) {
+    return p.PW == 1 ? launch_attn_pw<T, D, G, HPS, 1>(p, plan, st, query)
+                     : launch_attn_pw<T, D, G, HPS, kMaxProducerWarps>(p, plan, st, query);
 }
 
 template <typename T, int D>
-static int dispatch_g(const AttnParams& p, const AttnPlan& plan, int G, cudaStream_t st) {
+static int dispatch_g(const AttnParams& p, const AttnPlan& plan, int G, cudaStream_t st, int* query) {
     if (plan.HPS == 2) {
-        if (G == 1) return launch_attn<T, D, 1, 2>(p, plan, st);
+        if (G == 1) return launch_attn<T, D, 1, 2>(p, plan, st, query);
         set_error("two KV heads per slot is only built for MHA (group size 1), got %d", G);
         return TIDAL_ERR_ARG;
     }
     switch (G) {
-        case 1: return launch_attn<T, D, 1, 1>(p, plan, st);
-        case 2: return launch_attn<T, D, 2, 1>(p, plan, st);
-        case 4: return launch_attn<T, D, 4, 1>(p, plan, st);
-        case 8: return launch_attn<T, D, 8, 1>(p, plan, st);
+        case 1: return launch_attn<T, D, 1, 1>(p, plan, st, query);
+        case 2: return launch_attn<T, D, 2, 1>(p, plan, st, query);
+        case 4: return launch_attn<T, D, 4, 1>(p, plan, st, query);
+        case 8: return launch_attn<T, D, 8, 1>(p, plan, st, query);
         default:
             set_error("unsupported GQA group size %d (built: 1, 2, 4, 8)", G);
             return TIDAL_ERR_ARG;
@@ -554,10 +560,10 @@ static int dispatch_g(const AttnParams& p, const AttnPlan& plan, int G, cudaStre
 }
 
 template <typename T>
-static int dispatch_d(const AttnParams& p, const AttnPlan& plan, int D, int G, cudaStream_t st) {
+static int dispatch_d(const AttnParams& p, const AttnPlan& plan, int D, int G, cudaStream_t st, int* query) {
     switch (D) {
-        case 64: return dispatch_g<T, 64>(p, plan, G, st);
-        case 128: return dispatch_g<T, 128>(p, plan, G, st);
+        case 64: return dispatch_g<T, 64>(p, plan, G, st, query);
+        case 128: return dispatch_g<T, 128>(p, plan, G, st, query);
         default:
             set_error("unsupported head_dim %d (built: 64, 128)", D);
             return TIDAL_ERR_ARG;
@@ -704,73 +710,89 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     // a chunk should move at least ~64 KB so that its pipeline fills
     int min_tok = (64 * 1024) / (2 * row_bytes);
     if (min_tok < 1) min_tok = 1;
-    if (cluster > 1) plan.nchunks = cluster;
-    else plan.nchunks = a->num_chunks > 0 ? a->num_chunks
-                                          : tidal_plan_chunks(a->batch, plan.nslices, ntok, min_tok, sm_count_cached());
-    TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
-                  plan.nchunks, kMaxChunks);
     const int slots = plan.CW * (32 / lpr);
-    // a cluster CTA also holds a receive block for the merge, behind everything else
-    const size_t recv_bytes = cluster > 1 ? cluster_recv_bytes(plan.HC, kernel_G, D, cluster) : 0;
-    auto smem_base = [&](int S) {
-        return round16(use_mma ? attn_mma_smem_bytes(S, plan.HC, kernel_G, D, sum_heads)
-                               : attn_smem_bytes(S, plan.T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads));
-    };
-    auto smem_of = [&](int S) { return smem_base(S) + recv_bytes; };
-    int S = 8;
-    while (S > 1 && smem_of(S) > kSmemBudget) --S;
-    // no more stages than the longest chunk can use (short lists: less shared memory to set up)
-    const int iters = ((ntok + plan.nchunks - 1) / plan.nchunks + plan.T - 1) / plan.T;
-    if (S > iters) S = iters < 1 ? 1 : iters;
-    plan.S = S;
-    plan.smem = smem_of(S);
-    TIDAL_REQUIRE(plan.smem + sizeof(uint32_t) * 2 * kAddrBlock <= 227 * 1024, TIDAL_ERR_ARG, "shared memory %zu exceeds 227 KB (row %d bytes)", plan.smem, row_bytes);
-
+    const int copy_bytes = ((a->page_size == 1 && plan.HC == a->num_kv_heads && !per_head) ? 2 : 1) * row_bytes;
+    cudaStream_t st = (cudaStream_t)stream;
     AttnParams p;
-    p.q = a->d_q; p.o = a->d_o; p.kv = (const char*)a->d_kv;
-    p.page_table = a->d_page_table; p.pt_stride = a->page_table_stride;
-    p.seq_lens = a->d_seq_lens; p.seq_len = a->seq_len;
-    p.sel_idx = a->d_sel_idx; p.sel_counts = a->d_sel_counts;
-    p.sel_rows = sel ? a->sel_rows : 1; p.sel_count = a->sel_count; p.sel_physical = a->sel_physical;
-    p.extra_page = sel ? a->extra_page : -1; p.sel_stride = a->sel_stride;
-    p.scores = a->d_scores; p.score_rows = a->score_rows; p.score_stride = a->score_stride;
-    p.hist = a->d_hist; p.force_last = a->force_last;
-    p.part_o = (float*)((char*)d_ws + L->part_o_off);
-    p.part_ml = (float*)((char*)d_ws + L->part_ml_off);
-    p.shard_m = a->d_part_m; p.shard_l = a->d_part_l; p.shard_o = a->d_part_o;
-    p.status = (uint32_t*)((char*)d_ws + L->status_off);
-    p.B = a->batch; p.Hq = a->num_qo_heads; p.Hkv = a->num_kv_heads; p.page_size = a->page_size;
-    p.num_pages = a->num_pages;
-    p.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)D);
-    p.nchunks = plan.nchunks; p.HC = plan.HC; p.greal = G; p.per_head = per_head ? 1 : 0;
-    p.T = plan.T; p.S = plan.S; p.TG = plan.TG; p.CW = plan.CW; p.cluster = cluster;
-    p.recv_off = (uint32_t)smem_base(plan.S);
-    p.kv_fused = (a->page_size == 1 && plan.HC == a->num_kv_heads && !per_head) ? 1 : 0;
-    // One warp gets a bulk copy accepted every ~70 cycles, so short rows want more producer warps.
-    // On the CUDA-core kernel that is a second instance of the kernel: with rows of 1 KB and more the
-    // single-producer instance is kept, because a step that alternates between two instances pays more
-    // in cold instruction fetches than the extra producers gain (measured: 119.8 vs 121.5 us per step of
-    // a selection and a sparse layer at 32 x 128 heads).
-    const int copy_bytes = (p.kv_fused ? 2 : 1) * row_bytes;
-    if (use_mma) p.PW = copy_bytes <= 2048 ? kMmaMaxProducers : 1;
-    else p.PW = copy_bytes <= 512 ? kMaxProducerWarps : 1;
+    // Everything that depends on the cluster size; returns a negative code on a bad geometry.
+    auto build = [&](int cl) -> int {
+        if (cl > 1) plan.nchunks = cl;
+        else plan.nchunks = a->num_chunks > 0 ? a->num_chunks
+                                              : tidal_plan_chunks(a->batch, plan.nslices, ntok, min_tok, sm_count_cached());
+        TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
+                      plan.nchunks, kMaxChunks);
+        // a cluster CTA also holds a receive block for the merge, behind everything else
+        const size_t recv_bytes = cl > 1 ? cluster_recv_bytes(plan.HC, kernel_G, D, cl) : 0;
+        auto smem_base = [&](int S) {
+            return round16(use_mma ? attn_mma_smem_bytes(S, plan.HC, kernel_G, D, sum_heads)
+                                   : attn_smem_bytes(S, plan.T, row_bytes, plan.HC, plan.CW, slots, plan.HPS, kernel_G, D, sum_heads));
+        };
+        auto smem_of = [&](int S) { return smem_base(S) + recv_bytes; };
+        int S = 8;
+        while (S > 1 && smem_of(S) > kSmemBudget) --S;
+        // no more stages than the longest chunk can use (short lists: less shared memory to set up)
+        const int iters = ((ntok + plan.nchunks - 1) / plan.nchunks + plan.T - 1) / plan.T;
+        if (S > iters) S = iters < 1 ? 1 : iters;
+        plan.S = S;
+        plan.smem = smem_of(S);
+        TIDAL_REQUIRE(plan.smem + sizeof(uint32_t) * 2 * kAddrBlock <= 227 * 1024, TIDAL_ERR_ARG, "shared memory %zu exceeds 227 KB (row %d bytes)", plan.smem, row_bytes);
+
+        p.q = a->d_q; p.o = a->d_o; p.kv = (const char*)a->d_kv;
+        p.page_table = a->d_page_table; p.pt_stride = a->page_table_stride;
+        p.seq_lens = a->d_seq_lens; p.seq_len = a->seq_len;
+        p.sel_idx = a->d_sel_idx; p.sel_counts = a->d_sel_counts;
+        p.sel_rows = sel ? a->sel_rows : 1; p.sel_count = a->sel_count; p.sel_physical = a->sel_physical;
+        p.extra_page = sel ? a->extra_page : -1; p.sel_stride = a->sel_stride;
+        p.scores = a->d_scores; p.score_rows = a->score_rows; p.score_stride = a->score_stride;
+        p.hist = a->d_hist; p.force_last = a->force_last;
+        p.part_o = (float*)((char*)d_ws + L->part_o_off);
+        p.part_ml = (float*)((char*)d_ws + L->part_ml_off);
+        p.shard_m = a->d_part_m; p.shard_l = a->d_part_l; p.shard_o = a->d_part_o;
+        p.status = (uint32_t*)((char*)d_ws + L->status_off);
+        p.B = a->batch; p.Hq = a->num_qo_heads; p.Hkv = a->num_kv_heads; p.page_size = a->page_size;
+        p.num_pages = a->num_pages;
+        p.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)D);
+        p.nchunks = plan.nchunks; p.HC = plan.HC; p.greal = G; p.per_head = per_head ? 1 : 0;
+        p.T = plan.T; p.S = plan.S; p.TG = plan.TG; p.CW = plan.CW; p.cluster = cl;
+        p.recv_off = (uint32_t)smem_base(plan.S);
+        p.kv_fused = (a->page_size == 1 && plan.HC == a->num_kv_heads && !per_head) ? 1 : 0;
+        // One warp gets a bulk copy accepted every ~70 cycles, so short rows want more producer warps.
+        // On the CUDA-core kernel that is a second instance of the kernel: with rows of 1 KB and more the
+        // single-producer instance is kept, because a step that alternates between two instances pays more
+        // in cold instruction fetches than the extra producers gain (measured: 119.8 vs 121.5 us per step of
+        // a selection and a sparse layer at 32 x 128 heads).
+        if (use_mma) p.PW = copy_bytes <= 2048 ? kMmaMaxProducers : 1;
+        else p.PW = copy_bytes <= 512 ? kMaxProducerWarps : 1;
+        return TIDAL_OK;
+    };
+    // query != nullptr: do not launch, report how many clusters of this geometry the device holds at once
+    auto run = [&](int* query) -> int {
+        if (use_mma) return launch_attn_mma(p, D, a->dtype, dim3(plan.nchunks, plan.nslices, p.B), plan.smem, st, query);
+        switch (a->dtype) {
+            case TIDAL_DTYPE_F16: return dispatch_d<__half>(p, plan, D, kernel_G, st, query);
+            case TIDAL_DTYPE_BF16: return dispatch_d<__nv_bfloat16>(p, plan, D, kernel_G, st, query);
+            default: return dispatch_d<float>(p, plan, D, kernel_G, st, query);
+        }
+    };
+    int rc;
+    // Long lists on a cluster of 8 leave each CTA more than an SM takes in quickly (~40 B/cycle): with 16 CTAs
+    // per cluster (the non-portable size) twice as many SMs pull data — if the device can hold all clusters at
+    // once (a cluster sits inside one GPC), otherwise they would run one after the other.
+    const size_t cta_bytes_at_8 = (size_t)ntok * 2 * plan.HC * D * es / 8;      // what one CTA of an 8-cluster streams
+    if (cluster == 8 && cta_bytes_at_8 > ((size_t)192 << 10) && 16 * a->batch * plan.nslices <= sm_count_cached()) {
+        if ((rc = build(16)) != TIDAL_OK) return rc;
+        int resident = 0;
+        if ((rc = run(&resident)) != TIDAL_OK) return rc;
+        if (resident >= a->batch * plan.nslices) cluster = 16;
+    }
+    if ((rc = build(cluster)) != TIDAL_OK) return rc;
     const size_t part_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * D;
     const size_t ml_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * 2;
     TIDAL_REQUIRE(plan.nchunks == 1 || cluster > 1 ||
                       (L->part_o_off + part_need <= L->part_ml_off && L->part_ml_off + ml_need <= L->hist_off),
                   TIDAL_ERR_WORKSPACE, "workspace was sized for a smaller batch/heads/head_dim than this call");
 
-    cudaStream_t st = (cudaStream_t)stream;
-    int rc;
-    if (use_mma) {
-        rc = launch_attn_mma(p, D, a->dtype, dim3(plan.nchunks, plan.nslices, p.B), plan.smem, st);
-    } else {
-        switch (a->dtype) {
-            case TIDAL_DTYPE_F16: rc = dispatch_d<__half>(p, plan, D, kernel_G, st); break;
-            case TIDAL_DTYPE_BF16: rc = dispatch_d<__nv_bfloat16>(p, plan, D, kernel_G, st); break;
-            default: rc = dispatch_d<float>(p, plan, D, kernel_G, st); break;
-        }
-    }
+    rc = run(nullptr);
     if (rc != TIDAL_OK) return rc;
     if (plan.nchunks > 1 && cluster == 1) {
         switch (a->dtype) {

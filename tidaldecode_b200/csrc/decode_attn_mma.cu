@@ -131,8 +131,9 @@ __global__ void __launch_bounds__((kMmaWarps + 1 + kMmaMaxProducers) * 32) decod
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     // the prologue above touched no global memory; from here on this kernel is ordered
     // after the earlier kernels of the stream (see common.cuh)
-    // a cluster's CTAs write into each other's shared memory at the end: all of them must be running
-    if (p.cluster > 1) cooperative_groups::this_cluster().sync();
+    // a cluster's CTAs write into each other's shared memory at the end: all of them must be running by then.
+    // Arrive now, wait only before the first such store (store_attention_result).
+    if (p.cluster > 1) cluster_arrive_relaxed();
     if (threadIdx.x == 0) TIDAL_STAMP(1);
     pdl_wait();
     if (threadIdx.x == 0) TIDAL_STAMP(2);
@@ -440,21 +441,24 @@ __global__ void __launch_bounds__((kMmaWarps + 1 + kMmaMaxProducers) * 32) decod
 }
 
 template <typename T, int D>
-static int launch_one(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t st) {
+static int launch_one(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t st, int* query) {
     auto kern = decode_attn_mma_kernel<T, D>;
+    const dim3 block((kMmaWarps + 1 + p.PW) * 32);
+    if (query) return max_resident_clusters(kern, grid, block, smem, p.cluster, query);
     TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    TIDAL_CUDA_OK(launch_pdl(kern, grid, dim3((kMmaWarps + 1 + p.PW) * 32), smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
+    if (p.cluster > 8) TIDAL_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    TIDAL_CUDA_OK(launch_pdl(kern, grid, block, smem, st, (unsigned)(p.cluster > 1 ? p.cluster : 1), p));
     count_launch();
     return TIDAL_OK;
 }
 
-int launch_attn_mma(const AttnParams& p, int D, int dtype, dim3 grid, size_t smem, cudaStream_t st) {
+int launch_attn_mma(const AttnParams& p, int D, int dtype, dim3 grid, size_t smem, cudaStream_t st, int* query) {
     if (dtype == TIDAL_DTYPE_F16) {
-        if (D == 128) return launch_one<__half, 128>(p, grid, smem, st);
-        if (D == 64) return launch_one<__half, 64>(p, grid, smem, st);
+        if (D == 128) return launch_one<__half, 128>(p, grid, smem, st, query);
+        if (D == 64) return launch_one<__half, 64>(p, grid, smem, st, query);
     } else if (dtype == TIDAL_DTYPE_BF16) {
-        if (D == 128) return launch_one<__nv_bfloat16, 128>(p, grid, smem, st);
-        if (D == 64) return launch_one<__nv_bfloat16, 64>(p, grid, smem, st);
+        if (D == 128) return launch_one<__nv_bfloat16, 128>(p, grid, smem, st, query);
+        if (D == 64) return launch_one<__nv_bfloat16, 64>(p, grid, smem, st, query);
     }
     set_error("tensor-core attention is built for f16/bf16 and head_dim 64/128 (got dtype %d, head_dim %d)", dtype, D);
     return TIDAL_ERR_ARG;

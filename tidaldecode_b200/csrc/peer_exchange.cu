@@ -1,36 +1,31 @@
 // All-gather of one small block per rank over NVLink peer stores, for the per-layer exchange of
-// sequence-sharded decode attention (softmax partials and top-k candidates: a few KB to a few MB).
-// A collective library launch costs more than this exchange moves in time; here every rank's kernel
+// sequence-sharded decode attention (softmax partials and top-k candidates: a few KB to a few MB), with
+// what follows the exchange done in the same launch.  A collective library launch costs more than this
+// exchange moves in time; here every rank's kernel
 //   1. stores its block into its slot of every peer's staging buffer (plain peer stores through
 //      pointers the host obtained by exchanging memory handles; no multicast),
-//   2. fences, and adds 1 to its arrival counter on every peer (one add per CTA),
-//   3. waits — with an iteration limit — until every rank's counter on this GPU shows all CTAs of the
-//      current exchange, and
-//   4. copies the staged blocks into the caller's receive buffer, which the kernels that follow in the
-//      stream read with fixed addresses (the same graph can be replayed), and — if asked — merges the
-//      ranks' softmax partials (m, l, o) found in the blocks into the attention output on the spot, so
-//      that the exchange of a sparse layer is followed by no merge launch at all.
+//   2. fences; the LAST of its CTAs to get there adds 1 to this rank's arrival counter on every peer
+//      (one system-scope add per peer per exchange, whatever the grid),
+//   3. waits — with an iteration limit — until every rank's counter on this GPU shows the current
+//      exchange, and
+//   4. works on the staged blocks in place: copies them to the caller's receive buffer (if one is given),
+//      merges the ranks' softmax partials (m, l, o) into the attention output (if asked), and ranks the
+//      ranks' top-k candidates into the global selection, keeping the positions this rank owns (if asked:
+//      the one-CTA form of the top-k, one row per CTA), so that a selection layer is attention -> local
+//      top-k -> this launch, and a sparse layer attention -> this launch.
 // Staging and counters are double-buffered by the parity of an exchange counter kept in device memory
 // and advanced by the last CTA to finish, so nothing is reset between exchanges: a rank can be at most
 // one exchange ahead of another, because it needs the other's arrivals to finish the one in between.
-// The number of CTAs follows from slot_bytes alone — a property of the buffers, not of the call — so
-// that the arrivals expected per exchange are the same whatever each exchange carries: calls that move
-// fewer bytes than a slot holds (a sparse layer sends only partials, a selection layer also its
-// candidates) may be mixed freely on one set of buffers.
-#include "common.cuh"
+// The arrivals expected per exchange do not depend on the bytes or the grid of a call, so calls of
+// different sizes may follow each other on one set of buffers.
+#include "topk_common.cuh"
 
 namespace tidal {
 
-constexpr int kXchgThreads = 256;
-constexpr int kXchgMaxCtas = 32;
+constexpr int kXchgThreads = kTopkThreads;       // 1024: the candidate ranking is the top-k's one-CTA form
+constexpr int kXchgMaxCtas = 64;                 // all resident at once (one CTA per SM), so no CTA waits for an SM
 constexpr int kXchgMaxWorld = 16;
 constexpr uint32_t kXchgSpinLimit = 1u << 22;    // default wait limit (about half a second)
-
-// CTAs of every exchange on buffers with slots of slot_vec 16-byte vectors
-__host__ __device__ inline int exchange_ctas(int64_t slot_vec) {
-    int64_t c = (slot_vec + kXchgThreads - 1) / kXchgThreads;
-    return (int)(c < 1 ? 1 : (c > kXchgMaxCtas ? kXchgMaxCtas : c));
-}
 
 struct ExchangeParams {
     const uint4* send;
@@ -38,9 +33,8 @@ struct ExchangeParams {
     int64_t slot_vec;             // vectors between the blocks of two ranks (staging and receive buffer alike)
     uint4* const* peer_stage;     // [world]: every rank's staging buffer [2][world][slot_vec], as mapped on this GPU
     uint32_t* const* peer_count;  // [world]: every rank's arrival counters [2][world]
-    uint4* out;                   // local receive buffer [world][slot_vec]
-    uint32_t* epoch;              // local: exchanges completed
-    uint32_t* fin;                // local: CTAs of the current exchange that are done
+    uint4* out;                   // local receive buffer [world][slot_vec], or nullptr
+    uint32_t* state;              // local: [0] exchanges completed, [1] CTAs done, [2] CTAs that stored, [3] status sink
     uint32_t* status;
     uint32_t spin_limit;          // iterations a CTA polls for the other ranks before it gives up
     int rank, world;
@@ -48,6 +42,15 @@ struct ExchangeParams {
     void* merge_out;
     int64_t m_off, l_off, o_off;
     int merge_rows, merge_dim, merge_dtype;
+    // optional ranking of the ranks' candidates: scores [rows][k] fp32 and positions [rows][k] int32 at these word
+    // offsets of a block; per row the `select` best of the world * k, those in [own_lo, own_hi) written as
+    // position - own_lo to sel_out[row][...] in ascending order, their number to sel_count[row]
+    int cand_rows, cand_k, cand_select;
+    int64_t cs_off, ci_off;
+    int32_t own_lo, own_hi;
+    int32_t* sel_out;
+    int64_t sel_stride;
+    int32_t* sel_count;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -57,12 +60,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 }
 
 __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const ExchangeParams p) {
+    extern __shared__ __align__(16) unsigned char xsm[];      // kClusterSmem bytes when candidates are ranked
+    __shared__ int s_last;
     pdl_wait();
     pdl_launch_dependents();
     // every CTA reads the counter before the last one to finish advances it
-    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1u;
+    const uint32_t e = *reinterpret_cast<volatile uint32_t*>(&p.state[0]) + 1u;
     const int par = (int)(e & 1u);
-    const uint32_t target = ((e + 1u) / 2u) * gridDim.x;          // arrivals per rank after this exchange, for this parity
+    const uint32_t target = (e + 1u) / 2u;                   // arrivals per rank after this exchange, for this parity
     const int64_t stride = (int64_t)gridDim.x * kXchgThreads;
     const int64_t first = (int64_t)blockIdx.x * kXchgThreads + threadIdx.x;
 
@@ -72,12 +77,25 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
         const uint4 v = p.send[i];
         for (int r = 0; r < p.world; ++r) p.peer_stage[r][my_slot + i] = v;
     }
-    // 2. the stores of the whole CTA are ordered before its arrival
+    // 2. the stores of every CTA are ordered before the rank's arrival, which the last CTA to get here posts
     __threadfence_system();
     __syncthreads();
-    if ((int)threadIdx.x < p.world) atomicAdd_system(&p.peer_count[threadIdx.x][par * p.world + p.rank], 1u);
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t done = atomicAdd(&p.state[2], 1u);
+        s_last = (done == gridDim.x - 1) ? 1 : 0;
+        if (s_last) {
+            p.state[2] = 0;                                   // every CTA has added: ready for the next exchange
+            __threadfence_system();
+        }
+    }
+    __syncthreads();
+    if (s_last && (int)threadIdx.x < p.world) {
+        __threadfence_system();
+        atomicAdd_system(&p.peer_count[threadIdx.x][par * p.world + p.rank], 1u);
+    }
 
-    // 3. wait for every rank's arrivals on this GPU (bounded: a missing rank becomes a status bit, not a hang)
+    // 3. wait for every rank's arrival on this GPU (bounded: a missing rank becomes a status bit, not a hang)
     if ((int)threadIdx.x < p.world) {
         const uint32_t* c = &p.peer_count[p.rank][par * p.world + threadIdx.x];
         bool ok = false;
@@ -98,7 +116,7 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
     if (p.out)
         for (int r = 0; r < p.world; ++r)
             for (int64_t i = first; i < p.nvec; i += stride) p.out[(int64_t)r * p.slot_vec + i] = stage[(int64_t)r * p.slot_vec + i];
-    //    and the merge of the ranks' partials, in rank order (the arithmetic of merge_shards_kernel)
+    //    the merge of the ranks' partials, in rank order (the arithmetic of merge_shards_kernel)
     if (p.merge_out) {
         const float* st = reinterpret_cast<const float*>(stage);
         const int64_t slot_words = p.slot_vec * 4;
@@ -121,13 +139,48 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
             else reinterpret_cast<float*>(p.merge_out)[idx] = v;
         }
     }
+    //    and the global selection from the ranks' candidates: row r of rank s's block holds cand_k (score, position)
+    //    pairs; the row of world * cand_k candidates is ranked in place (segments one block apart), ties towards
+    //    the lower rank and place, which is the lower position because ranks hold ascending ranges
+    if (p.cand_rows > 0) {
+        TopkParams tp;
+        const int64_t slot_words = p.slot_vec * 4;
+        tp.scores = reinterpret_cast<const float*>(stage) + p.cs_off;
+        tp.in_idx = reinterpret_cast<const int32_t*>(stage) + p.ci_off;
+        tp.in_idx_stride = p.cand_k;
+        tp.rows = p.cand_rows;
+        tp.n = (int64_t)p.world * p.cand_k;
+        tp.row_stride = p.cand_k;
+        tp.k = p.cand_select;
+        tp.out_idx = p.sel_out;
+        tp.out_val = nullptr;
+        tp.out_stride = p.sel_stride;
+        tp.idx_offset = 0;
+        tp.force_last = 0;
+        tp.own_lo = p.own_lo;
+        tp.own_hi = p.own_hi;
+        tp.out_count = p.sel_count;
+        tp.hist = nullptr;
+        tp.row_state = nullptr;
+        tp.cand = nullptr;
+        tp.sel = nullptr;
+        tp.cand_cap = 0;
+        tp.status = p.status ? p.status : &p.state[3];
+        tp.seg_len = p.cand_k;
+        tp.seg_stride = slot_words;
+        tp.row_len = nullptr;
+        for (int row = blockIdx.x; row < p.cand_rows; row += gridDim.x) {
+            topk_cluster_row(tp, row, xsm);
+            __syncthreads();
+        }
+    }
 
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence();
-        if (atomicAdd(p.fin, 1u) == gridDim.x - 1) {
-            *p.fin = 0;
-            *reinterpret_cast<volatile uint32_t*>(p.epoch) = e;
+        if (atomicAdd(&p.state[1], 1u) == gridDim.x - 1) {
+            p.state[1] = 0;
+            *reinterpret_cast<volatile uint32_t*>(&p.state[0]) = e;
         }
     }
 }
@@ -139,11 +192,12 @@ using namespace tidal;
 extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream) {
     TIDAL_REQUIRE(a != nullptr, TIDAL_ERR_ARG, "args is NULL");
     TIDAL_REQUIRE(a->d_send && a->d_peer_stage && a->d_peer_count && a->d_state, TIDAL_ERR_ARG, "null pointer");
-    TIDAL_REQUIRE(a->d_recv || a->d_merge_out, TIDAL_ERR_ARG, "neither a receive buffer nor a merge output given");
+    TIDAL_REQUIRE(a->d_recv || a->d_merge_out || a->cand_rows > 0, TIDAL_ERR_ARG,
+                  "nothing to do: no receive buffer, no merge output, no candidates to rank");
+    const int64_t words = a->bytes / 4;
     if (a->d_merge_out) {
         TIDAL_REQUIRE(a->merge_rows >= 1 && a->merge_head_dim >= 1 && a->merge_dtype >= 0 && a->merge_dtype <= 2, TIDAL_ERR_ARG,
                       "bad merge geometry");
-        const int64_t words = a->bytes / 4;
         TIDAL_REQUIRE(a->merge_m_off >= 0 && a->merge_m_off + a->merge_rows <= words && a->merge_l_off >= 0 &&
                           a->merge_l_off + a->merge_rows <= words && a->merge_o_off >= 0 &&
                           a->merge_o_off + (int64_t)a->merge_rows * a->merge_head_dim <= words,
@@ -156,6 +210,19 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
                   (long long)a->slot_bytes);
     TIDAL_REQUIRE((((uintptr_t)a->d_send | (uintptr_t)a->d_recv) & 15) == 0, TIDAL_ERR_ARG, "send and recv must be 16-byte aligned");
     TIDAL_REQUIRE(a->wait_limit >= 0, TIDAL_ERR_ARG, "negative wait_limit");
+    TIDAL_REQUIRE(a->cand_rows >= 0, TIDAL_ERR_ARG, "negative cand_rows");
+    if (a->cand_rows > 0) {
+        const int64_t n = (int64_t)a->world * a->cand_k, per = (int64_t)a->cand_rows * a->cand_k;
+        TIDAL_REQUIRE(a->cand_k >= 1 && a->cand_select >= 1 && a->cand_select < n, TIDAL_ERR_ARG,
+                      "candidates: need 1 <= cand_select (%d) < world * cand_k (%lld)", a->cand_select, (long long)n);
+        TIDAL_REQUIRE(a->cand_select <= kClusterMaxK && n <= kClusterSmemCandMaxN, TIDAL_ERR_ARG,
+                      "candidates are ranked in shared memory: cand_select <= %d and world * cand_k <= %lld (rank larger sets "
+                      "with tidal_topk on the receive buffer)", kClusterMaxK, (long long)kClusterSmemCandMaxN);
+        TIDAL_REQUIRE(a->cand_score_off >= 0 && a->cand_score_off + per <= words && a->cand_idx_off >= 0 &&
+                          a->cand_idx_off + per <= words, TIDAL_ERR_ARG, "the candidates lie outside the exchanged bytes");
+        TIDAL_REQUIRE(a->d_sel_out != nullptr && a->sel_stride >= a->cand_select, TIDAL_ERR_ARG,
+                      "candidates need d_sel_out with sel_stride >= cand_select");
+    }
     ExchangeParams p;
     p.send = (const uint4*)a->d_send;
     p.nvec = a->bytes / 16;
@@ -163,8 +230,7 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
     p.peer_stage = (uint4* const*)a->d_peer_stage;
     p.peer_count = (uint32_t* const*)a->d_peer_count;
     p.out = (uint4*)a->d_recv;
-    p.epoch = a->d_state;
-    p.fin = a->d_state + 1;
+    p.state = a->d_state;
     p.status = a->d_status;
     p.spin_limit = a->wait_limit > 0 ? (uint32_t)a->wait_limit : kXchgSpinLimit;
     p.rank = a->rank;
@@ -172,22 +238,26 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
     p.merge_out = a->d_merge_out;
     p.m_off = a->merge_m_off; p.l_off = a->merge_l_off; p.o_off = a->merge_o_off;
     p.merge_rows = a->merge_rows; p.merge_dim = a->merge_head_dim; p.merge_dtype = a->merge_dtype;
-    // the CTA count follows from the slot size alone: the same for every call on these buffers, on every rank
-    const int ctas = exchange_ctas(p.slot_vec);
-    TIDAL_CUDA_OK(launch_pdl(peer_all_gather_kernel, dim3((unsigned)ctas), dim3(kXchgThreads), 0, (cudaStream_t)stream, 1, p));
+    p.cand_rows = a->cand_rows; p.cand_k = a->cand_k; p.cand_select = a->cand_select;
+    p.cs_off = a->cand_score_off; p.ci_off = a->cand_idx_off;
+    p.own_lo = a->own_lo; p.own_hi = a->own_hi;
+    p.sel_out = a->d_sel_out; p.sel_stride = a->sel_stride; p.sel_count = a->d_sel_count;
+    // a CTA per candidate row, and enough CTAs to move the block in two passes; all resident at once
+    int64_t ctas = (p.nvec + 2 * kXchgThreads - 1) / (2 * kXchgThreads);
+    if (ctas < a->cand_rows) ctas = a->cand_rows;
+    if (ctas < 1) ctas = 1;
+    if (ctas > kXchgMaxCtas) ctas = kXchgMaxCtas;
+    const size_t smem = a->cand_rows > 0 ? kClusterSmem : 0;
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(peer_all_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kClusterSmem));
+    TIDAL_CUDA_OK(launch_pdl(peer_all_gather_kernel, dim3((unsigned)ctas), dim3(kXchgThreads), smem, (cudaStream_t)stream, 1, p));
     count_launch();
     return TIDAL_OK;
-}
-
-extern "C" int tidal_peer_exchange_ctas(int64_t slot_bytes) {
-    if (slot_bytes <= 0 || slot_bytes % 16) return TIDAL_ERR_ARG;
-    return exchange_ctas(slot_bytes / 16);
 }
 
 extern "C" int tidal_peer_exchange_reset(uint32_t* d_count, uint32_t* d_state, int world, void* stream) {
     TIDAL_REQUIRE(d_count && d_state, TIDAL_ERR_ARG, "null pointer");
     TIDAL_REQUIRE(world >= 2 && world <= kXchgMaxWorld, TIDAL_ERR_ARG, "bad world %d (2..%d ranks)", world, kXchgMaxWorld);
     TIDAL_CUDA_OK(cudaMemsetAsync(d_count, 0, sizeof(uint32_t) * 2 * world, (cudaStream_t)stream));
-    TIDAL_CUDA_OK(cudaMemsetAsync(d_state, 0, sizeof(uint32_t) * 2, (cudaStream_t)stream));
+    TIDAL_CUDA_OK(cudaMemsetAsync(d_state, 0, sizeof(uint32_t) * 4, (cudaStream_t)stream));
     return TIDAL_OK;
 }

@@ -21,146 +21,12 @@
 // orders and emits without touching global memory again.  Larger problems split
 // the histogram and the scan over many independent CTAs per row with lists in
 // global memory (block-then-global) and finish with one CTA per row.
-#include <cooperative_groups.h>
-
+#include <cstdlib>
 #include <mutex>
 
-#include "common.cuh"
-
-namespace cg = cooperative_groups;
+#include "topk_common.cuh"
 
 namespace tidal {
-
-constexpr int kBins = TIDAL_TOPK_BINS;
-constexpr int kTopkThreads = 1024;
-constexpr int kSortMax = 4096;        // winners are position-sorted up to this k
-constexpr int kRankSortMax = 1024;    // ... by counting up to this k, by a bitonic network above
-constexpr int64_t kFusedMaxN = 1 << 18;
-
-struct TopkParams {
-    const float* scores;
-    const int32_t* in_idx;
-    int64_t in_idx_stride;
-    int32_t rows;
-    int64_t n, row_stride;
-    int32_t k;            // already min(k, n)
-    int32_t* out_idx;
-    float* out_val;
-    int64_t out_stride;
-    int32_t idx_offset, force_last, own_lo, own_hi;
-    int32_t* out_count;
-    uint32_t* hist;       // [rows][kBins] in global memory, or nullptr (fused kernel builds its own)
-    uint32_t* row_state;  // [rows][8]: 0 sel count, 1 cand count
-    uint64_t* cand;       // [rows][cand_cap]
-    uint64_t* sel;        // [rows][kMaxK]
-    int64_t cand_cap;
-    uint32_t* status;
-    int32_t seg_len;      // 0, or rows are made of segments seg_stride elements apart (cluster kernel only)
-    int64_t seg_stride;
-    const int32_t* row_len;  // nullptr, or per-row lengths on the device (cluster kernel only); n is then their bound
-};
-
-// Offset of element j of a row whose contiguous layout would start at row*stride.
-__device__ __forceinline__ size_t elem_off(const TopkParams& p, int64_t stride, int row, int64_t j) {
-    if (p.seg_len == 0) return (size_t)row * stride + (size_t)j;
-    const int64_t sg = j / p.seg_len;
-    return (size_t)sg * p.seg_stride + (size_t)row * stride + (size_t)(j - sg * p.seg_len);
-}
-
-__device__ __forceinline__ uint64_t make_key(float s, uint32_t pos, int64_t n, int force_last) {
-    uint32_t k32 = ordered_key(s);
-    if (force_last && (int64_t)pos == n - 1) k32 = 0xFFFFFFFFu;
-    return ((uint64_t)k32 << 32) | (uint64_t)(0xFFFFFFFFu - pos);
-}
-__device__ __forceinline__ uint32_t key_pos(uint64_t key) { return 0xFFFFFFFFu - (uint32_t)(key & 0xFFFFFFFFull); }
-__device__ __forceinline__ int key_bin(uint64_t key) { return (int)((uint32_t)(key >> 32) >> kDigit0Shift); }
-
-// Inclusive scan over the kTopkThreads threads of the block; `ws` has 32 words.
-// Ends with a barrier, so `ws` may be reused at once.
-__device__ __forceinline__ uint32_t block_scan_incl(uint32_t v, uint32_t* ws) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t n = __shfl_up_sync(0xffffffffu, v, off);
-        if (lane >= off) v += n;
-    }
-    if (lane == 31) ws[warp] = v;
-    __syncthreads();
-    if (warp == 0) {
-        uint32_t w = ws[lane];
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const uint32_t n = __shfl_up_sync(0xffffffffu, w, off);
-            if (lane >= off) w += n;
-        }
-        ws[lane] = w;
-    }
-    __syncthreads();
-    if (warp > 0) v += ws[warp - 1];
-    __syncthreads();
-    return v;
-}
-
-// Threshold bin b*: count(bins > b*) < k <= count(bins >= b*).  `h` is a shared
-// copy of the row's histogram; every thread returns the same (bin, above).
-__device__ void find_threshold_bin(const uint32_t* h, uint32_t* ws, uint32_t k, int* bin_out, uint32_t* above_out) {
-    constexpr int per = kBins / kTopkThreads;     // 4 bins per thread, thread 0 owns the top ones
-    const int t = threadIdx.x;
-    const int base = kBins - (t + 1) * per;
-    uint32_t mine = 0;
-#pragma unroll
-    for (int i = 0; i < per; ++i) mine += h[base + i];
-    const uint32_t incl = block_scan_incl(mine, ws), excl = incl - mine;
-    __shared__ int s_bin;
-    __shared__ uint32_t s_above;
-    if (t == 0) { s_bin = 0; s_above = 0; }
-    __syncthreads();
-    if (excl < k && k <= incl) {
-        uint32_t above = excl;
-        for (int i = per - 1; i >= 0; --i) {
-            const uint32_t c = h[base + i];
-            if (above + c >= k) { s_bin = base + i; s_above = above; break; }
-            above += c;
-        }
-    }
-    __syncthreads();
-    *bin_out = s_bin;
-    *above_out = s_above;
-    __syncthreads();
-}
-
-// One warp finds, in a 256-bin digit histogram, the digit d with
-// count(digits > d) < need <= count(digits >= d).  Results through shared words.
-__device__ __forceinline__ void warp_find_digit(const uint32_t* h, int nbins, uint32_t need, uint32_t* s_digit,
-                                                uint32_t* s_need, uint32_t* s_done) {
-    const int lane = threadIdx.x & 31;
-    const int per = nbins / 32 > 0 ? nbins / 32 : 1;      // 8 bins per lane (256), or 1 with 16 active lanes (16)
-    const bool active = lane * per < nbins;
-    const int base = nbins - (lane + 1) * per;            // lane 0 owns the top bins
-    uint32_t mine = 0;
-    if (active)
-        for (int i = 0; i < per; ++i) mine += h[base + i];
-    uint32_t incl = mine;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const uint32_t n = __shfl_up_sync(0xffffffffu, incl, off);
-        if (lane >= off) incl += n;
-    }
-    const uint32_t excl = incl - mine;
-    if (active && excl < need && need <= incl) {
-        uint32_t above = excl;
-        for (int i = per - 1; i >= 0; --i) {
-            const uint32_t c = h[base + i];
-            if (above + c >= need) {
-                *s_digit = (uint32_t)(base + i);
-                *s_need = need - above;
-                *s_done = (c == need - above) ? 1u : 0u;
-                break;
-            }
-            above += c;
-        }
-    }
-}
 
 __global__ void __launch_bounds__(kTopkThreads) topk_hist_kernel(const TopkParams p) {
     __shared__ uint32_t h[kBins];
@@ -429,277 +295,26 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
 }
 
 
-// ------------------------------------------------------------------ cluster path
-constexpr int kClusterMaxK = 2048;            // winners kept in shared memory
-constexpr int kClusterCand = 4096;            // candidates kept in shared memory
-constexpr int64_t kClusterMaxN = 1 << 21;
-constexpr int64_t kClusterSmemCandMaxN = 1 << 16;   // longer rows keep their candidates in the workspace
-constexpr size_t kClusterSmem = sizeof(uint32_t) * kBins                       // h
-                                + sizeof(uint64_t) * (kClusterMaxK + kClusterCand);  // lists (first CTA) / local histogram
-
-struct ClusterShared {
-    uint32_t nsel, ncand, cnt, digit, need, done;
-};
-
-template <typename F>
-__device__ __forceinline__ void for_each_cluster_candidate(const TopkParams& p, int row, int bstar, const uint64_t* cand,
-                                                           uint32_t ncand, bool overflow, F f) {
-    if (!overflow) {
-        for (uint32_t j = threadIdx.x; j < ncand; j += kTopkThreads) f(cand[j]);
-    } else {
-        for (int64_t j = threadIdx.x; j < p.n; j += kTopkThreads) {
-            const uint64_t key = make_key(p.scores[elem_off(p, p.row_stride, row, j)], (uint32_t)j, p.n, p.force_last);
-            if (key_bin(key) == bstar) f(key);
-        }
-    }
-}
-
-__global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkParams p_in) {
+// The one-launch path: one cluster of up to 8 CTAs per row (topk_cluster_row, topk_common.cuh).
+__global__ void __launch_bounds__(kTopkThreads) topk_cluster_kernel(const TopkParams p) {
     extern __shared__ __align__(16) unsigned char csm[];
-    TopkParams p = p_in;
-    uint32_t* h = reinterpret_cast<uint32_t*>(csm);                                   // [kBins]
-    uint64_t* sel = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);      // [kClusterMaxK]
-    // Candidates of the threshold bin: in shared memory for short rows; long rows can put thousands of
-    // keys into one bin (e.g. 1 % of 1 M tokens with high affinity), so theirs go to the workspace.
-    const bool cand_global = p.n > kClusterSmemCandMaxN && p.cand != nullptr;
-    uint64_t* cand = cand_global ? p.cand + (size_t)blockIdx.x / cg::this_cluster().num_blocks() * p.cand_cap
-                                 : sel + kClusterMaxK;                                // [kClusterCand] in shared memory
-    const uint32_t cand_capacity = cand_global ? (uint32_t)min(p.cand_cap, (int64_t)0x7fffffff) : (uint32_t)kClusterCand;
-    uint32_t* h_local = reinterpret_cast<uint32_t*>(sel);                             // own-slice histogram (no-hist path)
-    __shared__ uint32_t ws[32];
-    __shared__ ClusterShared sh;
     pdl_wait();
     pdl_launch_dependents();
+    topk_cluster_row(p, (int)(blockIdx.x / cg::this_cluster().num_blocks()), csm);
+}
 
-    cg::cluster_group cluster = cg::this_cluster();
-    const unsigned CS = cluster.num_blocks();
-    const unsigned rank = cluster.block_rank();
-    const int row = blockIdx.x / CS;
-    const int t = threadIdx.x;
-    if (p.row_len) {
-        // the row's length lives on the device (a decode step replayed as a CUDA graph grows it every step)
-        const int64_t n_dev = max(0, p.row_len[row]);
-        p.n = min(p.n, n_dev);
-        p.k = (int32_t)min((int64_t)p.k, p.n);
-        if (p.n == 0) {                       // uniform over the cluster: nobody reaches a cluster barrier
-            if (rank == 0 && t == 0 && p.out_count) p.out_count[row] = 0;
-            return;
+// Largest cluster the one-launch path uses per row (8).  TIDAL_TOPK_MAX_CLUSTER=1|2|4|8 in the environment
+// lowers it — a tuning knob for measurements, read once.
+static int topk_max_cluster() {
+    static int v = 0;
+    if (v == 0) {
+        v = 8;
+        if (const char* e = std::getenv("TIDAL_TOPK_MAX_CLUSTER")) {
+            const int x = std::atoi(e);
+            if (x == 1 || x == 2 || x == 4 || x == 8) v = x;
         }
     }
-    const float* srow = p.seg_len ? nullptr : p.scores + (size_t)row * p.row_stride;   // contiguous rows only
-    auto score_at = [&](int64_t j) -> float { return p.scores[elem_off(p, p.row_stride, row, j)]; };
-    const uint32_t k = (uint32_t)p.k;
-    const int64_t per = ((p.n + CS - 1) / CS + 3) & ~(int64_t)3;      // slice length, a multiple of 4
-    const int64_t lo = (int64_t)rank * per, hi = min(p.n, lo + per);
-
-    if (t == 0) { sh.nsel = 0; sh.ncand = 0; sh.cnt = 0; }
-
-    // ---- digit-0 histogram of the whole row into h
-    if (p.hist) {
-        for (int i = t; i < kBins; i += kTopkThreads) h[i] = p.hist[(size_t)row * kBins + i];
-        cluster.sync();            // the first CTA's counters are initialised before anyone pushes to them
-    } else {
-        for (int i = t; i < kBins; i += kTopkThreads) h_local[i] = 0;
-        __syncthreads();
-#pragma unroll 4
-        for (int64_t j = lo + t; j < hi; j += kTopkThreads)
-            atomicAdd(&h_local[key_bin(make_key(score_at(j), (uint32_t)j, p.n, p.force_last))], 1u);
-        cluster.sync();
-        for (int i = t; i < kBins; i += kTopkThreads) {
-            uint32_t a = 0;
-            for (unsigned r = 0; r < CS; ++r) a += cluster.map_shared_rank(h_local, r)[i];
-            h[i] = a;
-        }
-        cluster.sync();            // every CTA has read every local histogram: the list area may be written now
-    }
-    int bstar;
-    uint32_t above;
-    find_threshold_bin(h, ws, k, &bstar, &above);
-
-    // ---- scan the slice into this CTA's own lists (local shared-memory atomics), then hand them
-    //      over to the first CTA in two bulk copies: one remote atomic per CTA instead of one per key
-    __shared__ uint32_t my_nsel, my_ncand, base_sel, base_cand;
-    uint64_t* my_sel = sel;                      // [kClusterMaxK]   (every CTA has the same layout)
-    uint64_t* my_cand = sel + kClusterMaxK;      // [kClusterCand]
-    if (t == 0) { my_nsel = 0; my_ncand = 0; }
-    __syncthreads();
-    {
-        auto push = [&](float v, int64_t j) {
-            const uint64_t key = make_key(v, (uint32_t)j, p.n, p.force_last);
-            const int bin = key_bin(key);
-            if (bin > bstar) {
-                const uint32_t at = atomicAdd(&my_nsel, 1u);
-                if (at < (uint32_t)kClusterMaxK) my_sel[at] = key;
-            } else if (bin == bstar) {
-                const uint32_t at = atomicAdd(&my_ncand, 1u);
-                if (at < (uint32_t)kClusterCand) my_cand[at] = key;
-            }
-        };
-        const bool vec_ok = p.seg_len == 0 && ((reinterpret_cast<uintptr_t>(srow) & 15) == 0);
-        if (vec_ok) {
-            const int64_t hi4 = lo + ((hi - lo) & ~(int64_t)3);
-#pragma unroll 2
-            for (int64_t j = lo + 4 * (int64_t)t; j < hi4; j += 4 * kTopkThreads) {
-                const float4 v = *reinterpret_cast<const float4*>(srow + j);
-                push(v.x, j); push(v.y, j + 1); push(v.z, j + 2); push(v.w, j + 3);
-            }
-            for (int64_t j = hi4 + t; j < hi; j += kTopkThreads) push(srow[j], j);
-        } else {
-#pragma unroll 4
-            for (int64_t j = lo + t; j < hi; j += kTopkThreads) push(score_at(j), j);
-        }
-    }
-    __syncthreads();
-    if (CS > 1 || cand_global) {
-        ClusterShared* sh0 = cluster.map_shared_rank(&sh, 0);
-        // a CTA whose own candidate list overflowed reports a count beyond any capacity: the resolver
-        // then rescans the row instead of trusting the lists
-        const uint32_t nc = my_ncand > (uint32_t)kClusterCand ? 0x40000000u : my_ncand;
-        if (t == 0) {
-            base_sel = atomicAdd(&sh0->nsel, my_nsel);
-            base_cand = atomicAdd(&sh0->ncand, nc);
-        }
-        __syncthreads();
-        uint64_t* sel0 = cluster.map_shared_rank(sel, 0);
-        uint64_t* cand0 = cand_global ? cand : cluster.map_shared_rank(sel + kClusterMaxK, 0);
-        // read everything this thread will move before anyone writes (rank 0's source is its destination array)
-        constexpr int kSelPer = kClusterMaxK / kTopkThreads, kCandPer = kClusterCand / kTopkThreads;
-        uint64_t vs[kSelPer], vc[kCandPer];
-        const uint32_t ns = min(my_nsel, (uint32_t)kClusterMaxK), ncl = min(my_ncand, (uint32_t)kClusterCand);
-#pragma unroll
-        for (int u = 0; u < kSelPer; ++u) vs[u] = (t + u * kTopkThreads < ns) ? my_sel[t + u * kTopkThreads] : 0;
-#pragma unroll
-        for (int u = 0; u < kCandPer; ++u) vc[u] = (t + u * kTopkThreads < ncl) ? my_cand[t + u * kTopkThreads] : 0;
-        cluster.sync();               // all CTAs hold their keys in registers and know their offsets
-#pragma unroll
-        for (int u = 0; u < kSelPer; ++u) {
-            const uint32_t i = t + u * kTopkThreads;
-            if (i < ns && base_sel + i < (uint32_t)kClusterMaxK) sel0[base_sel + i] = vs[u];
-        }
-        if (nc < 0x40000000u) {
-#pragma unroll
-            for (int u = 0; u < kCandPer; ++u) {
-                const uint32_t i = t + u * kTopkThreads;
-                if (i < ncl && base_cand + i < cand_capacity) cand0[base_cand + i] = vc[u];
-            }
-        }
-    } else if (t == 0) {
-        sh.nsel = my_nsel;            // single CTA, lists already in place
-        sh.ncand = my_ncand;
-    }
-    cluster.sync();
-    if (rank != 0) return;
-
-    // ---- first CTA: resolve, order, emit — all in shared memory
-    int32_t* out_idx = p.out_idx + (size_t)row * p.out_stride;
-    float* out_val = p.out_val ? p.out_val + (size_t)row * p.out_stride : nullptr;
-    const bool own = p.own_hi > p.own_lo;
-    const uint32_t nsel = min(sh.nsel, (uint32_t)kClusterMaxK);
-    const uint32_t ncand_total = sh.ncand;
-    const bool overflow = ncand_total > cand_capacity;
-    uint32_t need = k - above;
-    if (sh.nsel != above && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
-
-    // Few candidates in shared memory (the usual case: a 12-bit first digit leaves a few dozen keys in the
-    // threshold bin): rank them directly — keys are distinct, so the `need` largest are those with fewer
-    // than `need` larger ones — instead of up to seven more radix passes with four barriers each.
-    const bool few = !overflow && !cand_global && ncand_total <= 256u && need <= ncand_total;
-    if (few) {
-        if ((uint32_t)t < ncand_total) {
-            const uint64_t key = cand[t];
-            uint32_t larger = 0;
-            for (uint32_t i = 0; i < ncand_total; ++i) larger += cand[i] > key ? 1u : 0u;
-            if (larger < need) {
-                const uint32_t at = nsel + atomicAdd(&sh.cnt, 1u);
-                if (at < (uint32_t)kClusterMaxK) sel[at] = key;
-            }
-        }
-        __syncthreads();
-    }
-    uint64_t prefix = (uint64_t)bstar << 52;
-    uint64_t known_mask = 0xFFFull << 52;
-    bool done = few || (need == ncand_total);
-    for (int shift = 44; !done && shift >= -4; shift -= 8) {
-        const int sft = shift < 0 ? 0 : shift;
-        const int nb = shift < 0 ? 16 : 256;
-        const uint32_t dmask = (uint32_t)nb - 1u;
-        if (t < 256) h[t] = 0;
-        __syncthreads();
-        for_each_cluster_candidate(p, row, bstar, cand, ncand_total, overflow, [&](uint64_t key) {
-            if ((key & known_mask) == prefix) atomicAdd(&h[(uint32_t)(key >> sft) & dmask], 1u);
-        });
-        __syncthreads();
-        if (t < 32) warp_find_digit(h, nb, need, &sh.digit, &sh.need, &sh.done);
-        __syncthreads();
-        prefix |= (uint64_t)sh.digit << sft;
-        known_mask |= (uint64_t)dmask << sft;
-        need = sh.need;
-        done = sh.done != 0;
-        __syncthreads();
-    }
-    const uint64_t thr = prefix;
-
-    // winners: sel[0, nsel) plus the candidates at or above the threshold, appended behind them
-    if (!few) {
-        for_each_cluster_candidate(p, row, bstar, cand, ncand_total, overflow, [&](uint64_t key) {
-            if (key >= thr) {
-                const uint32_t at = nsel + atomicAdd(&sh.cnt, 1u);
-                if (at < (uint32_t)kClusterMaxK) sel[at] = key;
-            }
-        });
-        __syncthreads();
-    }
-    const uint32_t got = min(nsel + sh.cnt, k);
-    if (nsel + sh.cnt != k && t == 0) atomicOr(p.status, TIDAL_DEV_TOPK_OVERFLOW);
-    // order by position: a key's low word is 0xFFFFFFFF - position, so rank by descending low word
-    uint64_t mine[kClusterMaxK / kTopkThreads];
-    uint32_t rank_of[kClusterMaxK / kTopkThreads];
-#pragma unroll
-    for (int u = 0; u < kClusterMaxK / kTopkThreads; ++u) {
-        const uint32_t j = t + u * kTopkThreads;
-        rank_of[u] = 0;
-        mine[u] = 0;
-        if (j < got) {
-            mine[u] = sel[j];
-            const uint32_t lowm = (uint32_t)mine[u];
-            uint32_t r = 0;
-            for (uint32_t i = 0; i < got; ++i) r += ((uint32_t)sel[i] > lowm) ? 1u : 0u;
-            rank_of[u] = r;
-        }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int u = 0; u < kClusterMaxK / kTopkThreads; ++u)
-        if (t + u * kTopkThreads < got) sel[rank_of[u]] = mine[u];
-    __syncthreads();
-    // emit in order with the ownership filter
-    uint32_t before = 0;
-    for (uint32_t base = 0; base < got; base += kTopkThreads) {
-        const uint32_t j = base + t;
-        int32_t v = 0;
-        float sc = 0.f;
-        bool keep = false;
-        if (j < got) {
-            const uint64_t key = sel[j];
-            const uint32_t pos = key_pos(key);
-            v = p.in_idx ? p.in_idx[elem_off(p, p.in_idx_stride, row, pos)] : (int32_t)pos + p.idx_offset;
-            keep = !own || (v >= p.own_lo && v < p.own_hi);
-            if (out_val) sc = (p.force_last && (int64_t)pos == p.n - 1) ? score_at(pos) : key_to_float((uint32_t)(key >> 32));
-        }
-        const uint32_t incl = block_scan_incl(keep ? 1u : 0u, ws);
-        if (keep) {
-            const uint32_t at = before + incl - 1;
-            out_idx[at] = own ? v - p.own_lo : v;
-            if (out_val) out_val[at] = sc;
-        }
-        if (t == kTopkThreads - 1) sh.cnt = before + incl;
-        __syncthreads();
-        before = sh.cnt;
-        __syncthreads();
-    }
-    if (t == 0 && p.out_count) p.out_count[row] = (int32_t)before;
-    if (p.hist)
-        for (int i = t; i < kBins; i += kTopkThreads) p.hist[(size_t)row * kBins + i] = 0;
+    return v;
 }
 
 }  // namespace tidal
@@ -750,7 +365,7 @@ extern "C" int tidal_topk(const tidal_topk_args* a, void* d_ws, size_t ws_bytes,
     }
     if (k <= kClusterMaxK && a->n <= kClusterMaxN) {
         // one cluster per row; 8 CTAs unless the row is short
-        int cs = 8;
+        int cs = topk_max_cluster();
         while (cs > 1 && a->n < (int64_t)cs * 2048) cs >>= 1;
         // per launch, like every other kernel here: the attribute belongs to the current device, and a process
         // may drive several

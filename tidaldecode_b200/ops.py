@@ -443,7 +443,7 @@ class PeerExchange:
         self.peer_stage = torch.tensor(ptrs, **i64)
         self.peer_count = torch.tensor([p + count_off for p in ptrs], **i64)
         self._own_count = ptrs[self.rank] + count_off
-        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)
 
     @classmethod
     def loopback(cls, slot_bytes: int, world: int, device, wait_limit: int = 0) -> "PeerExchange":
@@ -462,10 +462,6 @@ class PeerExchange:
         self.counters = self.buf[count_off:count_off + 8 * self.world].view(torch.int32).view(2, self.world)
         return self
 
-    @property
-    def ctas(self) -> int:
-        return lib.tidal_peer_exchange_ctas(self.slot_bytes)
-
     def reset(self) -> None:
         """Arrival counters and exchange count back to zero after a timed-out exchange.  A collective in
         effect: every rank calls it, with none of the group's exchanges in flight."""
@@ -482,10 +478,14 @@ class PeerExchange:
             dist.barrier(self.group)
 
     def all_gather(self, send: torch.Tensor, recv: Optional[torch.Tensor], nbytes: Optional[int] = None,
-                   status: Optional[torch.Tensor] = None, merge: Optional[tuple] = None) -> None:
+                   status: Optional[torch.Tensor] = None, merge: Optional[tuple] = None,
+                   candidates: Optional[dict] = None) -> None:
         """recv [world, slot] (any dtype, slot_bytes per row) <- the first nbytes of every rank's `send`.
         merge = (out [rows, D], m_off, l_off, o_off): the blocks hold softmax partials at these fp32 word offsets
-        and their merge goes to `out` in the same launch; recv may then be None."""
+        and their merge goes to `out` in the same launch; recv may then be None.
+        candidates = dict(rows, k, select, score_off, idx_off, own=(lo, hi), out=int32 [rows, >= select],
+        count=int32 [rows]): the blocks also hold top-k candidates, ranked in the same launch (see
+        tidal_exchange_args in include/tidal_b200.h)."""
         _need_cuda(send, recv, status)
         nbytes = send.numel() * send.element_size() if nbytes is None else int(nbytes)
         if recv is not None and recv.numel() * recv.element_size() < self.world * self.slot_bytes:
@@ -502,5 +502,14 @@ class PeerExchange:
         a.d_state, a.d_status = self.state.data_ptr(), _ptr(status)
         a.rank, a.world = self.rank, self.world
         a.wait_limit = self.wait_limit
+        if candidates is not None:
+            c = candidates
+            _need_cuda(c["out"], c["count"])
+            if c["out"].dtype != torch.int32 or c["count"].dtype != torch.int32:
+                raise RuntimeError("candidate outputs must be int32")
+            a.cand_rows, a.cand_k, a.cand_select = int(c["rows"]), int(c["k"]), int(c["select"])
+            a.cand_score_off, a.cand_idx_off = int(c["score_off"]), int(c["idx_off"])
+            a.own_lo, a.own_hi = int(c["own"][0]), int(c["own"][1])
+            a.d_sel_out, a.sel_stride, a.d_sel_count = c["out"].data_ptr(), c["out"].shape[-1], c["count"].data_ptr()
         with torch.cuda.device(send.device):
             check(lib.tidal_peer_all_gather(C.byref(a), _stream()), "tidal_peer_all_gather")

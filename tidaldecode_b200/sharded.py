@@ -170,21 +170,32 @@ class ShardedDecodeAttention:
         return (s[L["m"]:L["l"]].view(B, Hq), s[L["l"]:L["o"]].view(B, Hq), s[L["o"]:L["cs"]].view(B, Hq, D),
                 s[L["cs"]:L["ci"]].view(R, k), s[L["ci"]:L["total"]].view(torch.int32).view(R, k))
 
-    def _all_gather(self, words: Optional[int] = None) -> bool:
+    def _all_gather(self, words: Optional[int] = None, rank_candidates: bool = False, want_recv: bool = True) -> bool:
         """Every rank's packed block into recv; `words`: only the leading fp32 words are needed (sparse layers
         exchange the partials, not the candidate lists, and need no receive buffer).  True if the exchange also
-        merged the partials into self.out (the peer-store kernel does)."""
+        merged the partials into self.out and — with rank_candidates — ranked the candidates into
+        sel_local / sel_count (the peer-store kernel does both in its one launch)."""
         if self.world == 1:
             self.recv[0].copy_(self.send)
         elif self.peer is not None:
             L = self.layout
             n = L["total"] if words is None else (words + 3) // 4 * 4
-            self.peer.all_gather(self.send, self.recv if words is None else None, nbytes=n * 4, status=self._xstatus,
-                                 merge=(self.out.view(-1, self.D), L["m"], L["l"], L["o"]))
+            cand = None
+            if rank_candidates:
+                cand = dict(rows=self.rows, k=self.k, select=self.k_global, score_off=L["cs"], idx_off=L["ci"],
+                            own=(self.lo, max(self.hi, self.lo + 1)), out=self.sel_local, count=self.sel_count)
+            self.peer.all_gather(self.send, self.recv if (words is None and want_recv) else None, nbytes=n * 4,
+                                 status=self._xstatus, merge=(self.out.view(-1, self.D), L["m"], L["l"], L["o"]),
+                                 candidates=cand)
             return True
         else:
             dist.all_gather_into_tensor(self.recv.view(-1), self.send, group=self.group)
         return False
+
+    @property
+    def _fused_ranking(self) -> bool:
+        """The peer-store kernel ranks the candidates itself when they fit its shared-memory form."""
+        return self.peer is not None and self.k_global <= 2048 and self.world * self.k <= 65536 and self.k_global < self.world * self.k
 
     def exchange_status(self) -> int:
         """Fault bits of the peer exchange (0 when the library all-gather is in use)."""
@@ -214,15 +225,17 @@ class ShardedDecodeAttention:
             m.fill_(-float("inf"))
             l.zero_()
             o.zero_()
-        if not self._all_gather():
+        fused = self._fused_ranking
+        if not self._all_gather(rank_candidates=fused, want_recv=want_global or not fused):
             ops.merge_partials(self._rm, self._rl, self._ro, self.dtype, out=self.out, geometry=self._partial_geom)
         # global top-k of the world*k candidates, read in place; keep the positions this rank owns
         n_cand = self.world * k
-        if want_global:
+        if want_global:          # the whole global set, for callers that inspect it (the layers only need the owned part)
             ops.topk(self._rcs, self.k_global, self.ws, n=n_cand, in_idx=self._rci, out_idx=self.sel_global,
                      segments=self._cand_segments)
-        ops.topk(self._rcs, self.k_global, self.ws, n=n_cand, in_idx=self._rci, out_idx=self.sel_local,
-                 own_range=(self.lo, max(self.hi, self.lo + 1)), out_count=self.sel_count, segments=self._cand_segments)
+        if not fused:
+            ops.topk(self._rcs, self.k_global, self.ws, n=n_cand, in_idx=self._rci, out_idx=self.sel_local,
+                     own_range=(self.lo, max(self.hi, self.lo + 1)), out_count=self.sel_count, segments=self._cand_segments)
         if self.local_len == 0:
             self.sel_count.zero_()
         return self.out
