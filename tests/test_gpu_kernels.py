@@ -728,3 +728,66 @@ def test_peer_exchange_wait_runs_out_and_reset_recovers(T):
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     assert torch.equal(recv[0, :half], send[:half]) and torch.equal(recv[1, :half], other[:half])
+
+
+@pytest.mark.parametrize("world,B,Hq,D,k,rows_per_seq,dt", [
+    (2, 2, 8, 64, 24, 1, "f32"), (4, 4, 32, 128, 128, 1, "bf16"), (8, 8, 64, 128, 1024, 1, "bf16"),
+    (4, 1, 32, 128, 256, 1, "f16"), (2, 2, 8, 128, 48, 8, "bf16"),
+])
+def test_peer_exchange_merges_and_ranks_in_one_launch(T, world, B, Hq, D, k, rows_per_seq, dt):
+    """The exchange kernel's own merge of the ranks' partials and its ranking of their candidates against
+    tidal_merge_partials and tidal_topk on the gathered blocks.  One GPU stands for all ranks: rank 0's
+    kernel runs, the other ranks' blocks and arrivals are placed by the host beforehand (nothing waits on
+    another kernel).  Twice, so that both parities of the double buffer are used."""
+    from tidaldecode_b200.sharded import pack_layout
+
+    dev = torch.device("cuda", 0)
+    dtype = DT[dt]
+    rows = B * rows_per_seq
+    L = pack_layout(B, Hq, D, rows, k)
+    tot = (L["total"] + 3) // 4 * 4
+    px = T.PeerExchange.loopback(tot * 4, world, dev, wait_limit=100000)
+    g = torch.Generator().manual_seed(world * 100 + k)
+    n_loc = 5 * k                                                   # positions per rank
+    ws = T.Workspace(B, Hq, D, rows, world * k)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for exchange in range(1, 4):
+        blocks = torch.zeros(world, tot)
+        for r in range(world):
+            blocks[r, L["m"]:L["l"]] = torch.randn(B * Hq, generator=g) * 3
+            blocks[r, L["l"]:L["o"]] = torch.rand(B * Hq, generator=g) + 0.5
+            blocks[r, L["o"]:L["cs"]] = torch.randn(B * Hq * D, generator=g)
+            sc = torch.round(torch.randn(rows, k, generator=g) * 8) / 8         # ties across ranks
+            pos = torch.stack([torch.sort(torch.randperm(n_loc, generator=g)[:k]).values for _ in range(rows)]) + r * n_loc
+            blocks[r, L["cs"]:L["ci"]] = sc.reshape(-1)
+            blocks[r, L["ci"]:L["ci"] + rows * k] = pos.to(torch.int32).view(torch.float32).reshape(-1)
+        if exchange == 2:
+            blocks[1, L["m"]:L["l"]] = -float("inf")                 # a rank that attended nothing
+        blocks = blocks.to(dev)
+        par = exchange & 1
+        for r in range(1, world):
+            px.stage[par, r].copy_(blocks[r].view(torch.uint8))
+            px.counters[par, r] = (exchange + 1) // 2
+        own = (2 * n_loc, 3 * n_loc) if world > 2 else (0, n_loc)
+        out = torch.full((B * Hq, D), float("nan"), dtype=dtype, device=dev)
+        sel = torch.full((rows, k), -1, dtype=torch.int32, device=dev)
+        cnt = torch.full((rows,), -1, dtype=torch.int32, device=dev)
+        recv = torch.zeros(world, tot, device=dev)
+        px.all_gather(blocks[0].contiguous(), recv, status=status, merge=(out, L["m"], L["l"], L["o"]),
+                      candidates=dict(rows=rows, k=k, select=k, score_off=L["cs"], idx_off=L["ci"], own=own, out=sel, count=cnt))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.equal(recv, blocks)
+        flat = recv.view(-1)
+        want = T.merge_partials(flat[L["m"]:], flat[L["l"]:], flat[L["o"]:], dtype, geometry=(world, B, Hq, D, tot))
+        assert torch.equal(out.view(B, Hq, D), want)
+        want_sel = torch.full((rows, k), -1, dtype=torch.int32, device=dev)
+        want_cnt = torch.zeros(rows, dtype=torch.int32, device=dev)
+        T.topk(flat[L["cs"]:], k, ws, n=world * k, in_idx=flat.view(torch.int32)[L["ci"]:], out_idx=want_sel, own_range=own,
+               out_count=want_cnt, segments=(rows, k, tot, k))
+        torch.cuda.synchronize()
+        assert torch.equal(cnt, want_cnt)
+        for r in range(rows):
+            c = int(cnt[r])
+            assert torch.equal(sel[r, :c], want_sel[r, :c])
+    assert ws.status() == 0
