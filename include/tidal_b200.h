@@ -252,6 +252,51 @@ typedef struct tidal_rope_append_args {
 
 int tidal_rope_append(const tidal_rope_append_args* args, void* stream);
 
+/* ------------------------------------------------- Quest page metadata (legacy)
+ * The reference keeps, next to the KV pool, a second paged pool of the same layout with one ENTRY per
+ * KV page: plane 0 holds the element-wise maximum, plane 1 the minimum of the page's keys; its append
+ * kernels maintain it (kernels/include/decode/decode_page.cuh:393-444 for one new token, :466-557 for a
+ * prompt) and estimate_attn_score reads it (tidal/ops/csrc/estimate.cu:6-84 -> MaxPossibleSampleWithPagedKVCache,
+ * kernels/include/decode/decode_attn.cuh:141-172, 249-405).  TidalDecode's own layers use neither; they are
+ * here for callers of the reference's full operator surface.
+ *
+ * tidal_update_page_meta recomputes the entries of the KV pages that hold positions [first_pos, seq_len)
+ * of every sequence from the keys now in the pool (call it after the append: one token -> first_pos =
+ * seq_len - 1).  Entry e of a sequence (= its e-th KV page) lives in metadata page
+ * d_meta_table[b][e / meta_page_size] (NULL: page b * meta_table_stride + e / meta_page_size), slot
+ * e % meta_page_size.  Recomputing from the pool instead of folding the new key into the stored bounds
+ * gives the same values and needs no "first token of a page" initialisation. */
+typedef struct {
+    const void* d_kv;            /* [num_pages][2][page_size][Hkv][D] */
+    void* d_meta;                /* [num_meta_pages][2][meta_page_size][Hkv][D] */
+    const int32_t* d_page_table; /* as in tidal_attn_args */
+    int64_t page_table_stride;
+    const int32_t* d_meta_table;
+    int64_t meta_table_stride;
+    int32_t batch, num_kv_heads, head_dim, page_size, meta_page_size, dtype;
+    int64_t num_pages, num_meta_pages;
+    int32_t first_pos, seq_len;
+    uint32_t* d_status;          /* NULL or a device word that receives TIDAL_DEV_* bits */
+} tidal_page_meta_args;
+int tidal_update_page_meta(const tidal_page_meta_args* args, void* stream);
+
+/* out[b][h][e] = sum_d max(q[b][h][d] * max_e[d], q[b][h][d] * min_e[d]) for the first n_entries entries of
+ * every sequence: an upper bound of q.k over the keys of KV page e (no 1/sqrt(D) scale, as in the
+ * reference).  The reference leaves out the last entry — the page still being filled — by passing
+ * n_entries = entries - 1 (estimate.cu:52-54).  Query head h reads KV head h / (Hq / Hkv). */
+typedef struct {
+    const void* d_q;             /* [batch][Hq][D] */
+    const void* d_meta;
+    const int32_t* d_meta_table;
+    int64_t meta_table_stride;
+    void* d_out;                 /* [batch][Hq][out_stride] of out_dtype */
+    int64_t out_stride;
+    int32_t batch, num_qo_heads, num_kv_heads, head_dim, meta_page_size, n_entries, dtype, out_dtype;
+    int64_t num_meta_pages;
+    uint32_t* d_status;
+} tidal_estimate_args;
+int tidal_estimate(const tidal_estimate_args* args, void* stream);
+
 /* -------------------------------------------- cross-shard merge of partials
  * o[b][h][:] = sum_r 2^(m_r-M) o_r / sum_r 2^(m_r-M) l_r over `shards` sets of
  * partials laid out [shards][batch*Hq(*D)] — what every rank runs after the

@@ -316,6 +316,30 @@ def paged_to_dense(kv_data: torch.Tensor, indices: Sequence[int], seq_len: int) 
     return K.permute(1, 0, 2)[None], V.permute(1, 0, 2)[None]
 
 
+def page_key_bounds(K: torch.Tensor, page_size: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Quest's page metadata: element-wise maximum and minimum of the keys of every KV page
+    (kernels/include/decode/decode_page.cuh:417-441 folds one key at a time into the same values).
+    K [N,H,D] of one sequence -> (max [P,H,D], min [P,H,D]), P = ceil(N / page_size); a partly filled
+    last page is bounded over the keys it holds."""
+    N = K.shape[0]
+    P = (N + page_size - 1) // page_size
+    mx = torch.stack([K[p * page_size:min(N, (p + 1) * page_size)].max(dim=0).values for p in range(P)])
+    mn = torch.stack([K[p * page_size:min(N, (p + 1) * page_size)].min(dim=0).values for p in range(P)])
+    return mx, mn
+
+
+def estimate_scores(q: torch.Tensor, kmax: torch.Tensor, kmin: torch.Tensor) -> torch.Tensor:
+    """Quest's upper bound of q.k per page: sum_d max(q_d * max_d, q_d * min_d) in fp32
+    (kernels/src/test/test_max_possible.cu:80-104; kernel kernels/include/decode/decode_attn.cuh:141-172).
+    q [Hq,D]; kmax,kmin [P,Hkv,D] -> [Hq,P]."""
+    Hq, Hkv = q.shape[0], kmax.shape[1]
+    G = Hq // Hkv
+    qf = q.float()[:, None, :]                                             # [Hq,1,D]
+    mx = kmax.float().permute(1, 0, 2).repeat_interleave(G, 0)             # [Hq,P,D]
+    mn = kmin.float().permute(1, 0, 2).repeat_interleave(G, 0)
+    return torch.maximum(qf * mx, qf * mn).sum(-1)
+
+
 # ----------------------------------------------------------------------------
 # Sequence-sharded exact merge (no reference counterpart; the chunk merge it
 # generalises is decode_attn.cuh:213-232 `sync_state` / `state_t::merge`)

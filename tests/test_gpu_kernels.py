@@ -791,3 +791,68 @@ def test_peer_exchange_merges_and_ranks_in_one_launch(T, world, B, Hq, D, k, row
             c = int(cnt[r])
             assert torch.equal(sel[r, :c], want_sel[r, :c])
     assert ws.status() == 0
+
+
+@pytest.mark.parametrize("dt,B,Hq,Hkv,D,N,page,mpage", [
+    ("f16", 1, 32, 32, 128, 1000, 16, 16),      # the reference's shape: MHA, pages of 16 (test_max_possible.cu)
+    ("bf16", 2, 8, 2, 128, 333, 16, 4), ("f32", 1, 4, 4, 64, 77, 8, 3), ("f16", 1, 8, 8, 64, 40, 1, 16),
+])
+def test_quest_page_metadata_and_estimate(T, dt, B, Hq, Hkv, D, N, page, mpage):
+    """Per-page key bounds rebuilt from the pool (after a prompt, then after single-token appends) are exactly the
+    oracle's, and the estimate equals sum_d max(q_d max_d, q_d min_d) within the reference's 1e-3 / 1e-3
+    (kernels/src/test/test_max_possible.cu:29-154)."""
+    dtype = DT[dt]
+    q, K, V = make_qkv(600 + N, B, Hq, Hkv, D, N, dtype)
+    pool, table, ppb = build_pool(K, V, page, shuffle_seed=4)
+    g = torch.Generator().manual_seed(N)
+    mper = (ppb + mpage - 1) // mpage
+    mtable = torch.randperm(B * mper + 2, generator=g)[: B * mper].view(B, mper).to(torch.int32)
+    meta = torch.full((B * mper + 2, 2, mpage, Hkv, D), float("nan")).to(dtype).cuda()
+    pd, td, mtd = pool.cuda(), table.cuda(), mtable.cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    n0 = N - 3
+    T.update_page_meta(pd, meta, n0, 0, batch=B, page_table=td, meta_table=mtd, status=status)        # the prompt
+    for n in range(n0 + 1, N + 1):                                                                        # then token by token
+        T.update_page_meta(pd, meta, n, n - 1, batch=B, page_table=td, meta_table=mtd, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    out = T.estimate(q[:, :, 0].contiguous().cuda(), meta, ppb - 1, meta_table=mtd, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    mh = meta.cpu()
+    for b in range(B):
+        want_max, want_min = O.page_key_bounds(K[b].permute(1, 0, 2), page)            # [P,Hkv,D]
+        for e in range(ppb):
+            slot = mh[int(mtable[b, e // mpage]), :, e % mpage]
+            assert torch.equal(slot[0], want_max[e]) and torch.equal(slot[1], want_min[e]), (b, e)
+        want = O.estimate_scores(q[b, :, 0], want_max, want_min)[:, : ppb - 1]
+        assert torch.allclose(out[b, :, : ppb - 1].float().cpu(), want, rtol=1e-3 if dt == "f32" else 4e-3, atol=1e-3 if dt == "f32" else 3e-2)
+
+
+def test_estimate_through_the_reference_operator_names(T):
+    """append_kv_cache_prefill / _decode maintain the metadata pool they are given and estimate_attn_score reads it,
+    with the reference's argument lists (tidal/ops/csrc/bsk_ops.h:20-76)."""
+    import tidaldecode_b200._kernels as Kn
+
+    H, D, N, page = 8, 128, 100, 16
+    q, K, V = make_qkv(77, 1, H, H, D, N, torch.float16)
+    n_pages = (N + page - 1) // page
+    pool = torch.zeros(n_pages + 1, 2, page, H, D, dtype=torch.float16, device="cuda")
+    meta = torch.zeros(2, 2, page, H, D, dtype=torch.float16, device="cuda")
+    kv_idx = torch.arange(n_pages, dtype=torch.int32, device="cuda")
+    meta_idx = torch.tensor([1], dtype=torch.int32, device="cuda")
+    indptr = torch.tensor([0, n_pages], dtype=torch.int32, device="cuda")
+    mindptr = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    Kt, Vt = K[0].permute(1, 0, 2).contiguous().cuda(), V[0].permute(1, 0, 2).contiguous().cuda()      # [N,H,D]
+    n0 = N - 1
+    p0 = (n0 + page - 1) // page
+    Kn.append_kv_cache_prefill(Kt[:n0].contiguous(), Vt[:n0].contiguous(), pool, kv_idx[:p0].contiguous(), indptr, (n0 - 1) % page + 1,
+                               int(kv_idx[p0 - 1]), meta, meta_idx, mindptr, p0, 1, 0)
+    Kn.append_kv_cache_decode(Kt[n0:N].contiguous(), Vt[n0:N].contiguous(), pool, kv_idx, indptr, (N - 1) % page + 1, int(kv_idx[-1]),
+                              meta, meta_idx, mindptr, n_pages, 1, 0)
+    o = torch.zeros(H, n_pages - 1, dtype=torch.float16, device="cuda")
+    Kn.estimate_attn_score(q[:, :, 0].contiguous().cuda(), o, meta, meta_idx, mindptr, n_pages, 1, 0)
+    torch.cuda.synchronize()
+    mx, mn = O.page_key_bounds(K[0].permute(1, 0, 2), page)
+    want = O.estimate_scores(q[0, :, 0], mx, mn)[:, : n_pages - 1]
+    assert torch.allclose(o.float().cpu(), want, rtol=4e-3, atol=3e-2)

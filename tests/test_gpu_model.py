@@ -46,17 +46,21 @@ def test_kernels_rope_append_roundtrip(K):
     assert torch.allclose(qd.cpu().float(), O.apply_rope_fp32(q, torch.arange(n0), 1e4).float(), atol=2 ** -8, rtol=0)
     idx = pages[:n0].cuda()
     indptr = torch.tensor([0, n0], dtype=torch.int32, device="cuda")
-    K.append_kv_cache_prefill(kd, v.cuda(), pool, idx, indptr, 1, int(pages[n0 - 1]), pool, idx, indptr, 1, 0, 0)
+    meta = torch.zeros_like(pool)               # Quest's per-page key bounds; with pages of one token both planes equal the key
+    K.append_kv_cache_prefill(kd, v.cuda(), pool, idx, indptr, 1, int(pages[n0 - 1]), meta, idx, indptr, 1, 0, 0)
     # one decode token
     k1 = torch.randn(1, H, D, generator=g).half().cuda()
     v1 = torch.randn(1, H, D, generator=g).half().cuda()
     idx1 = pages[: n0 + 1].cuda()
     indptr1 = torch.tensor([0, n0 + 1], dtype=torch.int32, device="cuda")
-    K.append_kv_cache_decode(k1, v1, pool, idx1, indptr1, 1, int(pages[n0]), pool, idx1, indptr1, 1, 0, 0)
+    K.append_kv_cache_decode(k1, v1, pool, idx1, indptr1, 1, int(pages[n0]), meta, idx1, indptr1, 1, 0, 0)
     want = torch.zeros(64, 2, page, H, D, dtype=torch.float16)
     O.append_paged_kv(want, pages.tolist(), n0, kd.cpu(), v)
     O.append_paged_kv(want, pages.tolist(), n0 + 1, k1.cpu(), v1.cpu())
     assert torch.equal(pool.cpu(), want)
+    assert torch.equal(meta.cpu()[:, 0], want[:, 0]) and torch.equal(meta.cpu()[:, 1], want[:, 0])
+    # no metadata pool given: the append alone (TidalDecode's own layers never read the metadata)
+    K.append_kv_cache_decode(k1, v1, pool, idx1, indptr1, 1, int(pages[n0]), None, None, None, 0, 0, 0)
     with pytest.raises(RuntimeError):
         K.append_kv_cache_decode(kd, v.cuda(), pool, idx1, indptr1, 1, 0, pool, idx1, indptr1, 1, 0, 0)   # more than one token
 

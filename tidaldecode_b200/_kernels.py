@@ -12,8 +12,9 @@ Differences a caller can observe, all of them repairs of reference defects:
   * a `qk_product` buffer passed to `forward` IS written (the reference passes it
     on only when it is empty, approx_attn.cu:137): row h, column j holds the
     logit q_h.k/sqrt(D) of the j-th listed page, the newest token last;
-  * the Quest metadata pool arguments are accepted and ignored: no model code of
-    the reference reads them (only tidal/utils/__init__.py:176-214 could).
+  * the Quest metadata pool (per-page key bounds) is maintained by the append calls when one
+    is passed, and `estimate_attn_score` reads it, as in the reference; passing None for
+    `metadata_data` skips it (TidalDecode's own layers never read it).
 """
 from __future__ import annotations
 
@@ -96,7 +97,8 @@ def apply_rope_in_place(q: torch.Tensor, k: torch.Tensor, past_kv_len: int, rope
                      rope_scale=float(rope_scale), rope_mode=2, rotate_k_in_place=True)
 
 
-def _append(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx, layout, decode: bool) -> None:
+def _append(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx, metadata_data, metadata_indices,
+            metadata_last_page_len, layout, decode: bool) -> None:
     for t, n in ((k, "k"), (v, "v"), (kv_data, "kv_data"), (kv_indices, "kv_indices")):
         _check_input(t, n)
     _check(k.dim() == 3 and v.dim() == 3, "k and v must be [seq, heads, head_dim]")
@@ -107,32 +109,46 @@ def _append(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page
     _check(kv_data.shape[3] == k.shape[1] and kv_data.shape[4] == k.shape[2], "kv_data and k disagree on heads or head_dim")
     _check(k.shape == v.shape, "k and v must have one shape")
     page_size = kv_data.shape[2]
+    n_pages = kv_indices.numel()
+    seq_len = (n_pages - 1) * page_size + int(kv_last_page_len)
     if decode:
         _check(k.shape[0] == 1, "append_kv_cache_decode takes one token")
         pos0 = int(kv_last_page_idx) * page_size + int(kv_last_page_len) - 1
         _ops.rope_append(None, k, v, kv_data, batch=1, pos0=pos0, pages_per_seq=kv_data.shape[0], rope_mode=0)
     else:
-        n_pages = kv_indices.numel()
-        seq_len = (n_pages - 1) * page_size + int(kv_last_page_len)
         _check(k.shape[0] <= seq_len, "more new tokens than the sequence holds")
         _ops.rope_append(None, k, v, kv_data, batch=1, pos0=seq_len - k.shape[0], page_table=kv_indices.view(1, -1),
                          rope_mode=0)
+    if metadata_data is not None and isinstance(metadata_data, torch.Tensor) and metadata_data.numel() > 0:
+        # Quest's per-page key bounds: one metadata entry per KV page (decode_page.cuh:417-441); the entries of the
+        # pages the new tokens landed in are recomputed from the pool
+        _check_input(metadata_data, "metadata_data")
+        _check_input(metadata_indices, "metadata_indices")
+        _check(metadata_data.dim() == 5 and metadata_data.shape[1] == 2 and metadata_data.shape[3:] == kv_data.shape[3:]
+               and metadata_data.dtype == kv_data.dtype, "metadata_data must be [pages, 2, page_size, heads, head_dim] like kv_data")
+        _check(metadata_indices.dim() == 1 and metadata_indices.dtype == torch.int32, "metadata_indices must be int32 [num_pages]")
+        entries = (metadata_indices.numel() - 1) * metadata_data.shape[2] + int(metadata_last_page_len)
+        _check(entries == n_pages, f"the metadata must hold one entry per KV page ({entries} entries, {n_pages} pages)")
+        _ops.update_page_meta(kv_data, metadata_data, seq_len, seq_len - k.shape[0], batch=1,
+                              page_table=kv_indices.view(1, -1), meta_table=metadata_indices.view(1, -1))
 
 
 def append_kv_cache_decode(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx,
                            metadata_data, metadata_indices, metadata_indptr, metadata_last_page_len,
                            metadata_last_page_idx, layout) -> None:
-    """Write the new token's k,v [1,H,D] into slot (kv_last_page_idx, kv_last_page_len-1)
-    (tidal/ops/csrc/page.cu:6-99)."""
-    _append(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx, layout, True)
+    """Write the new token's k,v [1,H,D] into slot (kv_last_page_idx, kv_last_page_len-1) and fold its key into
+    the page's metadata entry (tidal/ops/csrc/page.cu:6-99)."""
+    _append(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx, metadata_data, metadata_indices,
+            metadata_last_page_len, layout, True)
 
 
 def append_kv_cache_prefill(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx,
                             metadata_data, metadata_indices, metadata_indptr, metadata_last_page_len,
                             metadata_last_page_idx, layout) -> None:
-    """Write the last seq tokens' k,v [seq,H,D] into the pages listed by kv_indices
-    (tidal/ops/csrc/page.cu:101-210)."""
-    _append(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx, layout, False)
+    """Write the last seq tokens' k,v [seq,H,D] into the pages listed by kv_indices and rebuild the metadata
+    entries of those pages (tidal/ops/csrc/page.cu:101-210)."""
+    _append(k, v, kv_data, kv_indices, kv_indptr, kv_last_page_len, kv_last_page_idx, metadata_data, metadata_indices,
+            metadata_last_page_len, layout, False)
 
 
 def topk_filtering(estimated_value: torch.Tensor, estimated_indices: torch.Tensor, d_out: torch.Tensor,
@@ -168,10 +184,21 @@ def topk_filtering(estimated_value: torch.Tensor, estimated_indices: torch.Tenso
 
 def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, metadata_last_page_len,
                         metadata_last_page_idx, layout) -> None:
-    """Quest's per-page upper bound (tidal/ops/csrc/estimate.cu:6-84).  TidalDecode's own
-    model code never calls it (tidal/models/*.py use exact logits), and it is not built."""
-    raise RuntimeError("estimate_attn_score is not part of the TidalDecode decode path and is not built; "
-                       "selection layers return exact logits through BatchDecodeWithPagedKVCachePyTorchWrapper.forward")
+    """Quest's per-page upper bound of q.k (tidal/ops/csrc/estimate.cu:6-84): o [heads, entries - 1] receives, for
+    every query head and every metadata entry but the last (the page still being filled, estimate.cu:52-54),
+    sum_d max(q_d * max_d, q_d * min_d)."""
+    _check_input(q, "q")
+    _check_input(o, "o")
+    _check_input(metadata_data, "metadata_data")
+    _check_input(metadata_indices, "metadata_indices")
+    _check(q.dim() == 3 and q.shape[0] == 1, "q must be [1, heads, head_dim]")
+    _check(metadata_data.dim() == 5 and metadata_data.shape[1] == 2, "metadata_data must be [pages, 2, page_size, heads, head_dim]")
+    _check(metadata_indices.dim() == 1 and metadata_indices.dtype == torch.int32, "metadata_indices must be int32 [num_pages]")
+    _check_layout(layout)
+    _check(metadata_data.shape[4] == q.shape[2], "head_dim of q and the metadata differ")
+    n = (metadata_indices.numel() - 1) * metadata_data.shape[2] + int(metadata_last_page_len) - 1
+    _check(o.dim() == 2 and o.shape[0] == q.shape[1] and o.shape[1] >= n, "o must be [heads, >= entries - 1]")
+    _ops.estimate(q, metadata_data, n, out=o.view(1, o.shape[0], o.shape[1]), meta_table=metadata_indices.view(1, -1))
 
 
 def prefill_with_paged_kv_cache(q, kv_data, kv_indices, kv_last_page_len, causal, layout, allow_fp16_qk_reduction,

@@ -19,7 +19,7 @@ TOPK_BINS = 4096
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",
-    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_topk_static_status", "tidal_rope_append", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather", "tidal_peer_exchange_reset", "tidal_prefill",
+    "tidal_decode_attention", "tidal_plan_chunks", "tidal_topk", "tidal_topk_static", "tidal_topk_static_status", "tidal_rope_append", "tidal_update_page_meta", "tidal_estimate", "tidal_merge_partials", "tidal_merge_partials_strided", "tidal_rms_norm", "tidal_decode_linear", "tidal_decode_qkv", "tidal_peer_all_gather", "tidal_peer_exchange_reset", "tidal_prefill",
 )
 
 
@@ -60,6 +60,27 @@ class RopeAppendArgs(C.Structure):
         ("batch", C.c_int32), ("tokens_per_seq", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32),
         ("head_dim", C.c_int32), ("page_size", C.c_int32), ("dtype", C.c_int32),
         ("num_pages", C.c_int64), ("d_status", C.c_void_p), ("d_q_src", C.c_void_p), ("kv_pos_base", C.c_int32),
+    ]
+
+
+class PageMetaArgs(C.Structure):
+    _fields_ = [
+        ("d_kv", C.c_void_p), ("d_meta", C.c_void_p), ("d_page_table", C.c_void_p), ("page_table_stride", C.c_int64),
+        ("d_meta_table", C.c_void_p), ("meta_table_stride", C.c_int64),
+        ("batch", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("page_size", C.c_int32),
+        ("meta_page_size", C.c_int32), ("dtype", C.c_int32),
+        ("num_pages", C.c_int64), ("num_meta_pages", C.c_int64), ("first_pos", C.c_int32), ("seq_len", C.c_int32),
+        ("d_status", C.c_void_p),
+    ]
+
+
+class EstimateArgs(C.Structure):
+    _fields_ = [
+        ("d_q", C.c_void_p), ("d_meta", C.c_void_p), ("d_meta_table", C.c_void_p), ("meta_table_stride", C.c_int64),
+        ("d_out", C.c_void_p), ("out_stride", C.c_int64),
+        ("batch", C.c_int32), ("num_qo_heads", C.c_int32), ("num_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("meta_page_size", C.c_int32), ("n_entries", C.c_int32), ("dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("num_meta_pages", C.c_int64), ("d_status", C.c_void_p),
     ]
 
 
@@ -131,6 +152,10 @@ def _load() -> C.CDLL:
     lib.tidal_topk_static_status.argtypes = [C.c_int, C.c_void_p]
     lib.tidal_rope_append.restype = C.c_int
     lib.tidal_rope_append.argtypes = [C.POINTER(RopeAppendArgs), C.c_void_p]
+    lib.tidal_update_page_meta.restype = C.c_int
+    lib.tidal_update_page_meta.argtypes = [C.POINTER(PageMetaArgs), C.c_void_p]
+    lib.tidal_estimate.restype = C.c_int
+    lib.tidal_estimate.argtypes = [C.POINTER(EstimateArgs), C.c_void_p]
     lib.tidal_merge_partials.restype = C.c_int
     lib.tidal_merge_partials.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                          C.c_void_p, C.c_int, C.c_void_p]

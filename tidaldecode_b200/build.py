@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtidal_b200.so")
-SOURCES = ["decode_attn.cu", "decode_attn_mma.cu", "topk.cu", "rope_append.cu", "rms_norm.cu", "decode_linear.cu", "peer_exchange.cu", "prefill_attn.cu", "workspace.cu"]
+SOURCES = ["decode_attn.cu", "decode_attn_mma.cu", "topk.cu", "rope_append.cu", "page_meta.cu", "rms_norm.cu", "decode_linear.cu", "peer_exchange.cu", "prefill_attn.cu", "workspace.cu"]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "attn_params.cuh"), os.path.join(CSRC, "topk_common.cuh"), os.path.join(os.path.dirname(HERE), "include", "tidal_b200.h")]
 
 NVCC_FLAGS = [

@@ -15,6 +15,8 @@
 // covers HC KV heads (all of them when logits are summed over heads, so the sum
 // is formed in shared memory in a fixed order); its slots either own HPS heads
 // each (HC = slots*HPS) or share a head among TG token groups (slots = HC*TG).
+#include <cstdlib>
+
 #include "attn_params.cuh"
 
 namespace tidal {
@@ -792,6 +794,12 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
                       (L->part_o_off + part_need <= L->part_ml_off && L->part_ml_off + ml_need <= L->hist_off),
                   TIDAL_ERR_WORKSPACE, "workspace was sized for a smaller batch/heads/head_dim than this call");
 
+    // TIDAL_DEBUG_PLAN=1 in the environment: one line per call on stderr with the planner's choices
+    static const bool debug_plan = std::getenv("TIDAL_DEBUG_PLAN") != nullptr;
+    if (debug_plan)
+        fprintf(stderr, "tidal plan: %s ntok %d B %d Hq %d Hkv %d | HC %d slices %d chunks %d cluster %d T %d S %d CW %d PW %d smem %zu fused %d\n",
+                use_mma ? "mma" : "cuda-core", ntok, a->batch, a->num_qo_heads, a->num_kv_heads, plan.HC, plan.nslices, plan.nchunks,
+                cluster, plan.T, plan.S, plan.CW, p.PW, plan.smem, p.kv_fused);
     rc = run(nullptr);
     if (rc != TIDAL_OK) return rc;
     if (plan.nchunks > 1 && cluster == 1) {

@@ -265,6 +265,60 @@ def rope_append(
         check(lib.tidal_rope_append(C.byref(a), _stream()), "tidal_rope_append")
 
 
+def update_page_meta(kv: torch.Tensor, meta: torch.Tensor, seq_len: int, first_pos: int, *, batch: int = 1,
+                     page_table: Optional[torch.Tensor] = None, pages_per_seq: Optional[int] = None,
+                     meta_table: Optional[torch.Tensor] = None, meta_pages_per_seq: Optional[int] = None,
+                     status: Optional[torch.Tensor] = None) -> None:
+    """Per-page key bounds (Quest metadata) of the KV pages that hold positions [first_pos, seq_len), recomputed
+    from the pool; see tidal_update_page_meta in include/tidal_b200.h.  kv [pages,2,page,Hkv,D],
+    meta [meta_pages,2,meta_page,Hkv,D] (plane 0 maxima, plane 1 minima, one entry per KV page)."""
+    _need_cuda(kv, meta, page_table, meta_table, status)
+    if kv.dim() != 5 or meta.dim() != 5 or kv.shape[1] != 2 or meta.shape[1] != 2 or kv.shape[3:] != meta.shape[3:] or kv.dtype != meta.dtype:
+        raise RuntimeError("kv and meta must be [pages,2,page,Hkv,D] pools of one dtype and head geometry")
+    a = _lib.PageMetaArgs()
+    a.d_kv, a.d_meta = kv.data_ptr(), meta.data_ptr()
+    if page_table is not None:
+        a.d_page_table, a.page_table_stride = page_table.data_ptr(), page_table.shape[-1]
+    else:
+        a.page_table_stride = pages_per_seq if pages_per_seq is not None else kv.shape[0] // batch
+    if meta_table is not None:
+        a.d_meta_table, a.meta_table_stride = meta_table.data_ptr(), meta_table.shape[-1]
+    else:
+        a.meta_table_stride = meta_pages_per_seq if meta_pages_per_seq is not None else meta.shape[0] // batch
+    a.batch, a.num_kv_heads, a.head_dim = int(batch), kv.shape[3], kv.shape[4]
+    a.page_size, a.meta_page_size, a.dtype = kv.shape[2], meta.shape[2], _dtype_code(kv)
+    a.num_pages, a.num_meta_pages = kv.shape[0], meta.shape[0]
+    a.first_pos, a.seq_len = int(first_pos), int(seq_len)
+    a.d_status = _ptr(status)
+    with torch.cuda.device(kv.device):
+        check(lib.tidal_update_page_meta(C.byref(a), _stream()), "tidal_update_page_meta")
+
+
+def estimate(q: torch.Tensor, meta: torch.Tensor, n_entries: int, *, out: Optional[torch.Tensor] = None,
+             meta_table: Optional[torch.Tensor] = None, meta_pages_per_seq: Optional[int] = None,
+             status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Quest's upper bound of q.k per KV page from the page metadata; see tidal_estimate in include/tidal_b200.h.
+    q [B,Hq,D]; returns out [B,Hq,>= n_entries] (q's dtype unless `out` is given)."""
+    _need_cuda(q, meta, out, meta_table, status)
+    if q.dim() != 3 or meta.dim() != 5 or meta.shape[1] != 2 or meta.shape[4] != q.shape[2] or meta.dtype != q.dtype:
+        raise RuntimeError("q must be [B,Hq,D] and meta [meta_pages,2,meta_page,Hkv,D] of the same dtype")
+    B, Hq, D = q.shape
+    if out is None:
+        out = torch.empty(B, Hq, max(int(n_entries), 1), dtype=q.dtype, device=q.device)
+    a = _lib.EstimateArgs()
+    a.d_q, a.d_meta, a.d_out, a.out_stride = q.data_ptr(), meta.data_ptr(), out.data_ptr(), out.shape[-1]
+    if meta_table is not None:
+        a.d_meta_table, a.meta_table_stride = meta_table.data_ptr(), meta_table.shape[-1]
+    else:
+        a.meta_table_stride = meta_pages_per_seq if meta_pages_per_seq is not None else meta.shape[0] // B
+    a.batch, a.num_qo_heads, a.num_kv_heads, a.head_dim = B, Hq, meta.shape[3], D
+    a.meta_page_size, a.n_entries, a.dtype, a.out_dtype = meta.shape[2], int(n_entries), _dtype_code(q), _dtype_code(out)
+    a.num_meta_pages, a.d_status = meta.shape[0], _ptr(status)
+    with torch.cuda.device(q.device):
+        check(lib.tidal_estimate(C.byref(a), _stream()), "tidal_estimate")
+    return out
+
+
 def merge_partials(m: torch.Tensor, l: torch.Tensor, o: torch.Tensor, dtype: torch.dtype,
                    out: Optional[torch.Tensor] = None, geometry: Optional[tuple] = None) -> torch.Tensor:
     """LSE-merge of [shards, B, Hq(, D)] partials; see tidal_merge_partials.  With

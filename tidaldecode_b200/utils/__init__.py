@@ -52,6 +52,7 @@ def append_kv(k: torch.Tensor, v: torch.Tensor, iController: InferenceController
     tps = _tokens_per_seq(k, c)
     ops.rope_append(None, k, v, c.kv_cache.buf_layer(layer_idx), batch=c.batch_size, pos0=c.kv_cache.seqlen - tps,
                     page_table=c.kv_cache.page_table, rope_mode=0)
+    _update_quest_metadata(c, layer_idx, tps)
 
 
 def rope_append_kv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iController: InferenceController, layer_idx: int,
@@ -64,6 +65,16 @@ def rope_append_kv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, iControlle
     ops.rope_append(q, k, v, c.kv_cache.buf_layer(layer_idx), batch=c.batch_size, pos0=c.kv_cache.seqlen - tps,
                     page_table=c.kv_cache.page_table, rope_theta=1e4 if rope_theta is None else rope_theta,
                     rope_scale=1.0 if rope_scale is None else rope_scale, rope_mode=rope_mode, inv_freq=inv_freq)
+    _update_quest_metadata(c, layer_idx, tps)
+
+
+def _update_quest_metadata(c: InferenceController, layer_idx: int, new_tokens: int) -> None:
+    """Per-page key bounds of the pages the new tokens landed in (only for controllers that keep them)."""
+    if c.metadata_cache is None:
+        return
+    n = c.kv_cache.seqlen
+    ops.update_page_meta(c.kv_cache.buf_layer(layer_idx), c.metadata_cache[layer_idx // c.kv_cache.layer_alias], n, n - new_tokens,
+                         batch=c.batch_size, page_table=c.kv_cache.page_table, meta_pages_per_seq=c.metadata_cache.shape[1] // c.batch_size)
 
 
 def prefill_forward(q: torch.Tensor, iController: InferenceController, layer_idx: int, rope_scale: Optional[float] = None,
@@ -77,8 +88,18 @@ def prefill_forward(q: torch.Tensor, iController: InferenceController, layer_idx
 
 
 def decode_estimate(q: torch.Tensor, iController: InferenceController, layer_idx: int) -> torch.Tensor:
-    """Quest's page-criticality estimate (tidal/utils/__init__.py:176-214); not used by TidalDecode layers."""
-    return _kernels.estimate_attn_score(q, None, None, None, None, 0, 0, iController.layout)
+    """Quest's page-criticality estimate (tidal/utils/__init__.py:176-214): per query head, an upper bound of
+    q.k for every KV page but the newest.  Needs a controller built with quest_metadata=True (the reference
+    always allocates the metadata pool; TidalDecode's own layers never read it, so here it is optional).
+    q [1, Hq, D] -> [Hq, pages - 1] in q's dtype."""
+    c = iController
+    if c.metadata_cache is None:
+        raise RuntimeError("decode_estimate needs InferenceController(..., quest_metadata=True)")
+    n = c.kv_cache.num_pages - 1
+    o = torch.empty(q.shape[1], max(n, 1), dtype=q.dtype, device=q.device)
+    ops.estimate(q[:1].contiguous(), c.metadata_cache[layer_idx // c.kv_cache.layer_alias], n, out=o.view(1, *o.shape),
+                 meta_pages_per_seq=c.metadata_cache.shape[1] // c.batch_size)
+    return o[:, :n]
 
 
 def decode_topk(iController: InferenceController):

@@ -30,7 +30,8 @@ from .utils import TensorLayout
 class InferenceController:
     def __init__(self, num_layers, num_heads, head_dim, page_size, token_budget, max_seq_len, dtype, device,
                  num_kv_heads: Optional[int] = None, batch_size: int = 1, head_reduce: str = "none",
-                 force_last_token: bool = True, layer_alias: int = 1):
+                 force_last_token: bool = True, layer_alias: int = 1, quest_metadata: bool = False,
+                 metadata_page_size: int = 16):
         assert page_size == 1, "Only support page_size=1"
         if head_reduce not in ("none", "sum"):
             raise ValueError("head_reduce must be 'none' or 'sum'")
@@ -40,9 +41,16 @@ class InferenceController:
         self.kv_cache = KvCache(num_layers=num_layers, num_heads=num_kv_heads, head_dim=head_dim, max_seq_len=max_seq_len,
                                 page_size=page_size, dtype=dtype, device=device, layer_alias=layer_alias,
                                 batch_size=batch_size)
-        # The reference allocates a second, equally large pool for Quest's per-page min/max
-        # (controller.py:31-39); no TidalDecode layer reads it, so none is allocated here.
+        # The reference always allocates a second pool for Quest's per-page min/max of the keys
+        # (controller.py:31-39); no TidalDecode layer reads it, so it exists only on request
+        # (quest_metadata=True: append_kv keeps it up to date, decode_estimate reads it).  One entry per KV
+        # page, metadata_page_size entries per metadata page, sequence b's pages at [b * per_seq, ...).
         self.metadata_cache = None
+        if quest_metadata:
+            kv_pages = (max_seq_len + page_size - 1) // page_size
+            per_seq = (kv_pages + metadata_page_size - 1) // metadata_page_size
+            self.metadata_cache = torch.zeros((max(1, num_layers // layer_alias), per_seq * batch_size, 2, metadata_page_size,
+                                               num_kv_heads, head_dim), dtype=dtype, device=device)
         self.layout = TensorLayout.NHD
         self.device = device
         self.dtype = dtype
