@@ -421,8 +421,8 @@ int tidal_peer_exchange_reset(uint32_t* d_count, uint32_t* d_state, int world, v
  * causal = 0: every row sees all kv_len tokens).  Replaces prefill_with_paged_kv_cache
  * (tidal/ops/csrc/bsk_ops.h:78-86, tidal/ops/csrc/batch_prefill.cu:27-117, kernel
  * kernels/include/prefill/prefill.cuh:688-870); RoPE is applied beforehand (tidal_rope_append), as
- * the reference's modules do (tidal/models/SearchAttention.py:154-163).  f16/bf16, head_dim 64 or
- * 128, NHD pool [pages][2][page_size][num_kv_heads][head_dim]; d_page_table lists the sequence's
+ * the reference's modules do (tidal/models/SearchAttention.py:154-163).  f16/bf16 (tensor cores) or
+ * fp32 (CUDA cores: the tensor cores have no fp32 operand mode), head_dim 64 or 128, NHD pool [pages][2][page_size][num_kv_heads][head_dim]; d_page_table lists the sequence's
  * pages in order.  sm_scale <= 0 means 1/sqrt(head_dim).  Allocates nothing, needs no workspace. */
 typedef struct {
     const void* d_q;             /* [n_q][num_qo_heads][head_dim] */

@@ -208,6 +208,29 @@ def gen_tiny_model(lt, mod, outdir):
     print("tiny model ok; tokens", toks)
 
 
+def gen_yarn_hook(mod, outdir):
+    """The reference's second hook, llama_tidal_forward_yarn (modify_llama.py:150-325), installed on a stack of YaRN-style
+    attention modules exactly as enable_llama_tidal_attention does for that model family (:379-391): outputs of the last
+    layer over a prompt and a few decode steps."""
+    from tests.golden.cases import YARN_CASE, run_attention_stack, yarn_case_model_and_inputs
+
+    mods, prompt, steps = yarn_case_model_and_inputs()
+    for i, m in enumerate(mods):
+        m.layer_id = i
+        m.flash_forward = m.forward
+        m.forward = types.MethodType(mod.llama_tidal_forward_yarn, m)
+        m.token_budget = YARN_CASE["top_k"]
+        m.sparse_layer_start = YARN_CASE["sparse_layer_start"]
+        m.correction_layer = YARN_CASE["correction_layer"]
+    out = run_attention_stack(mods, prompt, steps)
+    # the same stack without the hook (dense attention everywhere) must differ: the budget is below the context
+    dense_mods, _, _ = yarn_case_model_and_inputs()
+    dense = run_attention_stack(dense_mods, prompt, steps)
+    assert not torch.allclose(out, dense, atol=1e-4), "the hook did not change anything"
+    np.savez_compressed(os.path.join(outdir, "yarn_hook.npz"), out=out.numpy(), dense=dense.numpy())
+    print("yarn hook ok; |out - dense| max", float((out - dense).abs().max()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", required=True)
@@ -218,6 +241,7 @@ def main():
     gen_attention(mod, a.out)
     gen_rope(lt, a.out)
     gen_tiny_model(lt, mod, a.out)
+    gen_yarn_hook(mod, a.out)
 
 
 if __name__ == "__main__":

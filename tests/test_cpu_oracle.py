@@ -136,3 +136,49 @@ def test_causal_prefill_matches_the_reference_paths():
     full = O.causal_prefill(q[:3], K, V, causal=False)
     row = O.full_layer(q[:3].transpose(0, 1)[None], K.transpose(0, 1)[None], V.transpose(0, 1)[None])
     assert torch.allclose(full, row[0].transpose(0, 1), rtol=1e-5, atol=1e-6)
+
+
+def test_oracle_reproduces_reference_yarn_hook():
+    """The reference's second hook (llama_tidal_forward_yarn, fixture yarn_hook.npz) on the YaRN-style attention stack:
+    its decode-step arithmetic is the oracle's selection_layer / sparse_layer on the module's own rotated q, k."""
+    import types
+
+    from tests.golden.cases import YARN_CASE, run_attention_stack, yarn_case_model_and_inputs
+
+    z = load_golden("yarn_hook.npz")
+    mods, prompt, steps = yarn_case_model_and_inputs()
+    c = YARN_CASE
+
+    def hooked(self, hidden_states, attention_mask=None, position_ids=None, past_key_value=None, output_attentions=False,
+               use_cache=False, is_padded_inputs=False):
+        bsz, q_len, _ = hidden_states.shape
+        if q_len > 1 or self.layer_id < c["sparse_layer_start"]:
+            return self.flash_forward(hidden_states, attention_mask, position_ids, past_key_value, output_attentions, use_cache,
+                                      is_padded_inputs)
+        past_kv, past_len = past_key_value
+        q = self.q_proj(hidden_states).view(bsz, 1, self.num_heads, self.head_dim)
+        k = self.k_proj(hidden_states).view(bsz, 1, self.num_key_value_heads, self.head_dim)
+        v = self.v_proj(hidden_states).view(bsz, 1, self.num_key_value_heads, self.head_dim)
+        q, k = self.rotary_emb(q, k, past_len)
+        G = self.num_key_value_groups
+        K = torch.cat((past_kv[:, :past_len, 0, ::G], k), dim=1).transpose(1, 2)       # [B,Hkv,N,D]
+        V = torch.cat((past_kv[:, :past_len, 1, ::G], v), dim=1).transpose(1, 2)
+        kv = torch.stack([k, v], 2)[:, :, :, :, None, :].expand(bsz, 1, 2, self.num_key_value_heads, G, self.head_dim)
+        if past_len + 1 > past_kv.size(1):
+            past_kv = torch.cat([past_kv, torch.empty(bsz, 256, 2, self.num_heads, self.head_dim)], 1)
+        past_kv[:, past_len:past_len + 1] = kv.reshape(bsz, 1, 2, self.num_heads, self.head_dim)
+        qq = q.transpose(1, 2)
+        if self.layer_id in (c["sparse_layer_start"], c["correction_layer"]):
+            o, _, self.pos_dict = O.selection_layer(qq, K, V, c["top_k"], "none")
+        else:
+            o = O.sparse_layer(qq, K, V, self.pos_dict)
+        o = self.o_proj(o.transpose(1, 2).reshape(bsz, 1, self.hidden_size))
+        return o, None, (past_kv, past_len + 1)
+
+    for i, m in enumerate(mods):
+        m.layer_id = i
+        m.flash_forward = m.forward
+        m.forward = types.MethodType(hooked, m)
+    out = run_attention_stack(mods, prompt, steps)
+    want = torch.from_numpy(z["out"])
+    assert torch.allclose(out, want, rtol=0, atol=1e-5), (out - want).abs().max()

@@ -90,3 +90,26 @@ def test_enable_tidal_gqa_bf16_head_sum():
     got = _greedy(model, prompt, 6)
     assert sum(a == b for a, b in zip(got, want)) >= 5, (got, want)
     assert model._tidal_state.controller.workspace.status() == 0
+
+
+def test_enable_tidal_yarn_style_modules_match_reference():
+    """The YaRN form of the hook (modules with their own rotary_emb(q, k, past_len) and a tuple cache) against the
+    outputs the reference's llama_tidal_forward_yarn produced on the same attention stack (fixture yarn_hook.npz)."""
+    from tests.golden.cases import YARN_CASE, run_attention_stack, yarn_case_model_and_inputs
+    from tidaldecode_b200.enable_tidal import enable_tidal_yarn_modules
+
+    z = load_golden("yarn_hook.npz")
+    mods, prompt, steps = yarn_case_model_and_inputs()
+    mods = [m.cuda() for m in mods]
+    state = enable_tidal_yarn_modules(mods, "tidal", YARN_CASE["top_k"], YARN_CASE["sparse_layer_start"], YARN_CASE["correction_layer"],
+                                      max_seq_len=512)
+    assert all(hasattr(m, "flash_forward") for m in mods)
+    out = run_attention_stack(mods, prompt.cuda(), steps.cuda()).float().cpu()
+    want, dense = torch.from_numpy(z["out"]), torch.from_numpy(z["dense"])
+    err = (out - want).abs().max().item()
+    assert torch.allclose(out, want, rtol=1e-4, atol=2e-4), f"differs from the reference's hook by {err:.3e}"
+    assert (out - dense).abs().max() > 0.1, "the outputs must be those of sparse attention, not of the dense stack"
+    assert state.controller.workspace.status() == 0
+    # a second sequence through the same modules: the pool is recognised as stale and refilled
+    out2 = run_attention_stack(mods, prompt.cuda(), steps.cuda()).float().cpu()
+    assert torch.allclose(out2, out, rtol=0, atol=1e-6)

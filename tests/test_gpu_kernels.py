@@ -607,6 +607,9 @@ PREFILL_CASES = [
     ("f16", 2048, 2048, 4, 2, 128, 1, True),
     ("bf16", 1, 65, 2, 1, 128, 1, True),              # a single row
     ("f16", 17, 17, 32, 8, 128, 31, True),            # shortest length of the reference's sweep, one partial page
+    ("f32", 2048, 2048, 4, 4, 64, 1, True),           # configuration 1's prompt: fp32 storage, the CUDA-core kernel
+    ("f32", 130, 333, 8, 2, 128, 5, True),            # fp32 GQA, a later chunk, ragged pages
+    ("f32", 65, 65, 2, 2, 64, 16, False),
 ]
 
 
@@ -640,8 +643,8 @@ def test_prefill_rejects_what_it_does_not_compute(T):
     q = torch.zeros(4, 2, 128, device="cuda")
     pool = torch.zeros(4, 2, 1, 2, 128, device="cuda")
     table = torch.arange(4, dtype=torch.int32, device="cuda")
-    with pytest.raises(RuntimeError, match="fp16 or bf16"):
-        T.prefill(q, pool, table, 4)
+    with pytest.raises(RuntimeError, match="head_dim"):
+        T.prefill(torch.zeros(4, 2, 32, device="cuda").half(), torch.zeros(4, 2, 1, 2, 32, device="cuda").half(), table, 4)
     with pytest.raises(RuntimeError, match="kv_len"):
         T.prefill(q.half(), pool.half(), table, 3)
 

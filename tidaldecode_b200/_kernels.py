@@ -204,9 +204,9 @@ def estimate_attn_score(q, o, metadata_data, metadata_indices, metadata_indptr, 
 def prefill_with_paged_kv_cache(q, kv_data, kv_indices, kv_last_page_len, causal, layout, allow_fp16_qk_reduction,
                                 rope_scale, rope_theta) -> torch.Tensor:
     """Causal attention of q [seq,H,D] over the paged KV that already holds these tokens
-    (tidal/ops/csrc/batch_prefill.cu:27-117).  fp16/bf16 with head_dim 64 or 128 run this library's
-    tcgen05 kernel (tidal_prefill); fp32 (the tensor cores have no fp32 mode) and other head sizes go
-    to torch's fused attention over the gathered pages."""
+    (tidal/ops/csrc/batch_prefill.cu:27-117) by this library's own kernels (tidal_prefill): tcgen05 for
+    fp16/bf16, CUDA cores for fp32; head_dim 64 or 128 (anything else is refused, as the reference's
+    head-dim dispatch refuses what it was not built for)."""
     _check_input(q, "q")
     _check_input(kv_data, "kv_data")
     _check_input(kv_indices, "kv_indices")
@@ -215,24 +215,10 @@ def prefill_with_paged_kv_cache(q, kv_data, kv_indices, kv_last_page_len, causal
     page_size = kv_data.shape[2]
     n_pages = kv_indices.numel()
     seq_len = (n_pages - 1) * page_size + int(kv_last_page_len)
-    Hkv, D = kv_data.shape[3], kv_data.shape[4]
-    if q.dtype in (torch.float16, torch.bfloat16) and D in (64, 128) and q.dtype == kv_data.dtype:
-        return _ops.prefill(q.contiguous(), kv_data, kv_indices.to(torch.int32).contiguous(), seq_len, causal=bool(causal))
-    pages = kv_data.index_select(0, kv_indices.long())                       # [P,2,page,Hkv,D]
-    K = pages[:, 0].reshape(-1, Hkv, D)[:seq_len].transpose(0, 1)[None]       # [1,Hkv,N,D]
-    V = pages[:, 1].reshape(-1, Hkv, D)[:seq_len].transpose(0, 1)[None]
-    Hq = q.shape[1]
-    qq = q.transpose(0, 1)[None]                                              # [1,Hq,seq,D]
-    n_q = q.shape[0]
-    if causal and n_q > 1 and n_q == seq_len:
-        # the whole prompt at once: the fused causal kernel, no mask tensor
-        o = torch.nn.functional.scaled_dot_product_attention(qq, K, V, is_causal=True, enable_gqa=(Hq != Hkv))
-    else:
-        mask = None
-        if causal and n_q > 1:      # a later chunk of a prompt: rows see the history and their own prefix
-            mask = torch.ones(n_q, seq_len, dtype=torch.bool, device=q.device).tril(diagonal=seq_len - n_q)
-        o = torch.nn.functional.scaled_dot_product_attention(qq, K, V, attn_mask=mask, enable_gqa=(Hq != Hkv))
-    return o[0].transpose(0, 1).contiguous()
+    D = kv_data.shape[4]
+    _check(q.dtype == kv_data.dtype and q.dtype in (torch.float16, torch.bfloat16, torch.float32), "q and kv_data must share a dtype (f16, bf16, f32)")
+    _check(D in (64, 128), f"head_dim {D} is not built (64, 128)")
+    return _ops.prefill(q.contiguous(), kv_data, kv_indices.to(torch.int32).contiguous(), seq_len, causal=bool(causal))
 
 
 def rms_norm_forward(input: torch.Tensor, weight: torch.Tensor, output: torch.Tensor, epsilon: float) -> None:

@@ -422,6 +422,166 @@ static int launch_prefill(const PrefillParams& p, cudaStream_t st) {
     return p.n_q > kPfRows ? launch_prefill_sub<T, D, 2>(p, st) : launch_prefill_sub<T, D, 1>(p, st);
 }
 
+
+// ------------------------------------------------------------------ fp32 caches: CUDA cores
+// kind::f16 has no fp32 operand mode and kind::tf32 would not meet a 1e-4 tolerance, so fp32 storage (the
+// tiny reference-parity configuration) gets a plain tiled kernel: 64 query rows of one head per CTA, K/V tiles
+// of 64 tokens in shared memory (K transposed, so that a thread's four score columns are one 16-byte read),
+// 16 x 16 threads each owning a 4 x 4 block of the score tile and 4 rows x D/16 columns of the output,
+// online softmax with exact exp2f.  Same page lookup and bounds rule as the tensor-core kernel.
+constexpr int kPf32Rows = 64, kPf32Tile = 64;
+template <int D>
+__global__ void __launch_bounds__(256) prefill_f32_kernel(const __grid_constant__ PrefillParams p) {
+    extern __shared__ __align__(16) float fsm[];
+    float* Qs = fsm;                               // [64][D]
+    float* Kt = Qs + kPf32Rows * D;                // [D][64]
+    float* Vs = Kt + D * kPf32Tile;                // [64][D]
+    float* Ps = Vs + kPf32Tile * D;                // [64][64]
+    constexpr int DC = D / 16;                     // output columns per thread
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int n_qt = (p.n_q + kPf32Rows - 1) / kPf32Rows;
+    const int qt = n_qt - 1 - (int)blockIdx.x;     // longest rows first
+    const int h = blockIdx.y, kvh = h / (p.Hq / p.Hkv);
+    const int q0 = qt * kPf32Rows;
+    const int rows_here = min(kPf32Rows, p.n_q - q0);
+    const int64_t pos0 = p.kv_len - p.n_q + q0;
+    const int64_t kv_end = p.causal ? min(p.kv_len, pos0 + rows_here) : p.kv_len;
+    const int n_tiles = (int)((kv_end + kPf32Tile - 1) / kPf32Tile);
+    const float* q = reinterpret_cast<const float*>(p.q);
+    const float* kv = reinterpret_cast<const float*>(p.kv);
+    const int64_t row_elems = (int64_t)p.Hkv * D;
+    bool bad_page = false;
+
+    for (int i = tid; i < kPf32Rows * (D / 4); i += 256) {
+        const int r = i / (D / 4), c4 = i - r * (D / 4);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < rows_here) v = *reinterpret_cast<const float4*>(q + ((int64_t)(q0 + r) * p.Hq + h) * D + c4 * 4);
+        *reinterpret_cast<float4*>(Qs + r * D + c4 * 4) = v;
+    }
+    float o[4][DC], m_run[4], l_run[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        m_run[i] = -INFINITY;
+        l_run[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < DC; ++j) o[i][j] = 0.f;
+    }
+    for (int j = 0; j < n_tiles; ++j) {
+        const int64_t t0 = (int64_t)j * kPf32Tile;
+        __syncthreads();                           // the previous tile's K, V and P are no longer read
+        for (int i = tid; i < kPf32Tile * (D / 4); i += 256) {
+            const int c = i % kPf32Tile, d4 = i / kPf32Tile;      // consecutive threads: consecutive tokens
+            const int64_t t = t0 + c;
+            float4 kx = make_float4(0.f, 0.f, 0.f, 0.f), vx = kx;
+            if (t < p.kv_len) {
+                const int64_t pi = t / p.page_size, slot = t - pi * p.page_size;
+                const int64_t page = p.pages[pi];
+                if (page >= 0 && page < p.num_pages) {
+                    const float* src = kv + ((page * 2) * p.page_size + slot) * row_elems + (int64_t)kvh * D + d4 * 4;
+                    kx = *reinterpret_cast<const float4*>(src);
+                    vx = *reinterpret_cast<const float4*>(src + (int64_t)p.page_size * row_elems);
+                } else {
+                    bad_page = true;
+                }
+            }
+            Kt[(d4 * 4 + 0) * kPf32Tile + c] = kx.x;
+            Kt[(d4 * 4 + 1) * kPf32Tile + c] = kx.y;
+            Kt[(d4 * 4 + 2) * kPf32Tile + c] = kx.z;
+            Kt[(d4 * 4 + 3) * kPf32Tile + c] = kx.w;
+            *reinterpret_cast<float4*>(Vs + c * D + d4 * 4) = vx;
+        }
+        __syncthreads();
+        // S block: rows ty*4.., columns tx*4..
+        float s[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
+#pragma unroll 8
+        for (int d = 0; d < D; ++d) {
+            const float4 kc = *reinterpret_cast<const float4*>(Kt + d * kPf32Tile + tx * 4);
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float qa = Qs[(ty * 4 + a) * D + d];
+                s[a][0] = fmaf(qa, kc.x, s[a][0]);
+                s[a][1] = fmaf(qa, kc.y, s[a][1]);
+                s[a][2] = fmaf(qa, kc.z, s[a][2]);
+                s[a][3] = fmaf(qa, kc.w, s[a][3]);
+            }
+        }
+        // online softmax per row (the 16 threads of a row are the 16 lanes of a half warp)
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const int64_t my_pos = pos0 + ty * 4 + a;
+            const int64_t lim = p.causal ? min(p.kv_len - 1, my_pos) : p.kv_len - 1;
+            float mx = m_run[a];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                s[a][b] = (t0 + tx * 4 + b <= lim) ? s[a][b] * p.scale_log2 : -INFINITY;
+                mx = fmaxf(mx, s[a][b]);
+            }
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            const float msafe = mx == -INFINITY ? 0.f : mx;
+            const float alpha = exp2f(m_run[a] - msafe);          // 0 while nothing has been seen
+            float sum = 0.f;
+            float4 pr;
+            pr.x = exp2f(s[a][0] - msafe);
+            pr.y = exp2f(s[a][1] - msafe);
+            pr.z = exp2f(s[a][2] - msafe);
+            pr.w = exp2f(s[a][3] - msafe);
+            sum = (pr.x + pr.y) + (pr.z + pr.w);
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            m_run[a] = mx;
+            l_run[a] = fmaf(l_run[a], alpha, sum);
+#pragma unroll
+            for (int c = 0; c < DC; ++c) o[a][c] *= alpha;
+            *reinterpret_cast<float4*>(Ps + (ty * 4 + a) * kPf32Tile + tx * 4) = pr;
+        }
+        __syncthreads();
+        // O block: rows ty*4.., columns tx*DC..
+#pragma unroll 4
+        for (int c = 0; c < kPf32Tile; ++c) {
+            float vv[DC];
+#pragma unroll
+            for (int u = 0; u < DC; u += 4) {
+                const float4 v4 = *reinterpret_cast<const float4*>(Vs + c * D + tx * DC + u);
+                vv[u] = v4.x; vv[u + 1] = v4.y; vv[u + 2] = v4.z; vv[u + 3] = v4.w;
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float pa = Ps[(ty * 4 + a) * kPf32Tile + c];
+#pragma unroll
+                for (int u = 0; u < DC; ++u) o[a][u] = fmaf(pa, vv[u], o[a][u]);
+            }
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int r = ty * 4 + a;
+        if (r >= rows_here) continue;
+        const float inv = l_run[a] > 0.f ? 1.f / l_run[a] : 0.f;
+        float* dst = reinterpret_cast<float*>(p.o) + ((int64_t)(q0 + r) * p.Hq + h) * D + tx * DC;
+#pragma unroll
+        for (int u = 0; u < DC; u += 4)
+            *reinterpret_cast<float4*>(dst + u) = make_float4(o[a][u] * inv, o[a][u + 1] * inv, o[a][u + 2] * inv, o[a][u + 3] * inv);
+    }
+    if (bad_page && p.status) atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
+}
+
+template <int D>
+static int launch_prefill_f32(const PrefillParams& p, cudaStream_t st) {
+    const size_t smem = sizeof(float) * ((size_t)kPf32Rows * D + 2 * (size_t)kPf32Tile * D + (size_t)kPf32Rows * kPf32Tile);
+    TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_f32_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int n_qt = (p.n_q + kPf32Rows - 1) / kPf32Rows;
+    TIDAL_CUDA_OK(launch_pdl(prefill_f32_kernel<D>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(256), smem, st, 1, p));
+    count_launch();
+    return TIDAL_OK;
+}
+
 }  // namespace tidal
 
 using namespace tidal;
@@ -429,8 +589,7 @@ using namespace tidal;
 extern "C" int tidal_prefill(const tidal_prefill_args* a, void* stream) {
     TIDAL_REQUIRE(a != nullptr, TIDAL_ERR_ARG, "args is NULL");
     TIDAL_REQUIRE(a->d_q && a->d_o && a->d_kv && a->d_page_table, TIDAL_ERR_ARG, "null pointer");
-    TIDAL_REQUIRE(a->dtype == TIDAL_DTYPE_F16 || a->dtype == TIDAL_DTYPE_BF16, TIDAL_ERR_ARG,
-                  "tidal_prefill computes in fp16 or bf16 (dtype %d given)", a->dtype);
+    TIDAL_REQUIRE(a->dtype >= 0 && a->dtype <= 2, TIDAL_ERR_ARG, "unknown dtype %d", a->dtype);
     TIDAL_REQUIRE(a->head_dim == 64 || a->head_dim == 128, TIDAL_ERR_ARG, "head_dim %d not supported (64, 128)", a->head_dim);
     TIDAL_REQUIRE(a->num_qo_heads >= 1 && a->num_kv_heads >= 1 && a->num_qo_heads % a->num_kv_heads == 0, TIDAL_ERR_ARG,
                   "num_qo_heads (%d) must be a multiple of num_kv_heads (%d)", a->num_qo_heads, a->num_kv_heads);
@@ -458,6 +617,7 @@ extern "C" int tidal_prefill(const tidal_prefill_args* a, void* stream) {
     const float sc = a->sm_scale > 0.f ? a->sm_scale : 1.f / sqrtf((float)a->head_dim);
     p.scale_log2 = sc * kLog2e;
     cudaStream_t st = (cudaStream_t)stream;
+    if (a->dtype == TIDAL_DTYPE_F32) return a->head_dim == 128 ? launch_prefill_f32<128>(p, st) : launch_prefill_f32<64>(p, st);
     if (a->dtype == TIDAL_DTYPE_F16)
         return a->head_dim == 128 ? launch_prefill<__half, 128>(p, st) : launch_prefill<__half, 64>(p, st);
     return a->head_dim == 128 ? launch_prefill<__nv_bfloat16, 128>(p, st) : launch_prefill<__nv_bfloat16, 64>(p, st);

@@ -359,7 +359,7 @@ def prefill(q: torch.Tensor, kv_pool: torch.Tensor, page_table: torch.Tensor, kv
             sm_scale: float = 0.0, out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of the new rows q [n_q, Hq, D] of one sequence over its paged KV (which already
     holds their K,V); see tidal_prefill in include/tidal_b200.h.  kv_pool [pages, 2, page_size, Hkv, D],
-    page_table int32 [>= ceil(kv_len / page_size)]; f16/bf16, D 64 or 128."""
+    page_table int32 [>= ceil(kv_len / page_size)]; f16/bf16 (tensor cores) or f32 (CUDA cores), D 64 or 128."""
     _need_cuda(q, kv_pool, page_table, out, status)
     if q.dim() != 3 or kv_pool.dim() != 5 or kv_pool.shape[1] != 2:
         raise RuntimeError("q must be [n_q, Hq, D] and kv_pool [pages, 2, page_size, Hkv, D]")
