@@ -108,8 +108,11 @@ def test_argument_errors_without_gpu(L):
     pf = L.PrefillArgs()
     assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG
     pf.d_q = pf.d_o = pf.d_kv = pf.d_page_table = 256
-    pf.dtype, pf.head_dim, pf.num_qo_heads, pf.num_kv_heads, pf.page_size, pf.n_q, pf.kv_len = L.DTYPE_F32, 128, 8, 2, 1, 4, 4
-    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "fp16 or bf16" in L.last_error()
+    pf.dtype, pf.head_dim, pf.num_qo_heads, pf.num_kv_heads, pf.page_size, pf.n_q, pf.kv_len = 7, 128, 8, 2, 1, 4, 4
+    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "dtype" in L.last_error()
+    pf.dtype = L.DTYPE_F32
+    assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "num_pages" in L.last_error()     # the bounds of the page table entries
+    pf.num_pages = 16
     pf.dtype, pf.head_dim = L.DTYPE_BF16, 96
     assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "head_dim" in L.last_error()
     pf.head_dim, pf.num_kv_heads = 128, 3
@@ -118,6 +121,19 @@ def test_argument_errors_without_gpu(L):
     assert L.lib.tidal_prefill(C.byref(pf), None) == L.ERR_ARG and "kv_len" in L.last_error()
     r = L.RopeAppendArgs()
     assert L.lib.tidal_rope_append(C.byref(r), None) == L.ERR_ARG
+    pm = L.PageMetaArgs()
+    assert L.lib.tidal_update_page_meta(C.byref(pm), None) == L.ERR_ARG
+    pm.d_kv = pm.d_meta = 256
+    pm.batch, pm.num_kv_heads, pm.head_dim, pm.page_size, pm.meta_page_size, pm.num_pages, pm.num_meta_pages = 1, 8, 128, 16, 16, 4, 1
+    pm.seq_len, pm.first_pos = 10, 10
+    assert L.lib.tidal_update_page_meta(C.byref(pm), None) == L.ERR_ARG and "first_pos" in L.last_error()
+    es = L.EstimateArgs()
+    assert L.lib.tidal_estimate(C.byref(es), None) == L.ERR_ARG
+    es.d_q = es.d_meta = es.d_out = 256
+    es.batch, es.num_qo_heads, es.num_kv_heads, es.head_dim, es.meta_page_size, es.num_meta_pages = 1, 8, 3, 128, 16, 1
+    assert L.lib.tidal_estimate(C.byref(es), None) == L.ERR_ARG and "multiple" in L.last_error()
+    es.num_kv_heads, es.n_entries, es.out_stride = 8, 5, 4
+    assert L.lib.tidal_estimate(C.byref(es), None) == L.ERR_ARG and "out_stride" in L.last_error()
     assert L.lib.tidal_ws_bytes(1, 32, 128, 32, 32768) > 0
     assert L.lib.tidal_ws_bytes(0, 32, 128, 32, 32768) == 0
     assert L.lib.tidal_ws_init(None, 0, 1, 32, 128, 32, 32768, None) == L.ERR_ARG
