@@ -238,6 +238,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
 // matching wait sits right before the first store into another CTA's shared memory, so the prologue and
 // the whole streaming loop run without waiting for the slowest CTA of the cluster to start.
 __device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 
 __device__ __forceinline__ float fast_exp2(float x) {

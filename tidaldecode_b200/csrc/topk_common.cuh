@@ -147,8 +147,9 @@ constexpr int kClusterCountSortMax = 256;     // winners ordered by counting up 
 constexpr int kClusterCand = 4096;            // candidates kept in shared memory
 constexpr int64_t kClusterMaxN = 1 << 21;
 constexpr int64_t kClusterSmemCandMaxN = 1 << 16;   // longer rows keep their candidates in the workspace
-constexpr size_t kClusterSmem = sizeof(uint32_t) * kBins                       // h
-                                + sizeof(uint64_t) * (kClusterMaxK + kClusterCand);  // lists (first CTA) / local histogram
+constexpr size_t kClusterSmem = sizeof(uint32_t) * kBins                          // h
+                                + sizeof(uint64_t) * (kClusterMaxK + kClusterCand)    // this CTA's own lists / local histogram
+                                + sizeof(uint64_t) * (kClusterMaxK + kClusterCand);   // the lists gathered in the first CTA
 
 struct ClusterShared {
     uint32_t nsel, ncand, cnt, digit, need, done;
@@ -174,14 +175,15 @@ __device__ __forceinline__ void for_each_cluster_candidate(const TopkParams& p, 
 // a __syncthreads() must separate two calls.
 __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, unsigned char* csm) {
     uint32_t* h = reinterpret_cast<uint32_t*>(csm);                                   // [kBins]
-    uint64_t* sel = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);      // [kClusterMaxK]
+    uint64_t* my_sel = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);   // [kClusterMaxK] found by this CTA
+    uint64_t* my_cand = my_sel + kClusterMaxK;                                        // [kClusterCand]
+    uint64_t* g_sel = my_cand + kClusterCand;                                         // [kClusterMaxK] gathered (first CTA's is used)
+    uint64_t* g_cand = g_sel + kClusterMaxK;                                          // [kClusterCand]
     // Candidates of the threshold bin: in shared memory for short rows; long rows can put thousands of
     // keys into one bin (e.g. 1 % of 1 M tokens with high affinity), so theirs go to the workspace.
     const bool cand_global = p.n > kClusterSmemCandMaxN && p.cand != nullptr;
-    uint64_t* cand = cand_global ? p.cand + (size_t)row * p.cand_cap
-                                 : sel + kClusterMaxK;                                // [kClusterCand] in shared memory
     const uint32_t cand_capacity = cand_global ? (uint32_t)min(p.cand_cap, (int64_t)0x7fffffff) : (uint32_t)kClusterCand;
-    uint32_t* h_local = reinterpret_cast<uint32_t*>(sel);                             // own-slice histogram (no-hist path)
+    uint32_t* h_local = reinterpret_cast<uint32_t*>(my_sel);                          // own-slice histogram (no-hist path)
     __shared__ uint32_t ws[32];
     __shared__ ClusterShared sh;
 
@@ -206,11 +208,15 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
     const int64_t lo = (int64_t)rank * per, hi = min(p.n, lo + per);
 
     if (t == 0) { sh.nsel = 0; sh.ncand = 0; sh.cnt = 0; }
+    const bool gather = CS > 1 || cand_global;       // lists travel to the first CTA (or to the workspace)
 
     // ---- digit-0 histogram of the whole row into h
     if (p.hist) {
+        // The first CTA's counters must be initialised before anyone adds to them: arrive now (thread 0's
+        // store above is released by its own arrive), wait only right before the first remote add.
+        if (gather) cluster_arrive_release();
         for (int i = t; i < kBins; i += kTopkThreads) h[i] = p.hist[(size_t)row * kBins + i];
-        cluster.sync();            // the first CTA's counters are initialised before anyone pushes to them
+        __syncthreads();
     } else {
         for (int i = t; i < kBins; i += kTopkThreads) h_local[i] = 0;
         __syncthreads();
@@ -230,10 +236,8 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
     find_threshold_bin(h, ws, k, &bstar, &above);
 
     // ---- scan the slice into this CTA's own lists (local shared-memory atomics), then hand them
-    //      over to the first CTA in two bulk copies: one remote atomic per CTA instead of one per key
+    //      over to the first CTA's gather lists: one remote atomic per CTA and list instead of one per key
     __shared__ uint32_t my_nsel, my_ncand, base_sel, base_cand;
-    uint64_t* my_sel = sel;                      // [kClusterMaxK]   (every CTA has the same layout)
-    uint64_t* my_cand = sel + kClusterMaxK;      // [kClusterCand]
     if (t == 0) { my_nsel = 0; my_ncand = 0; }
     __syncthreads();
     {
@@ -263,7 +267,10 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
         }
     }
     __syncthreads();
-    if (CS > 1 || cand_global) {
+    uint64_t* sel = my_sel;                           // the lists the first CTA resolves from
+    uint64_t* cand = my_cand;
+    if (gather) {
+        if (p.hist) cluster_wait();                   // (the no-hist path has passed two full cluster barriers)
         ClusterShared* sh0 = cluster.map_shared_rank(&sh, 0);
         // a CTA whose own candidate list overflowed reports a count beyond any capacity: the resolver
         // then rescans the row instead of trusting the lists
@@ -273,34 +280,23 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
             base_cand = atomicAdd(&sh0->ncand, nc);
         }
         __syncthreads();
-        uint64_t* sel0 = cluster.map_shared_rank(sel, 0);
-        uint64_t* cand0 = cand_global ? cand : cluster.map_shared_rank(sel + kClusterMaxK, 0);
-        // read everything this thread will move before anyone writes (rank 0's source is its destination array)
-        constexpr int kSelPer = kClusterMaxK / kTopkThreads, kCandPer = kClusterCand / kTopkThreads;
-        uint64_t vs[kSelPer], vc[kCandPer];
+        // the gather lists are written by nobody else's scan, so every CTA copies as soon as it knows its offsets
+        uint64_t* sel0 = cluster.map_shared_rank(g_sel, 0);
+        uint64_t* cand0 = cand_global ? p.cand + (size_t)row * p.cand_cap : cluster.map_shared_rank(g_cand, 0);
         const uint32_t ns = min(my_nsel, (uint32_t)kClusterMaxK), ncl = min(my_ncand, (uint32_t)kClusterCand);
-#pragma unroll
-        for (int u = 0; u < kSelPer; ++u) vs[u] = (t + u * kTopkThreads < ns) ? my_sel[t + u * kTopkThreads] : 0;
-#pragma unroll
-        for (int u = 0; u < kCandPer; ++u) vc[u] = (t + u * kTopkThreads < ncl) ? my_cand[t + u * kTopkThreads] : 0;
-        cluster.sync();               // all CTAs hold their keys in registers and know their offsets
-#pragma unroll
-        for (int u = 0; u < kSelPer; ++u) {
-            const uint32_t i = t + u * kTopkThreads;
-            if (i < ns && base_sel + i < (uint32_t)kClusterMaxK) sel0[base_sel + i] = vs[u];
-        }
-        if (nc < 0x40000000u) {
-#pragma unroll
-            for (int u = 0; u < kCandPer; ++u) {
-                const uint32_t i = t + u * kTopkThreads;
-                if (i < ncl && base_cand + i < cand_capacity) cand0[base_cand + i] = vc[u];
-            }
-        }
+        for (uint32_t i = t; i < ns; i += kTopkThreads)
+            if (base_sel + i < (uint32_t)kClusterMaxK) sel0[base_sel + i] = my_sel[i];
+        if (nc < 0x40000000u)
+            for (uint32_t i = t; i < ncl; i += kTopkThreads)
+                if (base_cand + i < cand_capacity) cand0[base_cand + i] = my_cand[i];
+        sel = g_sel;
+        cand = cand_global ? p.cand + (size_t)row * p.cand_cap : g_cand;
+        cluster.sync();                               // everything pushed to the first CTA has landed
     } else if (t == 0) {
         sh.nsel = my_nsel;            // single CTA, lists already in place
         sh.ncand = my_ncand;
     }
-    cluster.sync();
+    if (!gather) __syncthreads();
     if (rank != 0) return;
 
     // ---- first CTA: resolve, order, emit — all in shared memory
