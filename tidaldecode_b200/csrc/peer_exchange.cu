@@ -61,7 +61,6 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 
 __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const ExchangeParams p) {
     extern __shared__ __align__(16) unsigned char xsm[];      // kClusterSmem bytes when candidates are ranked
-    __shared__ int s_last;
     pdl_wait();
     pdl_launch_dependents();
     // every CTA reads the counter before the last one to finish advances it
@@ -77,25 +76,22 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
         const uint4 v = p.send[i];
         for (int r = 0; r < p.world; ++r) p.peer_stage[r][my_slot + i] = v;
     }
-    // 2. the stores of every CTA are ordered before the rank's arrival, which the last CTA to get here posts
-    __threadfence_system();
+    // 2. the stores of every CTA are ordered before the rank's arrival, which the last CTA to get here posts.
+    //    One thread per CTA fences: the barrier orders the CTA's stores before it, and a release by that thread is
+    //    cumulative over what it has observed (fences by all 1024 threads cost microseconds, this costs one).
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();
         const uint32_t done = atomicAdd(&p.state[2], 1u);
-        s_last = (done == gridDim.x - 1) ? 1 : 0;
-        if (s_last) {
+        if (done == gridDim.x - 1) {
             p.state[2] = 0;                                   // every CTA has added: ready for the next exchange
-            __threadfence_system();
+            __threadfence_system();                           // ... and their stores, observed through the counter, go first
+            for (int r = 0; r < p.world; ++r) atomicAdd_system(&p.peer_count[r][par * p.world + p.rank], 1u);
         }
     }
-    __syncthreads();
-    if (s_last && (int)threadIdx.x < p.world) {
-        __threadfence_system();
-        atomicAdd_system(&p.peer_count[threadIdx.x][par * p.world + p.rank], 1u);
-    }
 
-    // 3. wait for every rank's arrival on this GPU (bounded: a missing rank becomes a status bit, not a hang)
+    // 3. wait for every rank's arrival on this GPU (bounded: a missing rank becomes a status bit, not a hang);
+    //    the acquiring loads and the barrier order every thread's later reads of the staged blocks
     if ((int)threadIdx.x < p.world) {
         const uint32_t* c = &p.peer_count[p.rank][par * p.world + threadIdx.x];
         bool ok = false;
@@ -109,7 +105,6 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
         if (!ok && p.status) atomicOr(p.status, TIDAL_DEV_WAIT_TIMEOUT);
     }
     __syncthreads();
-    __threadfence_system();
 
     // 4. staged blocks into the receive buffer
     const uint4* stage = p.peer_stage[p.rank] + (int64_t)par * p.world * p.slot_vec;
@@ -170,7 +165,11 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
         tp.seg_stride = slot_words;
         tp.row_len = nullptr;
         for (int row = blockIdx.x; row < p.cand_rows; row += gridDim.x) {
-            topk_cluster_row(tp, row, xsm);
+            // the candidates' order is the positions' order: threshold, then one ordered pass (no winners' list, no sort)
+            if (!topk_ordered_row(tp, row, xsm)) {
+                __syncthreads();
+                topk_cluster_row(tp, row, xsm);          // a threshold bin too crowded for shared memory
+            }
             __syncthreads();
         }
     }
@@ -242,9 +241,14 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
     p.cs_off = a->cand_score_off; p.ci_off = a->cand_idx_off;
     p.own_lo = a->own_lo; p.own_hi = a->own_hi;
     p.sel_out = a->d_sel_out; p.sel_stride = a->sel_stride; p.sel_count = a->d_sel_count;
-    // a CTA per candidate row, and enough CTAs to move the block in two passes; all resident at once
+    // a CTA per candidate row, enough CTAs to move the block in two passes and to merge two outputs per thread;
+    // all resident at once
     int64_t ctas = (p.nvec + 2 * kXchgThreads - 1) / (2 * kXchgThreads);
     if (ctas < a->cand_rows) ctas = a->cand_rows;
+    if (a->d_merge_out) {
+        const int64_t by_merge = ((int64_t)a->merge_rows * a->merge_head_dim + 2 * kXchgThreads - 1) / (2 * kXchgThreads);
+        if (ctas < by_merge) ctas = by_merge;
+    }
     if (ctas < 1) ctas = 1;
     if (ctas > kXchgMaxCtas) ctas = kXchgMaxCtas;
     const size_t smem = a->cand_rows > 0 ? kClusterSmem : 0;

@@ -312,7 +312,16 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
     // Few candidates in shared memory (the usual case: a 12-bit first digit leaves a few dozen keys in the
     // threshold bin): rank them directly — keys are distinct, so the `need` largest are those with fewer
     // than `need` larger ones — instead of up to seven more radix passes with four barriers each.
-    const bool few = !overflow && !cand_global && ncand_total <= 256u && need <= ncand_total;
+    // Candidates that went to the workspace but would fit shared memory after all are brought in: the passes
+    // below then run on shared memory, and a handful of them is ranked directly like any short row's.
+    bool cand_in_smem = !cand_global;
+    if (cand_global && !overflow && ncand_total <= (uint32_t)kClusterCand) {
+        for (uint32_t i = t; i < ncand_total; i += kTopkThreads) g_cand[i] = cand[i];
+        __syncthreads();
+        cand = g_cand;
+        cand_in_smem = true;
+    }
+    const bool few = !overflow && cand_in_smem && ncand_total <= 256u && need <= ncand_total;
     if (few) {
         if ((uint32_t)t < ncand_total) {
             const uint64_t key = cand[t];
@@ -422,6 +431,119 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
     if (t == 0 && p.out_count) p.out_count[row] = (int32_t)before;
     if (p.hist)
         for (int i = t; i < kBins; i += kTopkThreads) p.hist[(size_t)row * kBins + i] = 0;
+}
+
+// ------------------------------------------------------------------ one CTA, rows whose order is the wanted order
+// A row that one CTA handles alone (the gathered candidates of all ranks: world * k scores) needs neither the
+// winners' list nor a sort: find the exact key T of the k-th largest score — first digit by histogram, the rest
+// among the threshold bin's candidates — and then walk the row once more IN ORDER, keeping what is >= T: the
+// output comes out in ascending place (and the ownership filter is part of the same compaction).  Three passes
+// over scores that sit in L2, a handful of block-wide barriers, no sorting network (ordering 1024 winners by a
+// bitonic network alone costs more than all of this).  Same result as topk_cluster_row, bit for bit.
+// Returns false — for all threads alike, nothing written — if the threshold bin holds more candidates than
+// shared memory takes; the caller then uses topk_cluster_row.  `csm`: kClusterSmem bytes.
+__device__ __forceinline__ bool topk_ordered_row(const TopkParams& p, const int row, unsigned char* csm) {
+    uint32_t* h = reinterpret_cast<uint32_t*>(csm);                                   // [kBins]
+    uint64_t* cand = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);     // [kClusterCand]
+    __shared__ uint32_t ws[32];
+    __shared__ uint32_t s_ncand, s_digit, s_need, s_done, s_total;
+    __shared__ unsigned long long s_T;
+    const int t = threadIdx.x;
+    const int64_t n = p.n;
+    const uint32_t k = (uint32_t)p.k;
+    auto key_at = [&](int64_t j) -> uint64_t {
+        return make_key(p.scores[elem_off(p, p.row_stride, row, j)], (uint32_t)j, n, p.force_last);
+    };
+    for (int i = t; i < kBins; i += kTopkThreads) h[i] = 0;
+    if (t == 0) s_ncand = 0;
+    __syncthreads();
+#pragma unroll 4
+    for (int64_t j = t; j < n; j += kTopkThreads) atomicAdd(&h[key_bin(key_at(j))], 1u);
+    __syncthreads();
+    int bstar;
+    uint32_t above;
+    find_threshold_bin(h, ws, k, &bstar, &above);
+    uint32_t need = k - above;                          // winners among the threshold bin's keys (>= 1)
+#pragma unroll 4
+    for (int64_t j = t; j < n; j += kTopkThreads) {
+        const uint64_t key = key_at(j);
+        if (key_bin(key) == bstar) {
+            const uint32_t at = atomicAdd(&s_ncand, 1u);
+            if (at < (uint32_t)kClusterCand) cand[at] = key;
+        }
+    }
+    __syncthreads();
+    const uint32_t nc = s_ncand;
+    if (nc > (uint32_t)kClusterCand) return false;
+    if (nc <= (uint32_t)kTopkThreads) {
+        // keys are distinct: T is the candidate with exactly need - 1 larger ones
+        if ((uint32_t)t < nc) {
+            const uint64_t key = cand[t];
+            uint32_t larger = 0;
+            for (uint32_t i = 0; i < nc; ++i) larger += cand[i] > key ? 1u : 0u;
+            if (larger == need - 1) s_T = key;
+        }
+    } else {
+        // 8-bit radix passes over key bits 51..0 of the candidates until the digit's population is what is needed
+        uint64_t prefix = (uint64_t)bstar << 52, known_mask = 0xFFFull << 52;
+        bool done = false;
+        for (int shift = 44; !done && shift >= -4; shift -= 8) {
+            const int sft = shift < 0 ? 0 : shift;
+            const int nb = shift < 0 ? 16 : 256;
+            const uint32_t dmask = (uint32_t)nb - 1u;
+            if (t < 256) h[t] = 0;
+            __syncthreads();
+            for (uint32_t i = t; i < nc; i += kTopkThreads) {
+                const uint64_t key = cand[i];
+                if ((key & known_mask) == prefix) atomicAdd(&h[(uint32_t)(key >> sft) & dmask], 1u);
+            }
+            __syncthreads();
+            if (t < 32) warp_find_digit(h, nb, need, &s_digit, &s_need, &s_done);
+            __syncthreads();
+            prefix |= (uint64_t)s_digit << sft;
+            known_mask |= (uint64_t)dmask << sft;
+            need = s_need;
+            done = s_done != 0;
+            __syncthreads();
+        }
+        // winners among the candidates: key >= prefix (all keys of the last digit's group win)
+        if (t == 0) s_T = prefix;
+    }
+    __syncthreads();
+    const uint64_t T = s_T;
+    // ---- the row once more, in order: thread t takes a run of consecutive places
+    const int64_t per = (n + kTopkThreads - 1) / kTopkThreads;
+    const int64_t j0 = (int64_t)t * per, j1 = min(n, j0 + per);
+    const bool own = p.own_hi > p.own_lo;
+    auto value_of = [&](int64_t j) -> int32_t {
+        return p.in_idx ? p.in_idx[elem_off(p, p.in_idx_stride, row, j)] : (int32_t)j + p.idx_offset;
+    };
+    uint32_t mine = 0;
+    for (int64_t j = j0; j < j1; ++j)
+        if (key_at(j) >= T) {
+            const int32_t v = value_of(j);
+            mine += (!own || (v >= p.own_lo && v < p.own_hi)) ? 1u : 0u;
+        }
+    const uint32_t incl = block_scan_incl(mine, ws);
+    uint32_t at = incl - mine;
+    int32_t* out_idx = p.out_idx + (size_t)row * p.out_stride;
+    float* out_val = p.out_val ? p.out_val + (size_t)row * p.out_stride : nullptr;
+    if (mine)
+        for (int64_t j = j0; j < j1; ++j)
+            if (key_at(j) >= T) {
+                const int32_t v = value_of(j);
+                if (!own || (v >= p.own_lo && v < p.own_hi)) {
+                    out_idx[at] = own ? v - p.own_lo : v;
+                    if (out_val) out_val[at] = p.scores[elem_off(p, p.row_stride, row, j)];
+                    ++at;
+                }
+            }
+    if (t == kTopkThreads - 1) {
+        s_total = incl;
+        if (p.out_count) p.out_count[row] = (int32_t)incl;
+    }
+    __syncthreads();
+    return true;
 }
 
 }  // namespace tidal
