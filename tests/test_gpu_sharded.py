@@ -57,12 +57,12 @@ def _worker(rank, world, port, result_dir, reduce, exchange):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+@pytest.mark.parametrize("world,exchange", [(2, "nccl"), (2, "peer"), (4, "peer"), (4, "nccl"), (8, "peer")],
+                         ids=["2-nccl", "2-peer", "4-peer", "4-nccl", "8-peer"])
 @pytest.mark.parametrize("reduce", ["sum", "none"])
-def test_sharded_two_gpus(tmp_path, reduce, exchange):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = min(torch.cuda.device_count(), 4)
+def test_sharded_ranks(tmp_path, reduce, world, exchange):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     port = 29700 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(world, port, str(tmp_path), reduce, exchange), nprocs=world, join=True)
     res = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]

@@ -94,7 +94,7 @@ class GroupHealth:
 
 
 # largest group the peer-store exchange has run on; larger groups get NCCL unless exchange="peer" is asked for
-kPeerValidatedWorld = 4
+kPeerValidatedWorld = 8
 
 
 class ShardedDecodeAttention:
