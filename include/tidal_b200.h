@@ -366,19 +366,21 @@ int tidal_decode_qkv(const tidal_linear_args* lin, const tidal_rope_append_args*
  * byte r * slot_bytes.  Memory the caller sets up once:
  *   staging   per rank 2 * world * slot_bytes bytes, mapped on every rank (CUDA IPC / fabric handles);
  *             d_peer_stage[r] is rank r's staging buffer as addressed from this GPU (r = rank: its own);
- *   counters  per rank 2 * world uint32, zeroed, mapped the same way: d_peer_count[r];
+ *   flags     per rank 2 * world * TIDAL_XCHG_MAX_CTAS uint32, zeroed, mapped the same way: d_peer_count[r];
  *   d_state   4 uint32 of this rank's own memory, zeroed.
  * d_peer_stage and d_peer_count are device arrays of `world` pointers.  Nothing is reset between
  * calls.  Contract across calls on one set of buffers: slot_bytes, world and rank never change; `bytes`
- * and the optional parts may differ from call to call (a rank posts ONE arrival per exchange whatever
- * the call carries) as long as every rank passes the same values in the same call; the ranks issue their
- * calls in the same order.
+ * and the optional parts may differ from call to call (every CTA of a rank publishes the NUMBER of the
+ * exchange in its own flag word on every peer, and a call waits for as many flags per rank as it has
+ * CTAs itself) as long as every rank passes the same values in the same call; the ranks issue their
+ * calls in the same order, each counting its own calls.
  * A rank that never arrives makes the others' bounded waits run out (wait_limit polls, 0 = the
  * default of about half a second): TIDAL_DEV_WAIT_TIMEOUT is OR-ed into *d_status (if given) and the
- * call completes with incomplete data.  After that the arrival counters and the exchange count of the
- * ranks no longer agree, and every later call on these buffers would time out or read stale blocks:
- * tidal_peer_exchange_reset must run on EVERY rank, with no exchange in flight anywhere (a host-side
- * barrier before and after), before the buffers are used again. */
+ * call completes with incomplete data.  If the ranks' call counts no longer agree after that (a rank
+ * skipped the call rather than being late), every later call on these buffers would time out or read
+ * stale blocks: tidal_peer_exchange_reset must run on EVERY rank, with no exchange in flight anywhere
+ * (a host-side barrier before and after), before the buffers are used again. */
+#define TIDAL_XCHG_MAX_CTAS 64
 typedef struct {
     const void* d_send;
     void* d_recv;                /* NULL when only the merge / the ranking are wanted */
@@ -411,7 +413,7 @@ typedef struct {
     int32_t* d_sel_count;
 } tidal_exchange_args;
 int tidal_peer_all_gather(const tidal_exchange_args* args, void* stream);
-/* Zeroes this rank's arrival counters (d_count = d_peer_count[rank], 2 * world words) and d_state on
+/* Zeroes this rank's flag words (d_count = d_peer_count[rank], 2 * world * TIDAL_XCHG_MAX_CTAS words) and d_state on
  * the stream.  See tidal_peer_all_gather for when and how: every rank, nothing in flight. */
 int tidal_peer_exchange_reset(uint32_t* d_count, uint32_t* d_state, int world, void* stream);
 

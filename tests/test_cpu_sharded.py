@@ -233,25 +233,27 @@ def test_rank_leaving_between_steps_is_noticed_on_the_host(tmp_path):
     assert res["seconds"] < 30, res
 
 
-def test_peer_exchange_arrival_accounting_is_independent_of_payload():
-    """A rank posts ONE arrival per exchange (its last CTA to have stored does), so the count a rank waits for
-    follows from the number of exchanges alone and exchanges of different payloads and grids (selection layers
-    send partials and candidates and rank them, sparse layers only partials) can follow each other in any order
-    on one set of buffers: a model of the counters over sel, sparse, sparse, sel, ..."""
-    world = 4
+def test_peer_exchange_flags_are_independent_of_payload():
+    """Every CTA of a rank publishes the NUMBER of the exchange in its own flag word, and a call waits for as many
+    flags per rank as it has CTAs itself (all ranks launch the same grid for the same call).  So exchanges of
+    different payloads and grids (selection layers send partials and candidates and rank them, sparse layers only
+    partials) can follow each other in any order on one set of buffers: a model of the flag words over
+    sel, sparse, sparse, sel, ... in which a flag left by an earlier, larger grid never satisfies a later wait."""
+    from tidaldecode_b200 import _lib as L
+
+    world, max_ctas = 4, L.XCHG_MAX_CTAS
     grids = {"sel": 25, "sparse": 9}                             # CTAs of the two kinds of call differ
-    count = [[0] * world for _ in range(2)]                      # one rank's counters [parity][source rank]
-    stored = 0                                                   # the rank's own "CTAs that stored" word
+    flags = [[[0] * max_ctas for _ in range(world)] for _ in range(2)]      # one rank's flag words [parity][source][CTA]
     epoch = 0
     for payload in ("sel", "sparse", "sparse", "sel", "sparse", "sel", "sel", "sparse", "sparse", "sparse"):
         e = epoch + 1
         par = e & 1
-        target = (e + 1) // 2                                    # what the kernel waits for
+        g = grids[payload]
+        assert g <= max_ctas
+        # before anyone has published, no source rank's first g flags all show e (stale flags hold older numbers)
+        assert not any(all(flags[par][r][c] - e >= 0 for c in range(g)) for r in range(world))
         for r in range(world):
-            for cta in range(grids[payload]):
-                stored += 1
-                if stored == grids[payload]:                     # the last CTA to have stored posts the arrival and clears the word
-                    stored = 0
-                    count[par][r] += 1
-        assert all(c == target for c in count[par]), (payload, e, count, target)
+            for c in range(g):
+                flags[par][r][c] = e
+        assert all(flags[par][r][c] - e >= 0 for r in range(world) for c in range(g))
         epoch = e

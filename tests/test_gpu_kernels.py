@@ -709,15 +709,14 @@ def test_peer_exchange_wait_runs_out_and_reset_recovers(T):
     torch.cuda.synchronize()
     assert int(status.item()) == L.DEV_WAIT_TIMEOUT
     assert torch.equal(recv[0], send), "its own block still arrives"
-    # without a reset the counters stay skewed: the next exchange of this parity would pass on stale arrivals
     px.reset()
     status.zero_()
     torch.cuda.synchronize()
-    assert int(px.counters.abs().sum()) == 0 and int(px.state.abs().sum()) == 0
-    # the peer's part of exchange 1 (parity 1), as its kernel would have left it: block in slot [1][1], arrivals
+    assert int(px.flags.abs().sum()) == 0 and int(px.state.abs().sum()) == 0
+    # the peer's part of exchange 1 (parity 1), as its kernel would have left it: block in slot [1][1], every CTA's flag = 1
     other = torch.full((words,), 7.0, dtype=torch.float32, device=dev)
     px.stage[1, 1].copy_(other.view(torch.uint8))
-    px.counters[1, 1] = 1
+    px.flags[1, 1] = 1
     px.all_gather(send, recv, status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
@@ -725,7 +724,7 @@ def test_peer_exchange_wait_runs_out_and_reset_recovers(T):
     # and exchange 2 (parity 0) with another payload size on the same buffers
     half = words // 2 // 4 * 4
     px.stage[0, 1, : half * 4].copy_(other[:half].view(torch.uint8))
-    px.counters[0, 1] = 1
+    px.flags[0, 1] = 2
     recv.zero_()
     px.all_gather(send, recv, nbytes=half * 4, status=status)
     torch.cuda.synchronize()
@@ -770,7 +769,7 @@ def test_peer_exchange_merges_and_ranks_in_one_launch(T, world, B, Hq, D, k, row
         par = exchange & 1
         for r in range(1, world):
             px.stage[par, r].copy_(blocks[r].view(torch.uint8))
-            px.counters[par, r] = (exchange + 1) // 2
+            px.flags[par, r] = exchange
         own = (2 * n_loc, 3 * n_loc) if world > 2 else (0, n_loc)
         out = torch.full((B * Hq, D), float("nan"), dtype=dtype, device=dev)
         sel = torch.full((rows, k), -1, dtype=torch.int32, device=dev)

@@ -16,6 +16,7 @@ DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 ERR_ARG, ERR_WORKSPACE, ERR_CUDA = -1, -2, -3
 DEV_WAIT_TIMEOUT, DEV_BAD_INDEX, DEV_TOPK_OVERFLOW = 1, 2, 4
 TOPK_BINS = 4096
+XCHG_MAX_CTAS = 64
 
 EXPORTS = (
     "tidal_version", "tidal_last_error", "tidal_launch_count", "tidal_ws_bytes", "tidal_ws_init", "tidal_ws_release", "tidal_ws_status",

@@ -4,10 +4,10 @@
 // exchange moves in time; here every rank's kernel
 //   1. stores its block into its slot of every peer's staging buffer (plain peer stores through
 //      pointers the host obtained by exchanging memory handles; no multicast),
-//   2. fences; the LAST of its CTAs to get there adds 1 to this rank's arrival counter on every peer
-//      (one system-scope add per peer per exchange, whatever the grid),
-//   3. waits — with an iteration limit — until every rank's counter on this GPU shows the current
-//      exchange, and
+//   2. publishes, per CTA, the number of the current exchange in that CTA's flag word on every peer (one
+//      releasing store per peer: no atomics, no second level of signalling),
+//   3. waits — with an iteration limit — until the flags of every CTA of every rank on this GPU show the
+//      current exchange, and
 //   4. works on the staged blocks in place: copies them to the caller's receive buffer (if one is given),
 //      merges the ranks' softmax partials (m, l, o) into the attention output (if asked), and ranks the
 //      ranks' top-k candidates into the global selection, keeping the positions this rank owns (if asked:
@@ -16,14 +16,15 @@
 // Staging and counters are double-buffered by the parity of an exchange counter kept in device memory
 // and advanced by the last CTA to finish, so nothing is reset between exchanges: a rank can be at most
 // one exchange ahead of another, because it needs the other's arrivals to finish the one in between.
-// The arrivals expected per exchange do not depend on the bytes or the grid of a call, so calls of
-// different sizes may follow each other on one set of buffers.
+// Flags carry exchange numbers, not counts: a call waits for the flags of as many CTAs per rank as it runs
+// itself (every rank passes the same arguments, hence launches the same grid), so calls of different sizes
+// and grids may follow each other on one set of buffers, and a flag that arrives twice or late harms nothing.
 #include "topk_common.cuh"
 
 namespace tidal {
 
 constexpr int kXchgThreads = kTopkThreads;       // 1024: the candidate ranking is the top-k's one-CTA form
-constexpr int kXchgMaxCtas = 64;                 // all resident at once (one CTA per SM), so no CTA waits for an SM
+constexpr int kXchgMaxCtas = TIDAL_XCHG_MAX_CTAS;  // all resident at once (one CTA per SM), so no CTA waits for an SM
 constexpr int kXchgMaxWorld = 16;
 constexpr uint32_t kXchgSpinLimit = 1u << 22;    // default wait limit (about half a second)
 
@@ -32,9 +33,9 @@ struct ExchangeParams {
     int64_t nvec;                 // 16-byte vectors in a block
     int64_t slot_vec;             // vectors between the blocks of two ranks (staging and receive buffer alike)
     uint4* const* peer_stage;     // [world]: every rank's staging buffer [2][world][slot_vec], as mapped on this GPU
-    uint32_t* const* peer_count;  // [world]: every rank's arrival counters [2][world]
+    uint32_t* const* peer_count;  // [world]: every rank's flag words [2][world][kXchgMaxCtas]
     uint4* out;                   // local receive buffer [world][slot_vec], or nullptr
-    uint32_t* state;              // local: [0] exchanges completed, [1] CTAs done, [2] CTAs that stored, [3] status sink
+    uint32_t* state;              // local: [0] exchanges completed, [1] CTAs done, [2] unused, [3] status sink
     uint32_t* status;
     uint32_t spin_limit;          // iterations a CTA polls for the other ranks before it gives up
     int rank, world;
@@ -53,6 +54,9 @@ struct ExchangeParams {
     int32_t* sel_count;
 };
 
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -66,7 +70,6 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
     // every CTA reads the counter before the last one to finish advances it
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(&p.state[0]) + 1u;
     const int par = (int)(e & 1u);
-    const uint32_t target = (e + 1u) / 2u;                   // arrivals per rank after this exchange, for this parity
     const int64_t stride = (int64_t)gridDim.x * kXchgThreads;
     const int64_t first = (int64_t)blockIdx.x * kXchgThreads + threadIdx.x;
 
@@ -76,27 +79,20 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
         const uint4 v = p.send[i];
         for (int r = 0; r < p.world; ++r) p.peer_stage[r][my_slot + i] = v;
     }
-    // 2. the stores of every CTA are ordered before the rank's arrival, which the last CTA to get here posts.
-    //    One thread per CTA fences: the barrier orders the CTA's stores before it, and a release by that thread is
-    //    cumulative over what it has observed (fences by all 1024 threads cost microseconds, this costs one).
+    // 2. this CTA's flag on every peer: the barrier orders the CTA's stores before the releasing stores of the
+    //    lanes that publish (a release is cumulative over what its thread has observed), one lane per peer
     __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        const uint32_t done = atomicAdd(&p.state[2], 1u);
-        if (done == gridDim.x - 1) {
-            p.state[2] = 0;                                   // every CTA has added: ready for the next exchange
-            __threadfence_system();                           // ... and their stores, observed through the counter, go first
-            for (int r = 0; r < p.world; ++r) atomicAdd_system(&p.peer_count[r][par * p.world + p.rank], 1u);
-        }
-    }
+    if ((int)threadIdx.x < p.world)
+        st_release_sys(&p.peer_count[threadIdx.x][((size_t)par * p.world + p.rank) * kXchgMaxCtas + blockIdx.x], e);
 
-    // 3. wait for every rank's arrival on this GPU (bounded: a missing rank becomes a status bit, not a hang);
-    //    the acquiring loads and the barrier order every thread's later reads of the staged blocks
-    if ((int)threadIdx.x < p.world) {
-        const uint32_t* c = &p.peer_count[p.rank][par * p.world + threadIdx.x];
+    // 3. wait for the flags of every CTA of every rank on this GPU (bounded: a missing rank becomes a status bit,
+    //    not a hang); the acquiring loads and the barrier order every thread's later reads of the staged blocks
+    for (int i = threadIdx.x; i < p.world * (int)gridDim.x; i += kXchgThreads) {
+        const int r = i / (int)gridDim.x, c = i - r * (int)gridDim.x;
+        const uint32_t* f = &p.peer_count[p.rank][((size_t)par * p.world + r) * kXchgMaxCtas + c];
         bool ok = false;
         for (uint32_t it = 0; it < p.spin_limit; ++it) {
-            if ((int32_t)(ld_acquire_sys(c) - target) >= 0) {
+            if ((int32_t)(ld_acquire_sys(f) - e) >= 0) {
                 ok = true;
                 break;
             }
@@ -111,27 +107,60 @@ __global__ void __launch_bounds__(kXchgThreads) peer_all_gather_kernel(const Exc
     if (p.out)
         for (int r = 0; r < p.world; ++r)
             for (int64_t i = first; i < p.nvec; i += stride) p.out[(int64_t)r * p.slot_vec + i] = stage[(int64_t)r * p.slot_vec + i];
-    //    the merge of the ranks' partials, in rank order (the arithmetic of merge_shards_kernel)
+    //    the merge of the ranks' partials, in rank order (the arithmetic of merge_shards_kernel); a thread owns four
+    //    consecutive output elements when the rows allow 16-byte accesses, and all loads of a rank are independent
     if (p.merge_out) {
         const float* st = reinterpret_cast<const float*>(stage);
         const int64_t slot_words = p.slot_vec * 4;
-        const int64_t total = (int64_t)p.merge_rows * p.merge_dim;
-        for (int64_t idx = first; idx < total; idx += stride) {
-            const int64_t r = idx / p.merge_dim;
-            const int d = (int)(idx - r * p.merge_dim);
+        const int D = p.merge_dim;
+        const bool vec = (D % 4 == 0) && (p.o_off % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.merge_out) & 15) == 0);
+        const int lanes = vec ? D / 4 : D;                 // work items per row
+        const int64_t total = (int64_t)p.merge_rows * lanes;
+        for (int64_t u = first; u < total; u += stride) {
+            const int64_t r = u / lanes;
+            const int d = (int)(u - r * lanes) * (vec ? 4 : 1);
             float M = -INFINITY;
             for (int s = 0; s < p.world; ++s) M = fmaxf(M, st[s * slot_words + p.m_off + r]);
-            float acc = 0.f, L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float L = 0.f;
+#pragma unroll 4
             for (int s = 0; s < p.world; ++s) {
                 const float ms = st[s * slot_words + p.m_off + r];
                 const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
-                acc = fmaf(w, st[s * slot_words + p.o_off + r * p.merge_dim + d], acc);
+                const float* po = st + s * slot_words + p.o_off + r * D + d;
+                if (vec) {
+                    const float4 v = *reinterpret_cast<const float4*>(po);
+                    acc.x = fmaf(w, v.x, acc.x);
+                    acc.y = fmaf(w, v.y, acc.y);
+                    acc.z = fmaf(w, v.z, acc.z);
+                    acc.w = fmaf(w, v.w, acc.w);
+                } else {
+                    acc.x = fmaf(w, po[0], acc.x);
+                }
                 L = fmaf(w, st[s * slot_words + p.l_off + r], L);
             }
-            const float v = L > 0.f ? acc / L : 0.f;
-            if (p.merge_dtype == TIDAL_DTYPE_F16) reinterpret_cast<__half*>(p.merge_out)[idx] = __float2half_rn(v);
-            else if (p.merge_dtype == TIDAL_DTYPE_BF16) reinterpret_cast<__nv_bfloat16*>(p.merge_out)[idx] = __float2bfloat16_rn(v);
-            else reinterpret_cast<float*>(p.merge_out)[idx] = v;
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            const float vals[4] = {L > 0.f ? acc.x / L : 0.f, L > 0.f ? acc.y / L : 0.f, L > 0.f ? acc.z / L : 0.f,
+                                   L > 0.f ? acc.w / L : 0.f};
+            (void)inv;
+            const int64_t at = r * D + d;
+            const int nout = vec ? 4 : 1;
+            if (p.merge_dtype == TIDAL_DTYPE_F16) {
+                __half* o = reinterpret_cast<__half*>(p.merge_out) + at;
+                if (vec) {
+                    *reinterpret_cast<__half2*>(o) = __floats2half2_rn(vals[0], vals[1]);
+                    *reinterpret_cast<__half2*>(o + 2) = __floats2half2_rn(vals[2], vals[3]);
+                } else o[0] = __float2half_rn(vals[0]);
+            } else if (p.merge_dtype == TIDAL_DTYPE_BF16) {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.merge_out) + at;
+                if (vec) {
+                    *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(vals[0], vals[1]);
+                    *reinterpret_cast<__nv_bfloat162*>(o + 2) = __floats2bfloat162_rn(vals[2], vals[3]);
+                } else o[0] = __float2bfloat16_rn(vals[0]);
+            } else {
+                float* o = reinterpret_cast<float*>(p.merge_out) + at;
+                for (int i = 0; i < nout; ++i) o[i] = vals[i];
+            }
         }
     }
     //    and the global selection from the ranks' candidates: row r of rank s's block holds cand_k (score, position)
@@ -246,7 +275,7 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
     int64_t ctas = (p.nvec + 2 * kXchgThreads - 1) / (2 * kXchgThreads);
     if (ctas < a->cand_rows) ctas = a->cand_rows;
     if (a->d_merge_out) {
-        const int64_t by_merge = ((int64_t)a->merge_rows * a->merge_head_dim + 2 * kXchgThreads - 1) / (2 * kXchgThreads);
+        const int64_t by_merge = ((int64_t)a->merge_rows * a->merge_head_dim / 4 + kXchgThreads - 1) / kXchgThreads;   // one float4 per thread
         if (ctas < by_merge) ctas = by_merge;
     }
     if (ctas < 1) ctas = 1;
@@ -261,7 +290,7 @@ extern "C" int tidal_peer_all_gather(const tidal_exchange_args* a, void* stream)
 extern "C" int tidal_peer_exchange_reset(uint32_t* d_count, uint32_t* d_state, int world, void* stream) {
     TIDAL_REQUIRE(d_count && d_state, TIDAL_ERR_ARG, "null pointer");
     TIDAL_REQUIRE(world >= 2 && world <= kXchgMaxWorld, TIDAL_ERR_ARG, "bad world %d (2..%d ranks)", world, kXchgMaxWorld);
-    TIDAL_CUDA_OK(cudaMemsetAsync(d_count, 0, sizeof(uint32_t) * 2 * world, (cudaStream_t)stream));
+    TIDAL_CUDA_OK(cudaMemsetAsync(d_count, 0, sizeof(uint32_t) * 2 * world * kXchgMaxCtas, (cudaStream_t)stream));
     TIDAL_CUDA_OK(cudaMemsetAsync(d_state, 0, sizeof(uint32_t) * 4, (cudaStream_t)stream));
     return TIDAL_OK;
 }

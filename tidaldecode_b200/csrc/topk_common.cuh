@@ -437,40 +437,85 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
 // A row that one CTA handles alone (the gathered candidates of all ranks: world * k scores) needs neither the
 // winners' list nor a sort: find the exact key T of the k-th largest score — first digit by histogram, the rest
 // among the threshold bin's candidates — and then walk the row once more IN ORDER, keeping what is >= T: the
-// output comes out in ascending place (and the ownership filter is part of the same compaction).  Three passes
-// over scores that sit in L2, a handful of block-wide barriers, no sorting network (ordering 1024 winners by a
-// bitonic network alone costs more than all of this).  Same result as topk_cluster_row, bit for bit.
+// output comes out in ascending place (and the ownership filter is part of the same compaction).  Thread t owns
+// the run of consecutive places [t * E, (t + 1) * E); for rows of up to 8 * kTopkThreads scores it loads its keys
+// and values once and keeps them in registers through all three steps, so the row is read from memory once and
+// the whole routine is a handful of block-wide barriers — no sorting network (ordering 1024 winners by a bitonic
+// network alone costs more than all of this).  Same result as topk_cluster_row, bit for bit.
 // Returns false — for all threads alike, nothing written — if the threshold bin holds more candidates than
 // shared memory takes; the caller then uses topk_cluster_row.  `csm`: kClusterSmem bytes.
+constexpr int kOrderedRegs = 8;       // places per thread that are kept in registers
 __device__ __forceinline__ bool topk_ordered_row(const TopkParams& p, const int row, unsigned char* csm) {
     uint32_t* h = reinterpret_cast<uint32_t*>(csm);                                   // [kBins]
     uint64_t* cand = reinterpret_cast<uint64_t*>(csm + sizeof(uint32_t) * kBins);     // [kClusterCand]
     __shared__ uint32_t ws[32];
-    __shared__ uint32_t s_ncand, s_digit, s_need, s_done, s_total;
+    __shared__ uint32_t s_ncand, s_digit, s_need, s_done;
     __shared__ unsigned long long s_T;
     const int t = threadIdx.x;
     const int64_t n = p.n;
     const uint32_t k = (uint32_t)p.k;
-    auto key_at = [&](int64_t j) -> uint64_t {
-        return make_key(p.scores[elem_off(p, p.row_stride, row, j)], (uint32_t)j, n, p.force_last);
+    const int per = (int)((n + kTopkThreads - 1) / kTopkThreads);       // places per thread
+    const int64_t j0 = (int64_t)t * per;
+    const int cnt = (int)max((int64_t)0, min(n, j0 + per) - j0);
+    const bool in_regs = per <= kOrderedRegs;
+    const bool own = p.own_hi > p.own_lo;
+    // offsets of the run's places: within a segment consecutive, one division for the whole run
+    uint32_t seg = 0, off = (uint32_t)j0;
+    if (p.seg_len) {
+        seg = (uint32_t)(j0 / p.seg_len);
+        off = (uint32_t)(j0 - (int64_t)seg * p.seg_len);
+    }
+    auto place_off = [&](int i, int64_t stride) -> size_t {             // element offset of place j0 + i
+        if (!p.seg_len) return (size_t)row * stride + (size_t)(j0 + i);
+        uint32_t sg = seg, o = off + (uint32_t)i;
+        while (o >= (uint32_t)p.seg_len) {
+            o -= (uint32_t)p.seg_len;
+            ++sg;
+        }
+        return (size_t)sg * p.seg_stride + (size_t)row * stride + o;
     };
+    auto key_of = [&](int i) -> uint64_t {
+        return make_key(p.scores[place_off(i, p.row_stride)], (uint32_t)(j0 + i), n, p.force_last);
+    };
+    auto value_of = [&](int i) -> int32_t {
+        return p.in_idx ? p.in_idx[place_off(i, p.in_idx_stride)] : (int32_t)(j0 + i) + p.idx_offset;
+    };
+    uint64_t rk[kOrderedRegs];
+    int32_t rv[kOrderedRegs];
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < kOrderedRegs; ++i) {
+            rk[i] = i < cnt ? key_of(i) : 0ull;
+            rv[i] = i < cnt ? value_of(i) : 0;
+        }
+    }
     for (int i = t; i < kBins; i += kTopkThreads) h[i] = 0;
     if (t == 0) s_ncand = 0;
     __syncthreads();
-#pragma unroll 4
-    for (int64_t j = t; j < n; j += kTopkThreads) atomicAdd(&h[key_bin(key_at(j))], 1u);
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < kOrderedRegs; ++i)
+            if (i < cnt) atomicAdd(&h[key_bin(rk[i])], 1u);
+    } else {
+        for (int i = 0; i < cnt; ++i) atomicAdd(&h[key_bin(key_of(i))], 1u);
+    }
     __syncthreads();
     int bstar;
     uint32_t above;
     find_threshold_bin(h, ws, k, &bstar, &above);
     uint32_t need = k - above;                          // winners among the threshold bin's keys (>= 1)
-#pragma unroll 4
-    for (int64_t j = t; j < n; j += kTopkThreads) {
-        const uint64_t key = key_at(j);
+    auto collect = [&](uint64_t key) {
         if (key_bin(key) == bstar) {
             const uint32_t at = atomicAdd(&s_ncand, 1u);
             if (at < (uint32_t)kClusterCand) cand[at] = key;
         }
+    };
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < kOrderedRegs; ++i)
+            if (i < cnt) collect(rk[i]);
+    } else {
+        for (int i = 0; i < cnt; ++i) collect(key_of(i));
     }
     __syncthreads();
     const uint32_t nc = s_ncand;
@@ -511,37 +556,42 @@ __device__ __forceinline__ bool topk_ordered_row(const TopkParams& p, const int 
     }
     __syncthreads();
     const uint64_t T = s_T;
-    // ---- the row once more, in order: thread t takes a run of consecutive places
-    const int64_t per = (n + kTopkThreads - 1) / kTopkThreads;
-    const int64_t j0 = (int64_t)t * per, j1 = min(n, j0 + per);
-    const bool own = p.own_hi > p.own_lo;
-    auto value_of = [&](int64_t j) -> int32_t {
-        return p.in_idx ? p.in_idx[elem_off(p, p.in_idx_stride, row, j)] : (int32_t)j + p.idx_offset;
-    };
+    // ---- the row once more, in order
+    auto kept = [&](uint64_t key, int32_t v) -> bool { return key >= T && (!own || (v >= p.own_lo && v < p.own_hi)); };
     uint32_t mine = 0;
-    for (int64_t j = j0; j < j1; ++j)
-        if (key_at(j) >= T) {
-            const int32_t v = value_of(j);
-            mine += (!own || (v >= p.own_lo && v < p.own_hi)) ? 1u : 0u;
-        }
+    if (in_regs) {
+#pragma unroll
+        for (int i = 0; i < kOrderedRegs; ++i) mine += (i < cnt && kept(rk[i], rv[i])) ? 1u : 0u;
+    } else {
+        for (int i = 0; i < cnt; ++i)
+            if (key_of(i) >= T) mine += kept(T, value_of(i)) ? 1u : 0u;
+    }
     const uint32_t incl = block_scan_incl(mine, ws);
     uint32_t at = incl - mine;
     int32_t* out_idx = p.out_idx + (size_t)row * p.out_stride;
     float* out_val = p.out_val ? p.out_val + (size_t)row * p.out_stride : nullptr;
-    if (mine)
-        for (int64_t j = j0; j < j1; ++j)
-            if (key_at(j) >= T) {
-                const int32_t v = value_of(j);
-                if (!own || (v >= p.own_lo && v < p.own_hi)) {
-                    out_idx[at] = own ? v - p.own_lo : v;
-                    if (out_val) out_val[at] = p.scores[elem_off(p, p.row_stride, row, j)];
+    if (mine) {
+        if (in_regs) {
+#pragma unroll
+            for (int i = 0; i < kOrderedRegs; ++i)
+                if (i < cnt && kept(rk[i], rv[i])) {
+                    out_idx[at] = own ? rv[i] - p.own_lo : rv[i];
+                    if (out_val) out_val[at] = p.scores[place_off(i, p.row_stride)];
                     ++at;
                 }
-            }
-    if (t == kTopkThreads - 1) {
-        s_total = incl;
-        if (p.out_count) p.out_count[row] = (int32_t)incl;
+        } else {
+            for (int i = 0; i < cnt; ++i)
+                if (key_of(i) >= T) {
+                    const int32_t v = value_of(i);
+                    if (kept(T, v)) {
+                        out_idx[at] = own ? v - p.own_lo : v;
+                        if (out_val) out_val[at] = p.scores[place_off(i, p.row_stride)];
+                        ++at;
+                    }
+                }
+        }
     }
+    if (t == kTopkThreads - 1 && p.out_count) p.out_count[row] = (int32_t)incl;
     __syncthreads();
     return true;
 }

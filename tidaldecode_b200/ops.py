@@ -464,7 +464,7 @@ def qkv_rope_append(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, 
 
 class PeerExchange:
     """Buffers and peer mappings of tidal_peer_all_gather for one process group: staging and arrival
-    counters live in symmetric memory (torch.distributed._symmetric_memory: CUDA memory mapped on every
+    flag words live in symmetric memory (torch.distributed._symmetric_memory: CUDA memory mapped on every
     rank of the group), the pointer tables on the device.  One object per (group, slot size); every rank
     must construct it at the same point of the program (the constructor is a collective)."""
 
@@ -476,14 +476,18 @@ class PeerExchange:
         self.group = group
         stage_bytes, count_off = self._geometry(slot_bytes, self.world)
         with torch.cuda.device(device):
-            self.buf = symm_mem.empty(count_off + 256, dtype=torch.uint8, device=device)
+            self.buf = symm_mem.empty(count_off + self._flag_bytes(self.world), dtype=torch.uint8, device=device)
             self.buf.zero_()
             hdl = symm_mem.rendezvous(self.buf, group)
             self._hdl = hdl
             self._tables([int(p) for p in hdl.buffer_ptrs], count_off, device)
             torch.cuda.synchronize()
         self.wait_limit = int(wait_limit)
-        dist.barrier(group)                      # every rank's counters are zero before anyone adds to them
+        dist.barrier(group)                      # every rank's flag words are zero before anyone writes to them
+
+    @staticmethod
+    def _flag_bytes(world: int) -> int:
+        return 2 * world * _lib.XCHG_MAX_CTAS * 4          # one flag word per (parity, source rank, CTA)
 
     def _geometry(self, slot_bytes: int, world: int):
         if slot_bytes % 16:
@@ -502,22 +506,23 @@ class PeerExchange:
     @classmethod
     def loopback(cls, slot_bytes: int, world: int, device, wait_limit: int = 0) -> "PeerExchange":
         """Rank 0 of a `world`-rank exchange whose every table entry is this GPU's own buffer: no other
-        rank exists, so an exchange completes only if the missing ranks' arrivals were written by the
-        host beforehand (`counters`, `stage`), and otherwise runs into its wait limit.  For tests of the
+        rank exists, so an exchange completes only if the missing ranks' blocks and flags were written by the
+        host beforehand (`stage`, `flags`), and otherwise runs into its wait limit.  For tests of the
         timeout and reset behaviour on one GPU; nothing in it waits on another kernel."""
         self = cls.__new__(cls)
         self.world, self.rank, self.group, self._hdl = int(world), 0, None, None
         stage_bytes, count_off = self._geometry(slot_bytes, self.world)
         with torch.cuda.device(device):
-            self.buf = torch.zeros(count_off + 256, dtype=torch.uint8, device=device)
+            self.buf = torch.zeros(count_off + self._flag_bytes(self.world), dtype=torch.uint8, device=device)
             self._tables([self.buf.data_ptr()] * self.world, count_off, device)
         self.wait_limit = int(wait_limit)
         self.stage = self.buf[:stage_bytes].view(2, self.world, self.slot_bytes)       # [parity][rank][slot]
-        self.counters = self.buf[count_off:count_off + 8 * self.world].view(torch.int32).view(2, self.world)
+        self.flags = self.buf[count_off:count_off + self._flag_bytes(self.world)].view(torch.int32).view(
+            2, self.world, _lib.XCHG_MAX_CTAS)                                          # [parity][source rank][CTA]
         return self
 
     def reset(self) -> None:
-        """Arrival counters and exchange count back to zero after a timed-out exchange.  A collective in
+        """Flag words and exchange count back to zero after a timed-out exchange.  A collective in
         effect: every rank calls it, with none of the group's exchanges in flight."""
         import torch.distributed as dist
 
