@@ -58,10 +58,10 @@ __device__ __forceinline__ void split_range(const TopkParams& p, int row, int64_
         const uint64_t key = make_key(s[j], (uint32_t)j, p.n, p.force_last);
         const int bin = key_bin(key);
         if (bin > bstar) {
-            const uint32_t at = atomicAdd(sel_cnt, 1u);
+            const uint32_t at = append_slot(sel_cnt);
             if (at < (uint32_t)kMaxK) sel[at] = key;
         } else if (bin == bstar) {
-            const uint32_t at = atomicAdd(cand_cnt, 1u);
+            const uint32_t at = append_slot(cand_cnt);
             if ((int64_t)at < p.cand_cap) cand[at] = key;
         }
     }
@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kTopkThreads) topk_finish_kernel(const TopkPar
         if (t < 256) h[t] = 0;
         __syncthreads();
         for_each_candidate(p, row, bstar, ncand_total, overflow, [&](uint64_t key) {
-            if ((key & known_mask) == prefix) atomicAdd(&h[(uint32_t)(key >> sh) & dmask], 1u);
+            if ((key & known_mask) == prefix) count_digit(h, (uint32_t)(key >> sh) & dmask);
         });
         __syncthreads();
         if (t < 32) warp_find_digit(h, nb, need, &s_digit, &s_need, &s_done);
