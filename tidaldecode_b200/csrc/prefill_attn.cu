@@ -28,6 +28,11 @@ namespace tidal {
 
 constexpr int kPfRows = 128;     // query rows per CTA = MMA M = TMEM lanes
 constexpr int kPfTile = 64;      // KV tokens per tile
+#ifndef TIDAL_PF_PRODUCER_WARPS
+#define TIDAL_PF_PRODUCER_WARPS 4
+#endif
+constexpr int kPfProducerWarps = TIDAL_PF_PRODUCER_WARPS;   // warps that fetch K and V tiles
+constexpr int kPfExtraThreads = 32 * kPfProducerWarps + 32;  // producers and the MMA warp, beside 128 softmax threads per row block
 
 struct PrefillParams {
     const void* q;        // [n_q][Hq][D]
@@ -128,47 +133,84 @@ __device__ __forceinline__ uint32_t sw128_offset(int rows, int r, int c16) {
     return (uint32_t)((c16 >> 3) * rows * 128 + r * 128 + (((c16 & 7) ^ (r & 7)) << 4));
 }
 
-// Wait for an MMA commit: the tensor core answers within microseconds, so poll without sleeping
-// (try_wait itself suspends the thread for a while); past ~64 K polls something is wrong and the
-// wait backs off, then gives up like mbar_wait_bounded.
+// Waits of this kernel: mbarrier.try_wait with a suspend-time hint, so that a waiting warp sleeps in hardware
+// until the phase completes (or the hint runs out) instead of polling — a polling warp takes issue slots
+// from the warps it is waiting for.  Bounded: 2^15 tries of 16 us; on expiry the wait raises *abort_flag
+// (every other wait of the CTA then returns at once) and ORs TIDAL_DEV_WAIT_TIMEOUT into *status.
+__device__ __forceinline__ bool mbar_try_wait_suspended(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mma_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
-    for (uint32_t i = 0; i < (1u << 16); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_bounded(bar, parity, abort_flag, status);
+    for (uint32_t i = 0; i < (1u << 15); ++i) {
+        if (mbar_try_wait_suspended(bar, parity, 16384u)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) atomicOr(status, TIDAL_DEV_WAIT_TIMEOUT);
+    return false;
 }
 
+// A wait whose outcome the whole warp agrees on: a lane that gave up must not leave the others in the loop.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
+    return __all_sync(0xffffffffu, mma_wait(bar, parity, abort_flag, status));
+}
+
+// Roles (warp-specialised; nothing in the loop is a block-wide barrier):
+//   warps [0, 4 SUB)          softmax: thread t owns query row t of the CTA (lane of tensor memory = row)
+//   the next kPfProducerWarps producers: page lookups and cp.async of the K and V tiles into three-deep rings
+//   the last warp             issues every tcgen05.mma (one lane) and commits them to the barriers below
+// Barriers (mbarrier; "tile t" completes phase t / ring of a slot's barrier, waited for by parity):
+//   kfull[3], vfull[3]        producers -> MMA warp: tile landed and made visible to the async proxy (one arrival per producer warp)
+//   kempty[3], vempty[3]      tcgen05.commit after QK_t / PV_t -> producers: the slot may be overwritten
+//   sfull[SUB][2]             commit after QK_t of a row block -> its softmax warps: S buffer t & 1 is complete
+//                             (and, the pipe being in order, so is PV_(t-2): P buffer t & 1 may be overwritten)
+//   pfull[SUB][2]             softmax warps -> MMA warp: P_t is in shared memory, S buffer t & 1 has been read,
+//                             O has been rescaled if it had to be (4 arrivals)
+//   pvdone[SUB][2]            commit after PV_t: O holds tiles 0..t (awaited before a rescale and before the epilogue)
+//   alldone                   commit at the very end: no MMA is in flight when tensor memory is freed
 template <typename T, int D, int SUB>
-__global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
-    // SUB row blocks of 128 queries share every K/V tile (SUB = 2: half the L2 traffic per flop); one CTA per SM.
-    constexpr int kThreads = 128 * SUB, kRows = kPfRows * SUB;
+__global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
+    constexpr int kSoftmaxThreads = 128 * SUB, kProducerThreads = 32 * kPfProducerWarps, kRows = kPfRows * SUB;
     constexpr int kChunks = D / 8;                    // 16-byte chunks per row
     constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2, kPBytes = kPfRows * kPfTile * 2;
     constexpr uint32_t kSubCols = 2 * kPfTile + D;    // tensor-memory columns of one row block: S (two buffers), then O
     constexpr uint32_t kTmemCols = SUB * kSubCols <= 256 ? 256 : 512;
+    constexpr int kKFull = 0, kVFull = 3, kKEmpty = 6, kVEmpty = 9, kSFull = 12, kPFull = kSFull + 2 * SUB,
+                  kPvDone = kPFull + 2 * SUB, kAllDone = kPvDone + 2 * SUB, kNumBars = kAllDone + 1;
+    static_assert(kNumBars * 8 + 8 <= 256, "barrier block");
     // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
-    // operand tiles need (224 KB + 64 bytes with two row blocks at D = 128).
+    // operand tiles need (224 KB + 256 bytes with two row blocks at D = 128).
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + SUB * kQBytes;    // three buffers
     uint8_t* sV = sK + 3 * kKBytes;      // three buffers
-    uint8_t* sP = sV + 3 * kKBytes;      // two buffers per row block
-    uint64_t* bar = reinterpret_cast<uint64_t*>(sP + 2 * SUB * kPBytes);   // two barriers, used alternately
-    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bar + 2);
+    uint8_t* sP = sV + 3 * kKBytes;      // two buffers per row block: [buffer][row block]
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sP + 2 * SUB * kPBytes);
+    uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bar + kNumBars);
     int& abort_flag = *reinterpret_cast<int*>(&tmem_slot + 1);
 
-    const int tid = threadIdx.x, warp = tid >> 5, sub = warp >> 2, row = tid & 127;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_qt = (p.n_q + kRows - 1) / kRows;
     const int qt = n_qt - 1 - (int)blockIdx.x;        // longest rows first
     const int h = blockIdx.y, kvh = h / (p.Hq / p.Hkv);
     const int q0 = qt * kRows;
     const int64_t pos0 = p.kv_len - p.n_q + q0;       // position of row 0 of this CTA
     const int rows_here = min(kRows, p.n_q - q0);
-    int64_t kv_end = p.causal ? min(p.kv_len, pos0 + rows_here) : p.kv_len;   // tokens any row of the CTA sees
+    const int64_t kv_end = p.causal ? min(p.kv_len, pos0 + rows_here) : p.kv_len;   // tokens any row of the CTA sees
     const int n_tiles = (int)((kv_end + kPfTile - 1) / kPfTile);
 
     if (tid == 0) {
-        mbar_init(&bar[0], 1);
-        mbar_init(&bar[1], 1);
+#pragma unroll
+        for (int i = 0; i < kNumBars; ++i)
+            mbar_init(&bar[i], i < kKEmpty ? (uint32_t)kPfProducerWarps : (i >= kPFull && i < kPvDone) ? 4u : 1u);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -180,225 +222,259 @@ __global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)sub * kSubCols;   // this thread's lane, its row block's columns
     pdl_wait();
     pdl_launch_dependents();
-
-    const T* q = reinterpret_cast<const T*>(p.q);
-    const T* kv = reinterpret_cast<const T*>(p.kv);
-    const int64_t row_elems = (int64_t)p.Hkv * D;
-
-    // K or V rows of one tile of this KV head into a swizzled tile; rows past the sequence are zero.
-    // kChunks consecutive threads share a row.  The rows' places in the pool (page lookup) are read a
-    // whole iteration before the copies that use them are issued, so no copy waits for its address.
-    constexpr int kRowsPerThread = kPfTile / (kThreads / kChunks);
-    const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
-    const int my_c = tid % kChunks, my_r0 = tid / kChunks;
-    const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
-    const int64_t v_off = (int64_t)ps * row_elems;
     bool bad_page = false;
-    auto lookup_rows = [&](uint32_t t0, int64_t* off) {      // element offset of each of this thread's K rows, -1 past the end
+
+    if (tid < kSoftmaxThreads) {
+        // ================================================================== softmax: one thread per query row
+        const int sub = warp >> 2, row = tid & 127;
+        const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)sub * kSubCols;   // this thread's lane, its row block's columns
+        uint64_t* sfull = bar + kSFull + 2 * sub;
+        uint64_t* pfull = bar + kPFull + 2 * sub;
+        uint64_t* pvdone = bar + kPvDone + 2 * sub;
+        // The output row stays in tensor memory, scaled by 2^(-m_ref * scale); m_ref follows the running
+        // maximum only when that has grown by more than 2^8, so that most tiles need no rescaling pass.
+        float m_ref = -INFINITY, l_run = 0.f;
+        const int64_t my_pos = pos0 + tid;
+        const int64_t lim = p.causal ? min(p.kv_len - 1, my_pos) : p.kv_len - 1;   // last visible token
+        bool alive = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            if (!warp_wait(&sfull[j & 1], (uint32_t)((j >> 1) & 1), &abort_flag, p.status)) { alive = false; break; }
+            tc_fence_after();
+            float s[kPfTile];
+            tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile, s);
+            tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile + 32, s + 32);
+            tc_wait_ld();
+            const int64_t t0 = (int64_t)j * kPfTile;
+            if (t0 + kPfTile - 1 > lim) {
 #pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) {
-            const uint32_t t = t0 + my_r0 + i * (kThreads / kChunks);
-            off[i] = -1;
-            if (t < kv_len32) {
-                const uint32_t pi = ps == 1 ? t : t / ps;
-                const uint32_t slot = ps == 1 ? 0u : t - pi * ps;
-                const int64_t page = p.pages[pi];
-                if (page >= 0 && page < p.num_pages) off[i] = ((page * 2) * ps + slot) * row_elems;
-                else bad_page = true;                    // reads as a row past the end; reported once at the exit
+                for (int c = 0; c < kPfTile; ++c) s[c] = (t0 + c <= lim) ? s[c] : -INFINITY;
+            }
+            float mx4[4] = {m_ref, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < kPfTile; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const bool grow = (mx - m_ref) * p.scale_log2 > 8.f;      // also true while m_ref = -inf
+            float alpha = 1.f;
+            if (grow) {
+                alpha = fast_exp2((m_ref - mx) * p.scale_log2);       // 0 for m_ref = -inf
+                l_run *= alpha;
+                m_ref = mx;
+            }
+            const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                const uint32_t prow = smem_u32(sP) + ((j & 1) * SUB + sub) * kPBytes + row * 128;
+#pragma unroll
+                for (int c8 = 0; c8 < kPfTile / 8; ++c8) {
+                    float e[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        e[u] = fast_exp2(fmaf(s[c8 * 8 + u], p.scale_log2, -mb));
+                        sum4[u & 3] += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
+                    }
+                    const uint4 v = Vec16<T>::from_float(e);
+                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (row & 7)) << 4)), "r"(v.x),
+                                 "r"(v.y), "r"(v.z), "r"(v.w)
+                                 : "memory");
+                }
+            }
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            // O row *= alpha in the warps where some row's reference moved (tile 0: PV overwrites O anyway)
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                // PV_(j-1) may still be adding into O
+                if (!warp_wait(&pvdone[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), &abort_flag, p.status)) { alive = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int d0 = 0; d0 < D; d0 += 32) {
+                    float t[32];
+                    tc_ld32(t_lane + 2 * kPfTile + d0, t);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int u = 0; u < 32; ++u) t[u] *= alpha;
+                    tc_st32(t_lane + 2 * kPfTile + d0, t);
+                }
+                tc_wait_st();
+            }
+            fence_async_smem();       // P of this thread is visible to the tensor core's reads
+            tc_fence_before();        // its tensor-memory loads and stores are ordered before the arrival
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pfull[j & 1]);
+        }
+        if (alive) alive = warp_wait(&pvdone[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), &abort_flag, p.status);
+        tc_fence_after();
+        if (alive) {
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.o) + ((int64_t)(q0 + tid) * p.Hq + h) * D);
+#pragma unroll
+            for (int d0 = 0; d0 < D; d0 += 32) {
+                float t[32];
+                __syncwarp();
+                tc_ld32(t_lane + 2 * kPfTile + d0, t);
+                tc_wait_ld();
+                if (tid < rows_here) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float e[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) e[u] = t[c * 8 + u] * inv;
+                        dst[d0 / 8 + c] = Vec16<T>::from_float(e);
+                    }
+                }
             }
         }
-    };
-    auto stage_kv = [&](uint8_t* dst, const int64_t* off, int which) {
-        const uint32_t base = smem_u32(dst);
+    } else if (tid < kSoftmaxThreads + kProducerThreads) {
+        // ================================================================== producers
+        // kChunks consecutive threads share a row.  The rows' places in the pool (page lookup) are read a whole
+        // step before the copies that use them are issued, so no copy waits for its address.  Step u fetches
+        // K of tile u and V of tile u - 2 (PV runs two tiles behind QK) as one cp.async group and announces
+        // the group of the step before.
+        const int pt = tid - kSoftmaxThreads;
+        constexpr int kRowStep = kProducerThreads / kChunks, kRowsPerThread = kPfTile / kRowStep;
+        const T* q = reinterpret_cast<const T*>(p.q);
+        const T* kv = reinterpret_cast<const T*>(p.kv);
+        const int64_t row_elems = (int64_t)p.Hkv * D;
+        const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
+        const int my_c = pt % kChunks, my_r0 = pt / kChunks;
+        const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
+        const int64_t v_off = (int64_t)ps * row_elems;
+        auto lookup_rows = [&](uint32_t t0, int64_t* off) {      // element offset of each of this thread's K rows, -1 past the end
 #pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) {
-            const int r = my_r0 + i * (kThreads / kChunks);
-            const bool ok = off[i] >= 0;
-            const T* src = ok ? kv_head + off[i] + (which ? v_off : 0) : kv;
-            cp_async16(base + sw128_offset(kPfTile, r, my_c), src, ok ? 16u : 0u);
-        }
-    };
-    int64_t off_a[kRowsPerThread], off_b[kRowsPerThread];   // rows of tile j+2 and of tile j+1 at the top of iteration j
-
-    // Q tile, K of tiles 0 and 1, V of tile 0
-    {
-        const uint32_t base = smem_u32(sQ);
+            for (int i = 0; i < kRowsPerThread; ++i) {
+                const uint32_t t = t0 + my_r0 + i * kRowStep;
+                off[i] = -1;
+                if (t < kv_len32) {
+                    const uint32_t pi = ps == 1 ? t : t / ps;
+                    const uint32_t slot = ps == 1 ? 0u : t - pi * ps;
+                    const int64_t page = p.pages[pi];
+                    if (page >= 0 && page < p.num_pages) off[i] = ((page * 2) * ps + slot) * row_elems;
+                    else bad_page = true;                    // reads as a row past the end; reported once at the exit
+                }
+            }
+        };
+        auto stage_kv = [&](uint8_t* dst, const int64_t* off, int which) {   // rows past the sequence are zero
+            const uint32_t base = smem_u32(dst);
+#pragma unroll
+            for (int i = 0; i < kRowsPerThread; ++i) {
+                const int r = my_r0 + i * kRowStep;
+                const bool ok = off[i] >= 0;
+                const T* src = ok ? kv_head + off[i] + (which ? v_off : 0) : kv;
+                cp_async16(base + sw128_offset(kPfTile, r, my_c), src, ok ? 16u : 0u);
+            }
+        };
+        auto announce = [&](int g) {      // group g = K of tile g, V of tile g - 2 (and Q with group 0)
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                if (g < n_tiles) mbar_arrive(&bar[kKFull + g % 3]);
+                if (g >= 2 && g - 2 < n_tiles) mbar_arrive(&bar[kVFull + (g - 2) % 3]);
+            }
+        };
+        {
+            const uint32_t base = smem_u32(sQ);
 #pragma unroll 4
-        for (int r = my_r0; r < kRows; r += kThreads / kChunks) {
-            const bool ok = r < rows_here;
-            const T* src = ok ? q + ((int64_t)(q0 + r) * p.Hq + h) * D + my_c * 8 : q;
-            cp_async16(base + (r >> 7) * kQBytes + sw128_offset(kPfRows, r & 127, my_c), src, ok ? 16u : 0u);
+            for (int r = my_r0; r < kRows; r += kRowStep) {
+                const bool ok = r < rows_here;
+                const T* src = ok ? q + ((int64_t)(q0 + r) * p.Hq + h) * D + my_c * 8 : q;
+                cp_async16(base + (r >> 7) * kQBytes + sw128_offset(kPfRows, r & 127, my_c), src, ok ? 16u : 0u);
+            }
         }
-        lookup_rows(0, off_a);
-        lookup_rows(kPfTile, off_b);
-        stage_kv(sK, off_a, 0);
-        stage_kv(sV, off_a, 1);
-        if (n_tiles > 1) stage_kv(sK + kKBytes, off_b, 0);
-        lookup_rows(2 * kPfTile, off_a);
-        if (n_tiles > 2) stage_kv(sK + 2 * kKBytes, off_a, 0);
-        cp_async_commit();
-        lookup_rows(3 * kPfTile, off_a);      // K of tile 3 and V of tile 1 are fetched in iteration 0
-    }
-
-    constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
-    constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
-    constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
-    const uint32_t t_s = tmem, t_o = tmem + 2 * kPfTile;      // per row block: S buffers in columns [0,64) and [64,128), O after them
-
-    // operand descriptors of the tile origins; a step along K adds a constant to the address field
-    const uint64_t dq = smem_desc_sw128(smem_u32(sQ), 16, 1024), dk = smem_desc_sw128(smem_u32(sK), 16, 1024);
-    const uint64_t dp = smem_desc_sw128(smem_u32(sP), 16, 1024), dv = smem_desc_sw128(smem_u32(sV), v_lbo, v_sbo);
-    auto issue_qk = [&](int j, int kbuf) {     // one thread: S_j = Q K_j^T into S buffer j & 1
-        const uint64_t dkj = dk + (uint64_t)(((uint32_t)kbuf * kKBytes) >> 4);
+        int64_t off_k[kRowsPerThread], off_v1[kRowsPerThread], off_v2[kRowsPerThread];   // rows of tiles u, u - 1, u - 2
 #pragma unroll
-        for (int sb = 0; sb < SUB; ++sb)
+        for (int i = 0; i < kRowsPerThread; ++i) off_v1[i] = off_v2[i] = -1;
+        lookup_rows(0, off_k);
+        bool alive = true;
+        for (int u = 0; u < n_tiles + 2; ++u) {
+            if (u < n_tiles) {
+                if (u >= 3 && !warp_wait(&bar[kKEmpty + u % 3], (uint32_t)((u / 3 - 1) & 1), &abort_flag, p.status)) { alive = false; break; }
+                stage_kv(sK + (uint32_t)(u % 3) * kKBytes, off_k, 0);
+            }
+            if (u >= 2) {
+                const int v = u - 2;
+                if (v >= 3 && !warp_wait(&bar[kVEmpty + v % 3], (uint32_t)((v / 3 - 1) & 1), &abort_flag, p.status)) { alive = false; break; }
+                stage_kv(sV + (uint32_t)(v % 3) * kKBytes, off_v2, 1);
+            }
+            cp_async_commit();
+            if (u >= 1) {
+                cp_async_wait<1>();
+                announce(u - 1);
+            }
+#pragma unroll
+            for (int i = 0; i < kRowsPerThread; ++i) {
+                off_v2[i] = off_v1[i];
+                off_v1[i] = off_k[i];
+            }
+            lookup_rows((uint32_t)(u + 1) * kPfTile, off_k);
+        }
+        cp_async_wait<0>();
+        if (alive) announce(n_tiles + 1);
+    } else {
+        // ================================================================== MMA issue (one lane of the last warp)
+        constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
+        constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
+        constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
+        const uint32_t t_s = tmem, t_o = tmem + 2 * kPfTile;      // per row block: S buffers in columns [0,64) and [64,128), O after them
+        // operand descriptors of the tile origins; a step along K adds a constant to the address field
+        const uint64_t dq = smem_desc_sw128(smem_u32(sQ), 16, 1024), dk = smem_desc_sw128(smem_u32(sK), 16, 1024);
+        const uint64_t dp = smem_desc_sw128(smem_u32(sP), 16, 1024), dv = smem_desc_sw128(smem_u32(sV), v_lbo, v_sbo);
+        auto issue_qk = [&](int sb, int j, int kbuf) {     // S_j = Q K_j^T of row block sb into its S buffer j & 1
+            const uint64_t dkj = dk + (uint64_t)(((uint32_t)kbuf * kKBytes) >> 4);
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
                 const uint32_t a = sb * kQBytes + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
                 const uint32_t b = (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
                 tc_mma_f16(t_s + sb * kSubCols + (uint32_t)(j & 1) * kPfTile, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
             }
-    };
-
-    cp_async_wait<0>();
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-        tc_fence_after();
-        issue_qk(0, 0);
-        tc_commit(&bar[0]);
-        if (n_tiles > 1) issue_qk(1, 1);
-        tc_commit(&bar[1]);
-    }
-
-    // Software pipeline: at the barrier that ends iteration j one thread issues PV_j and QK_(j+2) and commits
-    // them to bar[j & 1]; iteration j itself only needs QK_j and PV_(j-2), issued two barriers earlier, so the
-    // tensor core has a whole iteration to run while the threads are in the softmax of the tile in between.
-    // (Two barriers because a wait may find its batch and the next one both complete: one barrier's parity
-    // could not tell that from "not yet".)  Batch b is phase (b >> 1) + 1 of bar[b & 1]; phase 0 is the prologue's.
-    // The output row stays in tensor memory, scaled by 2^(-m_ref * scale); m_ref follows the running
-    // maximum only when that has grown by more than 2^8, so that most tiles need no rescaling pass.
-    float m_ref = -INFINITY, l_run = 0.f;
-    const int64_t my_pos = pos0 + tid;
-    bool alive = true;
-
-    int k3 = 0;     // j % 3
-    for (int j = 0; j < n_tiles; ++j, k3 = (k3 == 2 ? 0 : k3 + 1)) {
-        // ---- S_j and PV_(j-2) are complete: K_j's buffer takes K of tile j+3, V_(j-2)'s buffer V of tile j+1
-        alive = mma_wait(&bar[j & 1], (uint32_t)((j >> 1) & 1), &abort_flag, p.status) && alive;
-        tc_fence_after();
-        if (j + 3 < n_tiles) stage_kv(sK + (uint32_t)k3 * kKBytes, off_a, 0);
-        if (j + 1 < n_tiles) stage_kv(sV + (uint32_t)(k3 == 2 ? 0 : k3 + 1) * kKBytes, off_b, 1);
-        cp_async_commit();
-        lookup_rows((uint32_t)(j + 4) * kPfTile, off_a);       // both used at the top of the next iteration
-        lookup_rows((uint32_t)(j + 2) * kPfTile, off_b);
-
-        // ---- softmax of this thread's row
-        float s[kPfTile];
-        __syncwarp();
-        tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile, s);
-        tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile + 32, s + 32);
-        tc_wait_ld();
-        const int64_t t0 = (int64_t)j * kPfTile;
-        const int64_t lim = p.causal ? min(p.kv_len - 1, my_pos) : p.kv_len - 1;   // last visible token
-        if (t0 + kPfTile - 1 > lim) {
+        };
+        bool alive = true;
+        // S of tiles 0 and 1
+        for (int t = 0; t < 2 && t < n_tiles && alive; ++t) {
+            alive = warp_wait(&bar[kKFull + t], 0u, &abort_flag, p.status);
+            if (alive && lane == 0) {
+                tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < kPfTile; ++c) s[c] = (t0 + c <= lim) ? s[c] : -INFINITY;
-        }
-        float mx4[4] = {m_ref, -INFINITY, -INFINITY, -INFINITY};   // four chains: nothing else hides the latency
-#pragma unroll
-        for (int c = 0; c < kPfTile; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const bool grow = (mx - m_ref) * p.scale_log2 > 8.f;      // also true while m_ref = -inf
-        float alpha = 1.f;
-        if (grow) {
-            alpha = fast_exp2((m_ref - mx) * p.scale_log2);       // 0 for m_ref = -inf
-            l_run *= alpha;
-            m_ref = mx;
-        }
-        const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        {
-            const uint32_t prow = smem_u32(sP) + ((j & 1) * SUB + sub) * kPBytes + row * 128;
-#pragma unroll
-            for (int c8 = 0; c8 < kPfTile / 8; ++c8) {
-                float e[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    e[u] = fast_exp2(fmaf(s[c8 * 8 + u], p.scale_log2, -mb));
-                    sum4[u & 3] += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
+                for (int sb = 0; sb < SUB; ++sb) {
+                    issue_qk(sb, t, t);
+                    tc_commit(&bar[kSFull + 2 * sb + t]);
                 }
-                const uint4 v = Vec16<T>::from_float(e);
-                asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (row & 7)) << 4)), "r"(v.x),
-                             "r"(v.y), "r"(v.z), "r"(v.w)
-                             : "memory");
+                tc_commit(&bar[kKEmpty + t]);
             }
-        }
-        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        // O row *= alpha in the warps where some row's reference moved (tile 0: PV overwrites O anyway)
-        if (j > 0 && __any_sync(0xffffffffu, grow)) {
-            // PV_(j-1) may still be adding into O: its batch is the one iteration j+1 would wait for
-            alive = mma_wait(&bar[(j - 1) & 1], (uint32_t)((((j - 1) >> 1) + 1) & 1), &abort_flag, p.status) && alive;
-            tc_fence_after();
-#pragma unroll
-            for (int d0 = 0; d0 < D; d0 += 32) {
-                float t[32];
-                tc_ld32(t_lane + 2 * kPfTile + d0, t);
-                tc_wait_ld();
-#pragma unroll
-                for (int u = 0; u < 32; ++u) t[u] *= alpha;
-                tc_st32(t_lane + 2 * kPfTile + d0, t);
-            }
-            tc_wait_st();
-        }
-
-        // ---- PV_j accumulates into O; QK of tile j+2 refills the S buffer this iteration has just read
-        cp_async_wait<1>();           // everything but this iteration's fetches has landed
-        fence_async_smem();
-        tc_fence_before();
-        if (__syncthreads_or(!alive)) break;      // every thread leaves in the same iteration
-        if (tid == 0) {
-            tc_fence_after();
-            const uint64_t dvj = dv + (uint64_t)(((uint32_t)k3 * kKBytes) >> 4);
-#pragma unroll
-            for (int sb = 0; sb < SUB; ++sb)
-#pragma unroll
-                for (int k = 0; k < kPfTile / 16; ++k)
-                    tc_mma_f16(t_o + sb * kSubCols, dp + (uint64_t)((((j & 1) * SUB + sb) * kPBytes + k * 32) >> 4),
-                               dvj + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-            if (j + 2 < n_tiles) issue_qk(j + 2, k3 == 0 ? 2 : k3 - 1);      // (j + 2) % 3
-            tc_commit(&bar[j & 1]);
-        }
-    }
-    cp_async_wait<0>();
-    alive = !__syncthreads_or(!alive);
-    if (alive) alive = mma_wait(&bar[(n_tiles - 1) & 1], (uint32_t)((((n_tiles - 1) >> 1) + 1) & 1), &abort_flag, p.status);
-    tc_fence_after();
-    alive = !__syncthreads_or(!alive);
-
-    if (alive) {
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.o) + ((int64_t)(q0 + tid) * p.Hq + h) * D);
-#pragma unroll
-        for (int d0 = 0; d0 < D; d0 += 32) {
-            float t[32];
             __syncwarp();
-            tc_ld32(t_lane + 2 * kPfTile + d0, t);
-            tc_wait_ld();
-            if (tid < rows_here) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float e[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) e[u] = t[c * 8 + u] * inv;
-                    dst[d0 / 8 + c] = Vec16<T>::from_float(e);
-                }
-            }
         }
+        int k3 = 0;     // j % 3
+        for (int j = 0; j < n_tiles && alive; ++j, k3 = (k3 == 2 ? 0 : k3 + 1)) {
+            const int kn = k3 == 0 ? 2 : k3 - 1;      // (j + 2) % 3
+            alive = warp_wait(&bar[kVFull + k3], (uint32_t)((j / 3) & 1), &abort_flag, p.status);
+            if (alive && j + 2 < n_tiles) alive = warp_wait(&bar[kKFull + kn], (uint32_t)(((j + 2) / 3) & 1), &abort_flag, p.status);
+#pragma unroll
+            for (int sb = 0; sb < SUB; ++sb) {
+                if (alive) alive = warp_wait(&bar[kPFull + 2 * sb + (j & 1)], (uint32_t)((j >> 1) & 1), &abort_flag, p.status);
+                if (alive && lane == 0) {
+                    tc_fence_after();
+                    const uint64_t dvj = dv + (uint64_t)(((uint32_t)k3 * kKBytes) >> 4);
+#pragma unroll
+                    for (int k = 0; k < kPfTile / 16; ++k)
+                        tc_mma_f16(t_o + sb * kSubCols, dp + (uint64_t)((((j & 1) * SUB + sb) * kPBytes + k * 32) >> 4),
+                                   dvj + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+                    tc_commit(&bar[kPvDone + 2 * sb + (j & 1)]);
+                    if (j + 2 < n_tiles) {
+                        issue_qk(sb, j + 2, kn);
+                        tc_commit(&bar[kSFull + 2 * sb + (j & 1)]);
+                    }
+                }
+                __syncwarp();
+            }
+            if (alive && lane == 0) {
+                tc_commit(&bar[kVEmpty + k3]);
+                if (j + 2 < n_tiles) tc_commit(&bar[kKEmpty + kn]);
+            }
+            __syncwarp();
+        }
+        // nothing of this CTA may still be running on the tensor core when its tensor memory is given back
+        if (lane == 0) tc_commit(&bar[kAllDone]);
+        __syncwarp();
+        warp_wait(&bar[kAllDone], 0u, &abort_flag, p.status);
     }
     if (bad_page && p.status) atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
     tc_fence_before();
@@ -409,10 +485,10 @@ __global__ void __launch_bounds__(128 * SUB, 1) prefill_attn_kernel(const __grid
 template <typename T, int D, int SUB>
 static int launch_prefill_sub(const PrefillParams& p, cudaStream_t st) {
     // Q, K x3, V x3, P x2, barriers
-    const size_t smem = (size_t)SUB * kPfRows * D * 2 + 6 * (size_t)kPfTile * D * 2 + 2 * (size_t)SUB * kPfRows * kPfTile * 2 + 64;
+    const size_t smem = (size_t)SUB * kPfRows * D * 2 + 6 * (size_t)kPfTile * D * 2 + 2 * (size_t)SUB * kPfRows * kPfTile * 2 + 256;
     TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel<T, D, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int n_qt = (p.n_q + kPfRows * SUB - 1) / (kPfRows * SUB);
-    TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D, SUB>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(128 * SUB), smem, st, 1, p));
+    TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D, SUB>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(128 * SUB + kPfExtraThreads), smem, st, 1, p));
     count_launch();
     return TIDAL_OK;
 }
