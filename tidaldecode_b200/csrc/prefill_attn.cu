@@ -5,19 +5,24 @@
 //
 // A row block = 128 query rows of one query head = the 128 lanes of tensor memory; a CTA holds one row
 // block (short calls) or two that share every K/V tile.  It walks the KV tokens its rows may see in
-// tiles of 64.  Per row block and tile:
-//   S = Q K^T     8 (D=128) MMAs of 128x64x16, Q and K as K-major operands with the 128-byte swizzle,
-//                 S in one of two 64-column buffers of tensor memory
-//   softmax       thread t owns row t (tcgen05.ld 32x32b: lane = row), running sum in registers,
-//                 P rounded to the storage type and written to shared memory as the next A operand
-//   O += P V      4 MMAs of 128xDx16, V rows as they lie in the cache (MN-major B operand); O stays in
-//                 tensor memory and is rescaled only when a row's maximum has grown by more than 2^8
-// The loop is software-pipelined: the barrier that ends iteration j is followed by one thread issuing
-// PV of tile j and QK of tile j+2, so the MMAs run under the softmax of tile j+1.  K and V tiles live in
-// three-deep rings, fetched at least one tile ahead (cp.async, 16 bytes per request, page lookup per
-// row, itself one iteration ahead of the copies).
-// Every wait on an mbarrier has an iteration limit; a CTA that gives up sets TIDAL_DEV_WAIT_TIMEOUT,
-// still frees its tensor memory and returns.
+// tiles of 128.  Per row block and tile:
+//   S = Q K^T     8 (D=128) MMAs of 128x128x16, Q and K as K-major operands in shared memory with the
+//                 128-byte swizzle, S (fp32) in the row block's 128 S columns of tensor memory
+//   softmax       thread t owns row t (tcgen05.ld 32x32b: lane = row) and holds its 128 S values in registers
+//                 (the softmax warps take registers from the other warps: setmaxnreg); P = exp2(..) rounded
+//                 to the storage type goes back into the first 64 of the S columns (two values per column),
+//                 running sum in registers
+//   O += P V      8 MMAs of 128xDx16 with P as the A operand read from tensor memory and V rows as they
+//                 lie in the cache (MN-major B operand); O stays in tensor memory and is rescaled only
+//                 when a row's maximum has grown by more than 2^8
+// S is single-buffered per row block (512 columns = 2 x (128 S + 128 O)), so a row block's chain is
+// softmax_j -> PV_j -> QK_(j+1) -> softmax_(j+1); the two row blocks of a CTA run half a period apart and
+// keep the tensor core busy during each other's softmax.  K and V tiles travel through one ring of five
+// 32 KB slots in the order K_0 V_0 K_1 V_1 ..., fetched by dedicated warps (cp.async, 16 bytes per
+// request; the page ids of a tile's rows are looked up two tiles ahead and kept in a small table in shared
+// memory).
+// Every wait on an mbarrier is bounded; a CTA that gives up sets TIDAL_DEV_WAIT_TIMEOUT, still frees its
+// tensor memory and returns.
 #include <cmath>
 #include <cstdlib>
 #include <type_traits>
@@ -27,12 +32,14 @@
 namespace tidal {
 
 constexpr int kPfRows = 128;     // query rows per CTA = MMA M = TMEM lanes
-constexpr int kPfTile = 64;      // KV tokens per tile
-#ifndef TIDAL_PF_PRODUCER_WARPS
-#define TIDAL_PF_PRODUCER_WARPS 4
-#endif
-constexpr int kPfProducerWarps = TIDAL_PF_PRODUCER_WARPS;   // warps that fetch K and V tiles
-constexpr int kPfExtraThreads = 32 * kPfProducerWarps + 32;  // producers and the MMA warp, beside 128 softmax threads per row block
+constexpr int kPfTile = 128;     // KV tokens per tile
+constexpr int kPfRing = 5;       // K/V tiles in flight in shared memory
+constexpr int kPfProducerWarps = 4;   // warps that fetch K and V tiles (the copy rate grows with the warps that issue)
+constexpr int kPfExtraThreads = 256;  // two more warp groups beside the softmax threads: four producer warps; the MMA warp and three spares
+// Registers per thread after the role split (setmaxnreg; two row blocks only): the softmax threads hold a whole
+// S row of 128 values.  The pool is 512 threads x the 128 registers the launch bound gives = the register file;
+// the two auxiliary warp groups give back (128 - 56) x 256 = 18432, the softmax groups take (200 - 128) x 256 = 18432.
+constexpr int kPfSoftmaxRegs = 200, kPfAuxRegs = 56;
 
 struct PrefillParams {
     const void* q;        // [n_q][Hq][D]
@@ -94,6 +101,28 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
         "r"(r[31])
         : "memory");
 }
+// 16 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// A operand in tensor memory (lane = row, two 16-bit values of consecutive k per column), B through a descriptor
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(zero)
+        : "memory");
+}
+template <uint32_t N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <uint32_t N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -165,37 +194,40 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 
 // Roles (warp-specialised; nothing in the loop is a block-wide barrier):
 //   warps [0, 4 SUB)          softmax: thread t owns query row t of the CTA (lane of tensor memory = row)
-//   the next kPfProducerWarps producers: page lookups and cp.async of the K and V tiles into three-deep rings
-//   the last warp             issues every tcgen05.mma (one lane) and commits them to the barriers below
-// Barriers (mbarrier; "tile t" completes phase t / ring of a slot's barrier, waited for by parity):
-//   kfull[3], vfull[3]        producers -> MMA warp: tile landed and made visible to the async proxy (one arrival per producer warp)
-//   kempty[3], vempty[3]      tcgen05.commit after QK_t / PV_t -> producers: the slot may be overwritten
-//   sfull[SUB][2]             commit after QK_t of a row block -> its softmax warps: S buffer t & 1 is complete
-//                             (and, the pipe being in order, so is PV_(t-2): P buffer t & 1 may be overwritten)
-//   pfull[SUB][2]             softmax warps -> MMA warp: P_t is in shared memory, S buffer t & 1 has been read,
-//                             O has been rescaled if it had to be (4 arrivals)
-//   pvdone[SUB][2]            commit after PV_t: O holds tiles 0..t (awaited before a rescale and before the epilogue)
+//   the next four warps       producers: page lookups and cp.async of the K and V tiles into the ring
+//   the next warp             issues every tcgen05.mma (one lane) and commits them to the barriers below
+//   the last three warps      only complete the warp group (setmaxnreg is a warp-group operation)
+// Barriers (mbarrier; the i-th completion of a barrier is waited for with parity i & 1):
+//   full[5], empty[5]         ring slots, tile i of the sequence K_0 V_0 K_1 V_1 ... uses slot i % 5:
+//                             producers -> MMA warp (one arrival per producer warp, after the copies have landed and
+//                             been made visible to the async proxy); tcgen05.commit after the last MMA that reads
+//                             the slot -> producers
+//   sfull[SUB]                commit after QK_t of a row block -> its softmax warps: S_t is complete (and, the pipe
+//                             being in order, so is PV_(t-1): O may be rescaled)
+//   pfull[SUB]                softmax warps -> MMA warp: P_t is in tensor memory, O has been rescaled if it had to be
+//                             (4 arrivals)
+//   pvdone[SUB]               commit after PV_t: awaited before the epilogue reads O
 //   alldone                   commit at the very end: no MMA is in flight when tensor memory is freed
 template <typename T, int D, int SUB>
 __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
     constexpr int kSoftmaxThreads = 128 * SUB, kProducerThreads = 32 * kPfProducerWarps, kRows = kPfRows * SUB;
     constexpr int kChunks = D / 8;                    // 16-byte chunks per row
-    constexpr uint32_t kQBytes = kPfRows * D * 2, kKBytes = kPfTile * D * 2, kPBytes = kPfRows * kPfTile * 2;
-    constexpr uint32_t kSubCols = 2 * kPfTile + D;    // tensor-memory columns of one row block: S (two buffers), then O
+    constexpr uint32_t kQBytes = kPfRows * D * 2, kTileBytes = kPfTile * D * 2;
+    constexpr uint32_t kSubCols = kPfTile + D;        // tensor-memory columns of one row block: S (P in its first half), then O
     constexpr uint32_t kTmemCols = SUB * kSubCols <= 256 ? 256 : 512;
-    constexpr int kKFull = 0, kVFull = 3, kKEmpty = 6, kVEmpty = 9, kSFull = 12, kPFull = kSFull + 2 * SUB,
-                  kPvDone = kPFull + 2 * SUB, kAllDone = kPvDone + 2 * SUB, kNumBars = kAllDone + 1;
+    constexpr int kFull = 0, kEmpty = kPfRing, kSFull = 2 * kPfRing, kPFull = kSFull + SUB, kPvDone = kPFull + SUB,
+                  kAllDone = kPvDone + SUB, kNumBars = kAllDone + 1;
     static_assert(kNumBars * 8 + 8 <= 256, "barrier block");
+    static_assert(32 % kChunks == 0 && kPfTile % (kPfProducerWarps * 32 / kChunks) == 0 && kPfTile % (kPfProducerWarps * 32) == 0, "producer mapping");
     // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
     // operand tiles need (224 KB + 256 bytes with two row blocks at D = 128).
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
-    uint8_t* sK = sQ + SUB * kQBytes;    // three buffers
-    uint8_t* sV = sK + 3 * kKBytes;      // three buffers
-    uint8_t* sP = sV + 3 * kKBytes;      // two buffers per row block: [buffer][row block]
-    uint64_t* bar = reinterpret_cast<uint64_t*>(sP + 2 * SUB * kPBytes);
+    uint8_t* sRing = sQ + SUB * kQBytes;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sRing + kPfRing * kTileBytes);
     uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bar + kNumBars);
     int& abort_flag = *reinterpret_cast<int*>(&tmem_slot + 1);
+    int32_t* pgtab = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bar) + 256);   // [2][kPfTile] page ids, -1 = row reads as zeros
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n_qt = (p.n_q + kRows - 1) / kRows;
@@ -210,7 +242,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < kNumBars; ++i)
-            mbar_init(&bar[i], i < kKEmpty ? (uint32_t)kPfProducerWarps : (i >= kPFull && i < kPvDone) ? 4u : 1u);
+            mbar_init(&bar[i], i < kEmpty ? (uint32_t)kPfProducerWarps : (i >= kPFull && i < kPvDone) ? 4u : 1u);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -228,11 +260,13 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
 
     if (tid < kSoftmaxThreads) {
         // ================================================================== softmax: one thread per query row
-        const int sub = warp >> 2, row = tid & 127;
-        const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)sub * kSubCols;   // this thread's lane, its row block's columns
-        uint64_t* sfull = bar + kSFull + 2 * sub;
-        uint64_t* pfull = bar + kPFull + 2 * sub;
-        uint64_t* pvdone = bar + kPvDone + 2 * sub;
+        if constexpr (SUB == 2) reg_inc<kPfSoftmaxRegs>();
+        const int sub = warp >> 2;
+        const uint32_t t_s = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)sub * kSubCols;   // this thread's lane: S columns of its row block
+        const uint32_t t_o = t_s + kPfTile;
+        uint64_t* sfull = bar + kSFull + sub;
+        uint64_t* pfull = bar + kPFull + sub;
+        uint64_t* pvdone = bar + kPvDone + sub;
         // The output row stays in tensor memory, scaled by 2^(-m_ref * scale); m_ref follows the running
         // maximum only when that has grown by more than 2^8, so that most tiles need no rescaling pass.
         float m_ref = -INFINITY, l_run = 0.f;
@@ -240,14 +274,16 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         const int64_t lim = p.causal ? min(p.kv_len - 1, my_pos) : p.kv_len - 1;   // last visible token
         bool alive = true;
         for (int j = 0; j < n_tiles; ++j) {
-            if (!warp_wait(&sfull[j & 1], (uint32_t)((j >> 1) & 1), &abort_flag, p.status)) { alive = false; break; }
+            if (!warp_wait(sfull, (uint32_t)(j & 1), &abort_flag, p.status)) { alive = false; break; }
             tc_fence_after();
-            float s[kPfTile];
-            tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile, s);
-            tc_ld32(t_lane + (uint32_t)(j & 1) * kPfTile + 32, s + 32);
-            tc_wait_ld();
             const int64_t t0 = (int64_t)j * kPfTile;
-            if (t0 + kPfTile - 1 > lim) {
+            const bool edge = t0 + kPfTile - 1 > lim;         // some column of this row is masked
+            // ---- the whole S row into registers, one wait
+            float s[kPfTile];
+#pragma unroll
+            for (int c0 = 0; c0 < kPfTile; c0 += 32) tc_ld32(t_s + c0, s + c0);
+            tc_wait_ld();
+            if (edge) {
 #pragma unroll
                 for (int c = 0; c < kPfTile; ++c) s[c] = (t0 + c <= lim) ? s[c] : -INFINITY;
             }
@@ -263,46 +299,47 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
                 m_ref = mx;
             }
             const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
+            // ---- P = exp2(S * scale - m_ref * scale), two values per column, into the first half of the S columns
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-            {
-                const uint32_t prow = smem_u32(sP) + ((j & 1) * SUB + sub) * kPBytes + row * 128;
 #pragma unroll
-                for (int c8 = 0; c8 < kPfTile / 8; ++c8) {
+            for (int c0 = 0; c0 < kPfTile; c0 += 32) {
+                uint32_t w[16];
+#pragma unroll
+                for (int c8 = 0; c8 < 4; ++c8) {
                     float e[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
-                        e[u] = fast_exp2(fmaf(s[c8 * 8 + u], p.scale_log2, -mb));
+                        e[u] = fast_exp2(fmaf(s[c0 + c8 * 8 + u], p.scale_log2, -mb));
                         sum4[u & 3] += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
                     }
                     const uint4 v = Vec16<T>::from_float(e);
-                    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(prow + (((uint32_t)c8 ^ (row & 7)) << 4)), "r"(v.x),
-                                 "r"(v.y), "r"(v.z), "r"(v.w)
-                                 : "memory");
+                    w[c8 * 4] = v.x;
+                    w[c8 * 4 + 1] = v.y;
+                    w[c8 * 4 + 2] = v.z;
+                    w[c8 * 4 + 3] = v.w;
                 }
+                tc_st16(t_s + c0 / 2, w);
             }
-            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            // O row *= alpha in the warps where some row's reference moved (tile 0: PV overwrites O anyway)
+            // O row *= alpha in the warps where some row's reference moved (tile 0: PV overwrites O anyway).
+            // PV_(j-1) is complete: S_j's commit covers every MMA issued before it.
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                // PV_(j-1) may still be adding into O
-                if (!warp_wait(&pvdone[(j - 1) & 1], (uint32_t)(((j - 1) >> 1) & 1), &abort_flag, p.status)) { alive = false; break; }
-                tc_fence_after();
 #pragma unroll
                 for (int d0 = 0; d0 < D; d0 += 32) {
                     float t[32];
-                    tc_ld32(t_lane + 2 * kPfTile + d0, t);
+                    tc_ld32(t_o + d0, t);
                     tc_wait_ld();
 #pragma unroll
                     for (int u = 0; u < 32; ++u) t[u] *= alpha;
-                    tc_st32(t_lane + 2 * kPfTile + d0, t);
+                    tc_st32(t_o + d0, t);
                 }
-                tc_wait_st();
             }
-            fence_async_smem();       // P of this thread is visible to the tensor core's reads
-            tc_fence_before();        // its tensor-memory loads and stores are ordered before the arrival
+            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            tc_wait_st();
+            tc_fence_before();        // the tensor-memory loads and stores above are ordered before the arrival
             __syncwarp();
-            if (lane == 0) mbar_arrive(&pfull[j & 1]);
+            if (lane == 0) mbar_arrive(pfull);
         }
-        if (alive) alive = warp_wait(&pvdone[(n_tiles - 1) & 1], (uint32_t)(((n_tiles - 1) >> 1) & 1), &abort_flag, p.status);
+        if (alive) alive = warp_wait(pvdone, (uint32_t)((n_tiles - 1) & 1), &abort_flag, p.status);
         tc_fence_after();
         if (alive) {
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -311,7 +348,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
             for (int d0 = 0; d0 < D; d0 += 32) {
                 float t[32];
                 __syncwarp();
-                tc_ld32(t_lane + 2 * kPfTile + d0, t);
+                tc_ld32(t_o + d0, t);
                 tc_wait_ld();
                 if (tid < rows_here) {
 #pragma unroll
@@ -326,50 +363,67 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         }
     } else if (tid < kSoftmaxThreads + kProducerThreads) {
         // ================================================================== producers
-        // kChunks consecutive threads share a row.  The rows' places in the pool (page lookup) are read a whole
-        // step before the copies that use them are issued, so no copy waits for its address.  Step u fetches
-        // K of tile u and V of tile u - 2 (PV runs two tiles behind QK) as one cp.async group and announces
-        // the group of the step before.
+        // kChunks consecutive threads share a row.  Step i fetches tile i of the sequence K_0 V_0 K_1 V_1 ...
+        // as one cp.async group and announces the group of the step before.  The page ids of tile t are loaded
+        // into registers two tiles ahead (end of the step that issued V_(t-2)), moved into the table in shared
+        // memory one tile later and read from there by the copies of K_t and V_t, so nothing waits for a lookup.
+        if constexpr (SUB == 2) reg_dec<kPfAuxRegs>();
         const int pt = tid - kSoftmaxThreads;
         constexpr int kRowStep = kProducerThreads / kChunks, kRowsPerThread = kPfTile / kRowStep;
+        constexpr int kIdsPerThread = kPfTile / kProducerThreads;
         const T* q = reinterpret_cast<const T*>(p.q);
         const T* kv = reinterpret_cast<const T*>(p.kv);
         const int64_t row_elems = (int64_t)p.Hkv * D;
         const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
         const int my_c = pt % kChunks, my_r0 = pt / kChunks;
         const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
-        const int64_t v_off = (int64_t)ps * row_elems;
-        auto lookup_rows = [&](uint32_t t0, int64_t* off) {      // element offset of each of this thread's K rows, -1 past the end
+        // Each warp looks up the rows it copies itself (rows my_r0 + i * kRowStep of its lanes), so the table needs no
+        // barrier between the warps: lane l's id i is that of row id_row(i).
+        constexpr int kWarpRows = kRowStep / kPfProducerWarps;   // adjacent rows of one pass that belong to one warp
+        auto id_row = [&](int i) {
+            const int x = lane * kIdsPerThread + i;
+            return kRowStep * (x / kWarpRows) + kWarpRows * (pt >> 5) + x % kWarpRows;
+        };
+        int32_t ids[kIdsPerThread];                              // page ids of the tile after the next copy's
+        auto load_ids = [&](uint32_t t0) {
 #pragma unroll
-            for (int i = 0; i < kRowsPerThread; ++i) {
-                const uint32_t t = t0 + my_r0 + i * kRowStep;
-                off[i] = -1;
-                if (t < kv_len32) {
-                    const uint32_t pi = ps == 1 ? t : t / ps;
-                    const uint32_t slot = ps == 1 ? 0u : t - pi * ps;
-                    const int64_t page = p.pages[pi];
-                    if (page >= 0 && page < p.num_pages) off[i] = ((page * 2) * ps + slot) * row_elems;
-                    else bad_page = true;                    // reads as a row past the end; reported once at the exit
-                }
+            for (int i = 0; i < kIdsPerThread; ++i) {
+                const uint32_t t = t0 + id_row(i);
+                ids[i] = -1;
+                if (t < kv_len32) ids[i] = p.pages[ps == 1 ? t : t / ps];
             }
         };
-        auto stage_kv = [&](uint8_t* dst, const int64_t* off, int which) {   // rows past the sequence are zero
+        auto store_ids = [&](uint32_t t0, int buf) {             // table entry: page id, or -1 for a row that reads as zeros
+#pragma unroll
+            for (int i = 0; i < kIdsPerThread; ++i) {
+                const uint32_t t = t0 + id_row(i);
+                int32_t v = ids[i];
+                if (t < kv_len32 && !(v >= 0 && (int64_t)v < p.num_pages)) {
+                    bad_page = true;                             // reported once at the exit
+                    v = -1;
+                }
+                pgtab[buf * kPfTile + id_row(i)] = v;
+            }
+        };
+        auto stage_kv = [&](uint8_t* dst, uint32_t t0, int buf, int which) {
             const uint32_t base = smem_u32(dst);
+            int32_t pg[kRowsPerThread];          // all ids first: a copy (an asm with a memory clobber) lets no later load pass it
+#pragma unroll
+            for (int i = 0; i < kRowsPerThread; ++i) pg[i] = pgtab[buf * kPfTile + my_r0 + i * kRowStep];
 #pragma unroll
             for (int i = 0; i < kRowsPerThread; ++i) {
                 const int r = my_r0 + i * kRowStep;
-                const bool ok = off[i] >= 0;
-                const T* src = ok ? kv_head + off[i] + (which ? v_off : 0) : kv;
+                const int64_t page = pg[i];
+                const bool ok = page >= 0;
+                const uint32_t slot = ps == 1 ? 0u : (t0 + r) % ps;
+                const T* src = ok ? kv_head + ((page * 2 + which) * ps + slot) * row_elems : kv;
                 cp_async16(base + sw128_offset(kPfTile, r, my_c), src, ok ? 16u : 0u);
             }
         };
-        auto announce = [&](int g) {      // group g = K of tile g, V of tile g - 2 (and Q with group 0)
+        auto announce = [&](int slot) {
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                if (g < n_tiles) mbar_arrive(&bar[kKFull + g % 3]);
-                if (g >= 2 && g - 2 < n_tiles) mbar_arrive(&bar[kVFull + (g - 2) % 3]);
-            }
+            if (lane == 0) mbar_arrive(&bar[kFull + slot]);
         };
         {
             const uint32_t base = smem_u32(sQ);
@@ -380,94 +434,105 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
                 cp_async16(base + (r >> 7) * kQBytes + sw128_offset(kPfRows, r & 127, my_c), src, ok ? 16u : 0u);
             }
         }
-        int64_t off_k[kRowsPerThread], off_v1[kRowsPerThread], off_v2[kRowsPerThread];   // rows of tiles u, u - 1, u - 2
-#pragma unroll
-        for (int i = 0; i < kRowsPerThread; ++i) off_v1[i] = off_v2[i] = -1;
-        lookup_rows(0, off_k);
+        load_ids(0);
+        store_ids(0, 0);
+        load_ids(kPfTile);                  // tile 1: into the table after V_0 has been issued
+        __syncwarp();
         bool alive = true;
-        for (int u = 0; u < n_tiles + 2; ++u) {
-            if (u < n_tiles) {
-                if (u >= 3 && !warp_wait(&bar[kKEmpty + u % 3], (uint32_t)((u / 3 - 1) & 1), &abort_flag, p.status)) { alive = false; break; }
-                stage_kv(sK + (uint32_t)(u % 3) * kKBytes, off_k, 0);
-            }
-            if (u >= 2) {
-                const int v = u - 2;
-                if (v >= 3 && !warp_wait(&bar[kVEmpty + v % 3], (uint32_t)((v / 3 - 1) & 1), &abort_flag, p.status)) { alive = false; break; }
-                stage_kv(sV + (uint32_t)(v % 3) * kKBytes, off_v2, 1);
-            }
+        int slot = 0, prev_slot = 0;
+        uint32_t wrap = 0;             // (i / ring) & 1
+        for (int i = 0; i < 2 * n_tiles; ++i) {
+            const int j = i >> 1;
+            if (i >= kPfRing && !warp_wait(&bar[kEmpty + slot], wrap ^ 1u, &abort_flag, p.status)) { alive = false; break; }
+            stage_kv(sRing + (uint32_t)slot * kTileBytes, (uint32_t)j * kPfTile, j & 1, i & 1);
             cp_async_commit();
-            if (u >= 1) {
+            if (i >= 1) {
                 cp_async_wait<1>();
-                announce(u - 1);
+                announce(prev_slot);
             }
-#pragma unroll
-            for (int i = 0; i < kRowsPerThread; ++i) {
-                off_v2[i] = off_v1[i];
-                off_v1[i] = off_k[i];
+            if (i & 1) {                   // V_j issued: tile j + 1's ids go into the table, tile j + 2's set off
+                store_ids((uint32_t)(j + 1) * kPfTile, (j + 1) & 1);
+                load_ids((uint32_t)(j + 2) * kPfTile);
+                __syncwarp();
             }
-            lookup_rows((uint32_t)(u + 1) * kPfTile, off_k);
+            prev_slot = slot;
+            if (++slot == kPfRing) {
+                slot = 0;
+                wrap ^= 1u;
+            }
         }
         cp_async_wait<0>();
-        if (alive) announce(n_tiles + 1);
-    } else {
-        // ================================================================== MMA issue (one lane of the last warp)
+        if (alive) announce(prev_slot);
+    } else if (warp == (kSoftmaxThreads + kProducerThreads) / 32) {
+        // ================================================================== MMA issue (one lane of this warp)
+        if constexpr (SUB == 2) reg_dec<kPfAuxRegs>();
         constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
         constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
         constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
-        const uint32_t t_s = tmem, t_o = tmem + 2 * kPfTile;      // per row block: S buffers in columns [0,64) and [64,128), O after them
         // operand descriptors of the tile origins; a step along K adds a constant to the address field
-        const uint64_t dq = smem_desc_sw128(smem_u32(sQ), 16, 1024), dk = smem_desc_sw128(smem_u32(sK), 16, 1024);
-        const uint64_t dp = smem_desc_sw128(smem_u32(sP), 16, 1024), dv = smem_desc_sw128(smem_u32(sV), v_lbo, v_sbo);
-        auto issue_qk = [&](int sb, int j, int kbuf) {     // S_j = Q K_j^T of row block sb into its S buffer j & 1
-            const uint64_t dkj = dk + (uint64_t)(((uint32_t)kbuf * kKBytes) >> 4);
+        const uint64_t dq = smem_desc_sw128(smem_u32(sQ), 16, 1024), dk = smem_desc_sw128(smem_u32(sRing), 16, 1024);
+        const uint64_t dv = smem_desc_sw128(smem_u32(sRing), v_lbo, v_sbo);
+        auto issue_qk = [&](int sb, int slot) {     // S = Q K^T of row block sb, K in ring slot `slot`
+            const uint64_t dkj = dk + (uint64_t)(((uint32_t)slot * kTileBytes) >> 4);
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {
                 const uint32_t a = sb * kQBytes + (k >> 2) * (kPfRows * 128) + (k & 3) * 32;
                 const uint32_t b = (k >> 2) * (kPfTile * 128) + (k & 3) * 32;
-                tc_mma_f16(t_s + sb * kSubCols + (uint32_t)(j & 1) * kPfTile, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
+                tc_mma_f16(tmem + sb * kSubCols, dq + (a >> 4), dkj + (b >> 4), idesc_qk, k > 0);
             }
         };
-        bool alive = true;
-        // S of tiles 0 and 1
-        for (int t = 0; t < 2 && t < n_tiles && alive; ++t) {
-            alive = warp_wait(&bar[kKFull + t], 0u, &abort_flag, p.status);
-            if (alive && lane == 0) {
-                tc_fence_after();
+        auto issue_pv = [&](int sb, int slot, uint32_t accumulate) {   // O (+)= P V of row block sb, V in ring slot `slot`
+            const uint64_t dvj = dv + (uint64_t)(((uint32_t)slot * kTileBytes) >> 4);
 #pragma unroll
-                for (int sb = 0; sb < SUB; ++sb) {
-                    issue_qk(sb, t, t);
-                    tc_commit(&bar[kSFull + 2 * sb + t]);
-                }
-                tc_commit(&bar[kKEmpty + t]);
+            for (int k = 0; k < kPfTile / 16; ++k)
+                tc_mma_f16_ts(tmem + sb * kSubCols + kPfTile, tmem + sb * kSubCols + k * 8, dvj + (uint64_t)((k * 16 * 128) >> 4), idesc_pv,
+                              (accumulate || k > 0) ? 1u : 0u);
+        };
+        int slot = 0;                 // the consumer walks the ring in sequence order
+        uint32_t wrap = 0;
+        auto advance = [&]() {
+            if (++slot == kPfRing) {
+                slot = 0;
+                wrap ^= 1u;
             }
-            __syncwarp();
-        }
-        int k3 = 0;     // j % 3
-        for (int j = 0; j < n_tiles && alive; ++j, k3 = (k3 == 2 ? 0 : k3 + 1)) {
-            const int kn = k3 == 0 ? 2 : k3 - 1;      // (j + 2) % 3
-            alive = warp_wait(&bar[kVFull + k3], (uint32_t)((j / 3) & 1), &abort_flag, p.status);
-            if (alive && j + 2 < n_tiles) alive = warp_wait(&bar[kKFull + kn], (uint32_t)(((j + 2) / 3) & 1), &abort_flag, p.status);
+        };
+        bool alive = warp_wait(&bar[kFull + 0], 0u, &abort_flag, p.status);      // Q and K_0
+        if (alive && lane == 0) {
+            tc_fence_after();
 #pragma unroll
             for (int sb = 0; sb < SUB; ++sb) {
-                if (alive) alive = warp_wait(&bar[kPFull + 2 * sb + (j & 1)], (uint32_t)((j >> 1) & 1), &abort_flag, p.status);
+                issue_qk(sb, 0);
+                tc_commit(&bar[kSFull + sb]);
+            }
+            tc_commit(&bar[kEmpty + 0]);
+        }
+        __syncwarp();
+        advance();
+        for (int j = 0; j < n_tiles && alive; ++j) {
+            const int v_slot = slot;
+            alive = warp_wait(&bar[kFull + v_slot], wrap, &abort_flag, p.status);       // V_j
+            advance();
+            const int k_slot = slot;
+            const bool more = j + 1 < n_tiles;
+            if (alive && more) alive = warp_wait(&bar[kFull + k_slot], wrap, &abort_flag, p.status);   // K_(j+1)
+            if (more) advance();
+#pragma unroll
+            for (int sb = 0; sb < SUB; ++sb) {
+                if (alive) alive = warp_wait(&bar[kPFull + sb], (uint32_t)(j & 1), &abort_flag, p.status);
                 if (alive && lane == 0) {
                     tc_fence_after();
-                    const uint64_t dvj = dv + (uint64_t)(((uint32_t)k3 * kKBytes) >> 4);
-#pragma unroll
-                    for (int k = 0; k < kPfTile / 16; ++k)
-                        tc_mma_f16(t_o + sb * kSubCols, dp + (uint64_t)((((j & 1) * SUB + sb) * kPBytes + k * 32) >> 4),
-                                   dvj + (uint64_t)((k * 16 * 128) >> 4), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                    tc_commit(&bar[kPvDone + 2 * sb + (j & 1)]);
-                    if (j + 2 < n_tiles) {
-                        issue_qk(sb, j + 2, kn);
-                        tc_commit(&bar[kSFull + 2 * sb + (j & 1)]);
+                    issue_pv(sb, v_slot, j > 0 ? 1u : 0u);
+                    tc_commit(&bar[kPvDone + sb]);
+                    if (more) {
+                        issue_qk(sb, k_slot);
+                        tc_commit(&bar[kSFull + sb]);
                     }
                 }
                 __syncwarp();
             }
             if (alive && lane == 0) {
-                tc_commit(&bar[kVEmpty + k3]);
-                if (j + 2 < n_tiles) tc_commit(&bar[kKEmpty + kn]);
+                tc_commit(&bar[kEmpty + v_slot]);
+                if (more) tc_commit(&bar[kEmpty + k_slot]);
             }
             __syncwarp();
         }
@@ -475,6 +540,8 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         if (lane == 0) tc_commit(&bar[kAllDone]);
         __syncwarp();
         warp_wait(&bar[kAllDone], 0u, &abort_flag, p.status);
+    } else {
+        if constexpr (SUB == 2) reg_dec<kPfAuxRegs>();      // the spare warps of the second auxiliary group
     }
     if (bad_page && p.status) atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
     tc_fence_before();
@@ -484,8 +551,8 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
 
 template <typename T, int D, int SUB>
 static int launch_prefill_sub(const PrefillParams& p, cudaStream_t st) {
-    // Q, K x3, V x3, P x2, barriers
-    const size_t smem = (size_t)SUB * kPfRows * D * 2 + 6 * (size_t)kPfTile * D * 2 + 2 * (size_t)SUB * kPfRows * kPfTile * 2 + 256;
+    // Q, the K/V ring, barriers, page-id table
+    const size_t smem = (size_t)SUB * kPfRows * D * 2 + (size_t)kPfRing * kPfTile * D * 2 + 256 + 2 * kPfTile * sizeof(int32_t);
     TIDAL_CUDA_OK(cudaFuncSetAttribute(prefill_attn_kernel<T, D, SUB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int n_qt = (p.n_q + kPfRows * SUB - 1) / (kPfRows * SUB);
     TIDAL_CUDA_OK(launch_pdl(prefill_attn_kernel<T, D, SUB>, dim3((unsigned)n_qt, (unsigned)p.Hq), dim3(128 * SUB + kPfExtraThreads), smem, st, 1, p));
