@@ -34,12 +34,22 @@ namespace tidal {
 constexpr int kPfRows = 128;     // query rows per CTA = MMA M = TMEM lanes
 constexpr int kPfTile = 128;     // KV tokens per tile
 constexpr int kPfRing = 5;       // K/V tiles in flight in shared memory
-constexpr int kPfProducerWarps = 4;   // warps that fetch K and V tiles (the copy rate grows with the warps that issue)
-constexpr int kPfExtraThreads = 256;  // two more warp groups beside the softmax threads: four producer warps; the MMA warp and three spares
-// Registers per thread after the role split (setmaxnreg; two row blocks only): the softmax threads hold a whole
-// S row of 128 values.  The pool is 512 threads x the 128 registers the launch bound gives = the register file;
-// the two auxiliary warp groups give back (128 - 56) x 256 = 18432, the softmax groups take (200 - 128) x 256 = 18432.
-constexpr int kPfSoftmaxRegs = 200, kPfAuxRegs = 56;
+constexpr int kPfProducerWarps = 8;   // warps that fetch K and V tiles: a warp keeps only so many copies in flight, the rate grows with the warps
+constexpr int kPfExtraThreads = 32 * kPfProducerWarps + 128;  // warp groups beside the softmax threads: the producer warps; the MMA warp and three spares
+// Registers per thread after the role split (setmaxnreg, a warp-group operation).  The softmax threads hold a whole
+// S row of 128 values and take registers from the other warps.  A CTA starts with `launch` registers per thread
+// (what the launch bound leaves: the register file divided by the threads, rounded down to 8; ptxas reports the
+// same figure as "Used N registers"), the auxiliary groups give back down to `aux`, the softmax groups grow to
+// `softmax`; the static_assert keeps the request inside what was given back, so that no setmaxnreg.inc can wait
+// for registers that never come.
+template <int SUB>
+struct PfRegs {
+    static constexpr int threads = 128 * SUB + kPfExtraThreads;
+    static constexpr int launch = 65536 / threads / 8 * 8;
+    static constexpr int softmax = SUB == 2 ? 176 : 200, aux = SUB == 2 ? 40 : 96;
+    static_assert((launch - aux) * kPfExtraThreads >= (softmax - launch) * 128 * SUB, "register pool");
+    static_assert(softmax >= launch && aux <= launch, "setmaxnreg direction");
+};
 
 struct PrefillParams {
     const void* q;        // [n_q][Hq][D]
@@ -194,7 +204,7 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 
 // Roles (warp-specialised; nothing in the loop is a block-wide barrier):
 //   warps [0, 4 SUB)          softmax: thread t owns query row t of the CTA (lane of tensor memory = row)
-//   the next four warps       producers: page lookups and cp.async of the K and V tiles into the ring
+//   the next eight warps      producers: page lookups and cp.async of the K and V tiles into the ring
 //   the next warp             issues every tcgen05.mma (one lane) and commits them to the barriers below
 //   the last three warps      only complete the warp group (setmaxnreg is a warp-group operation)
 // Barriers (mbarrier; the i-th completion of a barrier is waited for with parity i & 1):
@@ -218,7 +228,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
     constexpr int kFull = 0, kEmpty = kPfRing, kSFull = 2 * kPfRing, kPFull = kSFull + SUB, kPvDone = kPFull + SUB,
                   kAllDone = kPvDone + SUB, kNumBars = kAllDone + 1;
     static_assert(kNumBars * 8 + 8 <= 256, "barrier block");
-    static_assert(32 % kChunks == 0 && kPfTile % (kPfProducerWarps * 32 / kChunks) == 0 && kPfTile % (kPfProducerWarps * 32) == 0, "producer mapping");
+    static_assert(32 % kChunks == 0 && kPfTile % (kPfProducerWarps * 32 / kChunks) == 0 && kPfTile % kPfProducerWarps == 0, "producer mapping");
     // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
     // operand tiles need (224 KB + 256 bytes with two row blocks at D = 128).
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -260,7 +270,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
 
     if (tid < kSoftmaxThreads) {
         // ================================================================== softmax: one thread per query row
-        if constexpr (SUB == 2) reg_inc<kPfSoftmaxRegs>();
+        reg_inc<PfRegs<SUB>::softmax>();
         const int sub = warp >> 2;
         const uint32_t t_s = tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)sub * kSubCols;   // this thread's lane: S columns of its row block
         const uint32_t t_o = t_s + kPfTile;
@@ -367,10 +377,11 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         // as one cp.async group and announces the group of the step before.  The page ids of tile t are loaded
         // into registers two tiles ahead (end of the step that issued V_(t-2)), moved into the table in shared
         // memory one tile later and read from there by the copies of K_t and V_t, so nothing waits for a lookup.
-        if constexpr (SUB == 2) reg_dec<kPfAuxRegs>();
+        reg_dec<PfRegs<SUB>::aux>();
         const int pt = tid - kSoftmaxThreads;
         constexpr int kRowStep = kProducerThreads / kChunks, kRowsPerThread = kPfTile / kRowStep;
-        constexpr int kIdsPerThread = kPfTile / kProducerThreads;
+        constexpr int kIdsPerWarp = kPfTile / kPfProducerWarps, kIdsPerThread = kIdsPerWarp >= 32 ? kIdsPerWarp / 32 : 1;
+        const bool id_lane = lane * kIdsPerThread < kIdsPerWarp;    // with many warps only the first lanes hold an id
         const T* q = reinterpret_cast<const T*>(p.q);
         const T* kv = reinterpret_cast<const T*>(p.kv);
         const int64_t row_elems = (int64_t)p.Hkv * D;
@@ -390,7 +401,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
             for (int i = 0; i < kIdsPerThread; ++i) {
                 const uint32_t t = t0 + id_row(i);
                 ids[i] = -1;
-                if (t < kv_len32) ids[i] = p.pages[ps == 1 ? t : t / ps];
+                if (id_lane && t < kv_len32) ids[i] = p.pages[ps == 1 ? t : t / ps];
             }
         };
         auto store_ids = [&](uint32_t t0, int buf) {             // table entry: page id, or -1 for a row that reads as zeros
@@ -398,11 +409,11 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
             for (int i = 0; i < kIdsPerThread; ++i) {
                 const uint32_t t = t0 + id_row(i);
                 int32_t v = ids[i];
-                if (t < kv_len32 && !(v >= 0 && (int64_t)v < p.num_pages)) {
+                if (id_lane && t < kv_len32 && !(v >= 0 && (int64_t)v < p.num_pages)) {
                     bad_page = true;                             // reported once at the exit
                     v = -1;
                 }
-                pgtab[buf * kPfTile + id_row(i)] = v;
+                if (id_lane) pgtab[buf * kPfTile + id_row(i)] = v;
             }
         };
         auto stage_kv = [&](uint8_t* dst, uint32_t t0, int buf, int which) {
@@ -465,7 +476,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         if (alive) announce(prev_slot);
     } else if (warp == (kSoftmaxThreads + kProducerThreads) / 32) {
         // ================================================================== MMA issue (one lane of this warp)
-        if constexpr (SUB == 2) reg_dec<kPfAuxRegs>();
+        reg_dec<PfRegs<SUB>::aux>();
         constexpr uint32_t idesc_qk = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 0, kPfRows, kPfTile);
         constexpr uint32_t idesc_pv = instr_desc(sizeof(T) == 2 && !std::is_same<T, __half>::value, 1, kPfRows, D);
         constexpr uint32_t v_lbo = kPfTile * 128, v_sbo = 1024;   // next 64 elements of D; next 8 tokens
@@ -541,7 +552,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         __syncwarp();
         warp_wait(&bar[kAllDone], 0u, &abort_flag, p.status);
     } else {
-        if constexpr (SUB == 2) reg_dec<kPfAuxRegs>();      // the spare warps of the second auxiliary group
+        reg_dec<PfRegs<SUB>::aux>();      // the spare warps of the second auxiliary group
     }
     if (bad_page && p.status) atomicOr(p.status, TIDAL_DEV_BAD_INDEX);
     tc_fence_before();
