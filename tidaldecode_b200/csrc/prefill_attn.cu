@@ -34,6 +34,9 @@ namespace tidal {
 constexpr int kPfRows = 128;     // query rows per CTA = MMA M = TMEM lanes
 constexpr int kPfTile = 128;     // KV tokens per tile
 constexpr int kPfRing = 5;       // K/V tiles in flight in shared memory
+#ifndef TIDAL_PF_LAG
+#define TIDAL_PF_LAG 1
+#endif
 constexpr int kPfProducerWarps = 8;   // warps that fetch K and V tiles: a warp keeps only so many copies in flight, the rate grows with the warps
 constexpr int kPfExtraThreads = 32 * kPfProducerWarps + 128;  // warp groups beside the softmax threads: the producer warps; the MMA warp and three spares
 // Registers per thread after the role split (setmaxnreg, a warp-group operation).  The softmax threads hold a whole
@@ -450,30 +453,43 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         load_ids(kPfTile);                  // tile 1: into the table after V_0 has been issued
         __syncwarp();
         bool alive = true;
-        int slot = 0, prev_slot = 0;
+        // A tile is announced kLag steps after its copies were issued.  Measured: one step is best with a ring of
+        // five (two or three leave the MMA warp waiting for tiles: 8.4 -> 9.7 -> 12 ms on a 32 K prompt); what bounds
+        // a step is the rate at which the load/store unit accepts a warp's copies, not the wait for the group.
+        constexpr int kLag = TIDAL_PF_LAG;
+        static_assert(kLag >= 1 && kLag <= 3 && kLag + 2 <= kPfRing, "the ring holds the tiles in flight and the two being read");
+        int slot = 0;
         uint32_t wrap = 0;             // (i / ring) & 1
         for (int i = 0; i < 2 * n_tiles; ++i) {
             const int j = i >> 1;
             if (i >= kPfRing && !warp_wait(&bar[kEmpty + slot], wrap ^ 1u, &abort_flag, p.status)) { alive = false; break; }
             stage_kv(sRing + (uint32_t)slot * kTileBytes, (uint32_t)j * kPfTile, j & 1, i & 1);
             cp_async_commit();
-            if (i >= 1) {
-                cp_async_wait<1>();
-                announce(prev_slot);
+            if (i >= kLag) {
+                cp_async_wait<kLag>();
+                announce(slot >= kLag ? slot - kLag : slot - kLag + kPfRing);
             }
             if (i & 1) {                   // V_j issued: tile j + 1's ids go into the table, tile j + 2's set off
                 store_ids((uint32_t)(j + 1) * kPfTile, (j + 1) & 1);
                 load_ids((uint32_t)(j + 2) * kPfTile);
                 __syncwarp();
             }
-            prev_slot = slot;
             if (++slot == kPfRing) {
                 slot = 0;
                 wrap ^= 1u;
             }
         }
+        // the last kLag tiles, oldest first (slot = that of tile 2 n_tiles)
+        if (kLag >= 3) {
+            cp_async_wait<2>();
+            if (alive && 2 * n_tiles >= 3) announce((slot + 2 * kPfRing - 3) % kPfRing);
+        }
+        if (kLag >= 2) {
+            cp_async_wait<1>();
+            if (alive && 2 * n_tiles >= 2) announce((slot + 2 * kPfRing - 2) % kPfRing);
+        }
         cp_async_wait<0>();
-        if (alive) announce(prev_slot);
+        if (alive) announce((slot + 2 * kPfRing - 1) % kPfRing);
     } else if (warp == (kSoftmaxThreads + kProducerThreads) / 32) {
         // ================================================================== MMA issue (one lane of this warp)
         reg_dec<PfRegs<SUB>::aux>();
