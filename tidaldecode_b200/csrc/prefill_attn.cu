@@ -63,6 +63,7 @@ struct PrefillParams {
     int64_t kv_len;
     int64_t num_pages;    // pages in the pool: a table entry outside [0, num_pages) is skipped (zero rows) and reported
     int n_q, Hq, Hkv, page_size;
+    int ps_shift;         // log2(page_size) when that is a power of two, else -1 (the kernels then divide)
     int causal;
     float scale_log2;     // softmax scale x log2(e)
 };
@@ -404,7 +405,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
             for (int i = 0; i < kIdsPerThread; ++i) {
                 const uint32_t t = t0 + id_row(i);
                 ids[i] = -1;
-                if (id_lane && t < kv_len32) ids[i] = p.pages[ps == 1 ? t : t / ps];
+                if (id_lane && t < kv_len32) ids[i] = p.pages[p.ps_shift >= 0 ? t >> p.ps_shift : t / ps];
             }
         };
         auto store_ids = [&](uint32_t t0, int buf) {             // table entry: page id, or -1 for a row that reads as zeros
@@ -429,7 +430,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
                 const int r = my_r0 + i * kRowStep;
                 const int64_t page = pg[i];
                 const bool ok = page >= 0;
-                const uint32_t slot = ps == 1 ? 0u : (t0 + r) % ps;
+                const uint32_t slot = p.ps_shift >= 0 ? (t0 + r) & (ps - 1u) : (t0 + r) % ps;
                 const T* src = ok ? kv_head + ((page * 2 + which) * ps + slot) * row_elems : kv;
                 cp_async16(base + sw128_offset(kPfTile, r, my_c), src, ok ? 16u : 0u);
             }
@@ -783,6 +784,9 @@ extern "C" int tidal_prefill(const tidal_prefill_args* a, void* stream) {
     p.Hq = a->num_qo_heads;
     p.Hkv = a->num_kv_heads;
     p.page_size = a->page_size;
+    p.ps_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == a->page_size) p.ps_shift = sh;
     p.causal = a->causal ? 1 : 0;
     const float sc = a->sm_scale > 0.f ? a->sm_scale : 1.f / sqrtf((float)a->head_dim);
     p.scale_log2 = sc * kLog2e;
