@@ -388,6 +388,34 @@ def test_long_selection_lists(T, dt, B, Hq, Hkv, D, N, k, page, shuffle, kw):
         assert ws.status() == 0
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,k", [(8, 64, 8, 1024), (4, 32, 8, 2048), (3, 64, 8, 1500)])
+def test_sparse_lists_long_enough_for_several_clusters(T, B, Hq, Hkv, k):
+    """Lists of a thousand and more tokens with all KV heads in one CTA (bf16, page_size 1): the planner puts two
+    clusters of 8 (or four of 4) on each list; every cluster leaves its share in the workspace and the last to
+    arrive finishes.  Checked against the gathered oracle, three calls in a row (the arrival counters must be
+    back at zero each time), normalised output and un-normalised partials."""
+    D, N, dtype = 128, 5000, torch.bfloat16
+    q, K, V = make_qkv(29, B, Hq, Hkv, D, N, dtype)
+    pool, _, ppb = build_pool(K, V, 1)
+    g = torch.Generator().manual_seed(k)
+    sel = torch.stack([torch.sort(torch.randperm(N, generator=g)[:k]).values for _ in range(B)]).to(torch.int32)
+    ws = _ws(T, B, Hq, D, B, N)
+    qd, pd, sd = q[:, :, 0].contiguous().cuda(), pool.cuda(), sel.cuda()
+    want = torch.cat([O.gathered_attention(q[b:b + 1], K[b:b + 1], V[b:b + 1], sel[b:b + 1])[:, :, 0] for b in range(B)])
+    for rep in range(3):
+        o = T.decode_attention(qd, pd, N, ws, pages_per_seq=ppb, sel_idx=sd)
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        assert_close(o, want, dtype, f"call {rep}")
+    m = torch.empty(B, Hq, device="cuda")
+    l = torch.empty(B, Hq, device="cuda")
+    acc = torch.empty(B, Hq, D, device="cuda")
+    T.decode_attention(qd, pd, N, ws, pages_per_seq=ppb, sel_idx=sd, partials=(m, l, acc), want_out=False)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    assert_close((acc / l[..., None]).to(dtype), want, dtype, "partials")
+
+
 def test_bad_index_is_flagged_not_followed(T):
     B, H, D, N = 1, 8, 128, 100
     q, K, V = make_qkv(1, B, H, H, D, N, torch.float16)

@@ -47,6 +47,9 @@ struct AttnParams {
     int32_t cluster;  // > 1: that many CTAs along the chunk dimension form a cluster that covers the whole
                       // token list and merges through distributed shared memory (then nchunks == cluster)
     uint32_t recv_off; // cluster > 1: byte offset (in dynamic shared memory) of the CTA's receive block
+    int32_t nsuper;    // cluster > 1: clusters that share one token list (nchunks == cluster * nsuper); > 1: each cluster
+                       // leaves its merged share in part_o / part_ml and the last one to arrive finishes it
+    uint32_t* xc_count; // [B][head slices][kMaxCluster] arrivals of those clusters, zero at rest
 };
 
 __host__ __device__ inline size_t round16(size_t x) { return (x + 15) & ~(size_t)15; }
@@ -264,7 +267,7 @@ __host__ __device__ inline size_t cta_result_bytes(int HC, int G, int D) { retur
 // kernel must have ARRIVED at the cluster barrier at its start (cluster_arrive_relaxed, every thread); the
 // matching wait is here, before the first store into another CTA, so that every CTA is known to be running.
 // A thread owns four consecutive output elements; every thread of the CTA must call this.
-constexpr int kMaxCluster = 16;        // 8 is the portable limit; 16 needs the non-portable-size attribute
+constexpr int kMaxCluster = 16;        // 8 is the portable limit; 16 needs the non-portable-size attribute (WsLayout::xc_off holds 16 counters per list)
 template <typename T>
 struct alignas(sizeof(T) * 4) Pack4 {
     T v[4];
@@ -335,6 +338,7 @@ __device__ __forceinline__ void store_attention_result(const AttnParams& p, cons
     cluster.sync();                                   // release / acquire: everything pushed to this CTA has landed
     if (threadIdx.x == 0) TIDAL_STAMP(10);
     const int hi = min(units, (rank + 1) * per);
+    const int NS = p.nsuper, sup = chunk / CS;         // clusters on this list, and which of them this is
     for (int u = rank * per + threadIdx.x; u < hi; u += blockDim.x) {
         const int hg = u >> qshift, d = (u - (hg << qshift)) * 4, local = u - rank * per;
         float M = -INFINITY, L = 0.f;
@@ -350,9 +354,48 @@ __device__ __forceinline__ void store_attention_result(const AttnParams& p, cons
             acc.w = fmaf(w, v.w, acc.w);
             L = fmaf(w, ml.y, L);
         }
-        put_final(hg, d, acc, M, L);
+        if (NS <= 1) {
+            put_final(hg, d, acc, M, L);
+        } else {
+            const size_t ph = (size_t)b * p.Hq + qh0 + hg;
+            __stcg(reinterpret_cast<float4*>(p.part_o + (ph * NS + sup) * D + d), acc);
+            if (d == 0) __stcg(reinterpret_cast<float2*>(p.part_ml + (ph * NS + sup) * 2), make_float2(M, L));
+        }
     }
     if (threadIdx.x == 0) TIDAL_STAMP(11);
+    if (NS <= 1) return;
+    // Several clusters on one list: CTA `rank` of each holds the same share of the outputs.  The last of them to
+    // arrive (one counter per list and rank, left at zero again) merges the shares of all and writes the result.
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t* cnt = p.xc_count + ((size_t)b * gridDim.y + blockIdx.y) * kMaxCluster + rank;
+        const uint32_t seen = atomicAdd(cnt, 1u);
+        s_last = seen == (uint32_t)NS - 1u;
+        if (s_last) *cnt = 0u;
+        __threadfence();
+    }
+    __syncthreads();
+    if (!s_last) return;
+    for (int u = rank * per + threadIdx.x; u < hi; u += blockDim.x) {
+        const int hg = u >> qshift, d = (u - (hg << qshift)) * 4;
+        const size_t ph = (size_t)b * p.Hq + qh0 + hg;
+        float M = -INFINITY, L = 0.f;
+        for (int c = 0; c < NS; ++c) M = fmaxf(M, __ldcg(p.part_ml + (ph * NS + c) * 2));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = 0; c < NS; ++c) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (ph * NS + c) * 2));
+            const float w = (ml.x == -INFINITY) ? 0.f : fast_exp2(ml.x - M);
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(p.part_o + (ph * NS + c) * D + d));
+            acc.x = fmaf(w, v.x, acc.x);
+            acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z);
+            acc.w = fmaf(w, v.w, acc.w);
+            L = fmaf(w, ml.y, L);
+        }
+        put_final(hg, d, acc, M, L);
+    }
 }
 
 // Tensor-core kernel (decode_attn_mma.cu): 16-bit storage, up to 16 query heads per

@@ -44,6 +44,7 @@ struct WsLayout {
     size_t part_ml_off;    // float [max_batch*Hq][kMaxChunks][2]
     size_t hist_off;       // uint32 [max_rows][TIDAL_TOPK_BINS]   (top-k's own, when the caller gives none)
     size_t row_state_off;  // uint32 [max_rows][8]   per-row top-k state
+    size_t xc_off;         // uint32 [max_batch*Hq][16]  arrival counters of clusters that share one token list
     size_t cand_off;       // uint64 [max_rows][cand_cap]
     size_t sel_off;        // uint64 [max_rows][kMaxK]  keys certainly selected, before ordering
     size_t total;
@@ -69,6 +70,8 @@ inline WsLayout ws_layout(int max_batch, int num_qo_heads, int head_dim, int max
     off = align_up(off + sizeof(uint32_t) * (size_t)max_rows * TIDAL_TOPK_BINS, 256);
     L.row_state_off = off;
     off = align_up(off + sizeof(uint32_t) * (size_t)max_rows * 8, 256);
+    L.xc_off = off;
+    off = align_up(off + sizeof(uint32_t) * (size_t)max_batch * num_qo_heads * 16, 256);
     L.cand_cap = max_n < kCandCapMax ? max_n : kCandCapMax;
     if (L.cand_cap < 1) L.cand_cap = 1;
     L.cand_off = off;

@@ -717,8 +717,8 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     cudaStream_t st = (cudaStream_t)stream;
     AttnParams p;
     // Everything that depends on the cluster size; returns a negative code on a bad geometry.
-    auto build = [&](int cl) -> int {
-        if (cl > 1) plan.nchunks = cl;
+    auto build = [&](int cl, int ns) -> int {
+        if (cl > 1) plan.nchunks = cl * ns;
         else plan.nchunks = a->num_chunks > 0 ? a->num_chunks
                                               : tidal_plan_chunks(a->batch, plan.nslices, ntok, min_tok, sm_count_cached());
         TIDAL_REQUIRE(plan.nchunks >= 1 && plan.nchunks <= kMaxChunks, TIDAL_ERR_ARG, "num_chunks %d out of range [1,%d]",
@@ -756,6 +756,8 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
         p.sm_scale = a->sm_scale > 0.f ? a->sm_scale : 1.0f / sqrtf((float)D);
         p.nchunks = plan.nchunks; p.HC = plan.HC; p.greal = G; p.per_head = per_head ? 1 : 0;
         p.T = plan.T; p.S = plan.S; p.TG = plan.TG; p.CW = plan.CW; p.cluster = cl;
+        p.nsuper = cl > 1 ? ns : 1;
+        p.xc_count = (uint32_t*)((char*)d_ws + L->xc_off);
         p.recv_off = (uint32_t)smem_base(plan.S);
         p.kv_fused = (a->page_size == 1 && plan.HC == a->num_kv_heads && !per_head) ? 1 : 0;
         // One warp gets a bulk copy accepted every ~70 cycles, so short rows want more producer warps.
@@ -782,24 +784,42 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     // once (a cluster sits inside one GPC), otherwise they would run one after the other.
     const size_t cta_bytes_at_8 = (size_t)ntok * 2 * plan.HC * D * es / 8;      // what one CTA of an 8-cluster streams
     if (cluster == 8 && cta_bytes_at_8 > ((size_t)192 << 10) && 16 * a->batch * plan.nslices <= sm_count_cached()) {
-        if ((rc = build(16)) != TIDAL_OK) return rc;
+        if ((rc = build(16, 1)) != TIDAL_OK) return rc;
         int resident = 0;
         if ((rc = run(&resident)) != TIDAL_OK) return rc;
         if (resident >= a->batch * plan.nslices) cluster = 16;
     }
-    if ((rc = build(cluster)) != TIDAL_OK) return rc;
-    const size_t part_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * D;
-    const size_t ml_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * plan.nchunks * 2;
-    TIDAL_REQUIRE(plan.nchunks == 1 || cluster > 1 ||
+    // Otherwise several clusters per list (two of 8, else four of 4), as long as all of them are resident at once:
+    // each cluster merges inside itself as before and leaves its share in the workspace, the last to arrive finishes.
+    int nsuper = 1;
+    if (cluster == 8 && cta_bytes_at_8 > ((size_t)192 << 10)) {
+        const int tries[2][2] = {{8, 2}, {4, 4}};
+        for (int t = 0; t < 2 && nsuper == 1; ++t) {
+            const int cl = tries[t][0], ns = tries[t][1];
+            if (cl * ns * a->batch * plan.nslices > sm_count_cached()) continue;
+            if ((rc = build(cl, ns)) != TIDAL_OK) return rc;
+            int resident = 0;
+            if ((rc = run(&resident)) != TIDAL_OK) return rc;
+            if (resident >= ns * a->batch * plan.nslices) {
+                cluster = cl;
+                nsuper = ns;
+            }
+        }
+    }
+    if ((rc = build(cluster, nsuper)) != TIDAL_OK) return rc;
+    const int part_chunks = cluster > 1 ? nsuper : plan.nchunks;      // partials that go through the workspace
+    const size_t part_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * part_chunks * D;
+    const size_t ml_need = sizeof(float) * (size_t)a->batch * a->num_qo_heads * part_chunks * 2;
+    TIDAL_REQUIRE(part_chunks == 1 ||
                       (L->part_o_off + part_need <= L->part_ml_off && L->part_ml_off + ml_need <= L->hist_off),
                   TIDAL_ERR_WORKSPACE, "workspace was sized for a smaller batch/heads/head_dim than this call");
 
     // TIDAL_DEBUG_PLAN=1 in the environment: one line per call on stderr with the planner's choices
     static const bool debug_plan = std::getenv("TIDAL_DEBUG_PLAN") != nullptr;
     if (debug_plan)
-        fprintf(stderr, "tidal plan: %s ntok %d B %d Hq %d Hkv %d | HC %d slices %d chunks %d cluster %d T %d S %d CW %d PW %d smem %zu fused %d\n",
+        fprintf(stderr, "tidal plan: %s ntok %d B %d Hq %d Hkv %d | HC %d slices %d chunks %d cluster %d x %d T %d S %d CW %d PW %d smem %zu fused %d\n",
                 use_mma ? "mma" : "cuda-core", ntok, a->batch, a->num_qo_heads, a->num_kv_heads, plan.HC, plan.nslices, plan.nchunks,
-                cluster, plan.T, plan.S, plan.CW, p.PW, plan.smem, p.kv_fused);
+                cluster, nsuper, plan.T, plan.S, plan.CW, p.PW, plan.smem, p.kv_fused);
     rc = run(nullptr);
     if (rc != TIDAL_OK) return rc;
     if (plan.nchunks > 1 && cluster == 1) {
