@@ -210,7 +210,8 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 //   warps [0, 4 SUB)          softmax: thread t owns query row t of the CTA (lane of tensor memory = row)
 //   the next eight warps      producers: page lookups and cp.async of the K and V tiles into the ring
 //   the next warp             issues every tcgen05.mma (one lane) and commits them to the barriers below
-//   the last three warps      only complete the warp group (setmaxnreg is a warp-group operation)
+//   the next warp             looks up the page ids of each tile's rows, two tiles ahead of the copies
+//   the last two warps        only complete the warp group (setmaxnreg is a warp-group operation)
 // Barriers (mbarrier; the i-th completion of a barrier is waited for with parity i & 1):
 //   full[5], empty[5]         ring slots, tile i of the sequence K_0 V_0 K_1 V_1 ... uses slot i % 5:
 //                             producers -> MMA warp (one arrival per producer warp, after the copies have landed and
@@ -222,6 +223,8 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volati
 //                             (4 arrivals)
 //   pvdone[SUB]               commit after PV_t: awaited before the epilogue reads O
 //   alldone                   commit at the very end: no MMA is in flight when tensor memory is freed
+//   idsfull[2], idsempty[2]   lookup warp <-> producers: the page ids of tile t are in table t & 1 / every producer warp
+//                             has read them (one arrival per producer warp)
 template <typename T, int D, int SUB>
 __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_kernel(const __grid_constant__ PrefillParams p) {
     constexpr int kSoftmaxThreads = 128 * SUB, kProducerThreads = 32 * kPfProducerWarps, kRows = kPfRows * SUB;
@@ -230,9 +233,9 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
     constexpr uint32_t kSubCols = kPfTile + D;        // tensor-memory columns of one row block: S (P in its first half), then O
     constexpr uint32_t kTmemCols = SUB * kSubCols <= 256 ? 256 : 512;
     constexpr int kFull = 0, kEmpty = kPfRing, kSFull = 2 * kPfRing, kPFull = kSFull + SUB, kPvDone = kPFull + SUB,
-                  kAllDone = kPvDone + SUB, kNumBars = kAllDone + 1;
+                  kAllDone = kPvDone + SUB, kIdsFull = kAllDone + 1, kIdsEmpty = kIdsFull + 2, kNumBars = kIdsEmpty + 2;
     static_assert(kNumBars * 8 + 8 <= 256, "barrier block");
-    static_assert(32 % kChunks == 0 && kPfTile % (kPfProducerWarps * 32 / kChunks) == 0 && kPfTile % kPfProducerWarps == 0, "producer mapping");
+    static_assert(32 % kChunks == 0 && kPfTile % (kPfProducerWarps * 32 / kChunks) == 0, "producer mapping");
     // No static shared memory: the dynamic segment starts at offset 0 with the alignment the swizzled
     // operand tiles need (224 KB + 256 bytes with two row blocks at D = 128).
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -256,7 +259,7 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
     if (tid == 0) {
 #pragma unroll
         for (int i = 0; i < kNumBars; ++i)
-            mbar_init(&bar[i], i < kEmpty ? (uint32_t)kPfProducerWarps : (i >= kPFull && i < kPvDone) ? 4u : 1u);
+            mbar_init(&bar[i], (i < kEmpty || i >= kIdsEmpty) ? (uint32_t)kPfProducerWarps : (i >= kPFull && i < kPvDone) ? 4u : 1u);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -378,48 +381,17 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
     } else if (tid < kSoftmaxThreads + kProducerThreads) {
         // ================================================================== producers
         // kChunks consecutive threads share a row.  Step i fetches tile i of the sequence K_0 V_0 K_1 V_1 ...
-        // as one cp.async group and announces the group of the step before.  The page ids of tile t are loaded
-        // into registers two tiles ahead (end of the step that issued V_(t-2)), moved into the table in shared
-        // memory one tile later and read from there by the copies of K_t and V_t, so nothing waits for a lookup.
+        // as one cp.async group and announces the group of the step before.  The page ids of a tile's rows come
+        // from the table the lookup warp fills two tiles ahead, so no copy waits for a lookup.
         reg_dec<PfRegs<SUB>::aux>();
         const int pt = tid - kSoftmaxThreads;
         constexpr int kRowStep = kProducerThreads / kChunks, kRowsPerThread = kPfTile / kRowStep;
-        constexpr int kIdsPerWarp = kPfTile / kPfProducerWarps, kIdsPerThread = kIdsPerWarp >= 32 ? kIdsPerWarp / 32 : 1;
-        const bool id_lane = lane * kIdsPerThread < kIdsPerWarp;    // with many warps only the first lanes hold an id
         const T* q = reinterpret_cast<const T*>(p.q);
         const T* kv = reinterpret_cast<const T*>(p.kv);
         const int64_t row_elems = (int64_t)p.Hkv * D;
-        const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
+        const uint32_t ps = (uint32_t)p.page_size;
         const int my_c = pt % kChunks, my_r0 = pt / kChunks;
         const T* kv_head = kv + (int64_t)kvh * D + my_c * 8;
-        // Each warp looks up the rows it copies itself (rows my_r0 + i * kRowStep of its lanes), so the table needs no
-        // barrier between the warps: lane l's id i is that of row id_row(i).
-        constexpr int kWarpRows = kRowStep / kPfProducerWarps;   // adjacent rows of one pass that belong to one warp
-        auto id_row = [&](int i) {
-            const int x = lane * kIdsPerThread + i;
-            return kRowStep * (x / kWarpRows) + kWarpRows * (pt >> 5) + x % kWarpRows;
-        };
-        int32_t ids[kIdsPerThread];                              // page ids of the tile after the next copy's
-        auto load_ids = [&](uint32_t t0) {
-#pragma unroll
-            for (int i = 0; i < kIdsPerThread; ++i) {
-                const uint32_t t = t0 + id_row(i);
-                ids[i] = -1;
-                if (id_lane && t < kv_len32) ids[i] = p.pages[p.ps_shift >= 0 ? t >> p.ps_shift : t / ps];
-            }
-        };
-        auto store_ids = [&](uint32_t t0, int buf) {             // table entry: page id, or -1 for a row that reads as zeros
-#pragma unroll
-            for (int i = 0; i < kIdsPerThread; ++i) {
-                const uint32_t t = t0 + id_row(i);
-                int32_t v = ids[i];
-                if (id_lane && t < kv_len32 && !(v >= 0 && (int64_t)v < p.num_pages)) {
-                    bad_page = true;                             // reported once at the exit
-                    v = -1;
-                }
-                if (id_lane) pgtab[buf * kPfTile + id_row(i)] = v;
-            }
-        };
         auto stage_kv = [&](uint8_t* dst, uint32_t t0, int buf, int which) {
             const uint32_t base = smem_u32(dst);
             int32_t pg[kRowsPerThread];          // all ids first: a copy (an asm with a memory clobber) lets no later load pass it
@@ -449,10 +421,6 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
                 cp_async16(base + (r >> 7) * kQBytes + sw128_offset(kPfRows, r & 127, my_c), src, ok ? 16u : 0u);
             }
         }
-        load_ids(0);
-        store_ids(0, 0);
-        load_ids(kPfTile);                  // tile 1: into the table after V_0 has been issued
-        __syncwarp();
         bool alive = true;
         // A tile is announced kLag steps after its copies were issued.  Measured: one step is best with a ring of
         // five (two or three leave the MMA warp waiting for tiles: 8.4 -> 9.7 -> 12 ms on a 32 K prompt); what bounds
@@ -464,16 +432,16 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         for (int i = 0; i < 2 * n_tiles; ++i) {
             const int j = i >> 1;
             if (i >= kPfRing && !warp_wait(&bar[kEmpty + slot], wrap ^ 1u, &abort_flag, p.status)) { alive = false; break; }
+            if (!(i & 1) && !warp_wait(&bar[kIdsFull + (j & 1)], (uint32_t)((j >> 1) & 1), &abort_flag, p.status)) { alive = false; break; }
             stage_kv(sRing + (uint32_t)slot * kTileBytes, (uint32_t)j * kPfTile, j & 1, i & 1);
             cp_async_commit();
             if (i >= kLag) {
                 cp_async_wait<kLag>();
                 announce(slot >= kLag ? slot - kLag : slot - kLag + kPfRing);
             }
-            if (i & 1) {                   // V_j issued: tile j + 1's ids go into the table, tile j + 2's set off
-                store_ids((uint32_t)(j + 1) * kPfTile, (j + 1) & 1);
-                load_ids((uint32_t)(j + 2) * kPfTile);
+            if (i & 1) {                   // V_j issued: this warp has read table j & 1 for the last time
                 __syncwarp();
+                if (lane == 0) mbar_arrive(&bar[kIdsEmpty + (j & 1)]);
             }
             if (++slot == kPfRing) {
                 slot = 0;
@@ -568,6 +536,32 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
         if (lane == 0) tc_commit(&bar[kAllDone]);
         __syncwarp();
         warp_wait(&bar[kAllDone], 0u, &abort_flag, p.status);
+    } else if (warp == (kSoftmaxThreads + kProducerThreads) / 32 + 1) {
+        // ================================================================== page lookups
+        // Table t & 1 takes, for each of the 128 rows of tile t, the page that holds the token, or -1 for a row that
+        // reads as zeros (past the sequence, or a page id outside the pool: reported, not followed).
+        reg_dec<PfRegs<SUB>::aux>();
+        const uint32_t kv_len32 = (uint32_t)p.kv_len, ps = (uint32_t)p.page_size;
+        for (int t = 0; t < n_tiles; ++t) {
+            if (t >= 2 && !warp_wait(&bar[kIdsEmpty + (t & 1)], (uint32_t)(((t >> 1) - 1) & 1), &abort_flag, p.status)) break;
+            int32_t v[kPfTile / 32];
+#pragma unroll
+            for (int i = 0; i < kPfTile / 32; ++i) {
+                const uint32_t tok = (uint32_t)t * kPfTile + lane + 32 * i;
+                v[i] = -1;
+                if (tok < kv_len32) {
+                    v[i] = p.pages[p.ps_shift >= 0 ? tok >> p.ps_shift : tok / ps];
+                    if (!(v[i] >= 0 && (int64_t)v[i] < p.num_pages)) {
+                        bad_page = true;                         // reported once at the exit
+                        v[i] = -1;
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kPfTile / 32; ++i) pgtab[(t & 1) * kPfTile + lane + 32 * i] = v[i];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar[kIdsFull + (t & 1)]);
+        }
     } else {
         reg_dec<PfRegs<SUB>::aux>();      // the spare warps of the second auxiliary group
     }
