@@ -792,7 +792,9 @@ extern "C" int tidal_decode_attention(const tidal_attn_args* a, void* d_ws, size
     // Otherwise several clusters per list (two of 8, else four of 4), as long as all of them are resident at once:
     // each cluster merges inside itself as before and leaves its share in the workspace, the last to arrive finishes.
     int nsuper = 1;
-    if (cluster == 8 && cta_bytes_at_8 > ((size_t)192 << 10)) {
+    // Not with per-row counts in device memory: the lists may be much shorter than their width (a rank's share of a
+    // sharded selection), and the second merge would cost more than it gains (7.9 -> 11.1 us at an eighth of cfg5).
+    if (cluster == 8 && cta_bytes_at_8 > ((size_t)192 << 10) && a->d_sel_counts == nullptr) {
         const int tries[2][2] = {{8, 2}, {4, 4}};
         for (int t = 0; t < 2 && nsuper == 1; ++t) {
             const int cl = tries[t][0], ns = tries[t][1];
