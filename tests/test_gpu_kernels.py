@@ -638,6 +638,9 @@ PREFILL_CASES = [
     ("f32", 2048, 2048, 4, 4, 64, 1, True),           # configuration 1's prompt: fp32 storage, the CUDA-core kernel
     ("f32", 130, 333, 8, 2, 128, 5, True),            # fp32 GQA, a later chunk, ragged pages
     ("f32", 65, 65, 2, 2, 64, 16, False),
+    ("bf16", 1000, 5000, 8, 2, 128, 4, True),         # two row blocks, 40 tiles: the ring of five wraps many times, ragged on both ends
+    ("f16", 100, 3001, 4, 4, 128, 1, True),           # one row block, 24 tiles, odd length
+    ("bf16", 700, 700, 4, 4, 64, 2, False),           # head_dim 64 with two row blocks, non-causal
 ]
 
 
