@@ -1,6 +1,6 @@
 // Causal attention of a block of new query rows over one sequence's paged KV ("prefill"), on the
-// 5th-generation tensor cores: tcgen05.mma with both operands in shared memory and the accumulators in
-// tensor memory.  Takes the place of prefill_with_paged_kv_cache (tidal/ops/csrc/batch_prefill.cu:27-117,
+// 5th-generation tensor cores: tcgen05.mma with operands in shared memory (Q, K, V) and in tensor memory (P)
+// and the accumulators in tensor memory.  Takes the place of prefill_with_paged_kv_cache (tidal/ops/csrc/batch_prefill.cu:27-117,
 // kernels/include/prefill/prefill.cuh:688-870, an mma.sync kernel).
 //
 // A row block = 128 query rows of one query head = the 128 lanes of tensor memory; a CTA holds one row
@@ -19,8 +19,8 @@
 // softmax_j -> PV_j -> QK_(j+1) -> softmax_(j+1); the two row blocks of a CTA run half a period apart and
 // keep the tensor core busy during each other's softmax.  K and V tiles travel through one ring of five
 // 32 KB slots in the order K_0 V_0 K_1 V_1 ..., fetched by dedicated warps (cp.async, 16 bytes per
-// request; the page ids of a tile's rows are looked up two tiles ahead and kept in a small table in shared
-// memory).
+// request; a warp of its own looks the page ids of a tile's rows up two tiles ahead and parks them in a small
+// table in shared memory).
 // Every wait on an mbarrier is bounded; a CTA that gives up sets TIDAL_DEV_WAIT_TIMEOUT, still frees its
 // tensor memory and returns.
 #include <cmath>
@@ -38,7 +38,7 @@ constexpr int kPfRing = 5;       // K/V tiles in flight in shared memory
 #define TIDAL_PF_LAG 1
 #endif
 constexpr int kPfProducerWarps = 8;   // warps that fetch K and V tiles: a warp keeps only so many copies in flight, the rate grows with the warps
-constexpr int kPfExtraThreads = 32 * kPfProducerWarps + 128;  // warp groups beside the softmax threads: the producer warps; the MMA warp and three spares
+constexpr int kPfExtraThreads = 32 * kPfProducerWarps + 128;  // warp groups beside the softmax threads: the producer warps; the MMA warp, the lookup warp and two spares
 // Registers per thread after the role split (setmaxnreg, a warp-group operation).  The softmax threads hold a whole
 // S row of 128 values and take registers from the other warps.  A CTA starts with `launch` registers per thread
 // (what the launch bound leaves: the register file divided by the threads, rounded down to 8; ptxas reports the
