@@ -201,6 +201,30 @@ __device__ __forceinline__ bool mma_wait(uint64_t* bar, uint32_t parity, volatil
     return false;
 }
 
+// Two-wide fp32 arithmetic and the three-input maximum of this architecture: the softmax warps are short of issue
+// slots, and these halve the multiply-adds, the additions and the comparisons per score.
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 // A wait whose outcome the whole warp agrees on: a lane that gave up must not leave the others in the loop.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t* status) {
     return __all_sync(0xffffffffu, mma_wait(bar, parity, abort_flag, status));
@@ -306,7 +330,10 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
             }
             float mx4[4] = {m_ref, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < kPfTile; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
+            for (int c = 0; c < kPfTile; c += 8) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) mx4[i] = max3(mx4[i], s[c + i], s[c + 4 + i]);
+            }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const bool grow = (mx - m_ref) * p.scale_log2 > 8.f;      // also true while m_ref = -inf
             float alpha = 1.f;
@@ -317,7 +344,8 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
             }
             const float mb = (m_ref == -INFINITY ? 0.f : m_ref) * p.scale_log2;
             // ---- P = exp2(S * scale - m_ref * scale), two values per column, into the first half of the S columns
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), negmb2 = pack2(-mb, -mb);
+            uint64_t sum2[2] = {0ull, 0ull};         // four running sums, two per register pair
 #pragma unroll
             for (int c0 = 0; c0 < kPfTile; c0 += 32) {
                 uint32_t w[16];
@@ -325,9 +353,12 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
                 for (int c8 = 0; c8 < 4; ++c8) {
                     float e[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        e[u] = fast_exp2(fmaf(s[c0 + c8 * 8 + u], p.scale_log2, -mb));
-                        sum4[u & 3] += e[u];      // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
+                    for (int u = 0; u < 8; u += 2) {
+                        float x0, x1;
+                        unpack2(fma2(pack2(s[c0 + c8 * 8 + u], s[c0 + c8 * 8 + u + 1]), scale2, negmb2), x0, x1);
+                        e[u] = fast_exp2(x0);
+                        e[u + 1] = fast_exp2(x1);
+                        sum2[(u >> 1) & 1] = add2(sum2[(u >> 1) & 1], pack2(e[u], e[u + 1]));   // fp32 sum of the unrounded weights; P itself is rounded once, by the pack below
                     }
                     const uint4 v = Vec16<T>::from_float(e);
                     w[c8 * 4] = v.x;
@@ -350,7 +381,12 @@ __global__ void __launch_bounds__(128 * SUB + kPfExtraThreads, 1) prefill_attn_k
                     tc_st32(t_o + d0, t);
                 }
             }
-            l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            {
+                float a0, a1, a2, a3;
+                unpack2(sum2[0], a0, a1);
+                unpack2(sum2[1], a2, a3);
+                l_run += (a0 + a1) + (a2 + a3);
+            }
             tc_wait_st();
             tc_fence_before();        // the tensor-memory loads and stores above are ordered before the arrival
             __syncwarp();
