@@ -241,24 +241,9 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
     } else {
         for (int i = t; i < kBins; i += kTopkThreads) h_local[i] = 0;
         __syncthreads();
-        // (many loads in flight per thread: with two, a slice of 512 KB took 16 us — 32 KB in flight per SM)
-        if (p.seg_len == 0 && ((reinterpret_cast<uintptr_t>(srow) & 15) == 0)) {
-            const int64_t hi4 = lo + ((hi - lo) & ~(int64_t)3);
-#pragma unroll 8
-            for (int64_t j = lo + 4 * (int64_t)t; j < hi4; j += 4 * kTopkThreads) {
-                const float4 v = *reinterpret_cast<const float4*>(srow + j);
-                atomicAdd(&h_local[key_bin(make_key(v.x, (uint32_t)j, p.n, p.force_last))], 1u);
-                atomicAdd(&h_local[key_bin(make_key(v.y, (uint32_t)(j + 1), p.n, p.force_last))], 1u);
-                atomicAdd(&h_local[key_bin(make_key(v.z, (uint32_t)(j + 2), p.n, p.force_last))], 1u);
-                atomicAdd(&h_local[key_bin(make_key(v.w, (uint32_t)(j + 3), p.n, p.force_last))], 1u);
-            }
-            for (int64_t j = hi4 + t; j < hi; j += kTopkThreads)
-                atomicAdd(&h_local[key_bin(make_key(srow[j], (uint32_t)j, p.n, p.force_last))], 1u);
-        } else {
-#pragma unroll 8
-            for (int64_t j = lo + t; j < hi; j += kTopkThreads)
-                atomicAdd(&h_local[key_bin(make_key(score_at(j), (uint32_t)j, p.n, p.force_last))], 1u);
-        }
+#pragma unroll 4
+        for (int64_t j = lo + t; j < hi; j += kTopkThreads)
+            atomicAdd(&h_local[key_bin(make_key(score_at(j), (uint32_t)j, p.n, p.force_last))], 1u);
         cluster.sync();
         for (int i = t; i < kBins; i += kTopkThreads) {
             uint32_t a = 0;
@@ -291,7 +276,7 @@ __device__ __forceinline__ void topk_cluster_row(TopkParams p, const int row, un
         const bool vec_ok = p.seg_len == 0 && ((reinterpret_cast<uintptr_t>(srow) & 15) == 0);
         if (vec_ok) {
             const int64_t hi4 = lo + ((hi - lo) & ~(int64_t)3);
-#pragma unroll 8
+#pragma unroll 2
             for (int64_t j = lo + 4 * (int64_t)t; j < hi4; j += 4 * kTopkThreads) {
                 const float4 v = *reinterpret_cast<const float4*>(srow + j);
                 push(v.x, j); push(v.y, j + 1); push(v.z, j + 2); push(v.w, j + 3);
